@@ -1,0 +1,701 @@
+// Device-resident differential weight cache.
+//
+// Behavioural contract (what a caller of the reference's WeightCache observes,
+// sparse_transformers/csrc/weight_cache.h:229-359): after update(mask) the packed row j of
+// gate/up/down belongs to neuron active[j], where `active` evolves from the previous order
+// by (1) pairing the i-th removed neuron with the i-th added neuron (both ascending) and
+// overwriting the removed neuron's slot, (2) appending surplus additions in ascending
+// order, (3) deleting surplus removals in ascending order, each by moving the current last
+// row into the hole.  Here the *index plan* (active / pos_of / list of rewritten slots) is
+// computed by one thread block, and the data movement is a separate, fully parallel pass
+// that rewrites every changed slot j from the full pool row of neuron active[j].  Because
+// a packed row is by definition pool[active[j]], no packed->packed move is ever needed.
+#include "stx_cache.cuh"
+
+#include <algorithm>
+#include <new>
+
+namespace stx {
+
+constexpr int PLAN_THREADS = 1024;
+constexpr int PLAN_MFAST = 2048;  // surplus removals handled in shared memory
+constexpr int MAX_I = 65536;      // 2 mask words per plan thread
+
+struct Int2 {
+  int x, y;
+};
+
+// Exclusive scan of two counters over the block (thread order).  Ends with a barrier.
+__device__ __forceinline__ Int2 block_excl_scan2(Int2 v, Int2* total, Int2* warp_sums) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  Int2 inc = v;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    int a = __shfl_up_sync(0xffffffffu, inc.x, off);
+    int b = __shfl_up_sync(0xffffffffu, inc.y, off);
+    if (lane >= off) {
+      inc.x += a;
+      inc.y += b;
+    }
+  }
+  if (lane == 31) warp_sums[wid] = inc;
+  __syncthreads();
+  if (wid == 0) {
+    Int2 w = warp_sums[lane];
+    Int2 winc = w;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      int a = __shfl_up_sync(0xffffffffu, winc.x, off);
+      int b = __shfl_up_sync(0xffffffffu, winc.y, off);
+      if (lane >= off) {
+        winc.x += a;
+        winc.y += b;
+      }
+    }
+    warp_sums[lane] = Int2{winc.x - w.x, winc.y - w.y};
+    if (lane == 31) *total = winc;
+  }
+  __syncthreads();
+  Int2 base = warp_sums[wid];
+  Int2 r{base.x + inc.x - v.x, base.y + inc.y - v.y};
+  __syncthreads();
+  return r;
+}
+
+// One block.  Dynamic shared memory: 3*W + 3*PLAN_MFAST int32.
+__global__ void __launch_bounds__(PLAN_THREADS, 1)
+k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_bits,
+             int32_t* __restrict__ active, int32_t* __restrict__ pos_of, int32_t* __restrict__ lists,
+             int32_t* __restrict__ jobs, int32_t* __restrict__ state, int I) {
+  extern __shared__ int32_t sm[];
+  __shared__ Int2 s_ws[32];
+  __shared__ Int2 s_tot;
+  __shared__ int s_knew, s_slow;
+
+  const int W = (I + 31) >> 5;
+  uint32_t* s_rem = reinterpret_cast<uint32_t*>(sm);
+  int32_t* s_remoff = sm + W;
+  uint32_t* s_dirty = reinterpret_cast<uint32_t*>(sm + 2 * W);
+  int32_t* s_curpos = sm + 3 * W;
+  int32_t* s_tail = s_curpos + PLAN_MFAST;
+  int32_t* s_E = s_tail + PLAN_MFAST;
+  int32_t* added = lists;
+  int32_t* removed = lists + I;
+
+  const int t = threadIdx.x;
+  const int WPT = (W + PLAN_THREADS - 1) / PLAN_THREADS;  // 1 or 2
+
+  // ---- 1. diff words (weight_cache.h:84-110: added = new & ~old, removed = old & ~new)
+  uint32_t nbw[2] = {0, 0}, aw[2] = {0, 0}, rw[2] = {0, 0};
+  Int2 cnt{0, 0};
+  for (int k = 0; k < WPT; ++k) {
+    const int w = t * WPT + k;
+    if (w < W) {
+      uint32_t nb = new_bits[w];
+      const uint32_t ob = cur_bits[w];
+      if (w == W - 1 && (I & 31)) nb &= (1u << (I & 31)) - 1u;
+      nbw[k] = nb;
+      aw[k] = nb & ~ob;
+      rw[k] = ob & ~nb;
+      s_rem[w] = rw[k];
+      s_dirty[w] = 0u;
+      cnt.x += __popc(aw[k]);
+      cnt.y += __popc(rw[k]);
+    }
+  }
+  if (t == 0) s_slow = 0;
+  Int2 off = block_excl_scan2(cnt, &s_tot, s_ws);
+  const int na = s_tot.x, nr = s_tot.y;
+
+  // ---- 2. ascending id lists (torch::nonzero order)
+  for (int k = 0; k < WPT; ++k) {
+    const int w = t * WPT + k;
+    if (w < W) {
+      s_remoff[w] = off.y;
+      uint32_t a = aw[k], r = rw[k];
+      while (a) {
+        const int b = __ffs(a) - 1;
+        added[off.x++] = w * 32 + b;
+        a &= a - 1;
+      }
+      while (r) {
+        const int b = __ffs(r) - 1;
+        removed[off.y++] = w * 32 + b;
+        r &= r - 1;
+      }
+    }
+  }
+  const int K0 = state[ST_K];
+  __syncthreads();
+
+  if (na == 0 && nr == 0) {  // unchanged mask: the reference returns before touching anything
+    if (t == 0) {
+      state[ST_NJOBS] = 0;
+      state[ST_ADDED] = 0;
+      state[ST_REMOVED] = 0;
+    }
+    return;
+  }
+  const int pairs = min(na, nr);
+
+  // ---- 3. phase 1: i-th removed slot receives the i-th added neuron (weight_cache.h:248-277)
+  for (int i = t; i < pairs; i += PLAN_THREADS) {
+    const int r = removed[i], a = added[i];
+    const int p = pos_of[r];
+    if (p >= 0) {
+      active[p] = a;
+      pos_of[a] = p;
+      pos_of[r] = -1;
+      atomicOr(&s_dirty[p >> 5], 1u << (p & 31));
+    }
+  }
+  __syncthreads();
+
+  int Knew = K0;
+  if (na > nr) {
+    // ---- phase 2: append surplus additions in ascending order (weight_cache.h:280-307)
+    const int extra = na - nr;
+    for (int i = t; i < extra; i += PLAN_THREADS) {
+      const int a = added[pairs + i];
+      const int p = K0 + i;
+      if (p < I) {
+        active[p] = a;
+        pos_of[a] = p;
+        atomicOr(&s_dirty[p >> 5], 1u << (p & 31));
+      }
+    }
+    Knew = min(K0 + extra, I);
+  } else if (nr > na) {
+    // ---- phase 3: surplus removals, ascending, each filled by the then-last row
+    //      (weight_cache.h:310-353).  Sequential by definition; one thread replays it on
+    //      indices only.  All rows it can move live in the tail [n1, K0), so the fast path
+    //      keeps the tail, the holes' positions and the removal ids in shared memory.
+    const int m = nr - na;
+    const int n1 = K0 - m;
+    const bool fast = (m <= PLAN_MFAST) && (n1 >= 0);
+    if (fast) {
+      for (int i = t; i < m; i += PLAN_THREADS) {
+        const int e = removed[pairs + i];
+        const int p = pos_of[e];
+        s_E[i] = e;
+        s_curpos[i] = p;
+        s_tail[i] = active[n1 + i];
+        if (p < 0) s_slow = 1;  // inconsistent state (only after a NO_ACTIVE error): generic path
+      }
+    }
+    __syncthreads();
+    if (t == 0) {
+      int n = K0;
+      if (fast && !s_slow) {
+        for (int i = 0; i < m; ++i) {
+          const int e = s_E[i];
+          const int p = s_curpos[i];
+          const int last = n - 1;
+          if (p != last) {
+            const int x = s_tail[last - n1];
+            if (p >= n1) {
+              s_tail[p - n1] = x;
+            } else {
+              active[p] = x;
+              s_dirty[p >> 5] |= 1u << (p & 31);
+            }
+            pos_of[x] = p;
+            const uint32_t rwd = s_rem[x >> 5];
+            if ((rwd >> (x & 31)) & 1u) {  // x itself is removed later: track where it now sits
+              const int idx = s_remoff[x >> 5] + __popc(rwd & ((1u << (x & 31)) - 1u)) - pairs;
+              if (idx > i && idx < m) s_curpos[idx] = p;
+            }
+          }
+          pos_of[e] = -1;
+          --n;
+        }
+      } else {
+        for (int i = 0; i < m; ++i) {
+          const int e = removed[pairs + i];
+          const int p = pos_of[e];
+          if (p < 0) continue;  // not cached: the reference skips it
+          const int last = n - 1;
+          if (p != last) {
+            const int x = active[last];
+            active[p] = x;
+            pos_of[x] = p;
+            s_dirty[p >> 5] |= 1u << (p & 31);
+          }
+          pos_of[e] = -1;
+          --n;
+        }
+      }
+      s_knew = n;
+    }
+    __syncthreads();
+    Knew = s_knew;
+  }
+  __syncthreads();
+
+  // ---- 4. rewritten slots below the new K, ascending
+  Int2 jc{0, 0};
+  uint32_t dw[2] = {0, 0};
+  for (int k = 0; k < WPT; ++k) {
+    const int w = t * WPT + k;
+    if (w < W) {
+      uint32_t d = s_dirty[w];
+      const int lo = w * 32;
+      if (lo >= Knew) d = 0u;
+      else if (Knew - lo < 32) d &= (1u << (Knew - lo)) - 1u;
+      dw[k] = d;
+      jc.x += __popc(d);
+    }
+  }
+  Int2 joff = block_excl_scan2(jc, &s_tot, s_ws);
+  for (int k = 0; k < WPT; ++k) {
+    const int w = t * WPT + k;
+    uint32_t d = dw[k];
+    while (d) {
+      const int b = __ffs(d) - 1;
+      jobs[joff.x++] = w * 32 + b;
+      d &= d - 1;
+    }
+  }
+
+  // ---- 5. commit
+  if (Knew > 0) {
+    for (int k = 0; k < WPT; ++k) {
+      const int w = t * WPT + k;
+      if (w < W) cur_bits[w] = nbw[k];
+    }
+  }
+  if (t == 0) {
+    state[ST_K] = Knew;
+    state[ST_ADDED] = na;
+    state[ST_REMOVED] = nr;
+    if (Knew > 0) {
+      state[ST_NJOBS] = s_tot.x;
+      state[ST_VALID] = 1;
+      state[ST_EPOCH] = state[ST_EPOCH] + 1;
+    } else {
+      // the reference throws "No active weights" here, before it records the new mask
+      state[ST_NJOBS] = 0;
+      state[ST_STATUS] = state[ST_STATUS] | DEV_NO_ACTIVE;
+    }
+  }
+}
+
+// One warp per (job, matrix): packed[m][pos] = pool[m][active[pos]], 16-byte vectors.
+__global__ void __launch_bounds__(256)
+k_cache_copy_rows(const int32_t* __restrict__ jobs, const int32_t* __restrict__ active,
+                  const int32_t* __restrict__ state, const void* pool0, const void* pool1,
+                  const void* pool2, void* pk0, void* pk1, void* pk2, int nmat, int vec_per_row, int I) {
+  const int njobs = state[ST_NJOBS];
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int units = njobs * nmat;
+  for (int u = warp; u < units; u += nwarps) {
+    const int job = u / nmat, m = u - job * nmat;
+    const int pos = jobs[job];
+    if (pos < 0 || pos >= I) continue;
+    const int src = active[pos];
+    if (src < 0 || src >= I) continue;
+    const uint4* sp = reinterpret_cast<const uint4*>(m == 0 ? pool0 : (m == 1 ? pool1 : pool2)) +
+                      static_cast<size_t>(src) * vec_per_row;
+    uint4* dp = reinterpret_cast<uint4*>(m == 0 ? pk0 : (m == 1 ? pk1 : pk2)) +
+                static_cast<size_t>(pos) * vec_per_row;
+    int c = lane;
+    for (; c + 96 < vec_per_row; c += 128) {
+      uint4 v0 = ld_stream16(sp + c), v1 = ld_stream16(sp + c + 32), v2 = ld_stream16(sp + c + 64),
+            v3 = ld_stream16(sp + c + 96);
+      st16(dp + c, v0);
+      st16(dp + c + 32, v1);
+      st16(dp + c + 64, v2);
+      st16(dp + c + 96, v3);
+    }
+    for (; c < vec_per_row; c += 32) st16(dp + c, ld_stream16(sp + c));
+  }
+}
+
+// [R,C] -> [C,R] for 2- or 4-byte elements (32x32 tiles through shared memory).
+template <typename E>
+__global__ void __launch_bounds__(256) k_transpose(const E* __restrict__ in, E* __restrict__ out, int R, int C) {
+  __shared__ E tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int k = ty; k < 32; k += 8) {
+    const int r = r0 + k, c = c0 + tx;
+    if (r < R && c < C) tile[k][tx] = in[static_cast<size_t>(r) * C + c];
+  }
+  __syncthreads();
+  for (int k = ty; k < 32; k += 8) {
+    const int c = c0 + k, r = r0 + tx;
+    if (r < R && c < C) out[static_cast<size_t>(c) * R + r] = tile[tx][k];
+  }
+}
+
+__global__ void k_bytes_to_bits(const uint8_t* __restrict__ bytes, uint32_t* __restrict__ bits, int I) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool on = (i < I) && bytes[i] != 0;
+  const uint32_t w = __ballot_sync(0xffffffffu, on);
+  if ((threadIdx.x & 31) == 0 && i < I) bits[i >> 5] = w;
+}
+
+__global__ void k_bits_to_bytes(const uint32_t* __restrict__ bits, uint8_t* __restrict__ bytes, int I) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < I) bytes[i] = (bits[i >> 5] >> (i & 31)) & 1u;
+}
+
+// concat[0:K] = packed gate[0:K]; concat[K:2K] = packed up[0:K]  (K read on the device)
+__global__ void __launch_bounds__(256)
+k_concat(const uint4* __restrict__ pg, const uint4* __restrict__ pu, uint4* __restrict__ out,
+         const int32_t* __restrict__ state, int vec_per_row, int has_gate) {
+  const size_t n = static_cast<size_t>(state[ST_K]) * vec_per_row;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    if (has_gate) {
+      out[i] = ld_stream16(pg + i);
+      out[n + i] = ld_stream16(pu + i);
+    } else {
+      out[i] = ld_stream16(pu + i);
+    }
+  }
+}
+
+__global__ void k_fill_i32(int32_t* p, int32_t v, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
+}
+
+static size_t plan_smem_bytes(int64_t I) {
+  const int64_t W = (I + 31) / 32;
+  return static_cast<size_t>(3 * W + 3 * PLAN_MFAST) * sizeof(int32_t);
+}
+
+int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  STX_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    STX_CUDA(cudaFuncSetAttribute(k_cache_plan, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(plan_smem_bytes(MAX_I))));
+    attr_set[dev] = true;
+  }
+  k_cache_plan<<<1, PLAN_THREADS, plan_smem_bytes(c->I), s>>>(bits, c->cur_bits, c->active, c->pos_of,
+                                                             c->lists, c->jobs, c->state,
+                                                             static_cast<int>(c->I));
+  STX_LAUNCH_CHECK("k_cache_plan");
+  return STX_OK;
+}
+
+int cache_copy_rows(stx_cache* c, cudaStream_t s) {
+  const int nmat = c->has_gate ? 3 : 2;
+  const int vec = static_cast<int>(c->row_bytes / 16);
+  const int grid = num_sms() * 4;
+  if (c->has_gate) {
+    k_cache_copy_rows<<<grid, 256, 0, s>>>(c->jobs, c->active, c->state, c->pool_gate, c->pool_up,
+                                          c->pool_down, c->pk_gate, c->pk_up, c->pk_down, nmat, vec,
+                                          static_cast<int>(c->I));
+  } else {
+    k_cache_copy_rows<<<grid, 256, 0, s>>>(c->jobs, c->active, c->state, c->pool_up, c->pool_down, nullptr,
+                                          c->pk_up, c->pk_down, nullptr, nmat, vec, static_cast<int>(c->I));
+  }
+  STX_LAUNCH_CHECK("k_cache_copy_rows");
+  return STX_OK;
+}
+
+int cache_update_bits(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
+  int rc = cache_plan(c, bits, s);
+  if (rc != STX_OK) return rc;
+  return cache_copy_rows(c, s);
+}
+
+int cache_read_state(stx_cache* c, cudaStream_t s) {
+  STX_CUDA(cudaMemcpyAsync(c->host_state, c->state, ST_COUNT * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  STX_CUDA(cudaStreamSynchronize(s));
+  return STX_OK;
+}
+
+}  // namespace stx
+
+using namespace stx;
+
+extern "C" {
+
+int stx_cache_bytes(int64_t I, int64_t H, int dtype, int has_gate, unsigned flags, size_t* bytes_out) {
+  STX_CHECK_ARG(bytes_out, "stx_cache_bytes: bytes_out is null");
+  STX_CHECK_ARG(I > 0 && H > 0, "stx_cache_bytes: I and H must be positive");
+  const size_t mat = static_cast<size_t>(I) * H * dtype_size(dtype);
+  const int nmat = has_gate ? 3 : 2;
+  size_t total = mat /*pool_down*/ + nmat * mat /*packed*/;
+  if (!(flags & STX_CACHE_ALIAS_GATE_UP)) total += (nmat - 1) * mat;
+  total += static_cast<size_t>(I) * 5 * sizeof(int32_t) + 2 * ((I + 31) / 32) * sizeof(uint32_t) +
+           ST_COUNT * sizeof(int32_t);
+  *bytes_out = total;
+  return STX_OK;
+}
+
+int stx_cache_destroy(stx_cache_t* c) {
+  if (!c) return STX_OK;
+  cudaFree(c->own_gate);
+  cudaFree(c->own_up);
+  cudaFree(c->pool_down);
+  cudaFree(c->pk_gate);
+  cudaFree(c->pk_up);
+  cudaFree(c->pk_down);
+  cudaFree(c->concat);
+  cudaFree(c->active);
+  cudaFree(c->pos_of);
+  cudaFree(c->lists);
+  cudaFree(c->jobs);
+  cudaFree(c->cur_bits);
+  cudaFree(c->tmp_bits);
+  cudaFree(c->state);
+  if (c->host_state) cudaFreeHost(c->host_state);
+  delete c;
+  return STX_OK;
+}
+
+#define STX_ALLOC(ptr, bytes)                                                                   \
+  do {                                                                                          \
+    cudaError_t e__ = cudaMalloc(reinterpret_cast<void**>(&(ptr)), (bytes));                    \
+    if (e__ != cudaSuccess) {                                                                   \
+      set_error("stx_cache_create: cudaMalloc(%zu bytes) failed: %s", static_cast<size_t>(bytes), \
+                cudaGetErrorString(e__));                                                       \
+      stx_cache_destroy(c);                                                                     \
+      return STX_ERR_ALLOC;                                                                     \
+    }                                                                                           \
+  } while (0)
+
+int stx_cache_create(stx_cache_t** out, int64_t I, int64_t H, int dtype, int has_gate, const void* gate_w,
+                     const void* up_w, const void* down_w, const uint8_t* init_mask_bytes, unsigned flags,
+                     void* stream) {
+  STX_CHECK_ARG(out, "stx_cache_create: out is null");
+  *out = nullptr;
+  STX_CHECK_ARG(I > 0 && H > 0, "stx_cache_create: I and H must be positive");
+  STX_CHECK_ARG(dtype == STX_F32 || dtype == STX_F16 || dtype == STX_BF16, "stx_cache_create: bad dtype %d", dtype);
+  STX_CHECK_ARG(up_w && down_w, "stx_cache_create: up_w/down_w is null");
+  STX_CHECK_ARG(!has_gate || gate_w, "stx_cache_create: has_gate set but gate_w is null");
+  if (I > MAX_I) {
+    set_error("stx_cache_create: I=%lld exceeds the supported maximum %d", static_cast<long long>(I), MAX_I);
+    return STX_ERR_TOO_LARGE;
+  }
+  const size_t es = dtype_size(dtype);
+  if ((H * es) % 16 != 0) {
+    set_error("stx_cache_create: row size H*elem (%lld bytes) must be a multiple of 16", static_cast<long long>(H * es));
+    return STX_ERR_UNSUPPORTED;
+  }
+  const bool alias = (flags & STX_CACHE_ALIAS_GATE_UP) != 0;
+  if (alias && ((reinterpret_cast<uintptr_t>(up_w) & 15) || (has_gate && (reinterpret_cast<uintptr_t>(gate_w) & 15)))) {
+    set_error("stx_cache_create: aliased gate/up buffers must be 16-byte aligned");
+    return STX_ERR_INVALID_ARG;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  stx_cache* c = new (std::nothrow) stx_cache();
+  if (!c) {
+    set_error("stx_cache_create: out of host memory");
+    return STX_ERR_ALLOC;
+  }
+  c->I = I;
+  c->H = H;
+  c->dtype = dtype;
+  c->has_gate = has_gate ? 1 : 0;
+  c->flags = flags;
+  c->row_bytes = static_cast<size_t>(H) * es;
+  cudaGetDevice(&c->device);
+  const size_t mat = static_cast<size_t>(I) * c->row_bytes;
+  const size_t W = static_cast<size_t>((I + 31) / 32);
+
+  STX_ALLOC(c->pool_down, mat);
+  STX_ALLOC(c->pk_up, mat);
+  STX_ALLOC(c->pk_down, mat);
+  if (has_gate) STX_ALLOC(c->pk_gate, mat);
+  if (!alias) {
+    STX_ALLOC(c->own_up, mat);
+    if (has_gate) STX_ALLOC(c->own_gate, mat);
+  }
+  STX_ALLOC(c->active, I * sizeof(int32_t));
+  STX_ALLOC(c->pos_of, I * sizeof(int32_t));
+  STX_ALLOC(c->lists, 2 * I * sizeof(int32_t));
+  STX_ALLOC(c->jobs, I * sizeof(int32_t));
+  STX_ALLOC(c->cur_bits, W * sizeof(uint32_t));
+  STX_ALLOC(c->tmp_bits, W * sizeof(uint32_t));
+  STX_ALLOC(c->state, ST_COUNT * sizeof(int32_t));
+  if (cudaMallocHost(reinterpret_cast<void**>(&c->host_state), ST_COUNT * sizeof(int32_t)) != cudaSuccess) {
+    set_error("stx_cache_create: cudaMallocHost failed");
+    stx_cache_destroy(c);
+    return STX_ERR_ALLOC;
+  }
+
+  // pools (weight_cache.h:199-220): gate/up verbatim, down transposed [H,I] -> [I,H]
+  cudaError_t e = cudaSuccess;
+  if (alias) {
+    c->pool_up = up_w;
+    c->pool_gate = has_gate ? gate_w : nullptr;
+  } else {
+    e = cudaMemcpyAsync(c->own_up, up_w, mat, cudaMemcpyDeviceToDevice, s);
+    if (e == cudaSuccess && has_gate) e = cudaMemcpyAsync(c->own_gate, gate_w, mat, cudaMemcpyDeviceToDevice, s);
+    c->pool_up = c->own_up;
+    c->pool_gate = c->own_gate;
+  }
+  if (e == cudaSuccess) {
+    dim3 grid(static_cast<unsigned>((I + 31) / 32), static_cast<unsigned>((H + 31) / 32));
+    if (es == 4)
+      k_transpose<uint32_t><<<grid, 256, 0, s>>>(static_cast<const uint32_t*>(down_w),
+                                                static_cast<uint32_t*>(c->pool_down), static_cast<int>(H),
+                                                static_cast<int>(I));
+    else
+      k_transpose<uint16_t><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(down_w),
+                                                static_cast<uint16_t*>(c->pool_down), static_cast<int>(H),
+                                                static_cast<int>(I));
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemsetAsync(c->cur_bits, 0, W * sizeof(uint32_t), s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(c->state, 0, ST_COUNT * sizeof(int32_t), s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(c->pos_of, 0xff, I * sizeof(int32_t), s);  // -1
+  if (e == cudaSuccess) e = cudaMemsetAsync(c->active, 0xff, I * sizeof(int32_t), s);
+  if (e != cudaSuccess) {
+    int rc = cuda_fail(e, "stx_cache_create: initialisation");
+    stx_cache_destroy(c);
+    return rc;
+  }
+  if (init_mask_bytes) {
+    int rc = stx_cache_update(c, init_mask_bytes, stream);
+    if (rc != STX_OK) {
+      stx_cache_destroy(c);
+      return rc;
+    }
+  }
+  *out = c;
+  return STX_OK;
+}
+
+int stx_mask_bytes_to_bits(const uint8_t* bytes, int64_t I, uint32_t* bits_out, void* stream) {
+  STX_CHECK_ARG(bytes && bits_out && I > 0, "stx_mask_bytes_to_bits: bad argument");
+  const int threads = 256;
+  const int blocks = static_cast<int>((I + threads - 1) / threads);
+  k_bytes_to_bits<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(bytes, bits_out, static_cast<int>(I));
+  STX_LAUNCH_CHECK("k_bytes_to_bits");
+  return STX_OK;
+}
+
+int stx_mask_bits_to_bytes(const uint32_t* bits, int64_t I, uint8_t* bytes_out, void* stream) {
+  STX_CHECK_ARG(bits && bytes_out && I > 0, "stx_mask_bits_to_bytes: bad argument");
+  const int threads = 256;
+  const int blocks = static_cast<int>((I + threads - 1) / threads);
+  k_bits_to_bytes<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(bits, bytes_out, static_cast<int>(I));
+  STX_LAUNCH_CHECK("k_bits_to_bytes");
+  return STX_OK;
+}
+
+int stx_cache_update(stx_cache_t* c, const uint8_t* mask_bytes, void* stream) {
+  STX_CHECK_ARG(c && mask_bytes, "stx_cache_update: null argument");
+  int rc = stx_mask_bytes_to_bits(mask_bytes, c->I, c->tmp_bits, stream);
+  if (rc != STX_OK) return rc;
+  return cache_update_bits(c, c->tmp_bits, static_cast<cudaStream_t>(stream));
+}
+
+int stx_cache_update_bits(stx_cache_t* c, const uint32_t* mask_bits, void* stream) {
+  STX_CHECK_ARG(c && mask_bits, "stx_cache_update_bits: null argument");
+  return cache_update_bits(c, mask_bits, static_cast<cudaStream_t>(stream));
+}
+
+static int state_to_status(const stx_cache* c) {
+  const int32_t* h = c->host_state;
+  if (h[ST_STATUS] & DEV_BAD_INDEX) {
+    set_error("weight cache: a device bounds check failed (status 0x%x)", h[ST_STATUS]);
+    return STX_ERR_INVALID_ARG;
+  }
+  if (h[ST_K] == 0 && (h[ST_STATUS] & DEV_NO_ACTIVE)) {
+    set_error("No active weights");
+    return STX_ERR_NO_ACTIVE;
+  }
+  if (!h[ST_VALID]) {
+    set_error("Cache is not valid");
+    return STX_ERR_CACHE_INVALID;
+  }
+  return STX_OK;
+}
+
+int stx_cache_num_active(stx_cache_t* c, int64_t* k_out, void* stream) {
+  STX_CHECK_ARG(c && k_out, "stx_cache_num_active: null argument");
+  int rc = cache_read_state(c, static_cast<cudaStream_t>(stream));
+  if (rc != STX_OK) return rc;
+  *k_out = c->host_state[ST_K];
+  return state_to_status(c);
+}
+
+int stx_cache_concat_weight(stx_cache_t* c, void** ptr_out, int64_t* rows_out, void* stream) {
+  STX_CHECK_ARG(c && ptr_out && rows_out, "stx_cache_concat_weight: null argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = cache_read_state(c, s);
+  if (rc != STX_OK) return rc;
+  rc = state_to_status(c);
+  if (rc != STX_OK) return rc;
+  const int64_t K = c->host_state[ST_K];
+  if (!c->concat) {
+    const size_t bytes = static_cast<size_t>(c->has_gate ? 2 : 1) * c->I * c->row_bytes;
+    cudaError_t e = cudaMalloc(&c->concat, bytes);
+    if (e != cudaSuccess) {
+      c->concat = nullptr;
+      set_error("stx_cache_concat_weight: cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+      return STX_ERR_ALLOC;
+    }
+    c->concat_epoch = -1;
+  }
+  if (c->concat_epoch != c->host_state[ST_EPOCH]) {
+    const int vec = static_cast<int>(c->row_bytes / 16);
+    k_concat<<<num_sms() * 4, 256, 0, s>>>(static_cast<const uint4*>(c->pk_gate), static_cast<const uint4*>(c->pk_up),
+                                          static_cast<uint4*>(c->concat), c->state, vec, c->has_gate);
+    STX_LAUNCH_CHECK("k_concat");
+    c->concat_epoch = c->host_state[ST_EPOCH];
+  }
+  *ptr_out = c->concat;
+  *rows_out = c->has_gate ? 2 * K : K;
+  return STX_OK;
+}
+
+int stx_cache_active_down(stx_cache_t* c, void** ptr_out, int64_t* k_out, void* stream) {
+  STX_CHECK_ARG(c && ptr_out && k_out, "stx_cache_active_down: null argument");
+  int rc = cache_read_state(c, static_cast<cudaStream_t>(stream));
+  if (rc != STX_OK) return rc;
+  rc = state_to_status(c);
+  if (rc != STX_OK) return rc;
+  *ptr_out = c->pk_down;
+  *k_out = c->host_state[ST_K];
+  return STX_OK;
+}
+
+int stx_cache_packed_ptrs(stx_cache_t* c, void** gate_out, void** up_out, void** down_out,
+                          const int32_t** k_dev_out) {
+  STX_CHECK_ARG(c, "stx_cache_packed_ptrs: null cache");
+  if (gate_out) *gate_out = c->pk_gate;
+  if (up_out) *up_out = c->pk_up;
+  if (down_out) *down_out = c->pk_down;
+  if (k_dev_out) *k_dev_out = c->state + ST_K;
+  return STX_OK;
+}
+
+int stx_cache_active_indices(stx_cache_t* c, int32_t* host_out, int64_t cap, int64_t* k_out, void* stream) {
+  STX_CHECK_ARG(c && k_out, "stx_cache_active_indices: null argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = cache_read_state(c, s);
+  if (rc != STX_OK) return rc;
+  const int64_t K = c->host_state[ST_K];
+  *k_out = K;
+  if (host_out && K > 0) {
+    STX_CHECK_ARG(cap >= K, "stx_cache_active_indices: capacity %lld < K=%lld", static_cast<long long>(cap),
+                  static_cast<long long>(K));
+    STX_CUDA(cudaMemcpyAsync(host_out, c->active, K * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    STX_CUDA(cudaStreamSynchronize(s));
+  }
+  return STX_OK;
+}
+
+int stx_cache_last_update_stats(stx_cache_t* c, int64_t* added, int64_t* removed, int64_t* rows_copied, void* stream) {
+  STX_CHECK_ARG(c, "stx_cache_last_update_stats: null cache");
+  int rc = cache_read_state(c, static_cast<cudaStream_t>(stream));
+  if (rc != STX_OK) return rc;
+  if (added) *added = c->host_state[ST_ADDED];
+  if (removed) *removed = c->host_state[ST_REMOVED];
+  if (rows_copied) *rows_copied = c->host_state[ST_NJOBS];
+  return STX_OK;
+}
+
+}  // extern "C"

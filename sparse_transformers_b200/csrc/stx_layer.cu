@@ -1,0 +1,260 @@
+// Fused decode step of one sparse layer, and a stack of layers replayed as one CUDA graph.
+//
+// A layer step is: predictor -> mask bits -> cache plan -> row copies -> sparse MLP, all on
+// one stream with K resident on the device (no host read-back, no allocation), i.e. the
+// sparse branch of SkipDecoderLayer.forward (src/modeling_skip.py:236-238 and :258).
+#include "stx_cache.cuh"
+
+#include <new>
+#include <vector>
+
+namespace stx {
+int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
+                 int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch,
+                 cudaStream_t s);
+int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
+                const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
+                int act, int has_gate, int dtype, void* scratch, cudaStream_t s);
+}  // namespace stx
+
+struct stx_layer {
+  stx_cache* cache = nullptr;
+  const void* A = nullptr;
+  const void* Bm = nullptr;
+  int64_t r = 0;
+  int method = 0;
+  float param = 0.f;
+  int act = 0;
+  int64_t max_batch = 0;
+  uint32_t* bits = nullptr;
+  void* scores = nullptr;        // [max_batch, I], only for rules that need whole rows
+  void* pred_scratch = nullptr;
+  void* mlp_scratch = nullptr;
+  void* x_stage = nullptr;       // [max_batch, H] for the host-buffer entry point
+  void* out_stage = nullptr;
+};
+
+struct stx_stack {
+  std::vector<stx_layer*> layers;
+  int64_t B = 0, H = 0;
+  size_t es = 2;
+  void* x_in = nullptr;   // [B,H]
+  void* out = nullptr;    // [L,B,H]
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int64_t kernel_nodes = 0;
+};
+
+using namespace stx;
+
+extern "C" {
+
+int stx_layer_destroy(stx_layer_t* l) {
+  if (!l) return STX_OK;
+  cudaFree(l->bits);
+  cudaFree(l->scores);
+  cudaFree(l->pred_scratch);
+  cudaFree(l->mlp_scratch);
+  cudaFree(l->x_stage);
+  cudaFree(l->out_stage);
+  delete l;
+  return STX_OK;
+}
+
+int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64_t r, const void* Bm, int method,
+                     float param, int act, int64_t max_batch) {
+  STX_CHECK_ARG(out, "stx_layer_create: out is null");
+  *out = nullptr;
+  STX_CHECK_ARG(cache && A && Bm, "stx_layer_create: null pointer");
+  STX_CHECK_ARG(r > 0 && max_batch > 0, "stx_layer_create: r and max_batch must be positive");
+  STX_CHECK_ARG(method >= STX_MASK_THRESHOLD && method <= STX_MASK_STATISTICAL, "stx_layer_create: bad method %d", method);
+  STX_CHECK_ARG(act >= STX_ACT_RELU && act <= STX_ACT_GELU, "stx_layer_create: bad activation %d", act);
+  stx_layer* l = new (std::nothrow) stx_layer();
+  if (!l) {
+    set_error("stx_layer_create: out of host memory");
+    return STX_ERR_ALLOC;
+  }
+  l->cache = cache;
+  l->A = A;
+  l->Bm = Bm;
+  l->r = r;
+  l->method = method;
+  l->param = param;
+  l->act = act;
+  l->max_batch = max_batch;
+  const int64_t I = cache->I, H = cache->H;
+  size_t pred_bytes = 0, mlp_bytes = 0;
+  stx_predict_scratch_bytes(max_batch, I, r, &pred_bytes);
+  stx_mlp_scratch_bytes(max_batch, H, &mlp_bytes);
+  const size_t es = dtype_size(cache->dtype);
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&l->bits), ((I + 31) / 32) * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(&l->pred_scratch, pred_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&l->mlp_scratch, mlp_bytes);
+  if (e == cudaSuccess) e = cudaMemset(l->mlp_scratch, 0, mlp_bytes);
+  if (e == cudaSuccess && method != STX_MASK_THRESHOLD) e = cudaMalloc(&l->scores, static_cast<size_t>(max_batch) * I * es);
+  if (e != cudaSuccess) {
+    set_error("stx_layer_create: device allocation failed: %s", cudaGetErrorString(e));
+    stx_layer_destroy(l);
+    return STX_ERR_ALLOC;
+  }
+  *out = l;
+  return STX_OK;
+}
+
+int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, void* stream) {
+  STX_CHECK_ARG(l && x_pred && x_mlp && out, "stx_layer_step: null pointer");
+  STX_CHECK_ARG(B > 0 && B <= l->max_batch, "stx_layer_step: B=%lld outside 1..max_batch=%lld", static_cast<long long>(B),
+                static_cast<long long>(l->max_batch));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  stx_cache* c = l->cache;
+  int rc = stx_predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
+                            l->pred_scratch, stream);
+  if (rc != STX_OK) return rc;
+  rc = cache_update_bits(c, l->bits, s);
+  if (rc != STX_OK) return rc;
+  return mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
+                     c->has_gate, c->dtype, l->mlp_scratch, s);
+}
+
+int stx_layer_mask_bits(stx_layer_t* l, const uint32_t** bits_out) {
+  STX_CHECK_ARG(l && bits_out, "stx_layer_mask_bits: null pointer");
+  *bits_out = l->bits;
+  return STX_OK;
+}
+
+int stx_layer_step_host(stx_layer_t* l, const void* x_host, int64_t B, void* out_host, void* stream) {
+  STX_CHECK_ARG(l && x_host && out_host, "stx_layer_step_host: null pointer");
+  STX_CHECK_ARG(B > 0 && B <= l->max_batch, "stx_layer_step_host: B outside 1..max_batch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t bytes = static_cast<size_t>(B) * l->cache->H * dtype_size(l->cache->dtype);
+  if (!l->x_stage) {
+    const size_t cap = static_cast<size_t>(l->max_batch) * l->cache->H * dtype_size(l->cache->dtype);
+    cudaError_t e = cudaMalloc(&l->x_stage, cap);
+    if (e == cudaSuccess) e = cudaMalloc(&l->out_stage, cap);
+    if (e != cudaSuccess) {
+      set_error("stx_layer_step_host: staging allocation failed: %s", cudaGetErrorString(e));
+      return STX_ERR_ALLOC;
+    }
+  }
+  STX_CUDA(cudaMemcpyAsync(l->x_stage, x_host, bytes, cudaMemcpyHostToDevice, s));
+  int rc = stx_layer_step(l, l->x_stage, l->x_stage, B, l->out_stage, stream);
+  if (rc != STX_OK) return rc;
+  STX_CUDA(cudaMemcpyAsync(out_host, l->out_stage, bytes, cudaMemcpyDeviceToHost, s));
+  STX_CUDA(cudaStreamSynchronize(s));
+  return STX_OK;
+}
+
+int stx_stack_destroy(stx_stack_t* s) {
+  if (!s) return STX_OK;
+  if (s->exec) cudaGraphExecDestroy(s->exec);
+  if (s->graph) cudaGraphDestroy(s->graph);
+  cudaFree(s->x_in);
+  cudaFree(s->out);
+  delete s;
+  return STX_OK;
+}
+
+int stx_stack_create(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B) {
+  STX_CHECK_ARG(out, "stx_stack_create: out is null");
+  *out = nullptr;
+  STX_CHECK_ARG(layers && L > 0 && B > 0, "stx_stack_create: bad argument");
+  for (int64_t i = 0; i < L; ++i) {
+    STX_CHECK_ARG(layers[i], "stx_stack_create: layer %lld is null", static_cast<long long>(i));
+    STX_CHECK_ARG(layers[i]->cache->H == layers[0]->cache->H && layers[i]->cache->dtype == layers[0]->cache->dtype,
+                  "stx_stack_create: all layers must share H and dtype");
+    STX_CHECK_ARG(B <= layers[i]->max_batch, "stx_stack_create: B exceeds layer %lld max_batch", static_cast<long long>(i));
+  }
+  stx_stack* s = new (std::nothrow) stx_stack();
+  if (!s) {
+    set_error("stx_stack_create: out of host memory");
+    return STX_ERR_ALLOC;
+  }
+  s->layers.assign(layers, layers + L);
+  s->B = B;
+  s->H = layers[0]->cache->H;
+  s->es = dtype_size(layers[0]->cache->dtype);
+  const size_t xbytes = static_cast<size_t>(B) * s->H * s->es;
+  cudaError_t e = cudaMalloc(&s->x_in, xbytes);
+  if (e == cudaSuccess) e = cudaMalloc(&s->out, xbytes * L);
+  if (e == cudaSuccess) e = cudaMemset(s->x_in, 0, xbytes);
+  if (e != cudaSuccess) {
+    set_error("stx_stack_create: device allocation failed: %s", cudaGetErrorString(e));
+    stx_stack_destroy(s);
+    return STX_ERR_ALLOC;
+  }
+  // Capture the L steps (nothing executes during capture).
+  cudaStream_t cs = nullptr;
+  e = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
+  if (e != cudaSuccess) {
+    stx_stack_destroy(s);
+    return cuda_fail(e, "stx_stack_create: cudaStreamCreate");
+  }
+  int rc = STX_OK;
+  e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
+  if (e == cudaSuccess) {
+    for (int64_t i = 0; i < L && rc == STX_OK; ++i) {
+      rc = stx_layer_step(s->layers[i], s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs);
+    }
+    cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
+    if (rc == STX_OK && e2 != cudaSuccess) e = e2;
+  }
+  if (e == cudaSuccess && rc == STX_OK) e = cudaGraphInstantiate(&s->exec, s->graph, 0);
+  cudaStreamDestroy(cs);
+  if (rc != STX_OK) {
+    stx_stack_destroy(s);
+    return rc;
+  }
+  if (e != cudaSuccess) {
+    stx_stack_destroy(s);
+    return cuda_fail(e, "stx_stack_create: graph capture/instantiate");
+  }
+  size_t n = 0;
+  if (cudaGraphGetNodes(s->graph, nullptr, &n) == cudaSuccess && n > 0) {
+    std::vector<cudaGraphNode_t> nodes(n);
+    if (cudaGraphGetNodes(s->graph, nodes.data(), &n) == cudaSuccess) {
+      for (size_t i = 0; i < n; ++i) {
+        cudaGraphNodeType t;
+        if (cudaGraphNodeGetType(nodes[i], &t) == cudaSuccess && t == cudaGraphNodeTypeKernel) ++s->kernel_nodes;
+      }
+    }
+  }
+  *out = s;
+  return STX_OK;
+}
+
+int stx_stack_buffers(stx_stack_t* s, void** x_in_out, void** out_out) {
+  STX_CHECK_ARG(s, "stx_stack_buffers: null stack");
+  if (x_in_out) *x_in_out = s->x_in;
+  if (out_out) *out_out = s->out;
+  return STX_OK;
+}
+
+int stx_stack_step(stx_stack_t* s, const void* x, void* out, void* stream) {
+  STX_CHECK_ARG(s, "stx_stack_step: null stack");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t xbytes = static_cast<size_t>(s->B) * s->H * s->es;
+  if (x && x != s->x_in) STX_CUDA(cudaMemcpyAsync(s->x_in, x, xbytes, cudaMemcpyDeviceToDevice, st));
+  STX_CUDA(cudaGraphLaunch(s->exec, st));
+  if (out && out != s->out)
+    STX_CUDA(cudaMemcpyAsync(out, s->out, xbytes * s->layers.size(), cudaMemcpyDeviceToDevice, st));
+  return STX_OK;
+}
+
+int stx_stack_step_host(stx_stack_t* s, const void* x_host, void* out_host, void* stream) {
+  STX_CHECK_ARG(s && x_host && out_host, "stx_stack_step_host: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t xbytes = static_cast<size_t>(s->B) * s->H * s->es;
+  STX_CUDA(cudaMemcpyAsync(s->x_in, x_host, xbytes, cudaMemcpyHostToDevice, st));
+  STX_CUDA(cudaGraphLaunch(s->exec, st));
+  STX_CUDA(cudaMemcpyAsync(out_host, s->out, xbytes * s->layers.size(), cudaMemcpyDeviceToHost, st));
+  STX_CUDA(cudaStreamSynchronize(st));
+  return STX_OK;
+}
+
+int stx_stack_launches_per_step(stx_stack_t* s, int64_t* n_out) {
+  STX_CHECK_ARG(s && n_out, "stx_stack_launches_per_step: null pointer");
+  *n_out = s->kernel_nodes;
+  return STX_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,303 @@
+// Sparse gated MLP over packed active rows (decode-sized batches).
+//
+//   out[b,:] = sum_j act(x[b]·gate[j]) * (x[b]·up[j]) * down[j,:]        j = 0..K-1
+//
+// gate/up/down rows are the packed rows of the active neurons (one contiguous H-row per
+// neuron in each matrix), so every byte that is read is useful and every read is a
+// 16-byte coalesced vector.  Replaces sparse_mlp_forward_cpu (sparse_mlp_op.cpp:79-192),
+// the unfinished CUDA kernels (sparse_mlp_cuda.cu:28-88) and the two matmuls the models
+// actually run (src/modeling_skip.py:114-117).
+//
+// k_mlp_fused: persistent blocks, each owning a contiguous range of neurons.
+//   phase A  one warp per neuron: both dot products with x (shared memory), warp-shuffle
+//            reduction, activation and product in registers -> a[j,b] in shared memory
+//   phase B  one thread per 16-byte column chunk: acc[b,chunk] += a[j,b] * down[j,chunk]
+//            over the block's neurons, then one vector fp32 reduction per chunk into the
+//            global accumulator
+//   the last block to finish converts the accumulator to the output dtype and re-zeroes it.
+#include "stx_common.cuh"
+
+#include <algorithm>
+
+namespace stx {
+
+struct MlpArgs {
+  const void* x;
+  const void* gate;
+  const void* up;
+  const void* down;
+  void* combined;        // optional [B, 2K] (or [B,K]) in dtype
+  void* out;             // [B,H] in dtype
+  float* out_acc;        // [B,H] fp32, zero on entry, zero on exit
+  unsigned* counter;     // zero on entry, zero on exit
+  const int32_t* K_dev;  // device K (may be null -> K_host)
+  int K_host;
+  int up_after_gate;     // 1: up rows start K rows after `gate` (concat layout, device K)
+  int B, H, act, has_gate, a_cap;
+};
+
+template <typename T, int NB>
+__global__ void __launch_bounds__(256, 2) k_mlp_fused(const MlpArgs p) {
+  constexpr int V = DT<T>::V;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* x_s = reinterpret_cast<T*>(smem_raw);                                   // [NB][H]
+  float* a_s = reinterpret_cast<float*>(smem_raw + sizeof(T) * NB * p.H);    // [a_cap][NB]
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int H = p.H, nchunk = H / V;
+  const int K = p.K_dev ? *p.K_dev : p.K_host;
+  const T* gate = static_cast<const T*>(p.gate);
+  const T* up = static_cast<const T*>(p.up);
+  if (p.up_after_gate) up = gate + static_cast<size_t>(K) * H;
+  const T* down = static_cast<const T*>(p.down);
+  T* combined = static_cast<T*>(p.combined);
+  const int ldc = p.has_gate ? 2 * K : K;
+
+  // contiguous, balanced neuron range of this block
+  const int base = K / gridDim.x, rem = K % gridDim.x;
+  const int j0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
+  int j1 = j0 + base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
+  if (j1 - j0 > p.a_cap) j1 = j0 + p.a_cap;  // cannot happen for K <= capacity; never index past a_s
+
+  for (int b0 = 0; b0 < p.B; b0 += NB) {
+    const int nb = min(NB, p.B - b0);
+    if (j1 > j0) {
+      // stage the x tile
+      const uint4* xg = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + static_cast<size_t>(b0) * H);
+      uint4* xs4 = reinterpret_cast<uint4*>(x_s);
+      for (int i = tid; i < nb * nchunk; i += blockDim.x) xs4[i] = xg[i];
+      for (int i = nb * nchunk + tid; i < NB * nchunk; i += blockDim.x) xs4[i] = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+
+    // ---- phase A
+    for (int j = j0 + warp; j < j1; j += nwarps) {
+      float ag[NB], au[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) ag[b] = au[b] = 0.f;
+      const T* grow = gate + static_cast<size_t>(j) * H;
+      const T* urow = up + static_cast<size_t>(j) * H;
+      for (int c0 = lane; c0 < nchunk; c0 += 128) {
+        uint4 gv[4], uv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + 32 * u;
+          if (c < nchunk) {
+            uv[u] = ld_stream16(urow + c * V);
+            if (p.has_gate) gv[u] = ld_stream16(grow + c * V);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + 32 * u;
+          if (c < nchunk) {
+            float wu[V], wg[V];
+            Unpack<T>::run(uv[u], wu);
+            if (p.has_gate) Unpack<T>::run(gv[u], wg);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+              float xv[V];
+              Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + b * H + c * V), xv);
+#pragma unroll
+              for (int v = 0; v < V; ++v) {
+                au[b] = fmaf(xv[v], wu[v], au[b]);
+                if (p.has_gate) ag[b] = fmaf(xv[v], wg[v], ag[b]);
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const float u = warp_sum_xor(au[b]);
+        float a;
+        if (p.has_gate) {
+          const float g = warp_sum_xor(ag[b]);
+          a = apply_act(p.act, g) * u;
+        } else {
+          a = apply_act(p.act, u);
+        }
+        if (lane == 0) {
+          a_s[(j - j0) * NB + b] = a;
+          if (combined && b < nb) {
+            combined[static_cast<size_t>(b0 + b) * ldc + j] = DT<T>::from_f(a);
+            if (p.has_gate) combined[static_cast<size_t>(b0 + b) * ldc + K + j] = DT<T>::from_f(u);
+          }
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- phase B
+    if (j1 > j0) {
+      for (int c = tid; c < nchunk; c += blockDim.x) {
+        float acc[NB][V];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[b][v] = 0.f;
+        const T* dcol = down + c * V;
+        int j = j0;
+        for (; j + 4 <= j1; j += 4) {
+          uint4 dv[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) dv[u] = ld_stream16(dcol + static_cast<size_t>(j + u) * H);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float wd[V];
+            Unpack<T>::run(dv[u], wd);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+              const float a = a_s[(j + u - j0) * NB + b];
+#pragma unroll
+              for (int v = 0; v < V; ++v) acc[b][v] = fmaf(a, wd[v], acc[b][v]);
+            }
+          }
+        }
+        for (; j < j1; ++j) {
+          float wd[V];
+          Unpack<T>::run(ld_stream16(dcol + static_cast<size_t>(j) * H), wd);
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            const float a = a_s[(j - j0) * NB + b];
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[b][v] = fmaf(a, wd[v], acc[b][v]);
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          if (b < nb) {
+            float* dst = p.out_acc + static_cast<size_t>(b0 + b) * H + c * V;
+#pragma unroll
+            for (int v = 0; v < V; v += 4) red_add_f32x4(dst + v, acc[b][v], acc[b][v + 1], acc[b][v + 2], acc[b][v + 3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- last block converts and re-zeroes
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned ticket = atomicAdd(p.counter, 1u);
+    s_last = (ticket == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    T* out = static_cast<T*>(p.out);
+    const int n4 = p.B * H / 4;
+    float4* acc4 = reinterpret_cast<float4*>(p.out_acc);
+    for (int i = tid; i < n4; i += blockDim.x) {
+      const float4 v = __ldcg(acc4 + i);
+      out[4 * i + 0] = DT<T>::from_f(v.x);
+      out[4 * i + 1] = DT<T>::from_f(v.y);
+      out[4 * i + 2] = DT<T>::from_f(v.z);
+      out[4 * i + 3] = DT<T>::from_f(v.w);
+      acc4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (tid == 0) *p.counter = 0u;
+  }
+}
+
+template <typename T, int NB>
+static int launch_fused(const MlpArgs& a, int grid, int threads, cudaStream_t s) {
+  const size_t smem = sizeof(T) * NB * a.H + sizeof(float) * NB * a.a_cap;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !attr_set[dev]) {
+    STX_CUDA(cudaFuncSetAttribute(k_mlp_fused<T, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set[dev] = true;
+  }
+  if (smem > 200 * 1024) {
+    set_error("sparse MLP: shared-memory tile of %zu bytes exceeds 200 KiB (H too large)", smem);
+    return STX_ERR_TOO_LARGE;
+  }
+  k_mlp_fused<T, NB><<<grid, threads, smem, s>>>(a);
+  STX_LAUNCH_CHECK("k_mlp_fused");
+  return STX_OK;
+}
+
+template <typename T>
+static int dispatch_nb(MlpArgs& a, int grid, int threads, cudaStream_t s) {
+  if (a.B == 1) return launch_fused<T, 1>(a, grid, threads, s);
+  if (a.B == 2) return launch_fused<T, 2>(a, grid, threads, s);
+  return launch_fused<T, 4>(a, grid, threads, s);
+}
+
+// Shared by the op entry point and the fused layer step.
+int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
+                const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
+                int act, int has_gate, int dtype, void* scratch, cudaStream_t s) {
+  const size_t es = dtype_size(dtype);
+  const int V = static_cast<int>(16 / es);
+  const int nchunk = static_cast<int>(H / V);
+  MlpArgs a;
+  a.x = x;
+  a.gate = gate;
+  a.up = up;
+  a.down = down;
+  a.combined = combined;
+  a.out = out;
+  a.out_acc = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
+  a.counter = static_cast<unsigned*>(scratch);
+  a.K_dev = K_dev;
+  a.K_host = static_cast<int>(K_host);
+  a.up_after_gate = up_after_gate;
+  a.B = static_cast<int>(B);
+  a.H = static_cast<int>(H);
+  a.act = act;
+  a.has_gate = has_gate;
+  const int slots = (nchunk + 255) / 256;
+  int threads = (nchunk + slots - 1) / slots;
+  threads = std::min(256, std::max(64, (threads + 31) / 32 * 32));
+  int grid = num_sms() * 2;
+  if (!K_dev) grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, K_host)));
+  a.a_cap = static_cast<int>((K_cap + grid - 1) / grid);
+  switch (dtype) {
+    case STX_F32: return dispatch_nb<float>(a, grid, threads, s);
+    case STX_F16: return dispatch_nb<__half>(a, grid, threads, s);
+    default: return dispatch_nb<__nv_bfloat16>(a, grid, threads, s);
+  }
+}
+
+}  // namespace stx
+
+using namespace stx;
+
+extern "C" {
+
+int stx_mlp_scratch_bytes(int64_t B, int64_t H, size_t* bytes_out) {
+  STX_CHECK_ARG(bytes_out && B > 0 && H > 0, "stx_mlp_scratch_bytes: bad argument");
+  *bytes_out = 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
+  return STX_OK;
+}
+
+int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed,
+                           int64_t K, void* down_buf, void* combined_buf, int act, int has_gate, int dtype,
+                           void* scratch, void* stream) {
+  STX_CHECK_ARG(x && concat_w && down_packed && down_buf && scratch, "stx_sparse_mlp_forward: null pointer");
+  STX_CHECK_ARG(B > 0 && H > 0 && K >= 0, "stx_sparse_mlp_forward: bad sizes B=%lld H=%lld K=%lld",
+                static_cast<long long>(B), static_cast<long long>(H), static_cast<long long>(K));
+  STX_CHECK_ARG(dtype == STX_F32 || dtype == STX_F16 || dtype == STX_BF16, "stx_sparse_mlp_forward: bad dtype %d", dtype);
+  STX_CHECK_ARG(act >= STX_ACT_RELU && act <= STX_ACT_GELU, "stx_sparse_mlp_forward: bad activation %d", act);
+  const size_t es = dtype_size(dtype);
+  if ((H * es) % 16 != 0) {
+    set_error("stx_sparse_mlp_forward: H*elem must be a multiple of 16 bytes");
+    return STX_ERR_UNSUPPORTED;
+  }
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(concat_w) |
+                       reinterpret_cast<uintptr_t>(down_packed) | reinterpret_cast<uintptr_t>(scratch);
+  STX_CHECK_ARG((al & 15) == 0, "stx_sparse_mlp_forward: x, concat_w, down_packed and scratch must be 16-byte aligned");
+  const char* cw = static_cast<const char*>(concat_w);
+  const void* gate = has_gate ? cw : nullptr;
+  const void* up = has_gate ? cw + static_cast<size_t>(K) * H * es : cw;
+  return mlp_forward(x, B, H, gate, up, down_packed, nullptr, K, std::max<int64_t>(K, 1), 0, down_buf, combined_buf, act,
+                     has_gate ? 1 : 0, dtype, scratch, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

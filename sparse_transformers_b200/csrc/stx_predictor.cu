@@ -1,0 +1,204 @@
+// LoRA importance predictor -> per-row rule -> bit mask -> OR over the batch.
+//
+// Replaces FastLoRAProjection.forward (src/modeling_skip.py:52-53: scores = up(down(x)),
+// two bias-free nn.Linear) and _compute_binary_mask (src/modeling_skip.py:204-214).
+//
+// Arithmetic contract (what makes the mask reproducible bit for bit by a CPU restatement):
+//   t[b,k]  = round_dtype( sum_h x[b,h] * A[k,h] )      fp32 fused multiply-adds
+//   s[b,i]  = round_dtype( sum_k t[b,k] * Bm[i,k] )     fp32 fused multiply-adds
+// with a fixed summation order.  With V = 16 / sizeof(elem) elements per chunk:
+//   t: 32 partial sums; partial l adds chunks l, l+32, l+64, ... in ascending element order
+//      starting from +0; the partials are combined by the butterfly
+//      p[l] += p[l ^ 16]; p[l] += p[l ^ 8]; ... ; p[l] += p[l ^ 1].
+//   s: 8 partial sums; partial g adds chunks g, g+8, ... likewise; butterfly over 4, 2, 1.
+#include "stx_common.cuh"
+
+namespace stx {
+
+constexpr int PRED_BT = 8;  // batch rows accumulated per pass
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t_out, int B, int H, int r) {
+  constexpr int V = DT<T>::V;
+  const int lane = threadIdx.x & 31;
+  const int k = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (k >= r) return;
+  const int nchunk = H / V;
+  const T* arow = A + static_cast<size_t>(k) * H;
+  for (int b0 = 0; b0 < B; b0 += PRED_BT) {
+    float acc[PRED_BT];
+#pragma unroll
+    for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
+    const int nb = min(PRED_BT, B - b0);
+    for (int c = lane; c < nchunk; c += 32) {
+      float wa[V];
+      Unpack<T>::run(ld_stream16(arow + c * V), wa);
+#pragma unroll
+      for (int b = 0; b < PRED_BT; ++b) {
+        if (b < nb) {
+          float xv[V];
+          Unpack<T>::run(ld_cached16(x + static_cast<size_t>(b0 + b) * H + c * V), xv);
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[b] = fmaf(xv[v], wa[v], acc[b]);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < PRED_BT; ++b) {
+      const float s = warp_sum_xor(acc[b]);
+      if (lane == 0 && b < nb) t_out[static_cast<size_t>(b0 + b) * r + k] = DT<T>::round_f(s);
+    }
+  }
+}
+
+// One warp per mask word (32 neurons); 8 lanes cooperate on one neuron, 4 neurons per pass.
+// Dynamic shared memory: t [B,r] fp32.
+template <typename T>
+__global__ void __launch_bounds__(64)
+k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* __restrict__ bits,
+              T* __restrict__ scores_out, int B, int r, int I, float tau, int write_bits) {
+  constexpr int V = DT<T>::V;
+  extern __shared__ float t_s[];
+  for (int i = threadIdx.x; i < B * r; i += blockDim.x) t_s[i] = t[i];
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31;
+  const int w = blockIdx.x * 2 + (threadIdx.x >> 5);
+  const int W = (I + 31) >> 5;
+  if (w >= W) return;
+  const int g = lane & 7, q = lane >> 3;
+  const float tau_r = DT<T>::round_f(tau);
+  const bool vec_ok = (r % V) == 0 && ((reinterpret_cast<uintptr_t>(Bm) & 15) == 0);
+  const int nchunk = (r + V - 1) / V;
+  uint32_t word = 0u;
+
+  for (int pass = 0; pass < 8; ++pass) {
+    const int n = pass * 4 + q;
+    const int i = w * 32 + n;
+    const bool i_ok = i < I;
+    const T* brow = Bm + static_cast<size_t>(i_ok ? i : 0) * r;
+    bool on = false;
+    for (int b0 = 0; b0 < B; b0 += PRED_BT) {
+      float acc[PRED_BT];
+#pragma unroll
+      for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
+      const int nb = min(PRED_BT, B - b0);
+      if (i_ok) {
+        for (int c = g; c < nchunk; c += 8) {
+          float wv[V];
+          if (vec_ok) {
+            Unpack<T>::run(ld_stream16(brow + c * V), wv);
+          } else {
+#pragma unroll
+            for (int v = 0; v < V; ++v) wv[v] = (c * V + v < r) ? DT<T>::to_f(brow[c * V + v]) : 0.f;
+          }
+#pragma unroll
+          for (int b = 0; b < PRED_BT; ++b) {
+            if (b < nb) {
+              const float* tb = t_s + (b0 + b) * r + c * V;
+#pragma unroll
+              for (int v = 0; v < V; ++v)
+                if (vec_ok || c * V + v < r) acc[b] = fmaf(tb[v], wv[v], acc[b]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < PRED_BT; ++b) {
+        float s = acc[b];
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if (b < nb) {
+          const float sr = DT<T>::round_f(s);
+          if (scores_out && g == 0 && i_ok) scores_out[static_cast<size_t>(b0 + b) * I + i] = DT<T>::from_f(s);
+          on = on || (sr >= tau_r);
+        }
+      }
+    }
+    const uint32_t bal = __ballot_sync(0xffffffffu, on && i_ok && g == 0);
+    word |= ((bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u)) << (pass * 4);
+  }
+  if (write_bits && lane == 0) bits[w] = word;
+}
+
+template <typename T>
+static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
+                          int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
+                          int write_bits, cudaStream_t s) {
+  k_pred_t<T><<<static_cast<unsigned>((r + 3) / 4), 128, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(A),
+                                                               t_scratch, static_cast<int>(B), static_cast<int>(H),
+                                                               static_cast<int>(r));
+  STX_LAUNCH_CHECK("k_pred_t");
+  const int64_t W = (I + 31) / 32;
+  const size_t smem = static_cast<size_t>(B) * r * sizeof(float);
+  k_pred_scores<T><<<static_cast<unsigned>((W + 1) / 2), 64, smem, s>>>(
+      t_scratch, static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
+      static_cast<int>(r), static_cast<int>(I), tau, write_bits);
+  STX_LAUNCH_CHECK("k_pred_scores");
+  return STX_OK;
+}
+
+// Implemented in stx_select.cu: per-row rules that need the whole score row.
+int mask_from_scores(const void* scores, int64_t B, int64_t I, int dtype, int method, float param,
+                     uint32_t* bits_out, void* scratch, cudaStream_t s);
+
+int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
+                 int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch,
+                 cudaStream_t s) {
+  float* t_scratch = static_cast<float*>(scratch);
+  const int write_bits = method == STX_MASK_THRESHOLD ? 1 : 0;
+  int rc;
+  switch (dtype) {
+    case STX_F32:
+      rc = launch_predict<float>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
+      break;
+    case STX_F16:
+      rc = launch_predict<__half>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
+      break;
+    default:
+      rc = launch_predict<__nv_bfloat16>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
+      break;
+  }
+  if (rc != STX_OK || method == STX_MASK_THRESHOLD) return rc;
+  void* sel_scratch = static_cast<char*>(scratch) + align_up(static_cast<size_t>(B) * r * sizeof(float), 256);
+  return mask_from_scores(scores_out, B, I, dtype, method, param, bits, sel_scratch, s);
+}
+
+}  // namespace stx
+
+using namespace stx;
+
+extern "C" {
+
+int stx_predict_scratch_bytes(int64_t B, int64_t I, int64_t r, size_t* bytes_out) {
+  STX_CHECK_ARG(bytes_out && B > 0 && I > 0 && r > 0, "stx_predict_scratch_bytes: bad argument");
+  // t [B,r] fp32, then per-row selection scratch (B x 4 floats + B x ceil(I/32) words)
+  *bytes_out = align_up(static_cast<size_t>(B) * r * sizeof(float), 256) +
+               align_up(static_cast<size_t>(B) * (16 + ((I + 31) / 32) * sizeof(uint32_t)), 256);
+  return STX_OK;
+}
+
+int stx_predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
+                     int dtype, int method, float param, uint32_t* mask_bits_out, void* scores_out, void* scratch,
+                     void* stream) {
+  STX_CHECK_ARG(x && A && Bm && mask_bits_out && scratch, "stx_predict_mask: null pointer");
+  STX_CHECK_ARG(B > 0 && H > 0 && r > 0 && I > 0, "stx_predict_mask: sizes must be positive");
+  STX_CHECK_ARG(dtype == STX_F32 || dtype == STX_F16 || dtype == STX_BF16, "stx_predict_mask: bad dtype %d", dtype);
+  STX_CHECK_ARG(method >= STX_MASK_THRESHOLD && method <= STX_MASK_STATISTICAL, "stx_predict_mask: bad method %d",
+                method);
+  STX_CHECK_ARG(method == STX_MASK_THRESHOLD || scores_out, "stx_predict_mask: this rule needs scores_out");
+  if ((H * dtype_size(dtype)) % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(A) & 15)) {
+    set_error("stx_predict_mask: x and A rows must be 16-byte aligned (H*elem %% 16 == 0)");
+    return STX_ERR_UNSUPPORTED;
+  }
+  if (static_cast<size_t>(B) * r * sizeof(float) > 48 * 1024) {
+    set_error("stx_predict_mask: B*r=%lld exceeds the shared-memory tile (12288 values)", static_cast<long long>(B * r));
+    return STX_ERR_TOO_LARGE;
+  }
+  return predict_mask(x, B, H, A, r, Bm, I, dtype, method, param, mask_bits_out, scores_out, scratch,
+                      static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
