@@ -1,0 +1,133 @@
+"""Fused layer step / graph stack on the GPU vs the oracle pipeline on the same seeded inputs:
+masks and cache indices bit-exact, outputs within tolerance (1e-5 fp32, 2e-2 fp16/bf16,
+as max|a-b|/max|b|)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: 1e-5, torch.float16: 2e-2, torch.bfloat16: 2e-2}
+ODT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+class OracleLayer:
+    def __init__(self, w, gate, up, down, A, Bm):
+        f = lambda t: t.float().numpy()
+        self.w = w
+        self.gate, self.up, self.downT = f(gate), f(up), np.ascontiguousarray(f(down).T)
+        self.A, self.Bm = f(A), f(Bm)
+        self.cache = orc.OracleCache(w.I)
+        self.cache.update(np.ones(w.I, bool))
+
+    def step(self, x):
+        w = self.w
+        _, s = orc.predictor(x.float().numpy(), self.A, self.Bm, ODT[w.dtype])
+        _, mask = orc.mask_threshold(s, ODT[w.dtype], w.tau)
+        self.cache.update(mask)
+        wcat = np.concatenate([self.cache.gather(self.gate), self.cache.gather(self.up)]) if w.has_gate else self.cache.gather(self.up)
+        out, _ = orc.sparse_mlp(x.float().numpy(), wcat, self.cache.gather(self.downT), w.act, w.has_gate)
+        return mask, out
+
+
+def _run(w, steps, seed=0):
+    from sparse_transformers_b200 import SparseLayer
+    from sparse_transformers_b200.synth import HiddenStream, layer_weights
+    from stxgpu import DEV, rel_err
+
+    gen = torch.Generator().manual_seed(seed)
+    gate, up, down, A, Bm = layer_weights(w, gen)
+    xs = HiddenStream(w, gen)
+    layer = SparseLayer(gate.to(DEV), up.to(DEV), down.to(DEV), A.to(DEV), Bm.to(DEV), act=w.act, method="threshold",
+                        param=w.tau, max_batch=w.B, has_gate=w.has_gate)
+    ol = OracleLayer(w, gate, up, down, A, Bm)
+    ks, worst = [], 0.0
+    for t in range(steps):
+        x = xs.next()
+        out = layer.step(x.to(DEV))
+        torch.cuda.synchronize()
+        mask, ref = ol.step(x)
+        assert np.array_equal(layer.mask().cpu().numpy(), mask), f"mask differs at step {t}"
+        assert layer.active_indices().tolist() == ol.cache.active.tolist(), f"cache order differs at step {t}"
+        worst = max(worst, rel_err(out.float().cpu().numpy(), ref))
+        ks.append(layer.num_active())
+    assert worst <= TOL[w.dtype], worst
+    layer.close()
+    return ks
+
+
+def test_c1_llama1b_layer_fp32():
+    """Llama-3.2-1B-shaped layer, fp32, batch 1, AR(1) hidden states (the reference's own
+    CPU-runnable configuration), 24 steps."""
+    from sparse_transformers_b200.synth import WORKLOADS
+
+    ks = _run(WORKLOADS["C1"], steps=24)
+    assert 0.15 * 8192 < np.mean(ks[2:]) < 0.25 * 8192
+
+
+@pytest.mark.parametrize("name,scale", [("C2", dict(I=4096)), ("C3", dict(I=2048, H=1024))])
+def test_half_precision_shapes(name, scale):
+    from sparse_transformers_b200.synth import WORKLOADS
+
+    _run(WORKLOADS[name].scaled(layers=1, **scale), steps=8)
+
+
+def test_no_gate_relu_ragged():
+    from sparse_transformers_b200.synth import Workload
+
+    w = Workload("ragged", H=72, I=333, r=20, B=3, dtype=torch.float32, density=0.3, act="relu", has_gate=False, alpha=0.5)
+    _run(w, steps=10)
+
+
+def test_stack_graph_matches_eager_layers():
+    """The CUDA-graph replay of L layers equals stepping the layers one by one."""
+    from sparse_transformers_b200 import SparseLayer, SparseStack
+    from sparse_transformers_b200.synth import HiddenStream, WORKLOADS, layer_weights
+    from stxgpu import DEV
+
+    w = WORKLOADS["C2"].scaled(I=2048, H=512, layers=3)
+    gen = torch.Generator().manual_seed(1)
+    ws = [layer_weights(w, gen) for _ in range(w.layers)]
+    mk = lambda: [SparseLayer(*[t.to(DEV) for t in lw], act=w.act, param=w.tau, max_batch=w.B) for lw in ws]
+    eager, graphed = mk(), mk()
+    stack = SparseStack(graphed, w.B)
+    assert stack.launches_per_step >= 3 * w.layers
+    xs = HiddenStream(w, gen)
+    out = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=DEV)
+    xh = torch.empty(w.B, w.H, dtype=w.dtype).pin_memory()
+    oh = torch.empty(w.layers, w.B, w.H, dtype=w.dtype).pin_memory()
+    for t in range(6):
+        x = xs.next()
+        if t % 2 == 0:
+            stack.step(x.to(DEV), out)
+            torch.cuda.synchronize()
+            got = out.cpu()
+        else:
+            xh.copy_(x)
+            stack.step_host(xh, oh)
+            got = oh.clone()
+        for l in range(w.layers):
+            ref = eager[l].step(x.to(DEV))
+            torch.cuda.synchronize()
+            assert eager[l].active_indices().tolist() == graphed[l].active_indices().tolist()
+            assert torch.allclose(got[l].float(), ref.float().cpu(), rtol=2e-2, atol=2e-3)
+    stack.close()
+
+
+def test_step_host_equals_device_step():
+    from sparse_transformers_b200 import SparseLayer
+    from sparse_transformers_b200.synth import WORKLOADS, layer_weights
+    from stxgpu import DEV
+
+    w = WORKLOADS["C1"].scaled(I=1024, H=256)
+    gen = torch.Generator().manual_seed(2)
+    lw = layer_weights(w, gen)
+    a = SparseLayer(*[t.to(DEV) for t in lw], param=w.tau)
+    b = SparseLayer(*[t.to(DEV) for t in lw], param=w.tau)
+    x = torch.randn(1, w.H, generator=gen)
+    oh = torch.empty(1, w.H)
+    b.step_host(x, oh)
+    od = a.step(x.to(DEV)).cpu()
+    assert torch.allclose(od, oh, rtol=1e-5, atol=1e-6)
+    assert a.active_indices().tolist() == b.active_indices().tolist()
