@@ -201,6 +201,15 @@ int stx_layer_destroy(stx_layer_t* l);
  * out [B,H].  Asynchronous, no allocation, graph-capturable.                            */
 int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B,
                    void* out, void* stream);
+/* The same step restricted to some of its stages (bit mask); used to time stages apart.
+ * Stages that are skipped leave their outputs as the previous call left them.          */
+#define STX_STAGE_PREDICT 1u /* predictor -> mask bits                    */
+#define STX_STAGE_PLAN 2u    /* mask diff -> cache index plan             */
+#define STX_STAGE_COPY 4u    /* rewrite the changed packed rows           */
+#define STX_STAGE_MLP 8u     /* sparse gate/up/down projection            */
+#define STX_STAGE_ALL 15u
+int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B,
+                          void* out, void* stream, unsigned stages);
 /* Device pointer to the layer's current mask bits (ceil(I/32) words), valid after a step. */
 int stx_layer_mask_bits(stx_layer_t* l, const uint32_t** bits_out);
 
@@ -212,6 +221,9 @@ int stx_layer_step_host(stx_layer_t* l, const void* x_host, int64_t B, void* out
  * captured once into a CUDA graph and replayed, strictly serialised on one stream.
  * stx_stack_create ALLOCATES and runs one capture; the layers stay owned by the caller. */
 int stx_stack_create(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B);
+/* Same, capturing only the given STX_STAGE_* bits of every layer step.                  */
+int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B,
+                            unsigned stages);
 int stx_stack_destroy(stx_stack_t* s);
 /* Device addresses of the stack's own input [B,H] and output [L,B,H] buffers, which the
  * captured graph reads and writes.                                                     */

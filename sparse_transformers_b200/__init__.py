@@ -18,6 +18,11 @@ Unlike the reference's package, importing it does not touch thread-count setting
 from __future__ import annotations
 
 import os
+import sys
+
+if any(a == "sparse_transformers_b200.build" for a in getattr(sys, "orig_argv", [])):
+    # `python -m sparse_transformers_b200.build`: the libraries may not exist yet
+    raise SystemExit(__import__("runpy").run_path(os.path.join(os.path.dirname(__file__), "build.py"), run_name="__main__") and 0)
 
 import torch
 

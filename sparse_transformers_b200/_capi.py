@@ -16,6 +16,7 @@ F32, F16, BF16 = 0, 1, 2
 ACT_RELU, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID, ACT_GELU = range(5)
 MASK_THRESHOLD, MASK_TOPK, MASK_STATISTICAL = range(3)
 CACHE_ALIAS_GATE_UP = 1
+STAGE_PREDICT, STAGE_PLAN, STAGE_COPY, STAGE_MLP, STAGE_ALL = 1, 2, 4, 8, 15
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -54,9 +55,11 @@ SIGNATURES = {
     "stx_layer_create": (_i32, [_pp, _vp, _vp, _i64, _vp, _i32, _f32, _i32, _i64]),
     "stx_layer_destroy": (_i32, [_vp]),
     "stx_layer_step": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
+    "stx_layer_step_stages": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _u32]),
     "stx_layer_mask_bits": (_i32, [_vp, _pp]),
     "stx_layer_step_host": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "stx_stack_create": (_i32, [_pp, _pp, _i64, _i64]),
+    "stx_stack_create_stages": (_i32, [_pp, _pp, _i64, _i64, _u32]),
     "stx_stack_destroy": (_i32, [_vp]),
     "stx_stack_buffers": (_i32, [_vp, _pp, _pp]),
     "stx_stack_step": (_i32, [_vp, _vp, _vp, _vp]),

@@ -101,19 +101,39 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   return STX_OK;
 }
 
-int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, void* stream) {
-  STX_CHECK_ARG(l && x_pred && x_mlp && out, "stx_layer_step: null pointer");
+int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, void* stream,
+                          unsigned stages) {
+  STX_CHECK_ARG(l, "stx_layer_step: null layer");
   STX_CHECK_ARG(B > 0 && B <= l->max_batch, "stx_layer_step: B=%lld outside 1..max_batch=%lld", static_cast<long long>(B),
                 static_cast<long long>(l->max_batch));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   stx_cache* c = l->cache;
-  int rc = stx_predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
-                            l->pred_scratch, stream);
-  if (rc != STX_OK) return rc;
-  rc = cache_update_bits(c, l->bits, s);
-  if (rc != STX_OK) return rc;
-  return mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
+  int rc = STX_OK;
+  if (stages & STX_STAGE_PREDICT) {
+    STX_CHECK_ARG(x_pred, "stx_layer_step: x_pred is null");
+    rc = stx_predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
+                          l->pred_scratch, stream);
+    if (rc != STX_OK) return rc;
+  }
+  if (stages & STX_STAGE_PLAN) {
+    rc = cache_plan(c, l->bits, s);
+    if (rc != STX_OK) return rc;
+  }
+  if (stages & STX_STAGE_COPY) {
+    rc = cache_copy_rows(c, s);
+    if (rc != STX_OK) return rc;
+  }
+  if (stages & STX_STAGE_MLP) {
+    STX_CHECK_ARG(x_mlp && out, "stx_layer_step: x_mlp/out is null");
+    rc = mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
                      c->has_gate, c->dtype, l->mlp_scratch, s);
+  }
+  return rc;
+}
+
+int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, void* stream) {
+  STX_CHECK_ARG(l && x_pred && x_mlp && out, "stx_layer_step: null pointer");
+  return stx_layer_step_stages(l, x_pred, x_mlp, B, out, stream, STX_STAGE_ALL);
 }
 
 int stx_layer_mask_bits(stx_layer_t* l, const uint32_t** bits_out) {
@@ -155,6 +175,10 @@ int stx_stack_destroy(stx_stack_t* s) {
 }
 
 int stx_stack_create(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B) {
+  return stx_stack_create_stages(out, layers, L, B, STX_STAGE_ALL);
+}
+
+int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B, unsigned stages) {
   STX_CHECK_ARG(out, "stx_stack_create: out is null");
   *out = nullptr;
   STX_CHECK_ARG(layers && L > 0 && B > 0, "stx_stack_create: bad argument");
@@ -193,7 +217,7 @@ int stx_stack_create(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, i
   e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
   if (e == cudaSuccess) {
     for (int64_t i = 0; i < L && rc == STX_OK; ++i) {
-      rc = stx_layer_step(s->layers[i], s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs);
+      rc = stx_layer_step_stages(s->layers[i], s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs, stages);
     }
     cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
     if (rc == STX_OK && e2 != cudaSuccess) e = e2;

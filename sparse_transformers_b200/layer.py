@@ -123,7 +123,7 @@ class SparseLayer:
 class SparseStack:
     """L layers fed the same x [B,H], replayed as one CUDA graph; out is [L,B,H]."""
 
-    def __init__(self, layers: Sequence[SparseLayer], batch: int):
+    def __init__(self, layers: Sequence[SparseLayer], batch: int, stages: int = C.STAGE_ALL):
         self.layers = list(layers)
         self.B = int(batch)
         self.L = len(self.layers)
@@ -133,7 +133,7 @@ class SparseStack:
         arr = (ctypes.c_void_p * self.L)(*[l._layer for l in self.layers])
         h = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            C.check(C.lib.stx_stack_create(ctypes.byref(h), arr, self.L, self.B))
+            C.check(C.lib.stx_stack_create_stages(ctypes.byref(h), arr, self.L, self.B, stages))
         self._stack = h
         n = ctypes.c_int64()
         C.check(C.lib.stx_stack_launches_per_step(self._stack, ctypes.byref(n)))
@@ -154,6 +154,12 @@ class SparseStack:
         """x: device [B,H] or None (reuse the stack's input buffer); out: device [L,B,H] or None."""
         C.check(C.lib.stx_stack_step(self._stack, x.data_ptr() if x is not None else None,
                                      out.data_ptr() if out is not None else None, _stream()))
+
+    def buffers(self) -> tuple[int, int]:
+        """Device addresses of the stack's own input [B,H] and output [L,B,H] buffers."""
+        a, b = ctypes.c_void_p(), ctypes.c_void_p()
+        C.check(C.lib.stx_stack_buffers(self._stack, ctypes.byref(a), ctypes.byref(b)))
+        return a.value, b.value
 
     def step_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
         C.check(C.lib.stx_stack_step_host(self._stack, x_host.data_ptr(), out_host.data_ptr(), _stream()))

@@ -18,6 +18,13 @@ def stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+class _DevBytes:
+    """Library-owned device memory exposed through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
 class Cache:
     """stx_cache_t owner."""
 
@@ -69,9 +76,9 @@ class Cache:
     def _view(self, ptr, rows):
         n = rows * self.H
         es = torch.empty(0, dtype=self.dtype).element_size()
-        raw = torch.empty(n * es, dtype=torch.uint8, device=DEV)
-        rc = torch.cuda.cudart().cudaMemcpy(raw.data_ptr(), ptr, n * es, 3)  # device to device
-        assert int(rc) == 0
+        if n == 0:
+            return torch.empty(0, self.H, dtype=self.dtype, device=DEV)
+        raw = torch.as_tensor(_DevBytes(ptr, n * es), device=DEV).clone()
         return raw.view(self.dtype).view(rows, self.H)
 
     def concat(self) -> torch.Tensor:
