@@ -1,0 +1,433 @@
+#!/usr/bin/env python
+"""Benchmark of the contextual-sparsity MLP decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C2] [--impl reference]
+
+A *step* is one decode token through every layer of the workload's sparse-MLP stack:
+predictor -> mask -> differential weight-cache update -> sparse gate/up/down projection,
+layer after layer, strictly serialised on one stream.  Metric: decode tokens/s = B / t_step.
+
+Default workload (N = 1): "C2", the Llama-3.2-3B-shaped 28-layer stack, fp16, batch 1,
+random-init weights N(0, 0.02), AR(1) hidden states, ~20 % active neurons per token.
+For N > 1 the intermediate dimension is sharded over the ranks (one process per GPU,
+launched by torch.distributed.run) with an NCCL all-reduce of the partial sums per layer.
+
+One JSON line is printed by rank 0:
+  value      device-timed (CUDA events), inputs resident in HBM, CUDA-graph replay
+  e2e        the same steps through the host-buffer C-ABI call (pinned host x in, result out)
+  roofline   dominant kernel (the sparse MLP): algorithmic bytes / measured launch time
+  cpu_baseline  the reference's own CPU implementation on this box's host cores, bounded sample
+`--impl reference` times only that CPU implementation on the same workload definition.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "sparse_mlp_decode_tokens_per_s"
+UNIT = "tokens/s"
+DTYPE_NAME = {"torch.float32": "f32", "torch.float16": "f16", "torch.bfloat16": "bf16"}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--workload", default="C2")
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = workload default)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------ helpers
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+        self.t = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.t = threading.Thread(target=self._read, daemon=True)
+        self.t.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json copy bandwidth)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def traffic_ratio():
+    """DRAM bytes / algorithmic bytes of the MLP kernel from the committed ncu capture."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "k_mlp_fused_traffic.json")) as f:
+            return float(json.load(f)["dram_over_algorithmic"])
+    except Exception:
+        return None
+
+
+def mlp_algorithmic_bytes(w, K: float) -> float:
+    """Sparse-MLP launch: active gate/up/down rows read once + x, a and the output."""
+    s = w.dtype.itemsize if hasattr(w.dtype, "itemsize") else 2
+    nmat = 3 if w.has_gate else 2
+    return s * nmat * K * w.H + s * w.B * 2 * w.H + 4 * w.B * K
+
+
+def layer_step_algorithmic_bytes(w, K: float, dK: float) -> float:
+    """Whole layer step: predictor weights + active MLP weights + cache rows (pool read +
+    packed write) + activations, scores and masks."""
+    s = w.dtype.itemsize
+    nmat = 3 if w.has_gate else 2
+    return (s * (w.r * w.H + w.I * w.r) + s * nmat * K * w.H + 2 * s * nmat * dK * w.H
+            + s * w.B * (2 * w.H + w.r + 2 * K) + w.B * w.I * s + 2 * w.I / 8)
+
+
+# ------------------------------------------------------------------------------ CPU arm
+
+def cpu_reference_run(w, n_layers: int, steps: int, warmup: int, seed: int = 0):
+    """Times the reference's CPU path (compiled unmodified, oracle/_ref; else the C oracle) on
+    `n_layers` layers of the workload in fp32 (the reference cache is fp32-only).
+    Returns dict(value tokens/s for the full stack, kind, cores, sample, split)."""
+    import torch
+
+    from sparse_transformers_b200.synth import HiddenStream, layer_weights
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(seed)
+    w32 = w.scaled(dtype=torch.float32)
+    weights = [layer_weights(w32, gen) for _ in range(n_layers)]
+    xs = HiddenStream(w32, gen).take(warmup + steps)
+    kind = "reference"
+    try:
+        from oracle import ref_python as rp
+
+        if not rp.have_reference():
+            raise RuntimeError("no compiled reference")
+        layers = [rp.RefLayer(*lw, act=w.act, method="threshold", tau=w.tau, has_gate=w.has_gate) for lw in weights]
+
+        def step(x):
+            for l in layers:
+                l.step(x, op=True)
+    except Exception:
+        kind = "port"
+        import numpy as np
+
+        from oracle import oracle as orc
+
+        f = lambda t: t.float().numpy()
+        st = []
+        for (g, u, d, A, Bm) in weights:
+            c = orc.OracleCache(w.I)
+            c.update(np.ones(w.I, bool))
+            st.append((c, f(g), f(u), np.ascontiguousarray(f(d).T), f(A), f(Bm)))
+        cores = 1
+
+        def step(x):
+            xn = f(x)
+            for (c, g, u, dT, A, Bm) in st:
+                _, s = orc.predictor(xn, A, Bm, orc.F32)
+                _, m = orc.mask_threshold(s, orc.F32, w.tau)
+                c.update(m)
+                wcat = np.concatenate([c.gather(g), c.gather(u)]) if w.has_gate else c.gather(u)
+                orc.sparse_mlp(xn, wcat, c.gather(dT), "relu", w.has_gate)
+
+    for i in range(warmup):
+        step(xs[i])
+    times = []
+    for i in range(warmup, warmup + steps):
+        t0 = time.perf_counter()
+        step(xs[i])
+        times.append(time.perf_counter() - t0)
+    total = sum(times)
+    t_layer = total / (steps * n_layers)
+    t_token = t_layer * w.layers
+    sample = (f"{n_layers} of {w.layers} layers x {steps} decode steps of {w.name} in fp32 "
+              f"(predictor + WeightCache.update_active_weights + sparse_mlp forward), scaled to {w.layers} layers")
+    return {"value": w.B / t_token, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample,
+            "ms_per_layer_step": t_layer * 1e3, "ms_per_step": total / steps * 1e3 * w.layers / n_layers}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from sparse_transformers_b200.synth import WORKLOADS
+
+    w = WORKLOADS[args.workload]
+    if args.layers:
+        w = w.scaled(layers=args.layers)
+    r = cpu_reference_run(w, min(args.cpu_layers, w.layers), args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(w, args.gpus),
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(w, n_gpus):
+    return {"workload": w.name, "hidden": w.H, "intermediate": w.I, "predictor_rank": w.r, "layers": w.layers,
+            "batch": w.B, "density_per_row": w.density, "activation": w.act, "threshold": round(w.tau, 6),
+            "parallelism": "single GPU" if n_gpus == 1 else f"intermediate dim sharded over {n_gpus} GPUs + all-reduce per layer",
+            "l2": "distinct weights per layer: one step touches more bytes than the 126 MB L2"}
+
+
+# ------------------------------------------------------------------------------ GPU arm
+
+def run_native(args):
+    import torch
+    import torch.distributed as dist
+
+    import sparse_transformers_b200 as stb
+    from sparse_transformers_b200 import _capi as C
+    from sparse_transformers_b200.sharded import ShardedLayer, ShardedStack, shard_range
+    from sparse_transformers_b200.synth import HiddenStream, WORKLOADS, layer_weights
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+
+    w = WORKLOADS[args.workload]
+    if args.layers:
+        w = w.scaled(layers=args.layers)
+    K_steps, W_steps = args.steps, max(args.warmup, 0)
+
+    # ---- weights: generated on the device (identical on every rank), sliced per rank
+    gen = torch.Generator(device=dev).manual_seed(0)
+    layers = []
+    cpu_weights = []  # first layers kept on the host for the CPU baseline sample (fp32)
+    for li in range(w.layers):
+        gate, up, down, A, Bm = layer_weights(w, gen, device=dev)
+        if world == 1:
+            layers.append(stb.SparseLayer(gate, up, down, A, Bm, act=w.act, method="threshold", param=w.tau,
+                                          max_batch=w.B, has_gate=w.has_gate, alias_gate_up=True))
+        else:
+            lo, hi = shard_range(w.I, rank, world)
+            layers.append(ShardedLayer(gate[lo:hi].contiguous(), up[lo:hi].contiguous(), down[:, lo:hi].contiguous(), A,
+                                       Bm[lo:hi].contiguous(), act=w.act, method="threshold", param=w.tau,
+                                       max_batch=w.B, has_gate=w.has_gate))
+        del gate, up, down
+    torch.cuda.synchronize()
+
+    n_inst = 8  # steps of the stage-timing pass
+    xs_cpu = HiddenStream(w, torch.Generator().manual_seed(1)).take(2 * (W_steps + K_steps) + n_inst + 8)
+    xs_dev = xs_cpu.to(dev)
+    cursor = 0
+
+    if world == 1:
+        stack = stb.SparseStack(layers, w.B)
+    else:
+        stack = ShardedStack(layers, w.B, xs_dev[0])
+        cursor = 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    out_dev = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=dev)
+
+    # ---- device-timed region (inputs resident in HBM)
+    for _ in range(W_steps):
+        stack.step(xs_dev[cursor], out_dev)
+        cursor += 1
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K_steps):
+        stack.step(xs_dev[cursor], out_dev)
+        cursor += 1
+    ev1.record()
+    barrier()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the host-buffer call (pinned host in, result back to host)
+    x_pin = torch.empty(w.B, w.H, dtype=w.dtype).pin_memory()
+    o_pin = torch.empty(w.layers, w.B, w.H, dtype=w.dtype).pin_memory()
+    for _ in range(W_steps):
+        x_pin.copy_(xs_cpu[cursor])
+        stack.step_host(x_pin, o_pin)
+        cursor += 1
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K_steps):
+        x_pin.copy_(xs_cpu[cursor])
+        stack.step_host(x_pin, o_pin)
+        cursor += 1
+    barrier()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_total = float(e2e_s.item())
+
+    # ---- stage timing pass (single GPU): the dominant kernel's launches timed alone with
+    #      CUDA events on the launching stream, all layers back to back in one graph
+    roofline, stages_us, k_mean, dk_mean = None, None, None, None
+    if world == 1:
+        names = ("predict", "plan", "copy", "mlp")
+        st = {n: stb.SparseStack(layers, w.B, stages=b) for n, b in
+              zip(names, (C.STAGE_PREDICT, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_MLP))}
+        nbytes = w.B * w.H * w.dtype.itemsize
+        xin = [torch.as_tensor(_DevBytes(st[n].buffers()[0], nbytes), device=dev) for n in ("predict", "mlp")]
+        acc = dict.fromkeys(names, 0.0)
+        ks, dks = [], []
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        n_warm = 2
+        for i in range(n_inst + n_warm):
+            x = xs_dev[cursor]
+            cursor += 1
+            for v in xin:  # stage the input in the stacks' own buffers, outside the timed brackets
+                v.copy_(x.contiguous().view(torch.uint8).reshape(-1))
+            torch.cuda.synchronize()
+            for k, n in enumerate(names):  # one decode step, stage by stage over all layers
+                evs[k].record()
+                st[n].step(None, None)
+            evs[4].record()
+            torch.cuda.synchronize()
+            if i < n_warm:
+                continue
+            for n, a, b in zip(names, evs[:-1], evs[1:]):
+                acc[n] += a.elapsed_time(b) * 1e3 / w.layers  # microseconds per layer
+            for l in layers:
+                ks.append(l.num_active())
+                dks.append(l.update_stats()[2])
+        stages_us = {k: v / n_inst for k, v in acc.items()}
+        k_mean, dk_mean = statistics.mean(ks), statistics.mean(dks)
+        peak, peak_src = measured_peak_gbs()
+        alg = mlp_algorithmic_bytes(w, k_mean)
+        achieved = alg / (stages_us["mlp"] * 1e-6) / 1e9
+        ratio = traffic_ratio()
+        roofline = {"kernel": "k_mlp_fused", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_source": peak_src, "traffic": (ratio * alg if ratio else None),
+                    "algorithmic_bytes_per_launch": alg, "us_per_launch": stages_us["mlp"], "launches_timed": n_inst * w.layers}
+        for s_ in st.values():
+            s_.close()
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    ms_step = ms_total / K_steps
+    value = w.B / (ms_step * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K_steps, "warmup": W_steps,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
+        "vs_baseline": None, "dtype": DTYPE_NAME[str(w.dtype)], "data": "synthetic",
+        "config": workload_config(w, world),
+        "e2e": {"value": w.B / (e2e_total / K_steps), "unit": UNIT, "ms_per_step": e2e_total / K_steps * 1e3,
+                "h2d_bytes_per_step": w.B * w.H * w.dtype.itemsize, "d2h_bytes_per_step": w.layers * w.B * w.H * w.dtype.itemsize},
+        "gpu_launches": int(stack.launches_per_step * K_steps),
+        "clocks": clocks,
+    }
+    if roofline:
+        line["roofline"] = roofline
+        line["stages_us_per_layer"] = stages_us
+        line["active_neurons_mean"] = k_mean
+        line["rows_rewritten_mean"] = dk_mean
+        step_alg = layer_step_algorithmic_bytes(w, k_mean, dk_mean) * w.layers
+        line["step_algorithmic_gbs"] = step_alg / (ms_step * 1e-3) / 1e9
+        line["step_frac_of_peak"] = line["step_algorithmic_gbs"] / roofline["peak"]
+    if world == 1 and not args.no_cpu_baseline:
+        # free the device side first? not needed: the CPU sample uses its own host copies
+        try:
+            cb = cpu_reference_run(w, min(args.cpu_layers, w.layers), steps=24, warmup=2)
+            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        except Exception as e:  # the baseline is a reported extra, never a reason to lose the line
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                                    "sample": f"failed: {type(e).__name__}: {e}"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+class _DevBytes:
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

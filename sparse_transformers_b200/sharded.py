@@ -1,0 +1,92 @@
+"""Intermediate-dimension sharding of the sparse MLP over the GPUs of one node.
+
+Neurons are independent until the down projection sums over them, so rank g owns the
+contiguous neuron range shard_range(I, g, G): the matching rows of gate / up / the
+predictor's up matrix and the matching columns of down.  The predictor's down matrix A and
+the hidden states are replicated.  Every rank runs its own predictor slice, mask and
+differential weight cache (identical to a single-GPU cache built on the sliced weights) and
+produces a partial [B,H]; one all-reduce(sum) per layer per step combines them (NCCL over
+NVLink).  The per-row rules that need whole-row statistics (topk, statistical_topk) are not
+shard-local; sharded layers use the explicit-threshold rule.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from .layer import SparseLayer
+
+
+def shard_range(I: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous, balanced split; the first I % world shards get one extra neuron."""
+    base, rem = divmod(I, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def shard_weights(gate, up, down, A, Bm, rank: int, world: int):
+    """Slices of full-size weights owned by `rank` (views; call .contiguous() before upload)."""
+    lo, hi = shard_range(up.shape[0], rank, world)
+    return (gate[lo:hi] if gate is not None else None), up[lo:hi], down[:, lo:hi], A, Bm[lo:hi]
+
+
+class ShardedLayer:
+    """SparseLayer on this rank's shard plus the all-reduce of the partial sums."""
+
+    def __init__(self, gate, up, down, lora_down, lora_up, *, group=None, **kw):
+        if kw.get("method", "threshold") not in ("threshold", "naive"):
+            raise ValueError("sharded layers support the explicit-threshold rule only")
+        self.group = group
+        self.local = SparseLayer(gate, up, down, lora_down, lora_up, **kw)
+
+    def step(self, x_pred, x_mlp=None, out=None):
+        out = self.local.step(x_pred, x_mlp, out)
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    def close(self):
+        self.local.close()
+
+
+class ShardedStack:
+    """L sharded layers fed the same x [B,H]; the whole step (kernels + L all-reduces) is
+    captured once in a CUDA graph on this rank and replayed.  out: [L,B,H]."""
+
+    def __init__(self, layers: Sequence[ShardedLayer], batch: int, warmup_x: torch.Tensor):
+        self.layers = list(layers)
+        l0 = self.layers[0].local
+        self.B, self.L, self.H, self.dtype, self.device = int(batch), len(layers), l0.H, l0.dtype, l0.device
+        self.x_in = torch.zeros(self.B, self.H, dtype=self.dtype, device=self.device)
+        self.out = torch.zeros(self.L, self.B, self.H, dtype=self.dtype, device=self.device)
+        self.launches_per_step = 6 * self.L  # 5 kernels of this library + 1 NCCL kernel per layer
+        # eager warm-up on a side stream (NCCL communicators, function attributes), then capture
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.x_in.copy_(warmup_x)
+            for _ in range(2):
+                self._eager()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._eager()
+
+    def _eager(self):
+        for i, l in enumerate(self.layers):
+            l.step(self.x_in, self.x_in, self.out[i])
+
+    def step(self, x: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:
+        if x is not None:
+            self.x_in.copy_(x, non_blocking=True)
+        self.graph.replay()
+        if out is not None:
+            out.copy_(self.out, non_blocking=True)
+
+    def step_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        self.x_in.copy_(x_host, non_blocking=True)
+        self.graph.replay()
+        out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
