@@ -184,6 +184,19 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
                            void* combined_buf, int act, int has_gate, int dtype,
                            void* scratch, void* stream);
 
+/* No counterpart in the reference.  The same computation as stx_sparse_mlp_forward for
+ * callers that may not allocate device memory (a server that fixes its HBM budget at
+ * start-up, a plugin whose host owns the allocator): the scratch lives in a fixed
+ * ~256 KiB device array inside the library image, held by every GPU that loads it.
+ * Limit: B*H <= 65536 elements, else STX_ERR_TOO_LARGE.  The first call on a device
+ * resolves the array's address; make it outside stream capture.  All calls on a device
+ * share the array (it is cleared at the start of each call), so calls whose GPU work
+ * overlaps race: keep them ordered on one stream.  Allocates nothing.                   */
+int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t H, const void* concat_w,
+                                   const void* down_packed, int64_t K, void* down_buf,
+                                   void* combined_buf, int act, int has_gate, int dtype,
+                                   void* stream);
+
 /* ------------------------------------------------------------------ fused layer step
  * One decode step of one sparse layer: predictor -> mask -> cache update -> sparse MLP
  * (SkipDecoderLayer.forward's sparse branch, src/modeling_skip.py:236-238,258, with K

@@ -301,3 +301,79 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of stx_sparse_mlp_forward.
+//
+// Some hosts of this library are not allowed to allocate device memory at all: a serving
+// process that reserves its whole HBM budget at start-up and forbids later cudaMalloc calls
+// (they serialise the device and can fail under memory pressure), or a plugin that is handed
+// raw device pointers by an engine that owns the allocator and cannot lend it out.  Such a
+// caller has nowhere to get the scratch buffer that stx_sparse_mlp_forward asks for, so this
+// entry point brings its own: a fixed array in device global memory that is part of the
+// loaded library image.  Every GPU that loads libstx.so holds the array (about 256 KiB)
+// until the process exits.
+//
+// Limits and rules:
+//   * B * H must not exceed STX_NOALLOC_MAX_BH (65536) elements; larger calls are refused
+//     with STX_ERR_TOO_LARGE.
+//   * The first call on each device looks up the array's device address (once per device,
+//     with that device current).  Make that first call outside any stream capture.
+//   * All calls on a device share the one array.  It still holds whatever the previous call
+//     left there, so each call clears the part it uses before launching; two calls whose
+//     GPU work overlaps (different streams, or different host threads) race on it and give
+//     wrong results.  Keep calls on one stream, or otherwise ordered.
+//   * No cudaMalloc, cudaFree or other allocating routine is called.
+constexpr int64_t STX_NOALLOC_MAX_BH = 65536;
+constexpr size_t NOALLOC_BYTES = 256 + static_cast<size_t>(STX_NOALLOC_MAX_BH) * sizeof(float);
+
+// In host code this name is only a handle for the runtime, never a device address: the
+// address a kernel can use comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+namespace stx {
+
+static int noalloc_scratch_ptr(void** out) {
+  static void* ptrs[64] = {};
+  int dev = 0;
+  STX_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_error("stx_sparse_mlp_forward_noalloc: device index %d not supported", dev);
+    return STX_ERR_UNSUPPORTED;
+  }
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+    if (!p) {
+      set_error("stx_sparse_mlp_forward_noalloc: the scratch array has no device address");
+      return STX_ERR_CUDA;
+    }
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return STX_OK;
+}
+
+}  // namespace stx
+
+extern "C" int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t H, const void* concat_w,
+                                              const void* down_packed, int64_t K, void* down_buf, void* combined_buf,
+                                              int act, int has_gate, int dtype, void* stream) {
+  STX_CHECK_ARG(B > 0 && H > 0, "stx_sparse_mlp_forward_noalloc: bad sizes B=%lld H=%lld", static_cast<long long>(B),
+                static_cast<long long>(H));
+  if (B * H > STX_NOALLOC_MAX_BH) {
+    set_error("stx_sparse_mlp_forward_noalloc: B*H = %lld exceeds the built-in scratch of %lld elements; "
+              "use stx_sparse_mlp_forward with a caller-provided scratch buffer",
+              static_cast<long long>(B * H), static_cast<long long>(STX_NOALLOC_MAX_BH));
+    return STX_ERR_TOO_LARGE;
+  }
+  void* scratch = nullptr;
+  int rc = noalloc_scratch_ptr(&scratch);
+  if (rc != STX_OK) return rc;
+  // the array keeps the previous call's contents: clear the counter and the accumulator
+  const size_t used = 256 + static_cast<size_t>(B) * H * sizeof(float);
+  STX_CUDA(cudaMemsetAsync(scratch, 0, used, static_cast<cudaStream_t>(stream)));
+  return stx_sparse_mlp_forward(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, has_gate, dtype, scratch,
+                                stream);
+}

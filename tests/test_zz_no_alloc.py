@@ -1,0 +1,53 @@
+"""The allocation-free MLP entry point (stx_sparse_mlp_forward_noalloc), for callers that
+cannot hand the library a scratch buffer because they are not allowed to allocate device
+memory.  It must give the same result as the regular entry point, call after call, although
+all calls share one built-in scratch array.  This file sorts last on purpose."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: 1e-5, torch.float16: 2e-2}
+
+
+def _noalloc(x, concat, down_packed, act, has_gate=True):
+    from sparse_transformers_b200 import _capi as C
+    from stxgpu import ACT, DEV, DT, stream
+
+    B, H = x.shape
+    K = down_packed.shape[0]
+    out = torch.full((B, H), float("nan"), dtype=x.dtype, device=DEV)
+    comb = torch.full((B, concat.shape[0]), float("nan"), dtype=x.dtype, device=DEV)
+    C.check(C.lib.stx_sparse_mlp_forward_noalloc(x.data_ptr(), B, H, concat.data_ptr(), down_packed.data_ptr(), K,
+                                                 out.data_ptr(), comb.data_ptr(), ACT[act], int(has_gate), DT[x.dtype], stream()))
+    torch.cuda.synchronize()
+    return out, comb
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_noalloc_matches_regular_entry_point_twice(dtype):
+    from stxgpu import DEV, mlp_forward, rel_err
+
+    g = torch.Generator().manual_seed(123)
+    # two different calls in a row: the second one must not see the first one's leftovers
+    for (B, H, K, act) in [(2, 1024, 300, "silu"), (1, 3072, 777, "relu")]:
+        x = torch.randn(B, H, generator=g).to(dtype).to(DEV)
+        cw = (torch.randn(2 * K, H, generator=g) / H ** 0.5).to(dtype).to(DEV)
+        dp = (torch.randn(K, H, generator=g) / H ** 0.5).to(dtype).to(DEV)
+        ref, rcomb = mlp_forward(x, cw, dp, act)
+        out, comb = _noalloc(x, cw, dp, act)
+        assert rel_err(out.float().cpu().numpy(), ref.float().cpu().numpy()) <= TOL[dtype]
+        assert rel_err(comb.float().cpu().numpy(), rcomb.float().cpu().numpy()) <= TOL[dtype]
+        out2, _ = _noalloc(x, cw, dp, act)   # same call again
+        assert rel_err(out2.float().cpu().numpy(), ref.float().cpu().numpy()) <= TOL[dtype]
+
+
+def test_noalloc_rejects_sizes_beyond_the_builtin_scratch():
+    from sparse_transformers_b200 import _capi as C
+    from stxgpu import DEV, stream
+
+    x = torch.zeros(16, device=DEV)
+    rc = C.lib.stx_sparse_mlp_forward_noalloc(x.data_ptr(), 64, 4096, x.data_ptr(), x.data_ptr(), 1, x.data_ptr(), None,
+                                              0, 1, C.F32, stream())
+    assert rc == C.ERR_TOO_LARGE and "exceeds the built-in scratch" in C.last_error()
