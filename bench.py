@@ -114,7 +114,7 @@ def measured_peak_gbs():
 def traffic_ratio():
     """DRAM bytes / algorithmic bytes of the MLP kernel from the committed ncu capture."""
     try:
-        with open(os.path.join(ROOT, "profiles", "k_mlp_fused_traffic.json")) as f:
+        with open(os.path.join(ROOT, "profiles", "k_gateup_tma_traffic.json")) as f:
             return float(json.load(f)["dram_over_algorithmic"])
     except Exception:
         return None
@@ -337,14 +337,14 @@ def run_native(args):
     #      CUDA events on the launching stream, all layers back to back in one graph
     roofline, stages_us, k_mean, dk_mean = None, None, None, None
     if world == 1:
-        names = ("predict", "plan", "copy", "mlp")
+        names = ("predict", "plan", "copy", "gateup", "down")
         st = {n: stb.SparseStack(layers, w.B, stages=b) for n, b in
-              zip(names, (C.STAGE_PREDICT, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_MLP))}
+              zip(names, (C.STAGE_PREDICT, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_MLP_GATEUP, C.STAGE_MLP_DOWN))}
         nbytes = w.B * w.H * w.dtype.itemsize
-        xin = [torch.as_tensor(_DevBytes(st[n].buffers()[0], nbytes), device=dev) for n in ("predict", "mlp")]
+        xin = [torch.as_tensor(_DevBytes(st[n].buffers()[0], nbytes), device=dev) for n in ("predict", "gateup")]
         acc = dict.fromkeys(names, 0.0)
         ks, dks = [], []
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
         n_warm = 2
         for i in range(n_inst + n_warm):
             x = xs_dev[cursor]
@@ -355,7 +355,7 @@ def run_native(args):
             for k, n in enumerate(names):  # one decode step, stage by stage over all layers
                 evs[k].record()
                 st[n].step(None, None)
-            evs[4].record()
+            evs[len(names)].record()
             torch.cuda.synchronize()
             if i < n_warm:
                 continue
@@ -367,12 +367,19 @@ def run_native(args):
         stages_us = {k: v / n_inst for k, v in acc.items()}
         k_mean, dk_mean = statistics.mean(ks), statistics.mean(dks)
         peak, peak_src = measured_peak_gbs()
-        alg = mlp_algorithmic_bytes(w, k_mean)
-        achieved = alg / (stages_us["mlp"] * 1e-6) / 1e9
+        es = w.dtype.itemsize
+        alg = es * (2 if w.has_gate else 1) * k_mean * w.H + es * w.B * w.H + 4 * w.B * k_mean      # gate/up rows + x + a
+        alg_down = es * k_mean * w.H + 4 * w.B * k_mean + es * w.B * w.H                            # down rows + a + out
+        achieved = alg / (stages_us["gateup"] * 1e-6) / 1e9
         ratio = traffic_ratio()
-        roofline = {"kernel": "k_mlp_fused", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        roofline = {"kernel": "k_gateup_tma", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "peak_source": peak_src, "traffic": (ratio * alg if ratio else None),
-                    "algorithmic_bytes_per_launch": alg, "us_per_launch": stages_us["mlp"], "launches_timed": n_inst * w.layers}
+                    "algorithmic_bytes_per_launch": alg, "us_per_launch": stages_us["gateup"],
+                    "launches_timed": n_inst * w.layers,
+                    "second_kernel": {"kernel": "k_down_slab", "algorithmic_bytes_per_launch": alg_down,
+                                      "us_per_launch": stages_us["down"],
+                                      "achieved": alg_down / (stages_us["down"] * 1e-6) / 1e9,
+                                      "frac": alg_down / (stages_us["down"] * 1e-6) / 1e9 / peak}}
         for s_ in st.values():
             s_.close()
 

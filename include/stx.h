@@ -169,16 +169,18 @@ int stx_approx_topk_threshold(const void* scores, int64_t B, int64_t I, int64_t 
  * (sparse_mlp_op.cpp:53-192, sparse_mlp_cuda.cu:284-361) and the expression the models
  * run, SkipMLP._forward_sparse_weight_cache (src/modeling_skip.py:114-117).             */
 
-/* Bytes of scratch stx_sparse_mlp_forward needs (host function). */
-int stx_mlp_scratch_bytes(int64_t B, int64_t H, size_t* bytes_out);
+/* Bytes of scratch stx_sparse_mlp_forward needs for up to K active neurons (host function). */
+int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out);
 
 /* x [B,H]; concat_w [2K,H] (gate rows then up rows; [K,H] when has_gate == 0) with row
  * stride H; down_packed [K,H]: row j = column j of the [H,K] active down weight (pass
  * the storage of a [H,K] tensor whose strides are (1,H)).
  * combined_buf [B,2K] (or [B,K]): on return columns 0..K-1 hold act(gate)*up and columns
  * K..2K-1 hold up, as the reference leaves them (sparse_mlp_op.cpp:151-158).
- * down_buf [B,H]: the result.  scratch: stx_mlp_scratch_bytes() bytes; it is used as
- * an fp32 accumulator and a counter and is left zeroed for the next call.               */
+ * down_buf [B,H]: the result.  scratch: stx_mlp_scratch_bytes() bytes, 16-byte aligned,
+ * ZERO on the first call; its leading (256 + 4*B*H rounded up to 256) bytes are an fp32
+ * accumulator and a counter that every call leaves zeroed again, the rest holds the
+ * fp32 activations a[K][B] between the two kernels.                                     */
 int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* concat_w,
                            const void* down_packed, int64_t K, void* down_buf,
                            void* combined_buf, int act, int has_gate, int dtype,
@@ -188,7 +190,7 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
  * callers that may not allocate device memory (a server that fixes its HBM budget at
  * start-up, a plugin whose host owns the allocator): the scratch lives in a fixed
  * ~256 KiB device array inside the library image, held by every GPU that loads it.
- * Limit: B*H <= 65536 elements, else STX_ERR_TOO_LARGE.  The first call on a device
+ * Limit: B*(H+K) <= 65536 elements, else STX_ERR_TOO_LARGE.  The first call on a device
  * resolves the array's address; make it outside stream capture.  All calls on a device
  * share the array (it is cleared at the start of each call), so calls whose GPU work
  * overlaps race: keep them ordered on one stream.  Allocates nothing.                   */
@@ -219,8 +221,10 @@ int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_
 #define STX_STAGE_PREDICT 1u /* predictor -> mask bits                    */
 #define STX_STAGE_PLAN 2u    /* mask diff -> cache index plan             */
 #define STX_STAGE_COPY 4u    /* rewrite the changed packed rows           */
-#define STX_STAGE_MLP 8u     /* sparse gate/up/down projection            */
-#define STX_STAGE_ALL 15u
+#define STX_STAGE_MLP_GATEUP 8u  /* sparse gate/up projection + activation  */
+#define STX_STAGE_MLP_DOWN 16u   /* sparse down projection                   */
+#define STX_STAGE_MLP 24u        /* both                                     */
+#define STX_STAGE_ALL 31u
 int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B,
                           void* out, void* stream, unsigned stages);
 /* Device pointer to the layer's current mask bits (ceil(I/32) words), valid after a step. */

@@ -16,7 +16,7 @@ F32, F16, BF16 = 0, 1, 2
 ACT_RELU, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID, ACT_GELU = range(5)
 MASK_THRESHOLD, MASK_TOPK, MASK_STATISTICAL = range(3)
 CACHE_ALIAS_GATE_UP = 1
-STAGE_PREDICT, STAGE_PLAN, STAGE_COPY, STAGE_MLP, STAGE_ALL = 1, 2, 4, 8, 15
+STAGE_PREDICT, STAGE_PLAN, STAGE_COPY, STAGE_MLP_GATEUP, STAGE_MLP_DOWN, STAGE_MLP, STAGE_ALL = 1, 2, 4, 8, 16, 24, 31
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -50,7 +50,7 @@ SIGNATURES = {
     "stx_mask_bytes_to_bits": (_i32, [_vp, _i64, _vp, _vp]),
     "stx_approx_topk_scratch_bytes": (_i32, [_i64, _i64, _psz]),
     "stx_approx_topk_threshold": (_i32, [_vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp]),
-    "stx_mlp_scratch_bytes": (_i32, [_i64, _i64, _psz]),
+    "stx_mlp_scratch_bytes": (_i32, [_i64, _i64, _i64, _psz]),
     "stx_sparse_mlp_forward": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "stx_sparse_mlp_forward_noalloc": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _vp]),
     "stx_layer_create": (_i32, [_pp, _vp, _vp, _i64, _vp, _i32, _f32, _i32, _i64]),

@@ -14,7 +14,7 @@ int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, 
                  cudaStream_t s);
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
-                int act, int has_gate, int dtype, void* scratch, cudaStream_t s);
+                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s);
 }  // namespace stx
 
 struct stx_layer {
@@ -85,7 +85,7 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   const int64_t I = cache->I, H = cache->H;
   size_t pred_bytes = 0, mlp_bytes = 0;
   stx_predict_scratch_bytes(max_batch, I, r, &pred_bytes);
-  stx_mlp_scratch_bytes(max_batch, H, &mlp_bytes);
+  stx_mlp_scratch_bytes(max_batch, H, I, &mlp_bytes);
   const size_t es = dtype_size(cache->dtype);
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&l->bits), ((I + 31) / 32) * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMalloc(&l->pred_scratch, pred_bytes);
@@ -125,8 +125,9 @@ int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp,
   }
   if (stages & STX_STAGE_MLP) {
     STX_CHECK_ARG(x_mlp && out, "stx_layer_step: x_mlp/out is null");
+    const unsigned parts = ((stages & STX_STAGE_MLP_GATEUP) ? 1u : 0u) | ((stages & STX_STAGE_MLP_DOWN) ? 2u : 0u);
     rc = mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
-                     c->has_gate, c->dtype, l->mlp_scratch, s);
+                     c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, s);
   }
   return rc;
 }

@@ -18,6 +18,8 @@
 #include "stx_common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 namespace stx {
 
@@ -229,10 +231,33 @@ static int dispatch_nb(MlpArgs& a, int grid, int threads, cudaStream_t s) {
   return launch_fused<T, 4>(a, grid, threads, s);
 }
 
+int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
+                    const int32_t* K_dev, int64_t K_host, void* out, void* combined, int act, int has_gate, int dtype,
+                    void* scratch, int* status, unsigned parts, cudaStream_t s);
+
+// STX_MLP_KERNEL=plain forces the plain-load kernel (for A/B measurements); default: the
+// TMA-staged kernel wherever the shape fits it.
+static bool use_tma_kernel() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("STX_MLP_KERNEL");
+    v = (e && !strcmp(e, "plain")) ? 0 : 1;
+  }
+  return v == 1;
+}
+
 // Shared by the op entry point and the fused layer step.
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
-                int act, int has_gate, int dtype, void* scratch, cudaStream_t s) {
+                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s) {
+  if (use_tma_kernel() && !up_after_gate) {
+    // the streaming kernels keep a[K][B] behind the (always zero) accumulator region
+    void* a_region = static_cast<char*>(scratch) + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
+    const int rc = mlp_forward_tma(x, B, H, gate, up, down, K_dev, K_host, out, combined, act, has_gate, dtype, a_region,
+                                   status, parts, s);
+    if (rc != STX_ERR_UNSUPPORTED) return rc;
+  }
+  if (!(parts & 1u)) return STX_OK;  // the fused kernel below cannot be split: it runs as the first part
   const size_t es = dtype_size(dtype);
   const int V = static_cast<int>(16 / es);
   const int nchunk = static_cast<int>(H / V);
@@ -271,9 +296,11 @@ using namespace stx;
 
 extern "C" {
 
-int stx_mlp_scratch_bytes(int64_t B, int64_t H, size_t* bytes_out) {
-  STX_CHECK_ARG(bytes_out && B > 0 && H > 0, "stx_mlp_scratch_bytes: bad argument");
-  *bytes_out = 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
+int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out) {
+  STX_CHECK_ARG(bytes_out && B > 0 && H > 0 && K >= 0, "stx_mlp_scratch_bytes: bad argument");
+  // [counter | fp32 accumulator B*H (kept zero) | 256 | fp32 a[K][B]]
+  *bytes_out = 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256) + 256 +
+               align_up(static_cast<size_t>(B) * std::max<int64_t>(K, 1) * sizeof(float), 256);
   return STX_OK;
 }
 
@@ -297,7 +324,7 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
   const void* gate = has_gate ? cw : nullptr;
   const void* up = has_gate ? cw + static_cast<size_t>(K) * H * es : cw;
   return mlp_forward(x, B, H, gate, up, down_packed, nullptr, K, std::max<int64_t>(K, 1), 0, down_buf, combined_buf, act,
-                     has_gate ? 1 : 0, dtype, scratch, static_cast<cudaStream_t>(stream));
+                     has_gate ? 1 : 0, dtype, scratch, nullptr, 3u, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
@@ -315,8 +342,8 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
 // until the process exits.
 //
 // Limits and rules:
-//   * B * H must not exceed STX_NOALLOC_MAX_BH (65536) elements; larger calls are refused
-//     with STX_ERR_TOO_LARGE.
+//   * B * (H + K) must not exceed STX_NOALLOC_MAX_ELEMS (65536) elements; larger calls are
+//     refused with STX_ERR_TOO_LARGE.
 //   * The first call on each device looks up the array's device address (once per device,
 //     with that device current).  Make that first call outside any stream capture.
 //   * All calls on a device share the one array.  It still holds whatever the previous call
@@ -324,8 +351,8 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
 //     GPU work overlaps (different streams, or different host threads) race on it and give
 //     wrong results.  Keep calls on one stream, or otherwise ordered.
 //   * No cudaMalloc, cudaFree or other allocating routine is called.
-constexpr int64_t STX_NOALLOC_MAX_BH = 65536;
-constexpr size_t NOALLOC_BYTES = 256 + static_cast<size_t>(STX_NOALLOC_MAX_BH) * sizeof(float);
+constexpr int64_t STX_NOALLOC_MAX_ELEMS = 65536;
+constexpr size_t NOALLOC_BYTES = 1024 + static_cast<size_t>(STX_NOALLOC_MAX_ELEMS) * sizeof(float);
 
 // In host code this name is only a handle for the runtime, never a device address: the
 // address a kernel can use comes from cudaGetSymbolAddress below.
@@ -360,19 +387,21 @@ static int noalloc_scratch_ptr(void** out) {
 extern "C" int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t H, const void* concat_w,
                                               const void* down_packed, int64_t K, void* down_buf, void* combined_buf,
                                               int act, int has_gate, int dtype, void* stream) {
-  STX_CHECK_ARG(B > 0 && H > 0, "stx_sparse_mlp_forward_noalloc: bad sizes B=%lld H=%lld", static_cast<long long>(B),
-                static_cast<long long>(H));
-  if (B * H > STX_NOALLOC_MAX_BH) {
-    set_error("stx_sparse_mlp_forward_noalloc: B*H = %lld exceeds the built-in scratch of %lld elements; "
+  STX_CHECK_ARG(B > 0 && H > 0 && K >= 0, "stx_sparse_mlp_forward_noalloc: bad sizes B=%lld H=%lld K=%lld",
+                static_cast<long long>(B), static_cast<long long>(H), static_cast<long long>(K));
+  size_t need = 0;
+  stx_mlp_scratch_bytes(B, H, K, &need);
+  if (need > NOALLOC_BYTES) {
+    set_error("stx_sparse_mlp_forward_noalloc: B*(H+K) = %lld exceeds the built-in scratch of %lld elements; "
               "use stx_sparse_mlp_forward with a caller-provided scratch buffer",
-              static_cast<long long>(B * H), static_cast<long long>(STX_NOALLOC_MAX_BH));
+              static_cast<long long>(B * (H + K)), static_cast<long long>(STX_NOALLOC_MAX_ELEMS));
     return STX_ERR_TOO_LARGE;
   }
   void* scratch = nullptr;
   int rc = noalloc_scratch_ptr(&scratch);
   if (rc != STX_OK) return rc;
   // the array keeps the previous call's contents: clear the counter and the accumulator
-  const size_t used = 256 + static_cast<size_t>(B) * H * sizeof(float);
+  const size_t used = 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
   STX_CUDA(cudaMemsetAsync(scratch, 0, used, static_cast<cudaStream_t>(stream)));
   return stx_sparse_mlp_forward(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, has_gate, dtype, scratch,
                                 stream);

@@ -7,23 +7,33 @@
 //   t[b,k]  = round_dtype( sum_h x[b,h] * A[k,h] )      fp32 fused multiply-adds
 //   s[b,i]  = round_dtype( sum_k t[b,k] * Bm[i,k] )     fp32 fused multiply-adds
 // with a fixed summation order.  With V = 16 / sizeof(elem) elements per chunk:
-//   t: 32 partial sums; partial l adds chunks l, l+32, l+64, ... in ascending element order
-//      starting from +0; the partials are combined by the butterfly
-//      p[l] += p[l ^ 16]; p[l] += p[l ^ 8]; ... ; p[l] += p[l ^ 1].
+//   t: NT = min(1024, ceil(H/V) rounded up to 32) partial sums; partial u adds chunks
+//      u, u+NT, u+2NT, ... in ascending element order starting from +0.  Each group of 32
+//      consecutive partials is combined by the butterfly p[l] += p[l^16]; ... ; p[l] += p[l^1];
+//      the NT/32 group sums, padded with +0 to 32 values, are combined by the same butterfly.
 //   s: 8 partial sums; partial g adds chunks g, g+8, ... likewise; butterfly over 4, 2, 1.
+// Every thread issues all of its loads up front, so each kernel costs about one memory
+// round trip.
 #include "stx_common.cuh"
 
 namespace stx {
 
 constexpr int PRED_BT = 8;  // batch rows accumulated per pass
 
+__host__ __device__ inline int pred_t_threads(int H, int V) {
+  const int nchunk = (H + V - 1) / V;
+  const int nt = (nchunk + 31) / 32 * 32;
+  return nt < 1024 ? nt : 1024;
+}
+
+// One block per predictor row k; thread u owns chunks u, u+NT, ...
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t_out, int B, int H, int r) {
   constexpr int V = DT<T>::V;
-  const int lane = threadIdx.x & 31;
-  const int k = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (k >= r) return;
+  __shared__ float s_ws[32][PRED_BT];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+  const int k = blockIdx.x;
   const int nchunk = H / V;
   const T* arow = A + static_cast<size_t>(k) * H;
   for (int b0 = 0; b0 < B; b0 += PRED_BT) {
@@ -31,7 +41,7 @@ k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t
 #pragma unroll
     for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
     const int nb = min(PRED_BT, B - b0);
-    for (int c = lane; c < nchunk; c += 32) {
+    for (int c = tid; c < nchunk; c += blockDim.x) {
       float wa[V];
       Unpack<T>::run(ld_stream16(arow + c * V), wa);
 #pragma unroll
@@ -47,51 +57,92 @@ k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t
 #pragma unroll
     for (int b = 0; b < PRED_BT; ++b) {
       const float s = warp_sum_xor(acc[b]);
-      if (lane == 0 && b < nb) t_out[static_cast<size_t>(b0 + b) * r + k] = DT<T>::round_f(s);
+      if (lane == 0) s_ws[wid][b] = s;
     }
+    __syncthreads();
+    if (wid == 0) {
+      for (int b = 0; b < nb; ++b) {
+        const float s = warp_sum_xor(lane < nw ? s_ws[lane][b] : 0.f);
+        if (lane == 0) t_out[static_cast<size_t>(b0 + b) * r + k] = DT<T>::round_f(s);
+      }
+    }
+    __syncthreads();
   }
 }
 
-// One warp per mask word (32 neurons); 8 lanes cooperate on one neuron, 4 neurons per pass.
-// Dynamic shared memory: t [B,r] fp32.
+// One block (256 threads) per mask word: 8 lanes cooperate on one neuron, 32 neurons per
+// block.  Dynamic shared memory: t [B,r] fp32.
 template <typename T>
-__global__ void __launch_bounds__(64)
+__global__ void __launch_bounds__(256)
 k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* __restrict__ bits,
               T* __restrict__ scores_out, int B, int r, int I, float tau, int write_bits) {
   constexpr int V = DT<T>::V;
   extern __shared__ float t_s[];
-  for (int i = threadIdx.x; i < B * r; i += blockDim.x) t_s[i] = t[i];
-  __syncthreads();
-
-  const int lane = threadIdx.x & 31;
-  const int w = blockIdx.x * 2 + (threadIdx.x >> 5);
-  const int W = (I + 31) >> 5;
-  if (w >= W) return;
-  const int g = lane & 7, q = lane >> 3;
-  const float tau_r = DT<T>::round_f(tau);
+  __shared__ uint32_t s_nib[8];
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int g = lane & 7;
+  const int w = blockIdx.x;
+  const int i = w * 32 + (tid >> 3);
+  const bool i_ok = i < I;
   const bool vec_ok = (r % V) == 0 && ((reinterpret_cast<uintptr_t>(Bm) & 15) == 0);
   const int nchunk = (r + V - 1) / V;
-  uint32_t word = 0u;
+  const T* brow = Bm + static_cast<size_t>(i_ok ? i : 0) * r;
 
-  for (int pass = 0; pass < 8; ++pass) {
-    const int n = pass * 4 + q;
-    const int i = w * 32 + n;
-    const bool i_ok = i < I;
-    const T* brow = Bm + static_cast<size_t>(i_ok ? i : 0) * r;
-    bool on = false;
-    for (int b0 = 0; b0 < B; b0 += PRED_BT) {
-      float acc[PRED_BT];
+  // weights first (independent of t), then the t tile
+  constexpr int MAXC = 4;  // chunks held in registers per lane: r <= 8 * MAXC * V on the fast path
+  float wv[MAXC][V];
+  const bool in_regs = nchunk <= 8 * MAXC;
+  if (in_regs) {
 #pragma unroll
-      for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
-      const int nb = min(PRED_BT, B - b0);
-      if (i_ok) {
+    for (int q = 0; q < MAXC; ++q) {
+      const int c = g + 8 * q;
+#pragma unroll
+      for (int v = 0; v < V; ++v) wv[q][v] = 0.f;
+      if (i_ok && c < nchunk) {
+        if (vec_ok) {
+          Unpack<T>::run(ld_stream16(brow + c * V), wv[q]);
+        } else {
+#pragma unroll
+          for (int v = 0; v < V; ++v) wv[q][v] = (c * V + v < r) ? DT<T>::to_f(brow[c * V + v]) : 0.f;
+        }
+      }
+    }
+  }
+  for (int k = tid; k < B * r; k += blockDim.x) t_s[k] = t[k];
+  __syncthreads();
+
+  const float tau_r = DT<T>::round_f(tau);
+  bool on = false;
+  for (int b0 = 0; b0 < B; b0 += PRED_BT) {
+    float acc[PRED_BT];
+#pragma unroll
+    for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
+    const int nb = min(PRED_BT, B - b0);
+    if (i_ok) {
+      if (in_regs) {
+#pragma unroll
+        for (int q = 0; q < MAXC; ++q) {
+          const int c = g + 8 * q;
+          if (c < nchunk) {
+#pragma unroll
+            for (int b = 0; b < PRED_BT; ++b) {
+              if (b < nb) {
+                const float* tb = t_s + (b0 + b) * r + c * V;
+#pragma unroll
+                for (int v = 0; v < V; ++v)
+                  if (vec_ok || c * V + v < r) acc[b] = fmaf(tb[v], wv[q][v], acc[b]);
+              }
+            }
+          }
+        }
+      } else {
         for (int c = g; c < nchunk; c += 8) {
-          float wv[V];
+          float wc[V];
           if (vec_ok) {
-            Unpack<T>::run(ld_stream16(brow + c * V), wv);
+            Unpack<T>::run(ld_stream16(brow + c * V), wc);
           } else {
 #pragma unroll
-            for (int v = 0; v < V; ++v) wv[v] = (c * V + v < r) ? DT<T>::to_f(brow[c * V + v]) : 0.f;
+            for (int v = 0; v < V; ++v) wc[v] = (c * V + v < r) ? DT<T>::to_f(brow[c * V + v]) : 0.f;
           }
 #pragma unroll
           for (int b = 0; b < PRED_BT; ++b) {
@@ -99,41 +150,47 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
               const float* tb = t_s + (b0 + b) * r + c * V;
 #pragma unroll
               for (int v = 0; v < V; ++v)
-                if (vec_ok || c * V + v < r) acc[b] = fmaf(tb[v], wv[v], acc[b]);
+                if (vec_ok || c * V + v < r) acc[b] = fmaf(tb[v], wc[v], acc[b]);
             }
           }
         }
       }
+    }
 #pragma unroll
-      for (int b = 0; b < PRED_BT; ++b) {
-        float s = acc[b];
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        if (b < nb) {
-          const float sr = DT<T>::round_f(s);
-          if (scores_out && g == 0 && i_ok) scores_out[static_cast<size_t>(b0 + b) * I + i] = DT<T>::from_f(s);
-          on = on || (sr >= tau_r);
-        }
+    for (int b = 0; b < PRED_BT; ++b) {
+      float s = acc[b];
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      if (b < nb) {
+        const float sr = DT<T>::round_f(s);
+        if (scores_out && g == 0 && i_ok) scores_out[static_cast<size_t>(b0 + b) * I + i] = DT<T>::from_f(s);
+        on = on || (sr >= tau_r);
       }
     }
-    const uint32_t bal = __ballot_sync(0xffffffffu, on && i_ok && g == 0);
-    word |= ((bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u)) << (pass * 4);
   }
-  if (write_bits && lane == 0) bits[w] = word;
+  const uint32_t bal = __ballot_sync(0xffffffffu, on && i_ok && g == 0);
+  if (lane == 0) s_nib[wid] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
+  __syncthreads();
+  if (write_bits && tid == 0) {
+    uint32_t word = 0u;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) word |= s_nib[q] << (4 * q);
+    bits[w] = word;
+  }
 }
 
 template <typename T>
 static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
                           int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
                           int write_bits, cudaStream_t s) {
-  k_pred_t<T><<<static_cast<unsigned>((r + 3) / 4), 128, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(A),
-                                                               t_scratch, static_cast<int>(B), static_cast<int>(H),
-                                                               static_cast<int>(r));
+  k_pred_t<T><<<static_cast<unsigned>(r), pred_t_threads(static_cast<int>(H), DT<T>::V), 0, s>>>(
+      static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B), static_cast<int>(H),
+      static_cast<int>(r));
   STX_LAUNCH_CHECK("k_pred_t");
   const int64_t W = (I + 31) / 32;
   const size_t smem = static_cast<size_t>(B) * r * sizeof(float);
-  k_pred_scores<T><<<static_cast<unsigned>((W + 1) / 2), 64, smem, s>>>(
+  k_pred_scores<T><<<static_cast<unsigned>(W), 256, smem, s>>>(
       t_scratch, static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
       static_cast<int>(r), static_cast<int>(I), tau, write_bits);
   STX_LAUNCH_CHECK("k_pred_scores");

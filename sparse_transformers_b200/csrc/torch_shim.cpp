@@ -204,7 +204,7 @@ torch::Tensor sparse_mlp_forward(const torch::Tensor& input, const torch::Tensor
 
   void* stream = cur_stream(input.device());
   size_t sbytes = 0;
-  check(stx_mlp_scratch_bytes(B, H, &sbytes), "forward");
+  check(stx_mlp_scratch_bytes(B, H, K, &sbytes), "forward");
   void* scratch = mlp_scratch(input.device(), stream, sbytes);
   check(stx_sparse_mlp_forward(x.data_ptr(), B, H, wcat.data_ptr(), wdown.data_ptr(), K, down_proj_buffer.data_ptr(),
                                combined_proj_buffer.data_ptr(), act, has_gate ? 1 : 0, to_stx_dtype(dtype), scratch, stream),

@@ -105,12 +105,13 @@ def mlp_forward(x, concat, down_packed, act, has_gate=True):
     out = torch.full((B, H), float("nan"), dtype=x.dtype, device=DEV)
     comb = torch.full((B, concat.shape[0]), float("nan"), dtype=x.dtype, device=DEV)
     n = ctypes.c_size_t()
-    C.check(C.lib.stx_mlp_scratch_bytes(B, H, ctypes.byref(n)))
+    C.check(C.lib.stx_mlp_scratch_bytes(B, H, K, ctypes.byref(n)))
     scratch = torch.zeros(n.value, dtype=torch.uint8, device=DEV)
     C.check(C.lib.stx_sparse_mlp_forward(x.data_ptr(), B, H, concat.data_ptr(), down_packed.data_ptr(), K, out.data_ptr(),
                                          comb.data_ptr(), ACT[act], int(has_gate), DT[x.dtype], scratch.data_ptr(), stream()))
     torch.cuda.synchronize()
-    assert int(scratch.view(torch.int32).abs().sum()) == 0, "scratch must be left zeroed"
+    lead = 256 + (B * H * 4 + 255) // 256 * 256
+    assert int(scratch[:lead].view(torch.int32).abs().sum()) == 0, "counter and accumulator must be left zeroed"
     return out, comb
 
 

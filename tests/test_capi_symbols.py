@@ -41,7 +41,7 @@ def test_argument_checks_need_no_gpu():
     n = ctypes.c_size_t()
     assert C.lib.stx_cache_bytes(8192, 3072, C.F16, 1, 0, ctypes.byref(n)) == C.OK
     assert n.value >= 6 * 8192 * 3072 * 2
-    assert C.lib.stx_mlp_scratch_bytes(1, 3072, ctypes.byref(n)) == C.OK and n.value >= 3072 * 4
+    assert C.lib.stx_mlp_scratch_bytes(1, 3072, 8192, ctypes.byref(n)) == C.OK and n.value >= 3072 * 4
     assert C.lib.stx_cache_update(None, None, None) == C.ERR_INVALID_ARG
     assert b"null" in C.lib.stx_last_error()
     h = ctypes.c_void_p()

@@ -74,7 +74,7 @@ def test_zero_active_gives_zero_output():
     from sparse_transformers_b200 import _capi as C
     from stxgpu import stream
     out = torch.full((2, 64), 7.0, device=DEV)
-    n = ctypes.c_size_t(); C.lib.stx_mlp_scratch_bytes(2, 64, ctypes.byref(n))
+    n = ctypes.c_size_t(); C.lib.stx_mlp_scratch_bytes(2, 64, 0, ctypes.byref(n))
     scratch = torch.zeros(n.value, dtype=torch.uint8, device=DEV)
     C.check(C.lib.stx_sparse_mlp_forward(x.data_ptr(), 2, 64, cw_buf.data_ptr(), dp_buf.data_ptr(), 0, out.data_ptr(), None,
                                          C.ACT_SILU, 1, C.F32, scratch.data_ptr(), stream()))
