@@ -1,31 +1,35 @@
 // Sparse gated MLP over packed active rows, decode batches — two streaming kernels.
 //
 //   a[j,b]   = act(x[b]·gate[j]) * (x[b]·up[j])            k_gateup_tma   (K neurons)
-//   out[b,:] = sum_j a[j,b] * down[j,:]                    k_down_slab
+//   out[b,:] = sum_j a[j,b] * down[j,:]                    k_down_rows
 //
-// k_gateup_tma: one persistent CTA per SM owns a contiguous range of neurons and walks it in
-// tiles of R neurons.  A producer warp streams each tile's gate and up rows (two contiguous
-// ranges of the packed pools) into a ring of shared-memory stages with 1-D bulk async copies
-// (cp.async.bulk global -> shared, completion counted on an mbarrier), so (S-1) stages of
-// loads are in flight per SM without occupying registers.  Consumer warp (r, part) computes
-// the dot products of x with its part of gate row r and up row r from shared memory, reduces
-// them with a shuffle butterfly and stores two partial sums; the last warp to finish a
-// neuron adds the parts in a fixed order, applies the activation and writes a[j,:].  There
-// is no CTA-wide barrier in the loop: warps are only coupled through the stage ring.
+// k_gateup_tma: one persistent CTA per SM owns a contiguous range of neurons.  Every warp is
+// its own producer and consumer: lane 0 issues two 1-D bulk async copies (cp.async.bulk
+// global -> shared, completion counted on the warp's mbarrier) that bring the gate row and the
+// up row of the warp's next neuron into the warp's private shared-memory buffer; the warp then
+// computes both dot products with x (shared memory) from that buffer, reduces them with a
+// shuffle butterfly and writes a[j,:].  Warps never synchronise with each other inside the
+// loop, so with K/148 neurons per SM and up to 16 warps, all rows of a 20 %-dense layer are in
+// flight at once and the kernel costs about one memory round trip plus the stream time.
 //
-// k_down_slab: CTA c owns two 16-byte column chunks (one 32-byte sector per row) of the
-// output and walks all K packed down rows for them, so no partial sums ever cross CTAs: the
-// result is written once, in the output dtype, in a fixed summation order (deterministic),
-// with no atomics and no scratch to re-zero.
+// k_down_rows: the packed down rows are split over a (column slab, row range) grid; the CTAs
+// of one column slab form a thread-block cluster and add their partial sums through
+// distributed shared memory in rank order, so the result is written once, in the output
+// dtype, deterministically, with no global atomics and no scratch to re-zero.  A slab is 256
+// bytes wide (sixteen 16-byte chunks), which keeps DRAM bursts long.
 //
 // Every wait on an mbarrier is bounded: when the limit is hit the kernel records
 // DEV_TIMEOUT in the status word and carries on with the same control flow (the result is
 // then garbage, but no thread is left waiting and the context stays usable).
 #include "stx_common.cuh"
 
+#include <cooperative_groups.h>
+
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+
+namespace cg = cooperative_groups;
 
 namespace stx {
 
@@ -39,9 +43,7 @@ struct GateUpArgs {
   const int32_t* K_dev;
   int K_host;
   int B, H, act, has_gate;
-  int R, S;              // neurons per tile, stages
-  int nconsumer;         // consumer threads (multiple of 32)
-  uint32_t stage_bytes;  // R * nmat * row_bytes
+  int nwarps;
 };
 
 struct DownArgs {
@@ -64,9 +66,6 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -82,7 +81,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
   for (uint32_t it = 0; it < MBAR_WAIT_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 128) __nanosleep(64);
+    if (it > 256) __nanosleep(32);
   }
   return false;
 }
@@ -93,236 +92,159 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void consumer_sync(int nthreads) {
-  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-}
 
-constexpr int GU_MAXR = 4;    // neurons per tile
-constexpr int GU_MAXS = 8;    // ring stages
-constexpr int GU_MAXP = 16;   // parts per neuron
-
-// Shared-memory layout (dynamic):
-//   [0, 256)   full[S], empty[S] mbarriers
-//   cnt    [S][R] int                       arrival counters per (stage, neuron)
-//   part_s [S][R][nparts][2][NB] float      partial dot products
-//   x_s    [NB][H] T
-//   stages [S][stage_bytes]                 (each: gate rows | up rows)
+// Shared-memory layout (dynamic): [0,256) mbarriers | x_s [NB][H] T | bufs [nwarps][nmat][H] T
 template <typename T, int NB>
-__global__ void __launch_bounds__(544, 1) k_gateup_tma(const GateUpArgs p) {
+__global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
   constexpr int V = DT<T>::V;
   extern __shared__ __align__(128) unsigned char smem[];
-
-  const int tid = threadIdx.x;
-  const int NT = p.nconsumer;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int NWp = p.nwarps;
   const int H = p.H, nchunk = H / V;
-  const int R = p.R, S = p.S;
-  const int NW = NT >> 5, nparts = NW / R;
   const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
   const int nmat = p.has_gate ? 2 : 1;
 
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = full + 16;
-  int* cnt = reinterpret_cast<int*>(smem + 256);                                   // [S][R]
-  float* part_base = reinterpret_cast<float*>(smem + 256 + 128);                   // [S][R][nparts][2][NB]
-  const size_t part_bytes = (sizeof(float) * S * R * nparts * 2 * NB + 127) / 128 * 128;
-  T* x_s = reinterpret_cast<T*>(smem + 256 + 128 + part_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  T* x_s = reinterpret_cast<T*>(smem + 256);
   const size_t x_bytes = (sizeof(T) * NB * H + 127) / 128 * 128;
-  unsigned char* stages = smem + 256 + 128 + part_bytes + x_bytes;
+  unsigned char* mybuf = smem + 256 + x_bytes + static_cast<size_t>(warp) * nmat * row_bytes;
+  uint64_t* mybar = &bars[warp];
 
   const int K = p.K_dev ? *p.K_dev : p.K_host;
   const int base = K / gridDim.x, rem = K % gridDim.x;
   const int j0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
   const int j1 = j0 + base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
-  const int ntile = (j1 - j0 + R - 1) / R;
-  const int nbt = (p.B + NB - 1) / NB;
-  const int total = ntile * nbt;  // flat sequence of (batch tile, neuron tile)
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], NW);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (tid < S * R) cnt[tid] = 0;
-  __syncthreads();
-
-  bool timed_out = false;
-
-  if (tid >= NT) {
-    // ------------------------------------------------------------------ producer warp
-    if (tid == NT) {
-      const char* gsrc = static_cast<const char*>(p.gate);
-      const char* usrc = static_cast<const char*>(p.up);
-      for (int g = 0; g < total; ++g) {
-        const int s = g % S;
-        if (g >= S) {
-          if (!mbar_wait_bounded(&empty[s], ((g / S) - 1) & 1)) timed_out = true;
-        }
-        const int it = g % ntile;
-        const int r0 = j0 + it * R;
-        const int nrows = min(R, j1 - r0);
-        const uint32_t bytes = static_cast<uint32_t>(nrows) * row_bytes;
-        unsigned char* st = stages + static_cast<size_t>(s) * p.stage_bytes;
-        mbar_expect_tx(&full[s], bytes * nmat);
-        const size_t off = static_cast<size_t>(r0) * row_bytes;
-        if (p.has_gate) bulk_load(st, gsrc + off, bytes, &full[s]);
-        bulk_load(st + (p.has_gate ? 1 : 0) * static_cast<size_t>(R) * row_bytes, usrc + off, bytes, &full[s]);
-      }
-      if (timed_out && p.status) atomicOr(p.status, DEV_TIMEOUT);
-    }
-    return;
-  }
-
-  // -------------------------------------------------------------------- consumers
-  const int lane = tid & 31, warp = tid >> 5;
-  const int my_r = warp % R, my_part = warp / R;
-  const bool a_active = my_part < nparts;          // warps beyond R*nparts only release stages
-  const int cpp = (nchunk + nparts - 1) / nparts;  // chunks per part
-  const int c_lo = my_part * cpp, c_hi = min(nchunk, c_lo + cpp);
+  const char* gsrc = static_cast<const char*>(p.gate);
+  const char* usrc = static_cast<const char*>(p.up);
   T* combined = static_cast<T*>(p.combined);
   const int ldc = p.has_gate ? 2 * K : K;
 
-  int g = 0;
+  if (tid == 0) {
+    for (int w = 0; w < NWp; ++w) mbar_init(&bars[w], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int j) {
+    mbar_expect_tx(mybar, row_bytes * nmat);
+    const size_t off = static_cast<size_t>(j) * row_bytes;
+    if (p.has_gate) bulk_load(mybuf, gsrc + off, row_bytes, mybar);
+    bulk_load(mybuf + (p.has_gate ? row_bytes : 0), usrc + off, row_bytes, mybar);
+  };
+
+  bool timed_out = false;
+  uint32_t phase = 0;
+  const int nbt = (p.B + NB - 1) / NB;
   for (int bt = 0; bt < nbt; ++bt) {
     const int b0 = bt * NB;
     const int nb = min(NB, p.B - b0);
-    if (ntile > 0) {
-      if (bt > 0) consumer_sync(NT);  // everyone done with the previous x tile
+    int j = j0 + warp;
+    if (lane == 0 && j < j1) issue(j);  // the first rows stream in while x is staged
+    if (bt > 0) __syncthreads();        // everyone done with the previous x tile
+    {
       const uint4* xg = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + static_cast<size_t>(b0) * H);
       uint4* xs4 = reinterpret_cast<uint4*>(x_s);
-      for (int i = tid; i < NB * nchunk; i += NT) xs4[i] = i < nb * nchunk ? xg[i] : make_uint4(0, 0, 0, 0);
-      consumer_sync(NT);
+      for (int i = tid; i < NB * nchunk; i += blockDim.x) xs4[i] = i < nb * nchunk ? xg[i] : make_uint4(0, 0, 0, 0);
     }
+    __syncthreads();
 
-    for (int it = 0; it < ntile; ++it, ++g) {
-      const int s = g % S;
-      const int r0 = j0 + it * R;
-      const int nrows = min(R, j1 - r0);
-      const unsigned char* st = stages + static_cast<size_t>(s) * p.stage_bytes;
-      const T* g_s = reinterpret_cast<const T*>(st);
-      const T* u_s = reinterpret_cast<const T*>(st + (p.has_gate ? 1 : 0) * static_cast<size_t>(R) * row_bytes);
-      if (!mbar_wait_bounded(&full[s], (g / S) & 1)) timed_out = true;
-
-      if (a_active && my_r < nrows) {
-        float ag[NB], au[NB];
+    for (; j < j1; j += NWp) {
+      if (!mbar_wait_bounded(mybar, phase)) timed_out = true;
+      phase ^= 1u;
+      const T* grow = reinterpret_cast<const T*>(mybuf);
+      const T* urow = reinterpret_cast<const T*>(mybuf + (p.has_gate ? row_bytes : 0));
+      float ag[NB], au[NB];
 #pragma unroll
-        for (int b = 0; b < NB; ++b) ag[b] = au[b] = 0.f;
-        const T* grow = g_s + static_cast<size_t>(my_r) * H;
-        const T* urow = u_s + static_cast<size_t>(my_r) * H;
-        int c = c_lo + lane;
-        // two chunks per iteration: independent accumulation chains, loads issued together
-        for (; c + 32 < c_hi; c += 64) {
-          const uint4 u0 = *reinterpret_cast<const uint4*>(urow + c * V);
-          const uint4 u1 = *reinterpret_cast<const uint4*>(urow + (c + 32) * V);
-          uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
-          if (p.has_gate) {
-            g0 = *reinterpret_cast<const uint4*>(grow + c * V);
-            g1 = *reinterpret_cast<const uint4*>(grow + (c + 32) * V);
-          }
-          float wu0[V], wu1[V], wg0[V], wg1[V];
-          Unpack<T>::run(u0, wu0);
-          Unpack<T>::run(u1, wu1);
-          Unpack<T>::run(g0, wg0);
-          Unpack<T>::run(g1, wg1);
-#pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            float x0[V], x1[V];
-            Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + b * H + c * V), x0);
-            Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + b * H + (c + 32) * V), x1);
-            float su0 = 0.f, su1 = 0.f, sg0 = 0.f, sg1 = 0.f;
-#pragma unroll
-            for (int v = 0; v < V; ++v) {
-              su0 = fmaf(x0[v], wu0[v], su0);
-              su1 = fmaf(x1[v], wu1[v], su1);
-              if (p.has_gate) {
-                sg0 = fmaf(x0[v], wg0[v], sg0);
-                sg1 = fmaf(x1[v], wg1[v], sg1);
-              }
-            }
-            au[b] += su0 + su1;
-            ag[b] += sg0 + sg1;
-          }
+      for (int b = 0; b < NB; ++b) ag[b] = au[b] = 0.f;
+      int c = lane;
+      for (; c + 32 < nchunk; c += 64) {  // two chunks per iteration: independent chains
+        const uint4 u0 = *reinterpret_cast<const uint4*>(urow + c * V);
+        const uint4 u1 = *reinterpret_cast<const uint4*>(urow + (c + 32) * V);
+        uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
+        if (p.has_gate) {
+          g0 = *reinterpret_cast<const uint4*>(grow + c * V);
+          g1 = *reinterpret_cast<const uint4*>(grow + (c + 32) * V);
         }
-        for (; c < c_hi; c += 32) {
-          float wu[V], wg[V];
-          Unpack<T>::run(*reinterpret_cast<const uint4*>(urow + c * V), wu);
-          if (p.has_gate) Unpack<T>::run(*reinterpret_cast<const uint4*>(grow + c * V), wg);
-#pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            float xv[V];
-            Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + b * H + c * V), xv);
-            float su = 0.f, sg = 0.f;
-#pragma unroll
-            for (int v = 0; v < V; ++v) {
-              su = fmaf(xv[v], wu[v], su);
-              if (p.has_gate) sg = fmaf(xv[v], wg[v], sg);
-            }
-            au[b] += su;
-            ag[b] += sg;
-          }
-        }
-        float* ps = part_base + (((s * R + my_r) * nparts + my_part) * 2) * NB;
+        float wu0[V], wu1[V], wg0[V], wg1[V];
+        Unpack<T>::run(u0, wu0);
+        Unpack<T>::run(u1, wu1);
+        Unpack<T>::run(g0, wg0);
+        Unpack<T>::run(g1, wg1);
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-          const float u = warp_sum_xor(au[b]);
-          const float gg = p.has_gate ? warp_sum_xor(ag[b]) : 0.f;
-          if (lane == 0) {
-            ps[b] = gg;
-            ps[NB + b] = u;
-          }
-        }
-        // last warp to finish neuron r adds the parts (fixed order) and publishes a[j,:]
-        int last = 0;
-        if (lane == 0) {
-          __threadfence_block();
-          last = (atomicAdd(&cnt[s * R + my_r], 1) == nparts - 1);
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence_block();
-          if (lane < NB) {
-            const int b = lane;
-            float gsum = 0.f, usum = 0.f;
-            const volatile float* pr = part_base + ((s * R + my_r) * nparts * 2) * NB;
-            for (int q = 0; q < nparts; ++q) {
-              gsum += pr[(q * 2) * NB + b];
-              usum += pr[(q * 2 + 1) * NB + b];
-            }
-            const float a = p.has_gate ? apply_act(p.act, gsum) * usum : apply_act(p.act, usum);
-            const int j = r0 + my_r;
-            if (b < nb) {
-              p.a_out[static_cast<size_t>(j) * p.B + b0 + b] = a;
-              if (combined) {
-                combined[static_cast<size_t>(b0 + b) * ldc + j] = DT<T>::from_f(a);
-                if (p.has_gate) combined[static_cast<size_t>(b0 + b) * ldc + K + j] = DT<T>::from_f(usum);
-              }
+          float x0[V], x1[V];
+          Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + b * H + c * V), x0);
+          Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + b * H + (c + 32) * V), x1);
+          float su0 = 0.f, su1 = 0.f, sg0 = 0.f, sg1 = 0.f;
+#pragma unroll
+          for (int v = 0; v < V; ++v) {
+            su0 = fmaf(x0[v], wu0[v], su0);
+            su1 = fmaf(x1[v], wu1[v], su1);
+            if (p.has_gate) {
+              sg0 = fmaf(x0[v], wg0[v], sg0);
+              sg1 = fmaf(x1[v], wg1[v], sg1);
             }
           }
-          if (lane == 0) cnt[s * R + my_r] = 0;
+          au[b] += su0 + su1;
+          ag[b] += sg0 + sg1;
         }
       }
+      for (; c < nchunk; c += 32) {
+        float wu[V], wg[V];
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(urow + c * V), wu);
+        if (p.has_gate) Unpack<T>::run(*reinterpret_cast<const uint4*>(grow + c * V), wg);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          float xv[V];
+          Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + b * H + c * V), xv);
+          float su = 0.f, sg = 0.f;
+#pragma unroll
+          for (int v = 0; v < V; ++v) {
+            su = fmaf(xv[v], wu[v], su);
+            if (p.has_gate) sg = fmaf(xv[v], wg[v], sg);
+          }
+          au[b] += su;
+          ag[b] += sg;
+        }
+      }
+      // the buffer is free again: fetch the next neuron's rows before the reduction
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
+      if (lane == 0 && j + NWp < j1) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue(j + NWp);
+      }
+      float a_mine = 0.f, u_mine = 0.f;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const float u = warp_sum_xor(au[b]);
+        const float gsum = p.has_gate ? warp_sum_xor(ag[b]) : 0.f;
+        if (lane == b) {
+          u_mine = u;
+          a_mine = p.has_gate ? apply_act(p.act, gsum) * u : apply_act(p.act, u);
+        }
+      }
+      if (lane < nb) {
+        p.a_out[static_cast<size_t>(j) * p.B + b0 + lane] = a_mine;
+        if (combined) {
+          combined[static_cast<size_t>(b0 + lane) * ldc + j] = DT<T>::from_f(a_mine);
+          if (p.has_gate) combined[static_cast<size_t>(b0 + lane) * ldc + K + j] = DT<T>::from_f(u_mine);
+        }
+      }
     }
   }
   if (timed_out && p.status && lane == 0) atomicOr(p.status, DEV_TIMEOUT);
 }
 
-
 // ------------------------------------------------------------------------------------------
 // 16-bit weights: the dot products run on the tensor pipe (mma.sync m16n8k16, fp32
-// accumulate), which multiplies fp16/bf16 operands exactly and needs no conversion
-// instructions; on the FMA pipe the per-element conversions make the kernel issue-bound.
-// The 8 batch columns of the MMA hold up to 8 rows of x, so batches up to 8 cost the same
-// as batch 1.  Tile = 8 shared-memory rows: 4 gate + 4 up rows of 4 neurons (or 8 up rows
-// without a gate); MMA rows 8..15 are fed zeros.  Warp w owns the k-windows w, w+16, ...
-// (a window = 32 consecutive k); its x fragments stay in registers for the whole kernel.
-// The summation over k is order-free, so each thread takes its A and B fragments from the
-// same 16-byte chunk (k-slots are permuted identically on both sides) and rows are padded by
-// 64 bytes in shared memory, which makes the 16-byte fragment loads conflict-free.
-constexpr int MMA_MAXW = 16;  // windows per warp: H <= 16 warps * 16 * 32 = 8192
-
+// accumulate).  It multiplies fp16/bf16 operands exactly and needs no conversion
+// instructions (on the FMA pipe the per-element conversions make the kernel issue-bound),
+// and its 8 batch columns hold up to 8 rows of x, so batches up to 8 cost the same as
+// batch 1.  A warp's private buffer holds one tile of 4 rows: gate and up rows of 2 neurons
+// (or the up rows of 4 neurons without a gate); MMA rows 4..15 are fed zeros.  The summation
+// over k is order-free, so each thread takes its A and B fragments from the same 16-byte
+// chunk (the k-slots are permuted identically on both sides); rows are padded by 64 bytes in
+// shared memory, which makes the 16-byte fragment loads conflict-free.
 template <typename T> struct MmaOp;
 template <> struct MmaOp<__half> {
   static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
@@ -339,201 +261,185 @@ template <> struct MmaOp<__nv_bfloat16> {
   }
 };
 
-// Shared-memory layout (dynamic):
-//   [0, 256)   full[S], empty[S] mbarriers; cnt[S] at +192
-//   part_s [S][8 rows][16 parts][8 cols] float
-//   stages [S][8][row_bytes + 64]
+constexpr int MMA_TILE_ROWS = 4;
+
+// Shared-memory layout (dynamic): [0,256) mbarriers | x_s [min(B,8)][H*2 + 64] | bufs [nwarps][4][H*2 + 64]
 template <typename T>
-__global__ void __launch_bounds__(544, 1) k_gateup_mma(const GateUpArgs p) {
+__global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int NW = 16, NT = NW * 32;
-  const int tid = threadIdx.x;
-  const int H = p.H, S = p.S;
-  const int R = p.has_gate ? 4 : 8;  // neurons per tile
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, tq = lane & 3;  // fragment row (and batch column of B) / k-slot group
+  const int NWp = p.nwarps;
+  const int H = p.H;
+  const int nwin = H / 32;                  // a window = 32 consecutive k = 4 chunks of 16 bytes
   const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
   const uint32_t row_stride = row_bytes + 64;
-  const int nwin = H / 32;
+  const int TR = p.has_gate ? 2 : 4;        // neurons per tile
 
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = full + 8;
-  int* cnt = reinterpret_cast<int*>(smem + 192);
-  float* part_base = reinterpret_cast<float*>(smem + 256);
-  unsigned char* stages = smem + 256 + static_cast<size_t>(S) * 8 * 16 * 8 * sizeof(float);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  unsigned char* x_s = smem + 256;
+  const int xrows = min(p.B, 8);
+  unsigned char* mybuf = smem + 256 + xrows * static_cast<size_t>(row_stride) +
+                         static_cast<size_t>(warp) * MMA_TILE_ROWS * row_stride;
+  uint64_t* mybar = &bars[warp];
 
   const int K = p.K_dev ? *p.K_dev : p.K_host;
-  const int base = K / gridDim.x, rem = K % gridDim.x;
-  const int j0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
-  const int j1 = j0 + base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
-  const int ntile = (j1 - j0 + R - 1) / R;
-  const int nbt = (p.B + 7) / 8;
-  const int total = ntile * nbt;
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], NW);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (tid < S) cnt[tid] = 0;
-  __syncthreads();
-
-  bool timed_out = false;
-
-  if (tid >= NT) {
-    if (tid == NT) {
-      const char* gsrc = static_cast<const char*>(p.gate);
-      const char* usrc = static_cast<const char*>(p.up);
-      for (int g = 0; g < total; ++g) {
-        const int s = g % S;
-        if (g >= S) {
-          if (!mbar_wait_bounded(&empty[s], ((g / S) - 1) & 1)) timed_out = true;
-        }
-        const int it = g % ntile;
-        const int r0 = j0 + it * R;
-        const int nrows = min(R, j1 - r0);
-        unsigned char* st = stages + static_cast<size_t>(s) * 8 * row_stride;
-        mbar_expect_tx(&full[s], static_cast<uint32_t>(nrows) * row_bytes * (p.has_gate ? 2 : 1));
-        for (int i = 0; i < nrows; ++i) {
-          const size_t off = static_cast<size_t>(r0 + i) * row_bytes;
-          if (p.has_gate) {
-            bulk_load(st + static_cast<size_t>(i) * row_stride, gsrc + off, row_bytes, &full[s]);
-            bulk_load(st + static_cast<size_t>(4 + i) * row_stride, usrc + off, row_bytes, &full[s]);
-          } else {
-            bulk_load(st + static_cast<size_t>(i) * row_stride, usrc + off, row_bytes, &full[s]);
-          }
-        }
-      }
-      if (timed_out && p.status) atomicOr(p.status, DEV_TIMEOUT);
-    }
-    return;
-  }
-
-  // -------------------------------------------------------------------- consumers
-  const int lane = tid & 31, warp = tid >> 5;
-  const int gq = lane >> 2, tq = lane & 3;  // fragment row / k-slot group
+  const int ntile_all = (K + TR - 1) / TR;  // tiles are interleaved over the CTAs
+  const char* gsrc = static_cast<const char*>(p.gate);
+  const char* usrc = static_cast<const char*>(p.up);
   T* combined = static_cast<T*>(p.combined);
   const int ldc = p.has_gate ? 2 * K : K;
 
-  int g = 0;
+  if (tid == 0) {
+    for (int w = 0; w < NWp; ++w) mbar_init(&bars[w], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int tile) {
+    const int r0 = tile * TR;
+    const int nr = min(TR, K - r0);
+    mbar_expect_tx(mybar, static_cast<uint32_t>(nr) * row_bytes * (p.has_gate ? 2 : 1));
+    for (int i = 0; i < nr; ++i) {
+      const size_t off = static_cast<size_t>(r0 + i) * row_bytes;
+      if (p.has_gate) {
+        bulk_load(mybuf + static_cast<size_t>(i) * row_stride, gsrc + off, row_bytes, mybar);
+        bulk_load(mybuf + static_cast<size_t>(TR + i) * row_stride, usrc + off, row_bytes, mybar);
+      } else {
+        bulk_load(mybuf + static_cast<size_t>(i) * row_stride, usrc + off, row_bytes, mybar);
+      }
+    }
+  };
+
+  bool timed_out = false;
+  uint32_t phase = 0;
+  const int nbt = (p.B + 7) / 8;
   for (int bt = 0; bt < nbt; ++bt) {
     const int b0 = bt * 8;
     const int nb = min(8, p.B - b0);
-    // x fragments of this warp's windows: batch row gq, chunk (4*window + tq)
-    uint4 xf[MMA_MAXW];
-#pragma unroll
-    for (int q = 0; q < MMA_MAXW; ++q) {
-      const int w = warp + NW * q;
-      xf[q] = make_uint4(0, 0, 0, 0);
-      if (w < nwin && gq < nb && ntile > 0)
-        xf[q] = ld_cached16(static_cast<const T*>(p.x) + static_cast<size_t>(b0 + gq) * H + (4 * w + tq) * 8);
+    // tile index of this warp: blockIdx.x + gridDim.x * (warp + NWp * k)
+    int tile = blockIdx.x + gridDim.x * warp;
+    if (lane == 0 && tile < ntile_all) issue(tile);  // first rows stream in while x is staged
+    if (bt > 0) __syncthreads();
+    for (int i = tid; i < nb * (H / 8); i += blockDim.x) {
+      const int b = i / (H / 8), c = i % (H / 8);
+      *reinterpret_cast<uint4*>(x_s + static_cast<size_t>(b) * row_stride + c * 16) =
+          ld_cached16(static_cast<const T*>(p.x) + static_cast<size_t>(b0 + b) * H + c * 8);
     }
+    __syncthreads();
 
-    for (int it = 0; it < ntile; ++it, ++g) {
-      const int s = g % S;
-      const int r0 = j0 + it * R;
-      const int nrows = min(R, j1 - r0);
-      const unsigned char* st = stages + static_cast<size_t>(s) * 8 * row_stride;
-      const unsigned char* arow = st + static_cast<size_t>(gq) * row_stride + tq * 16;
-      if (!mbar_wait_bounded(&full[s], (g / S) & 1)) timed_out = true;
-
-      float d[4] = {0.f, 0.f, 0.f, 0.f};
-      float e[4] = {0.f, 0.f, 0.f, 0.f};  // second chain for instruction-level parallelism
-#pragma unroll
-      for (int q = 0; q < MMA_MAXW; ++q) {
-        const int w = warp + NW * q;
-        if (w < nwin) {
-          const uint4 av = *reinterpret_cast<const uint4*>(arow + static_cast<size_t>(w) * 64);
-          MmaOp<T>::run(d, av.x, av.y, xf[q].x, xf[q].y);
-          MmaOp<T>::run(e, av.z, av.w, xf[q].z, xf[q].w);
+    const unsigned char* arow = mybuf + static_cast<size_t>(gq < MMA_TILE_ROWS ? gq : 0) * row_stride + tq * 16;
+    const bool x_on = gq < nb;  // batch columns beyond the tile multiply by zero
+    const unsigned char* xrow = x_s + static_cast<size_t>(x_on ? gq : 0) * row_stride + tq * 16;
+    for (; tile < ntile_all; tile += gridDim.x * NWp) {
+      const int r0 = tile * TR;
+      const int nr = min(TR, K - r0);
+      if (!mbar_wait_bounded(mybar, phase)) timed_out = true;
+      phase ^= 1u;
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+      float d2[4] = {0.f, 0.f, 0.f, 0.f}, d3[4] = {0.f, 0.f, 0.f, 0.f};
+      int w = 0;
+      for (; w + 1 < nwin; w += 2) {
+        uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
+        if (gq < MMA_TILE_ROWS) {
+          a0 = *reinterpret_cast<const uint4*>(arow + static_cast<size_t>(w) * 64);
+          a1 = *reinterpret_cast<const uint4*>(arow + static_cast<size_t>(w + 1) * 64);
         }
+        uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+        if (x_on) {
+          x0 = *reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(w) * 64);
+          x1 = *reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(w + 1) * 64);
+        }
+        MmaOp<T>::run(d0, a0.x, a0.y, x0.x, x0.y);
+        MmaOp<T>::run(d1, a0.z, a0.w, x0.z, x0.w);
+        MmaOp<T>::run(d2, a1.x, a1.y, x1.x, x1.y);
+        MmaOp<T>::run(d3, a1.z, a1.w, x1.z, x1.w);
       }
-      // lane (gq,tq): row gq, batch columns 2tq and 2tq+1
-      float* ps = part_base + ((static_cast<size_t>(s) * 8 + gq) * 16 + warp) * 8 + 2 * tq;
-      ps[0] = d[0] + e[0];
-      ps[1] = d[1] + e[1];
+      for (; w < nwin; ++w) {
+        uint4 a0 = make_uint4(0, 0, 0, 0);
+        if (gq < MMA_TILE_ROWS) a0 = *reinterpret_cast<const uint4*>(arow + static_cast<size_t>(w) * 64);
+        uint4 x0 = make_uint4(0, 0, 0, 0);
+        if (x_on) x0 = *reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(w) * 64);
+        MmaOp<T>::run(d0, a0.x, a0.y, x0.x, x0.y);
+        MmaOp<T>::run(d1, a0.z, a0.w, x0.z, x0.w);
+      }
+      // the buffer is free again: fetch this warp's next tile before the epilogue
       __syncwarp();
-      int last = 0;
-      if (lane == 0) {
-        __threadfence_block();
-        last = (atomicAdd(&cnt[s], 1) == NW - 1);
+      const int next = tile + gridDim.x * NWp;
+      if (lane == 0 && next < ntile_all) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue(next);
       }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      if (last) {
-        __threadfence_block();
-        // sum the 16 parts in ascending order: lane -> (row gq, cols 2tq, 2tq+1)
-        const volatile float* pr = part_base + ((static_cast<size_t>(s) * 8 + gq) * 16) * 8 + 2 * tq;
-        float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-        for (int q = 0; q < NW; ++q) {
-          s0 += pr[q * 8];
-          s1 += pr[q * 8 + 1];
-        }
-        if (p.has_gate) {
-          // rows 0..3 gate, rows 4..7 up of the same neurons: bring up sums to the gate lanes
-          const float u0 = __shfl_down_sync(0xffffffffu, s0, 16);
-          const float u1 = __shfl_down_sync(0xffffffffu, s1, 16);
-          if (gq < 4 && gq < nrows) {
-            const int j = r0 + gq;
-            const float a0 = apply_act(p.act, s0) * u0, a1 = apply_act(p.act, s1) * u1;
-            const int c0 = 2 * tq, c1 = 2 * tq + 1;
-            if (c0 < nb) {
-              p.a_out[static_cast<size_t>(j) * p.B + b0 + c0] = a0;
-              if (combined) {
-                combined[static_cast<size_t>(b0 + c0) * ldc + j] = DT<T>::from_f(a0);
-                combined[static_cast<size_t>(b0 + c0) * ldc + K + j] = DT<T>::from_f(u0);
-              }
-            }
-            if (c1 < nb) {
-              p.a_out[static_cast<size_t>(j) * p.B + b0 + c1] = a1;
-              if (combined) {
-                combined[static_cast<size_t>(b0 + c1) * ldc + j] = DT<T>::from_f(a1);
-                combined[static_cast<size_t>(b0 + c1) * ldc + K + j] = DT<T>::from_f(u1);
-              }
-            }
-          }
-        } else if (gq < nrows) {
+      // lane (gq,tq): tile row gq, batch columns 2tq and 2tq+1
+      const float s0 = (d0[0] + d1[0]) + (d2[0] + d3[0]);
+      const float s1 = (d0[1] + d1[1]) + (d2[1] + d3[1]);
+      const int c0 = 2 * tq, c1 = 2 * tq + 1;
+      if (p.has_gate) {
+        // rows 0,1 = gate of neurons r0, r0+1; rows 2,3 = their up rows (8 lanes further)
+        const float u0 = __shfl_down_sync(0xffffffffu, s0, 8);
+        const float u1 = __shfl_down_sync(0xffffffffu, s1, 8);
+        if (gq < nr) {
           const int j = r0 + gq;
-          const float a0 = apply_act(p.act, s0), a1 = apply_act(p.act, s1);
-          const int c0 = 2 * tq, c1 = 2 * tq + 1;
+          const float a0 = apply_act(p.act, s0) * u0, a1 = apply_act(p.act, s1) * u1;
           if (c0 < nb) {
             p.a_out[static_cast<size_t>(j) * p.B + b0 + c0] = a0;
-            if (combined) combined[static_cast<size_t>(b0 + c0) * ldc + j] = DT<T>::from_f(a0);
+            if (combined) {
+              combined[static_cast<size_t>(b0 + c0) * ldc + j] = DT<T>::from_f(a0);
+              combined[static_cast<size_t>(b0 + c0) * ldc + K + j] = DT<T>::from_f(u0);
+            }
           }
           if (c1 < nb) {
             p.a_out[static_cast<size_t>(j) * p.B + b0 + c1] = a1;
-            if (combined) combined[static_cast<size_t>(b0 + c1) * ldc + j] = DT<T>::from_f(a1);
+            if (combined) {
+              combined[static_cast<size_t>(b0 + c1) * ldc + j] = DT<T>::from_f(a1);
+              combined[static_cast<size_t>(b0 + c1) * ldc + K + j] = DT<T>::from_f(u1);
+            }
           }
         }
-        if (lane == 0) cnt[s] = 0;
+      } else if (gq < nr) {
+        const int j = r0 + gq;
+        const float a0 = apply_act(p.act, s0), a1 = apply_act(p.act, s1);
+        if (c0 < nb) {
+          p.a_out[static_cast<size_t>(j) * p.B + b0 + c0] = a0;
+          if (combined) combined[static_cast<size_t>(b0 + c0) * ldc + j] = DT<T>::from_f(a0);
+        }
+        if (c1 < nb) {
+          p.a_out[static_cast<size_t>(j) * p.B + b0 + c1] = a1;
+          if (combined) combined[static_cast<size_t>(b0 + c1) * ldc + j] = DT<T>::from_f(a1);
+        }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
     }
   }
   if (timed_out && p.status && lane == 0) atomicOr(p.status, DEV_TIMEOUT);
 }
 
-// CTA c owns column chunks 2c and 2c+1 (32 bytes of every row).  Thread t: chunk 2c + (t&1),
-// rows (t>>1), (t>>1)+256, ...; eight row loads (and their a values) are issued before the
-// first use, so a CTA has 64 KB in flight and a 20 % dense layer needs one round trip.
-// Reduction: shuffle butterfly over the 16 row lanes of a warp (xor 2,4,8,16), then the 16
-// warps in ascending order.
+// Grid (nslab, CS), cluster (1, CS, 1): CTA (sx, sy) owns the 256-byte column slab sx and the
+// row range sy of CS.  Thread t: chunk sx*16 + (t & 15), rows lo + (t >> 4) + 32*k.
+// Reduction order: the two row lanes of a warp, then the 16 warps ascending, then the
+// cluster ranks ascending.
 constexpr int DOWN_THREADS = 512;
-constexpr int DOWN_ROWS = DOWN_THREADS / 2;
-constexpr int DOWN_UNROLL = 8;
+constexpr int DOWN_MAXCS = 8;
 
 template <typename T, int NB>
-__global__ void __launch_bounds__(DOWN_THREADS) k_down_slab(const DownArgs p) {
+__global__ void __launch_bounds__(DOWN_THREADS, 2) k_down_rows(const DownArgs p) {
   constexpr int V = DT<T>::V;
-  __shared__ float red_s[DOWN_THREADS / 32][2][NB][V];
+  constexpr int DOWN_UNROLL = NB == 1 ? 8 : (NB == 2 ? 4 : 2);
+  extern __shared__ __align__(16) float dsm[];
+  float* red_s = dsm;                                    // [16 warps][16 chunks][NB][V]
+  float* clu_s = dsm + 16 * 16 * NB * V;                 // [CS][16 chunks][NB][V]  (used on rank 0)
+  cg::cluster_group cluster = cg::this_cluster();
+  const int CS = gridDim.y;
+  const int rank = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int cid = tid & 1, rl = tid >> 1;
+  const int cl = tid & 15, rl = tid >> 4;
   const int H = p.H, nchunk = H / V;
-  const int c = blockIdx.x * 2 + cid;
+  const int c = blockIdx.x * 16 + cl;
   const bool c_ok = c < nchunk;
   const int K = p.K_dev ? *p.K_dev : p.K_host;
+  const int lo = static_cast<int>(static_cast<int64_t>(K) * rank / CS);
+  const int hi = static_cast<int>(static_cast<int64_t>(K) * (rank + 1) / CS);
   const T* dcol = static_cast<const T*>(p.down) + (c_ok ? c : 0) * V;
+  float* clu0 = cluster.map_shared_rank(clu_s, 0);
 
   for (int b0 = 0; b0 < p.B; b0 += NB) {
     const int nb = min(NB, p.B - b0);
@@ -543,16 +449,16 @@ __global__ void __launch_bounds__(DOWN_THREADS) k_down_slab(const DownArgs p) {
 #pragma unroll
       for (int v = 0; v < V; ++v) acc[b][v] = 0.f;
     if (c_ok) {
-      for (int j = rl; j < K; j += DOWN_ROWS * DOWN_UNROLL) {
+      for (int j = lo + rl; j < hi; j += 32 * DOWN_UNROLL) {
         uint4 dv[DOWN_UNROLL];
         float av[DOWN_UNROLL][NB];
 #pragma unroll
         for (int u = 0; u < DOWN_UNROLL; ++u) {
-          const int jj = j + DOWN_ROWS * u;
+          const int jj = j + 32 * u;
           dv[u] = make_uint4(0, 0, 0, 0);
-          if (jj < K) dv[u] = ld_stream16(dcol + static_cast<size_t>(jj) * H);
+          if (jj < hi) dv[u] = ld_stream16(dcol + static_cast<size_t>(jj) * H);
 #pragma unroll
-          for (int b = 0; b < NB; ++b) av[u][b] = (jj < K && b < nb) ? p.a[static_cast<size_t>(jj) * p.B + b0 + b] : 0.f;
+          for (int b = 0; b < NB; ++b) av[u][b] = (jj < hi && b < nb) ? p.a[static_cast<size_t>(jj) * p.B + b0 + b] : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < DOWN_UNROLL; ++u) {
@@ -569,40 +475,34 @@ __global__ void __launch_bounds__(DOWN_THREADS) k_down_slab(const DownArgs p) {
     for (int b = 0; b < NB; ++b)
 #pragma unroll
       for (int v = 0; v < V; ++v) {
-        float s = acc[b][v];
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        s += __shfl_xor_sync(0xffffffffu, s, 8);
-        s += __shfl_xor_sync(0xffffffffu, s, 16);
-        if (lane < 2) red_s[warp][lane][b][v] = s;
+        const float s = acc[b][v] + __shfl_xor_sync(0xffffffffu, acc[b][v], 16);
+        if (lane < 16) red_s[((warp * 16 + cl) * NB + b) * V + v] = s;
       }
     __syncthreads();
-    // 2 chunks x NB rows x V elements results
-    for (int i = tid; i < 2 * NB * V; i += blockDim.x) {
-      const int v = i % V, b = (i / V) % NB, cc = i / (V * NB);
-      const int col_chunk = blockIdx.x * 2 + cc;
-      if (b < nb && col_chunk < nchunk) {
-        float s = 0.f;
+    // CTA partial for its slab: 16 chunks x NB x V values, each summed over the 16 warps
+    for (int i = tid; i < 16 * NB * V; i += DOWN_THREADS) {
+      float s = 0.f;
 #pragma unroll
-        for (int w = 0; w < DOWN_THREADS / 32; ++w) s += red_s[w][cc][b][v];
-        static_cast<T*>(p.out)[static_cast<size_t>(b0 + b) * H + col_chunk * V + v] = DT<T>::from_f(s);
+      for (int w = 0; w < 16; ++w) s += red_s[w * 16 * NB * V + i];
+      clu0[rank * 16 * NB * V + i] = s;  // distributed shared memory of cluster rank 0
+    }
+    cluster.sync();
+    if (rank == 0) {
+      for (int i = tid; i < 16 * NB * V; i += DOWN_THREADS) {
+        const int v = i % V, b = (i / V) % NB, cc = i / (V * NB);
+        const int col_chunk = blockIdx.x * 16 + cc;
+        if (b < nb && col_chunk < nchunk) {
+          float s = 0.f;
+          for (int r = 0; r < CS; ++r) s += clu_s[r * 16 * NB * V + i];
+          static_cast<T*>(p.out)[static_cast<size_t>(b0 + b) * H + col_chunk * V + v] = DT<T>::from_f(s);
+        }
       }
     }
-    __syncthreads();
+    cluster.sync();  // rank 0's buffer may be overwritten by the next batch tile only now
   }
 }
 
 constexpr size_t TMA_SMEM_BUDGET = 220 * 1024;
-
-// STX_GATEUP=fma forces the FMA-pipe consumer for 16-bit types (A/B measurements).
-static bool use_mma_path() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("STX_GATEUP");
-    v = (e && !strcmp(e, "fma")) ? 0 : 1;
-  }
-  return v == 1;
-}
 
 template <typename T, int NB>
 static int launch_gateup(const GateUpArgs& a, int grid, size_t smem, cudaStream_t s) {
@@ -614,7 +514,7 @@ static int launch_gateup(const GateUpArgs& a, int grid, size_t smem, cudaStream_
                                   static_cast<int>(TMA_SMEM_BUDGET + 4096)));
     attr_set[dev] = true;
   }
-  k_gateup_tma<T, NB><<<grid, a.nconsumer + 32, smem, s>>>(a);
+  k_gateup_tma<T, NB><<<grid, a.nwarps * 32, smem, s>>>(a);
   STX_LAUNCH_CHECK("k_gateup_tma");
   return STX_OK;
 }
@@ -629,7 +529,7 @@ static int launch_gateup_mma(const GateUpArgs& a, int grid, size_t smem, cudaStr
                                   static_cast<int>(TMA_SMEM_BUDGET + 4096)));
     attr_set[dev] = true;
   }
-  k_gateup_mma<T><<<grid, 16 * 32 + 32, smem, s>>>(a);
+  k_gateup_mma<T><<<grid, a.nwarps * 32, smem, s>>>(a);
   STX_LAUNCH_CHECK("k_gateup_mma");
   return STX_OK;
 }
@@ -638,16 +538,70 @@ int launch_gateup_mma<float>(const GateUpArgs&, int, size_t, cudaStream_t) {
   return STX_ERR_UNSUPPORTED;
 }
 
+// The tensor-pipe kernel pays off once several batch rows share one pass over the weights;
+// at batch 1-3 the FMA-pipe kernel measured faster.  STX_GATEUP=fma / mma forces one of them
+// (A/B measurements).
+static bool use_mma_path(int B) {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("STX_GATEUP");
+    v = !e ? 2 : (!strcmp(e, "fma") ? 0 : (!strcmp(e, "mma") ? 1 : 2));
+  }
+  return v == 2 ? B >= 4 : v == 1;
+}
+
+template <typename T, int NB>
+static int launch_down(const DownArgs& d, cudaStream_t s) {
+  constexpr int V = DT<T>::V;
+  const int nchunk = d.H / V;
+  const int nslab = (nchunk + 15) / 16;
+  int cs = 1;  // largest power of two that keeps at most two CTAs per SM
+  while (cs * 2 <= DOWN_MAXCS && nslab * cs * 2 <= 2 * num_sms()) cs *= 2;
+  const size_t smem = sizeof(float) * (16 * 16 + DOWN_MAXCS * 16) * NB * V;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    STX_CUDA(cudaFuncSetAttribute(k_down_rows<T, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nslab, cs, 1);
+  cfg.blockDim = dim3(DOWN_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = cs;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  STX_CUDA(cudaLaunchKernelEx(&cfg, k_down_rows<T, NB>, d));
+  return STX_OK;
+}
+
 template <typename T, int NB>
 static int launch_both(const GateUpArgs& g, int grid, size_t smem, const DownArgs& d, unsigned parts, cudaStream_t s) {
   if (parts & 1u) {
-    int rc = g.R == 0 ? launch_gateup_mma<T>(g, grid, smem, s) : launch_gateup<T, NB>(g, grid, smem, s);
+    int rc = STX_ERR_UNSUPPORTED;
+    if (sizeof(T) == 2 && (g.H % 32) == 0 && use_mma_path(g.B)) {
+      // tensor-pipe kernel: 4-row tiles with padded rows, x tile of 8 padded rows
+      const size_t stride = static_cast<size_t>(g.H) * sizeof(T) + 64;
+      const size_t fixed = 256 + static_cast<size_t>(std::min(g.B, 8)) * stride;
+      if (fixed + 2 * MMA_TILE_ROWS * stride <= TMA_SMEM_BUDGET) {
+        GateUpArgs m = g;
+        m.nwarps = static_cast<int>(std::min<size_t>(16, (TMA_SMEM_BUDGET - fixed) / (MMA_TILE_ROWS * stride)));
+        rc = launch_gateup_mma<T>(m, num_sms(), fixed + static_cast<size_t>(m.nwarps) * MMA_TILE_ROWS * stride, s);
+      }
+    }
+    if (rc == STX_ERR_UNSUPPORTED) rc = launch_gateup<T, NB>(g, grid, smem, s);
     if (rc != STX_OK) return rc;
   }
   if (parts & 2u) {
-    const int nchunk = d.H / DT<T>::V;
-    k_down_slab<T, NB><<<(nchunk + 1) / 2, DOWN_THREADS, 0, s>>>(d);
-    STX_LAUNCH_CHECK("k_down_slab");
+    constexpr int NBD = NB > 4 ? 4 : NB;  // the down kernel walks batches of at most 4
+    int rc = launch_down<T, NBD>(d, s);
+    if (rc != STX_OK) return rc;
   }
   return STX_OK;
 }
@@ -675,45 +629,12 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   if (nchunk < 32) return STX_ERR_UNSUPPORTED;
   const uintptr_t al = reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(down);
   if (al & 15) return STX_ERR_UNSUPPORTED;
-  const int NW = 16, NT = NW * 32;
   const int nb = B >= 8 ? 8 : (B >= 4 ? 4 : (B >= 2 ? 2 : 1));
   const int nmat = has_gate ? 2 : 1;
   const size_t row_bytes = static_cast<size_t>(H) * es;
   const size_t x_bytes = (es * nb * H + 127) / 128 * 128;
-  int R = 0, S = 0;
-  const bool use_mma = es == 2 && (H % 32) == 0 && H <= 16 * MMA_MAXW * 32 && use_mma_path();
-  size_t mma_smem = 0;
-  if (use_mma) {
-    const size_t stage = 8 * (row_bytes + 64);
-    for (int st = GU_MAXS; st >= 2; --st) {
-      const size_t need = 256 + static_cast<size_t>(st) * 8 * 16 * 8 * sizeof(float) + st * stage;
-      if (need <= TMA_SMEM_BUDGET) {
-        S = st;
-        mma_smem = need;
-        break;
-      }
-    }
-  }
-  if (use_mma && S >= 2) {
-    // R == 0 marks the tensor-pipe kernel; its tile height is fixed by has_gate
-  } else
-  for (int r = GU_MAXR; r >= 1; r >>= 1) {
-    const size_t stage = static_cast<size_t>(r) * nmat * row_bytes;
-    for (int st = GU_MAXS; st >= 2; --st) {
-      const size_t part_bytes = (sizeof(float) * st * r * (NW / r) * 2 * nb + 127) / 128 * 128;
-      if (256 + 128 + part_bytes + x_bytes + st * stage <= TMA_SMEM_BUDGET) {
-        S = st;
-        break;
-      }
-    }
-    if (S >= 3 || (r == 1 && S >= 2)) {
-      R = r;
-      break;
-    }
-    S = 0;
-  }
-  const bool mma = use_mma && S >= 2 && R == 0;
-  if (R == 0 && !mma) return STX_ERR_UNSUPPORTED;
+  if (256 + x_bytes + 2 * nmat * row_bytes > TMA_SMEM_BUDGET) return STX_ERR_UNSUPPORTED;
+  const int nwarps = static_cast<int>(std::min<size_t>(16, (TMA_SMEM_BUDGET - 256 - x_bytes) / (nmat * row_bytes)));
   GateUpArgs a;
   a.x = x;
   a.gate = gate;
@@ -727,18 +648,10 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   a.H = static_cast<int>(H);
   a.act = act;
   a.has_gate = has_gate;
-  a.R = R;
-  a.S = S;
-  a.nconsumer = NT;
-  a.stage_bytes = static_cast<uint32_t>(static_cast<size_t>(R) * nmat * row_bytes);
-  size_t smem = mma_smem;
-  if (!mma) {
-    const size_t part_bytes = (sizeof(float) * S * R * (NW / R) * 2 * nb + 127) / 128 * 128;
-    smem = 256 + 128 + part_bytes + x_bytes + static_cast<size_t>(S) * a.stage_bytes;
-  }
-  const int tile_r = mma ? (has_gate ? 4 : 8) : R;
+  a.nwarps = nwarps;
+  const size_t smem = 256 + x_bytes + static_cast<size_t>(nwarps) * nmat * row_bytes;
   int grid = num_sms();
-  if (!K_dev) grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, (K_host + tile_r - 1) / tile_r)));
+  if (!K_dev) grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, K_host)));
   DownArgs d;
   d.a = a.a_out;
   d.down = down;
