@@ -18,7 +18,8 @@
 namespace stx {
 
 constexpr int PLAN_THREADS = 1024;
-constexpr int PLAN_MFAST = 2048;  // surplus removals handled in shared memory
+constexpr int PLAN_MFAST = 2048;     // surplus removals replayed from shared memory
+constexpr int PLAN_LIST_CAP = 4096;  // added / removed ids kept in shared memory
 constexpr int MAX_I = 65536;      // 2 mask words per plan thread
 
 struct Int2 {
@@ -41,7 +42,7 @@ __device__ __forceinline__ Int2 block_excl_scan2(Int2 v, Int2* total, Int2* warp
   if (lane == 31) warp_sums[wid] = inc;
   __syncthreads();
   if (wid == 0) {
-    Int2 w = warp_sums[lane];
+    Int2 w = lane < static_cast<int>(blockDim.x >> 5) ? warp_sums[lane] : Int2{0, 0};
     Int2 winc = w;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -62,7 +63,14 @@ __device__ __forceinline__ Int2 block_excl_scan2(Int2 v, Int2* total, Int2* warp
   return r;
 }
 
-// One block.  Dynamic shared memory: 3*W + 3*PLAN_MFAST int32.
+// One block of PLAN_THREADS threads.  Dynamic shared memory (int32 words):
+//   s_rem[W] s_remoff[W] s_dirty[W] | s_added[CAP] s_removed[CAP] s_rpos[CAP] | s_tail[MFAST]
+//
+// Common case (both diff lists fit PLAN_LIST_CAP, surplus removals fit PLAN_MFAST): the lists
+// live in shared memory and the kernel makes two dependent trips to global memory — (1) mask
+// words and K, (2) pos_of of every removed neuron plus the tail of `active` — everything
+// else is shared-memory work and fire-and-forget stores.  Otherwise a generic path keeps the
+// lists in global memory.
 __global__ void __launch_bounds__(PLAN_THREADS, 1)
 k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_bits,
              int32_t* __restrict__ active, int32_t* __restrict__ pos_of, int32_t* __restrict__ lists,
@@ -76,16 +84,17 @@ k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_b
   uint32_t* s_rem = reinterpret_cast<uint32_t*>(sm);
   int32_t* s_remoff = sm + W;
   uint32_t* s_dirty = reinterpret_cast<uint32_t*>(sm + 2 * W);
-  int32_t* s_curpos = sm + 3 * W;
-  int32_t* s_tail = s_curpos + PLAN_MFAST;
-  int32_t* s_E = s_tail + PLAN_MFAST;
-  int32_t* added = lists;
-  int32_t* removed = lists + I;
+  int32_t* s_added = sm + 3 * W;
+  int32_t* s_removed = s_added + PLAN_LIST_CAP;
+  int32_t* s_rpos = s_removed + PLAN_LIST_CAP;
+  int32_t* s_tail = s_rpos + PLAN_LIST_CAP;
 
   const int t = threadIdx.x;
-  const int WPT = (W + PLAN_THREADS - 1) / PLAN_THREADS;  // 1 or 2
+  const int NT = blockDim.x;
+  const int WPT = (W + NT - 1) / NT;  // <= 2 by construction of the launch
 
   // ---- 1. diff words (weight_cache.h:84-110: added = new & ~old, removed = old & ~new)
+  const int K0 = state[ST_K];
   uint32_t nbw[2] = {0, 0}, aw[2] = {0, 0}, rw[2] = {0, 0};
   Int2 cnt{0, 0};
   for (int k = 0; k < WPT; ++k) {
@@ -107,6 +116,21 @@ k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_b
   Int2 off = block_excl_scan2(cnt, &s_tot, s_ws);
   const int na = s_tot.x, nr = s_tot.y;
 
+  if (na == 0 && nr == 0) {  // unchanged mask: the reference returns before touching anything
+    if (t == 0) {
+      state[ST_NJOBS] = 0;
+      state[ST_ADDED] = 0;
+      state[ST_REMOVED] = 0;
+    }
+    return;
+  }
+  const int pairs = min(na, nr);
+  const int m = nr > na ? nr - na : 0;   // surplus removals
+  const int n1 = K0 - m;                 // size after phase 3 when every removal is found
+  const bool fast = na <= PLAN_LIST_CAP && nr <= PLAN_LIST_CAP && m <= PLAN_MFAST && n1 >= 0;
+  int32_t* added = fast ? s_added : lists;
+  int32_t* removed = fast ? s_removed : lists + I;
+
   // ---- 2. ascending id lists (torch::nonzero order)
   for (int k = 0; k < WPT; ++k) {
     const int w = t * WPT + k;
@@ -125,95 +149,127 @@ k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_b
       }
     }
   }
-  const int K0 = state[ST_K];
-  __syncthreads();
-
-  if (na == 0 && nr == 0) {  // unchanged mask: the reference returns before touching anything
-    if (t == 0) {
-      state[ST_NJOBS] = 0;
-      state[ST_ADDED] = 0;
-      state[ST_REMOVED] = 0;
-    }
-    return;
-  }
-  const int pairs = min(na, nr);
-
-  // ---- 3. phase 1: i-th removed slot receives the i-th added neuron (weight_cache.h:248-277)
-  for (int i = t; i < pairs; i += PLAN_THREADS) {
-    const int r = removed[i], a = added[i];
-    const int p = pos_of[r];
-    if (p >= 0) {
-      active[p] = a;
-      pos_of[a] = p;
-      pos_of[r] = -1;
-      atomicOr(&s_dirty[p >> 5], 1u << (p & 31));
-    }
-  }
   __syncthreads();
 
   int Knew = K0;
-  if (na > nr) {
-    // ---- phase 2: append surplus additions in ascending order (weight_cache.h:280-307)
-    const int extra = na - nr;
-    for (int i = t; i < extra; i += PLAN_THREADS) {
-      const int a = added[pairs + i];
-      const int p = K0 + i;
-      if (p < I) {
+  if (fast) {
+    // ---- one round of reads: position of every removed neuron, and the tail of `active`
+    for (int i = t; i < nr; i += NT) {
+      const int p = pos_of[s_removed[i]];
+      s_rpos[i] = p;
+      if (p < 0) s_slow = 1;  // inconsistent state (only after a NO_ACTIVE error): generic replay
+    }
+    for (int i = t; i < m; i += NT) s_tail[i] = active[n1 + i];
+    __syncthreads();
+    // ---- phase 1: i-th removed slot receives the i-th added neuron (weight_cache.h:248-277)
+    for (int i = t; i < pairs; i += NT) {
+      const int r = s_removed[i], a = s_added[i];
+      const int p = s_rpos[i];
+      if (p >= 0) {
         active[p] = a;
         pos_of[a] = p;
+        pos_of[r] = -1;
+        atomicOr(&s_dirty[p >> 5], 1u << (p & 31));
+        if (m > 0 && p >= n1) s_tail[p - n1] = a;  // keep the shared-memory copy of the tail current
+      }
+    }
+    if (na > nr) {
+      // ---- phase 2: append surplus additions in ascending order (weight_cache.h:280-307)
+      const int extra = na - nr;
+      for (int i = t; i < extra; i += NT) {
+        const int a = s_added[pairs + i];
+        const int p = K0 + i;
+        if (p < I) {
+          active[p] = a;
+          pos_of[a] = p;
+          atomicOr(&s_dirty[p >> 5], 1u << (p & 31));
+        }
+      }
+      Knew = min(K0 + extra, I);
+    }
+    __syncthreads();
+    if (m > 0) {
+      // ---- phase 3: surplus removals, ascending, each filled by the then-last row
+      //      (weight_cache.h:310-353).  Sequential by definition; one thread replays it on
+      //      indices only.  Every row it can move lives in the tail [n1, K0).
+      if (t == 0) {
+        int n = K0;
+        if (!s_slow) {
+          for (int i = 0; i < m; ++i) {
+            const int e = s_removed[pairs + i];
+            const int p = s_rpos[pairs + i];
+            const int last = n - 1;
+            if (p != last) {
+              const int x = s_tail[last - n1];
+              if (p >= n1) {
+                s_tail[p - n1] = x;
+              } else {
+                active[p] = x;
+                s_dirty[p >> 5] |= 1u << (p & 31);
+              }
+              pos_of[x] = p;
+              const uint32_t rwd = s_rem[x >> 5];
+              if ((rwd >> (x & 31)) & 1u) {  // x itself is removed later: track where it now sits
+                const int idx = s_remoff[x >> 5] + __popc(rwd & ((1u << (x & 31)) - 1u));
+                if (idx > pairs + i && idx < nr) s_rpos[idx] = p;
+              }
+            }
+            pos_of[e] = -1;
+            --n;
+          }
+        } else {
+          for (int i = 0; i < m; ++i) {
+            const int e = s_removed[pairs + i];
+            const int p = pos_of[e];
+            if (p < 0) continue;  // not cached: the reference skips it
+            const int last = n - 1;
+            if (p != last) {
+              const int x = active[last];
+              active[p] = x;
+              pos_of[x] = p;
+              s_dirty[p >> 5] |= 1u << (p & 31);
+            }
+            pos_of[e] = -1;
+            --n;
+          }
+        }
+        s_knew = n;
+      }
+      __syncthreads();
+      Knew = s_knew;
+    }
+  } else {
+    // ---------------------------------------------------------------- generic path (global lists)
+    for (int i = t; i < pairs; i += NT) {
+      const int r = removed[i], a = added[i];
+      const int p = pos_of[r];
+      if (p >= 0) {
+        active[p] = a;
+        pos_of[a] = p;
+        pos_of[r] = -1;
         atomicOr(&s_dirty[p >> 5], 1u << (p & 31));
       }
     }
-    Knew = min(K0 + extra, I);
-  } else if (nr > na) {
-    // ---- phase 3: surplus removals, ascending, each filled by the then-last row
-    //      (weight_cache.h:310-353).  Sequential by definition; one thread replays it on
-    //      indices only.  All rows it can move live in the tail [n1, K0), so the fast path
-    //      keeps the tail, the holes' positions and the removal ids in shared memory.
-    const int m = nr - na;
-    const int n1 = K0 - m;
-    const bool fast = (m <= PLAN_MFAST) && (n1 >= 0);
-    if (fast) {
-      for (int i = t; i < m; i += PLAN_THREADS) {
-        const int e = removed[pairs + i];
-        const int p = pos_of[e];
-        s_E[i] = e;
-        s_curpos[i] = p;
-        s_tail[i] = active[n1 + i];
-        if (p < 0) s_slow = 1;  // inconsistent state (only after a NO_ACTIVE error): generic path
-      }
-    }
     __syncthreads();
-    if (t == 0) {
-      int n = K0;
-      if (fast && !s_slow) {
-        for (int i = 0; i < m; ++i) {
-          const int e = s_E[i];
-          const int p = s_curpos[i];
-          const int last = n - 1;
-          if (p != last) {
-            const int x = s_tail[last - n1];
-            if (p >= n1) {
-              s_tail[p - n1] = x;
-            } else {
-              active[p] = x;
-              s_dirty[p >> 5] |= 1u << (p & 31);
-            }
-            pos_of[x] = p;
-            const uint32_t rwd = s_rem[x >> 5];
-            if ((rwd >> (x & 31)) & 1u) {  // x itself is removed later: track where it now sits
-              const int idx = s_remoff[x >> 5] + __popc(rwd & ((1u << (x & 31)) - 1u)) - pairs;
-              if (idx > i && idx < m) s_curpos[idx] = p;
-            }
-          }
-          pos_of[e] = -1;
-          --n;
+    if (na > nr) {
+      const int extra = na - nr;
+      for (int i = t; i < extra; i += NT) {
+        const int a = added[pairs + i];
+        const int p = K0 + i;
+        if (p < I) {
+          active[p] = a;
+          pos_of[a] = p;
+          atomicOr(&s_dirty[p >> 5], 1u << (p & 31));
         }
-      } else {
+      }
+      Knew = min(K0 + extra, I);
+    } else if (nr > na) {
+      if (t == 0) {
+        int n = K0;
         for (int i = 0; i < m; ++i) {
           const int e = removed[pairs + i];
           const int p = pos_of[e];
-          if (p < 0) continue;  // not cached: the reference skips it
+          if (p < 0) continue;
           const int last = n - 1;
           if (p != last) {
             const int x = active[last];
@@ -224,13 +280,13 @@ k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_b
           pos_of[e] = -1;
           --n;
         }
+        s_knew = n;
       }
-      s_knew = n;
+      __syncthreads();
+      Knew = s_knew;
     }
     __syncthreads();
-    Knew = s_knew;
   }
-  __syncthreads();
 
   // ---- 4. rewritten slots below the new K, ascending
   Int2 jc{0, 0};
@@ -365,7 +421,7 @@ __global__ void k_fill_i32(int32_t* p, int32_t v, size_t n) {
 
 static size_t plan_smem_bytes(int64_t I) {
   const int64_t W = (I + 31) / 32;
-  return static_cast<size_t>(3 * W + 3 * PLAN_MFAST) * sizeof(int32_t);
+  return static_cast<size_t>(3 * W + 3 * PLAN_LIST_CAP + PLAN_MFAST) * sizeof(int32_t);
 }
 
 int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
@@ -377,7 +433,10 @@ int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
                                   static_cast<int>(plan_smem_bytes(MAX_I))));
     attr_set[dev] = true;
   }
-  k_cache_plan<<<1, PLAN_THREADS, plan_smem_bytes(c->I), s>>>(bits, c->cur_bits, c->active, c->pos_of,
+  // two mask words per thread at most; small index spaces use fewer threads (cheaper barriers)
+  const int W = static_cast<int>((c->I + 31) / 32);
+  const int threads = W <= 256 ? 256 : (W <= 512 ? 512 : PLAN_THREADS);
+  k_cache_plan<<<1, threads, plan_smem_bytes(c->I), s>>>(bits, c->cur_bits, c->active, c->pos_of,
                                                              c->lists, c->jobs, c->state,
                                                              static_cast<int>(c->I));
   STX_LAUNCH_CHECK("k_cache_plan");
