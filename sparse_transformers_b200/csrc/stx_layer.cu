@@ -11,10 +11,11 @@
 namespace stx {
 int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
                  int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch,
-                 cudaStream_t s);
+                 int32_t* idx_out, int32_t* count_out, unsigned* ticket, cudaStream_t s);
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
-                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s);
+                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts, const int32_t* row_idx,
+                cudaStream_t s);
 }  // namespace stx
 
 struct stx_layer {
@@ -27,6 +28,9 @@ struct stx_layer {
   int act = 0;
   int64_t max_batch = 0;
   uint32_t* bits = nullptr;
+  int32_t* idx = nullptr;        // [I] active neuron ids in ascending order (set bits of `bits`)
+  int32_t* count = nullptr;      // [0] number of active neurons, [1] last-block ticket of the predictor
+  bool gather = true;            // MLP gathers rows from the full pools (needs H*elem >= 512 bytes)
   void* scores = nullptr;        // [max_batch, I], only for rules that need whole rows
   void* pred_scratch = nullptr;
   void* mlp_scratch = nullptr;
@@ -43,6 +47,7 @@ struct stx_stack {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   int64_t kernel_nodes = 0;
+  std::vector<cudaEvent_t> events;  // fork points (one per layer) + the final join
 };
 
 using namespace stx;
@@ -52,6 +57,8 @@ extern "C" {
 int stx_layer_destroy(stx_layer_t* l) {
   if (!l) return STX_OK;
   cudaFree(l->bits);
+  cudaFree(l->idx);
+  cudaFree(l->count);
   cudaFree(l->scores);
   cudaFree(l->pred_scratch);
   cudaFree(l->mlp_scratch);
@@ -87,7 +94,13 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   stx_predict_scratch_bytes(max_batch, I, r, &pred_bytes);
   stx_mlp_scratch_bytes(max_batch, H, I, &mlp_bytes);
   const size_t es = dtype_size(cache->dtype);
+  // 16-bit rows narrower than 32 chunks fall back to the packed cache inside the MLP
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&l->bits), ((I + 31) / 32) * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&l->idx), I * sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&l->count), 64);
+  if (e == cudaSuccess) e = cudaMemset(l->count, 0, 64);
+  if (e == cudaSuccess) e = cudaMemset(l->idx, 0, I * sizeof(int32_t));
+  l->gather = (H * es) >= 512 && (H * es) % 16 == 0;
   if (e == cudaSuccess) e = cudaMalloc(&l->pred_scratch, pred_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&l->mlp_scratch, mlp_bytes);
   if (e == cudaSuccess) e = cudaMemset(l->mlp_scratch, 0, mlp_bytes);
@@ -101,35 +114,69 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   return STX_OK;
 }
 
+// One step with the cache maintenance (plan + row copies) optionally on a second stream.
+// With `gather` the MLP reads the active rows straight from the full pools through the list
+// of set mask bits, so it needs neither the index plan nor the copied rows: the differential
+// cache is then kept current off the critical path (side stream), which is where a GPU wants
+// it — contiguity of the active rows buys nothing when every row is a multi-KB burst.
+static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, cudaStream_t s,
+                              cudaStream_t side, cudaEvent_t fork_ev, unsigned stages) {
+  stx_cache* c = l->cache;
+  int rc = STX_OK;
+  if (stages & STX_STAGE_PREDICT) {
+    STX_CHECK_ARG(x_pred, "stx_layer_step: x_pred is null");
+    rc = predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
+                      l->pred_scratch, l->gather ? l->idx : nullptr, l->count, reinterpret_cast<unsigned*>(l->count + 1), s);
+    if (rc != STX_OK) return rc;
+  }
+  const bool forked = side != s && l->gather;
+  cudaStream_t cs = forked ? side : s;  // stream of the cache maintenance
+  if (forked && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY))) {
+    STX_CUDA(cudaEventRecord(fork_ev, s));
+    STX_CUDA(cudaStreamWaitEvent(side, fork_ev, 0));
+  }
+  if (!l->gather) {
+    // the MLP reads the packed cache: plan and copies come first, on the same stream
+    if (stages & STX_STAGE_PLAN) {
+      rc = cache_plan(c, l->bits, s);
+      if (rc != STX_OK) return rc;
+    }
+    if (stages & STX_STAGE_COPY) {
+      rc = cache_copy_rows(c, s);
+      if (rc != STX_OK) return rc;
+    }
+  }
+  if (stages & STX_STAGE_MLP) {
+    STX_CHECK_ARG(x_mlp && out, "stx_layer_step: x_mlp/out is null");
+    const unsigned parts = ((stages & STX_STAGE_MLP_GATEUP) ? 1u : 0u) | ((stages & STX_STAGE_MLP_DOWN) ? 2u : 0u);
+    if (l->gather)
+      rc = mlp_forward(x_mlp, B, c->H, c->pool_gate, c->pool_up, c->pool_down, l->count, 0, c->I, 0, out, nullptr, l->act,
+                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, l->idx, s);
+    else
+      rc = mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
+                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, nullptr, s);
+    if (rc != STX_OK) return rc;
+  }
+  if (l->gather) {
+    if (stages & STX_STAGE_PLAN) {
+      rc = cache_plan(c, l->bits, cs);
+      if (rc != STX_OK) return rc;
+    }
+    if (stages & STX_STAGE_COPY) {
+      rc = cache_copy_rows(c, cs);
+      if (rc != STX_OK) return rc;
+    }
+  }
+  return rc;
+}
+
 int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, void* stream,
                           unsigned stages) {
   STX_CHECK_ARG(l, "stx_layer_step: null layer");
   STX_CHECK_ARG(B > 0 && B <= l->max_batch, "stx_layer_step: B=%lld outside 1..max_batch=%lld", static_cast<long long>(B),
                 static_cast<long long>(l->max_batch));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  stx_cache* c = l->cache;
-  int rc = STX_OK;
-  if (stages & STX_STAGE_PREDICT) {
-    STX_CHECK_ARG(x_pred, "stx_layer_step: x_pred is null");
-    rc = stx_predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
-                          l->pred_scratch, stream);
-    if (rc != STX_OK) return rc;
-  }
-  if (stages & STX_STAGE_PLAN) {
-    rc = cache_plan(c, l->bits, s);
-    if (rc != STX_OK) return rc;
-  }
-  if (stages & STX_STAGE_COPY) {
-    rc = cache_copy_rows(c, s);
-    if (rc != STX_OK) return rc;
-  }
-  if (stages & STX_STAGE_MLP) {
-    STX_CHECK_ARG(x_mlp && out, "stx_layer_step: x_mlp/out is null");
-    const unsigned parts = ((stages & STX_STAGE_MLP_GATEUP) ? 1u : 0u) | ((stages & STX_STAGE_MLP_DOWN) ? 2u : 0u);
-    rc = mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
-                     c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, s);
-  }
-  return rc;
+  return layer_step_streams(l, x_pred, x_mlp, B, out, s, s, nullptr, stages);
 }
 
 int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, void* stream) {
@@ -169,6 +216,7 @@ int stx_stack_destroy(stx_stack_t* s) {
   if (!s) return STX_OK;
   if (s->exec) cudaGraphExecDestroy(s->exec);
   if (s->graph) cudaGraphDestroy(s->graph);
+  for (cudaEvent_t ev : s->events) cudaEventDestroy(ev);
   cudaFree(s->x_in);
   cudaFree(s->out);
   delete s;
@@ -207,24 +255,43 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
     stx_stack_destroy(s);
     return STX_ERR_ALLOC;
   }
-  // Capture the L steps (nothing executes during capture).
-  cudaStream_t cs = nullptr;
+  // Capture the L steps (nothing executes during capture).  The critical path (predictor ->
+  // sparse MLP, layer after layer) stays on one stream; each layer's cache maintenance forks
+  // off after its predictor onto a side stream and everything joins at the end of the step.
+  cudaStream_t cs = nullptr, side = nullptr;
   e = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking);
+  for (int64_t i = 0; i <= L && e == cudaSuccess; ++i) {
+    cudaEvent_t ev = nullptr;
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e == cudaSuccess) s->events.push_back(ev);
+  }
   if (e != cudaSuccess) {
+    if (cs) cudaStreamDestroy(cs);
+    if (side) cudaStreamDestroy(side);
     stx_stack_destroy(s);
-    return cuda_fail(e, "stx_stack_create: cudaStreamCreate");
+    return cuda_fail(e, "stx_stack_create: stream/event creation");
   }
   int rc = STX_OK;
   e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
   if (e == cudaSuccess) {
+    bool forked = false;
     for (int64_t i = 0; i < L && rc == STX_OK; ++i) {
-      rc = stx_layer_step_stages(s->layers[i], s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs, stages);
+      stx_layer* l = s->layers[i];
+      rc = layer_step_streams(l, s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs, side, s->events[i], stages);
+      forked = forked || (l->gather && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY)));
+    }
+    if (rc == STX_OK && forked) {  // join
+      cudaError_t ej = cudaEventRecord(s->events[L], side);
+      if (ej == cudaSuccess) ej = cudaStreamWaitEvent(cs, s->events[L], 0);
+      if (ej != cudaSuccess) e = ej;
     }
     cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
-    if (rc == STX_OK && e2 != cudaSuccess) e = e2;
+    if (rc == STX_OK && e == cudaSuccess && e2 != cudaSuccess) e = e2;
   }
   if (e == cudaSuccess && rc == STX_OK) e = cudaGraphInstantiate(&s->exec, s->graph, 0);
   cudaStreamDestroy(cs);
+  cudaStreamDestroy(side);
   if (rc != STX_OK) {
     stx_stack_destroy(s);
     return rc;

@@ -41,6 +41,7 @@ struct GateUpArgs {
   float* a_out;          // [K][B] fp32
   int* status;           // optional device status word
   const int32_t* K_dev;
+  const int32_t* row_idx;  // optional: row j of this launch is row row_idx[j] of gate/up (gather from the full pools)
   int K_host;
   int B, H, act, has_gate;
   int nwarps;
@@ -51,6 +52,7 @@ struct DownArgs {
   const void* down;      // packed [K][H]
   void* out;             // [B][H] dtype
   const int32_t* K_dev;
+  const int32_t* row_idx;  // optional gather indices, as in GateUpArgs
   int K_host;
   int B, H;
 };
@@ -127,7 +129,7 @@ __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
 
   auto issue = [&](int j) {
     mbar_expect_tx(mybar, row_bytes * nmat);
-    const size_t off = static_cast<size_t>(j) * row_bytes;
+    const size_t off = static_cast<size_t>(p.row_idx ? p.row_idx[j] : j) * row_bytes;
     if (p.has_gate) bulk_load(mybuf, gsrc + off, row_bytes, mybar);
     bulk_load(mybuf + (p.has_gate ? row_bytes : 0), usrc + off, row_bytes, mybar);
   };
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
     const int nr = min(TR, K - r0);
     mbar_expect_tx(mybar, static_cast<uint32_t>(nr) * row_bytes * (p.has_gate ? 2 : 1));
     for (int i = 0; i < nr; ++i) {
-      const size_t off = static_cast<size_t>(r0 + i) * row_bytes;
+      const size_t off = static_cast<size_t>(p.row_idx ? p.row_idx[r0 + i] : r0 + i) * row_bytes;
       if (p.has_gate) {
         bulk_load(mybuf + static_cast<size_t>(i) * row_stride, gsrc + off, row_bytes, mybar);
         bulk_load(mybuf + static_cast<size_t>(TR + i) * row_stride, usrc + off, row_bytes, mybar);
@@ -456,7 +458,7 @@ __global__ void __launch_bounds__(DOWN_THREADS, 2) k_down_rows(const DownArgs p)
         for (int u = 0; u < DOWN_UNROLL; ++u) {
           const int jj = j + 32 * u;
           dv[u] = make_uint4(0, 0, 0, 0);
-          if (jj < hi) dv[u] = ld_stream16(dcol + static_cast<size_t>(jj) * H);
+          if (jj < hi) dv[u] = ld_stream16(dcol + static_cast<size_t>(p.row_idx ? p.row_idx[jj] : jj) * H);
 #pragma unroll
           for (int b = 0; b < NB; ++b) av[u][b] = (jj < hi && b < nb) ? p.a[static_cast<size_t>(jj) * p.B + b0 + b] : 0.f;
         }
@@ -621,8 +623,8 @@ static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const
 // these kernels; the caller then uses the plain-load kernel.
 // scratch: fp32 a[K][B] at offset 256.  parts: bit 0 = gate/up kernel, bit 1 = down kernel.
 int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
-                    const int32_t* K_dev, int64_t K_host, void* out, void* combined, int act, int has_gate, int dtype,
-                    void* scratch, int* status, unsigned parts, cudaStream_t s) {
+                    const int32_t* K_dev, int64_t K_host, const int32_t* row_idx, void* out, void* combined, int act,
+                    int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s) {
   const size_t es = dtype_size(dtype);
   const int V = static_cast<int>(16 / es);
   const int nchunk = static_cast<int>(H / V);
@@ -643,6 +645,7 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   a.a_out = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
   a.status = status;
   a.K_dev = K_dev;
+  a.row_idx = row_idx;
   a.K_host = static_cast<int>(K_host);
   a.B = static_cast<int>(B);
   a.H = static_cast<int>(H);
@@ -657,6 +660,7 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   d.down = down;
   d.out = out;
   d.K_dev = K_dev;
+  d.row_idx = row_idx;
   d.K_host = static_cast<int>(K_host);
   d.B = static_cast<int>(B);
   d.H = static_cast<int>(H);
