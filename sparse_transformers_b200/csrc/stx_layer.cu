@@ -11,11 +11,11 @@
 namespace stx {
 int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
                  int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch,
-                 int32_t* idx_out, int32_t* count_out, unsigned* ticket, cudaStream_t s);
+                 cudaStream_t s);
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
-                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts, const int32_t* row_idx,
-                cudaStream_t s);
+                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts,
+                const uint32_t* mask_bits, int32_t* idx_out, int32_t* count_out, cudaStream_t s);
 }  // namespace stx
 
 struct stx_layer {
@@ -100,7 +100,7 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&l->count), 64);
   if (e == cudaSuccess) e = cudaMemset(l->count, 0, 64);
   if (e == cudaSuccess) e = cudaMemset(l->idx, 0, I * sizeof(int32_t));
-  l->gather = (H * es) >= 512 && (H * es) % 16 == 0;
+  l->gather = (H * es) >= 512 && (H * es) % 16 == 0 && I <= 65536 && (I + 131) / 132 + 4 <= 512;
   if (e == cudaSuccess) e = cudaMalloc(&l->pred_scratch, pred_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&l->mlp_scratch, mlp_bytes);
   if (e == cudaSuccess) e = cudaMemset(l->mlp_scratch, 0, mlp_bytes);
@@ -126,7 +126,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
   if (stages & STX_STAGE_PREDICT) {
     STX_CHECK_ARG(x_pred, "stx_layer_step: x_pred is null");
     rc = predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
-                      l->pred_scratch, l->gather ? l->idx : nullptr, l->count, reinterpret_cast<unsigned*>(l->count + 1), s);
+                      l->pred_scratch, s);
     if (rc != STX_OK) return rc;
   }
   const bool forked = side != s && l->gather;
@@ -151,10 +151,10 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
     const unsigned parts = ((stages & STX_STAGE_MLP_GATEUP) ? 1u : 0u) | ((stages & STX_STAGE_MLP_DOWN) ? 2u : 0u);
     if (l->gather)
       rc = mlp_forward(x_mlp, B, c->H, c->pool_gate, c->pool_up, c->pool_down, l->count, 0, c->I, 0, out, nullptr, l->act,
-                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, l->idx, s);
+                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, l->bits, l->idx, l->count, s);
     else
       rc = mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
-                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, nullptr, s);
+                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, nullptr, nullptr, nullptr, s);
     if (rc != STX_OK) return rc;
   }
   if (l->gather) {

@@ -231,8 +231,14 @@ static int dispatch_nb(MlpArgs& a, int grid, int threads, cudaStream_t s) {
   return launch_fused<T, 4>(a, grid, threads, s);
 }
 
+struct GatherSpec {
+  const uint32_t* mask_bits;
+  int32_t* idx;
+  int32_t* count;
+  int I;
+};
 int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
-                    const int32_t* K_dev, int64_t K_host, const int32_t* row_idx, void* out, void* combined, int act,
+                    const int32_t* K_dev, int64_t K_host, const GatherSpec* gs, void* out, void* combined, int act,
                     int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s);
 
 // STX_MLP_KERNEL=plain forces the plain-load kernel (for A/B measurements); default: the
@@ -246,17 +252,20 @@ static bool use_tma_kernel() {
   return v == 1;
 }
 
-// Shared by the op entry point and the fused layer step.  row_idx (optional): gather rows
-// row_idx[0..K) of gate/up/down instead of rows 0..K-1 (streaming kernels only).
+// Shared by the op entry point and the fused layer step.  Gather mode (mask_bits != null,
+// streaming kernels only): gate/up/down are full [I,H] pools and the rows are those of the set
+// mask bits; idx_out [I] / count_out receive the list of active neuron ids and its length.
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
-                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts, const int32_t* row_idx,
-                cudaStream_t s) {
+                int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts,
+                const uint32_t* mask_bits, int32_t* idx_out, int32_t* count_out, cudaStream_t s) {
+  const bool row_idx = mask_bits != nullptr;
+  GatherSpec gs{mask_bits, idx_out, count_out, static_cast<int>(K_cap)};
   if ((use_tma_kernel() || row_idx) && !up_after_gate) {
     // the streaming kernels keep a[K][B] behind the (always zero) accumulator region
     void* a_region = static_cast<char*>(scratch) + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
-    const int rc = mlp_forward_tma(x, B, H, gate, up, down, K_dev, K_host, row_idx, out, combined, act, has_gate, dtype,
-                                   a_region, status, parts, s);
+    const int rc = mlp_forward_tma(x, B, H, gate, up, down, K_dev, K_host, row_idx ? &gs : nullptr, out, combined, act,
+                                   has_gate, dtype, a_region, status, parts, s);
     if (rc != STX_ERR_UNSUPPORTED) return rc;
   }
   if (row_idx) {
@@ -330,7 +339,7 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
   const void* gate = has_gate ? cw : nullptr;
   const void* up = has_gate ? cw + static_cast<size_t>(K) * H * es : cw;
   return mlp_forward(x, B, H, gate, up, down_packed, nullptr, K, std::max<int64_t>(K, 1), 0, down_buf, combined_buf, act,
-                     has_gate ? 1 : 0, dtype, scratch, nullptr, 3u, nullptr, static_cast<cudaStream_t>(stream));
+                     has_gate ? 1 : 0, dtype, scratch, nullptr, 3u, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -41,10 +41,24 @@ struct GateUpArgs {
   float* a_out;          // [K][B] fp32
   int* status;           // optional device status word
   const int32_t* K_dev;
-  const int32_t* row_idx;  // optional: row j of this launch is row row_idx[j] of gate/up (gather from the full pools)
+  // gather mode (mask_bits != null): the rows are those of the set mask bits, in ascending
+  // order, taken from full [I,H] pools; every CTA lists the bits itself, CTA 0 also
+  // publishes the list and its length for the down kernel
+  const uint32_t* mask_bits;
+  int32_t* idx_out;
+  int32_t* count_out;
+  int I;
   int K_host;
   int B, H, act, has_gate;
   int nwarps;
+};
+
+// Gather mode of the fused layer step: rows are the set bits of `mask_bits` in the full pools.
+struct GatherSpec {
+  const uint32_t* mask_bits;
+  int32_t* idx;    // [I] out: active neuron ids, ascending
+  int32_t* count;  // out: their number
+  int I;
 };
 
 struct DownArgs {
@@ -95,7 +109,75 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 
+
+constexpr int GATHER_MY_CAP = 512;  // per-CTA share of the active list: ceil(I / grid) + tile <= 512
+
+// Lists the set bits of the mask in ascending order (rank rho = 0..K-1).  Bits are grouped in
+// tiles of TR consecutive ranks; tile t belongs to CTA t % gridDim.x and lands in that CTA's
+// s_my[(t / gridDim.x) * TR + rho % TR].  CTA 0 also writes the whole list and K to global
+// memory.  All threads of the block must call it; returns K.  Ends with a barrier.
+__device__ __forceinline__ int cta_list_active(const uint32_t* __restrict__ bits, int I, int TR, int32_t* s_my,
+                                               int32_t* idx_out, int32_t* count_out) {
+  __shared__ int s_wsum[32];
+  __shared__ int s_total;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
+  const int W = (I + 31) >> 5;
+  const int WPT = (W + blockDim.x - 1) / blockDim.x;
+  uint32_t wv[8];  // W <= 2048 and at least 256 threads: WPT <= 8
+  int cnt = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int w = tid * WPT + k;
+    wv[k] = (k < WPT && w < W) ? __ldcg(bits + w) : 0u;
+    cnt += __popc(wv[k]);
+  }
+  int inc = cnt;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, inc, off);
+    if (lane >= off) inc += v;
+  }
+  if (lane == 31) s_wsum[wid] = inc;
+  __syncthreads();
+  if (wid == 0) {
+    const int v = lane < nw ? s_wsum[lane] : 0;
+    int winc = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, winc, off);
+      if (lane >= off) winc += u;
+    }
+    s_wsum[lane] = winc - v;
+    if (lane == 31) s_total = winc;
+  }
+  __syncthreads();
+  int rho = s_wsum[wid] + inc - cnt;
+  const bool publish = blockIdx.x == 0 && idx_out != nullptr;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    uint32_t b = wv[k];
+    const int w = tid * WPT + k;
+    while (b) {
+      const int n = w * 32 + __ffs(b) - 1;
+      b &= b - 1;
+      if (publish) idx_out[rho] = n;
+      const int tile = rho / TR;
+      if (tile % static_cast<int>(gridDim.x) == static_cast<int>(blockIdx.x)) {
+        const int slot = (tile / static_cast<int>(gridDim.x)) * TR + rho % TR;
+        if (slot < GATHER_MY_CAP) s_my[slot] = n;
+      }
+      ++rho;
+    }
+  }
+  const int K = s_total;
+  if (publish && tid == 0) *count_out = K;
+  __syncthreads();
+  return K;
+}
+
 // Shared-memory layout (dynamic): [0,256) mbarriers | x_s [NB][H] T | bufs [nwarps][nmat][H] T
+// Rank rho (packed row, or rho-th active neuron) belongs to CTA rho % gridDim.x; inside the
+// CTA, warp w takes its local slots w, w + nwarps, ...
 template <typename T, int NB>
 __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
   constexpr int V = DT<T>::V;
@@ -112,24 +194,28 @@ __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
   unsigned char* mybuf = smem + 256 + x_bytes + static_cast<size_t>(warp) * nmat * row_bytes;
   uint64_t* mybar = &bars[warp];
 
-  const int K = p.K_dev ? *p.K_dev : p.K_host;
-  const int base = K / gridDim.x, rem = K % gridDim.x;
-  const int j0 = blockIdx.x * base + min(static_cast<int>(blockIdx.x), rem);
-  const int j1 = j0 + base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
+  __shared__ int32_t s_my[GATHER_MY_CAP];
   const char* gsrc = static_cast<const char*>(p.gate);
   const char* usrc = static_cast<const char*>(p.up);
   T* combined = static_cast<T*>(p.combined);
-  const int ldc = p.has_gate ? 2 * K : K;
+  const bool gather = p.mask_bits != nullptr;
+  const int G = gridDim.x;
 
   if (tid == 0) {
     for (int w = 0; w < NWp; ++w) mbar_init(&bars[w], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  // the list of active rows (gather mode) or K (packed mode); also orders the barrier init
+  const int K = gather ? cta_list_active(p.mask_bits, p.I, 1, s_my, p.idx_out, p.count_out)
+                       : (p.K_dev ? *p.K_dev : p.K_host);
+  if (!gather) __syncthreads();
+  const int ldc = p.has_gate ? 2 * K : K;
+  const int nlocal = K > static_cast<int>(blockIdx.x) ? (K - 1 - static_cast<int>(blockIdx.x)) / G + 1 : 0;
 
-  auto issue = [&](int j) {
+  auto issue = [&](int q) {  // q: local slot; rank = blockIdx.x + G*q
     mbar_expect_tx(mybar, row_bytes * nmat);
-    const size_t off = static_cast<size_t>(p.row_idx ? p.row_idx[j] : j) * row_bytes;
+    const int row = gather ? s_my[q] : static_cast<int>(blockIdx.x) + G * q;
+    const size_t off = static_cast<size_t>(row) * row_bytes;
     if (p.has_gate) bulk_load(mybuf, gsrc + off, row_bytes, mybar);
     bulk_load(mybuf + (p.has_gate ? row_bytes : 0), usrc + off, row_bytes, mybar);
   };
@@ -140,9 +226,9 @@ __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
   for (int bt = 0; bt < nbt; ++bt) {
     const int b0 = bt * NB;
     const int nb = min(NB, p.B - b0);
-    int j = j0 + warp;
-    if (lane == 0 && j < j1) issue(j);  // the first rows stream in while x is staged
-    if (bt > 0) __syncthreads();        // everyone done with the previous x tile
+    int q = warp;
+    if (lane == 0 && q < nlocal) issue(q);  // the first rows stream in while x is staged
+    if (bt > 0) __syncthreads();            // everyone done with the previous x tile
     {
       const uint4* xg = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + static_cast<size_t>(b0) * H);
       uint4* xs4 = reinterpret_cast<uint4*>(x_s);
@@ -150,7 +236,8 @@ __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
     }
     __syncthreads();
 
-    for (; j < j1; j += NWp) {
+    for (; q < nlocal; q += NWp) {
+      const int j = static_cast<int>(blockIdx.x) + G * q;  // rank of this row
       if (!mbar_wait_bounded(mybar, phase)) timed_out = true;
       phase ^= 1u;
       const T* grow = reinterpret_cast<const T*>(mybuf);
@@ -211,9 +298,9 @@ __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
       }
       // the buffer is free again: fetch the next neuron's rows before the reduction
       __syncwarp();
-      if (lane == 0 && j + NWp < j1) {
+      if (lane == 0 && q + NWp < nlocal) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        issue(j + NWp);
+        issue(q + NWp);
       }
       float a_mine = 0.f, u_mine = 0.f;
 #pragma unroll
@@ -285,25 +372,31 @@ __global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
                          static_cast<size_t>(warp) * MMA_TILE_ROWS * row_stride;
   uint64_t* mybar = &bars[warp];
 
-  const int K = p.K_dev ? *p.K_dev : p.K_host;
-  const int ntile_all = (K + TR - 1) / TR;  // tiles are interleaved over the CTAs
+  __shared__ int32_t s_my[GATHER_MY_CAP];
   const char* gsrc = static_cast<const char*>(p.gate);
   const char* usrc = static_cast<const char*>(p.up);
   T* combined = static_cast<T*>(p.combined);
-  const int ldc = p.has_gate ? 2 * K : K;
+  const bool gather = p.mask_bits != nullptr;
+  const int G = gridDim.x;
 
   if (tid == 0) {
     for (int w = 0; w < NWp; ++w) mbar_init(&bars[w], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
+  const int K = gather ? cta_list_active(p.mask_bits, p.I, TR, s_my, p.idx_out, p.count_out)
+                       : (p.K_dev ? *p.K_dev : p.K_host);
+  if (!gather) __syncthreads();
+  const int ldc = p.has_gate ? 2 * K : K;
+  const int ntile_all = (K + TR - 1) / TR;  // tile t belongs to CTA t % G, local slot t / G
+  const int nlocal = ntile_all > static_cast<int>(blockIdx.x) ? (ntile_all - 1 - static_cast<int>(blockIdx.x)) / G + 1 : 0;
 
-  auto issue = [&](int tile) {
-    const int r0 = tile * TR;
+  auto issue = [&](int q) {
+    const int r0 = (static_cast<int>(blockIdx.x) + G * q) * TR;
     const int nr = min(TR, K - r0);
     mbar_expect_tx(mybar, static_cast<uint32_t>(nr) * row_bytes * (p.has_gate ? 2 : 1));
     for (int i = 0; i < nr; ++i) {
-      const size_t off = static_cast<size_t>(p.row_idx ? p.row_idx[r0 + i] : r0 + i) * row_bytes;
+      const int row = gather ? s_my[q * TR + i] : r0 + i;
+      const size_t off = static_cast<size_t>(row) * row_bytes;
       if (p.has_gate) {
         bulk_load(mybuf + static_cast<size_t>(i) * row_stride, gsrc + off, row_bytes, mybar);
         bulk_load(mybuf + static_cast<size_t>(TR + i) * row_stride, usrc + off, row_bytes, mybar);
@@ -319,9 +412,8 @@ __global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
   for (int bt = 0; bt < nbt; ++bt) {
     const int b0 = bt * 8;
     const int nb = min(8, p.B - b0);
-    // tile index of this warp: blockIdx.x + gridDim.x * (warp + NWp * k)
-    int tile = blockIdx.x + gridDim.x * warp;
-    if (lane == 0 && tile < ntile_all) issue(tile);  // first rows stream in while x is staged
+    int q = warp;
+    if (lane == 0 && q < nlocal) issue(q);  // first rows stream in while x is staged
     if (bt > 0) __syncthreads();
     for (int i = tid; i < nb * (H / 8); i += blockDim.x) {
       const int b = i / (H / 8), c = i % (H / 8);
@@ -333,8 +425,8 @@ __global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
     const unsigned char* arow = mybuf + static_cast<size_t>(gq < MMA_TILE_ROWS ? gq : 0) * row_stride + tq * 16;
     const bool x_on = gq < nb;  // batch columns beyond the tile multiply by zero
     const unsigned char* xrow = x_s + static_cast<size_t>(x_on ? gq : 0) * row_stride + tq * 16;
-    for (; tile < ntile_all; tile += gridDim.x * NWp) {
-      const int r0 = tile * TR;
+    for (; q < nlocal; q += NWp) {
+      const int r0 = (static_cast<int>(blockIdx.x) + G * q) * TR;
       const int nr = min(TR, K - r0);
       if (!mbar_wait_bounded(mybar, phase)) timed_out = true;
       phase ^= 1u;
@@ -367,10 +459,9 @@ __global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
       }
       // the buffer is free again: fetch this warp's next tile before the epilogue
       __syncwarp();
-      const int next = tile + gridDim.x * NWp;
-      if (lane == 0 && next < ntile_all) {
+      if (lane == 0 && q + NWp < nlocal) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        issue(next);
+        issue(q + NWp);
       }
       // lane (gq,tq): tile row gq, batch columns 2tq and 2tq+1
       const float s0 = (d0[0] + d1[0]) + (d2[0] + d3[0]);
@@ -416,7 +507,9 @@ __global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
 }
 
 // Grid (nslab, CS), cluster (1, CS, 1): CTA (sx, sy) owns the 256-byte column slab sx and the
-// row range sy of CS.  Thread t: chunk sx*16 + (t & 15), rows lo + (t >> 4) + 32*k.
+// ranks j = sy (mod CS).  Thread t: chunk sx*16 + (t & 15), ranks sy + CS*((t >> 4) + 32*k).
+// In gather mode rank j is row row_idx[j] of the full pool; the index and K are loaded
+// together, so the row loads are two dependent trips away from the kernel start.
 // Reduction order: the two row lanes of a warp, then the 16 warps ascending, then the
 // cluster ranks ascending.
 constexpr int DOWN_THREADS = 512;
@@ -438,8 +531,6 @@ __global__ void __launch_bounds__(DOWN_THREADS, 2) k_down_rows(const DownArgs p)
   const int c = blockIdx.x * 16 + cl;
   const bool c_ok = c < nchunk;
   const int K = p.K_dev ? *p.K_dev : p.K_host;
-  const int lo = static_cast<int>(static_cast<int64_t>(K) * rank / CS);
-  const int hi = static_cast<int>(static_cast<int64_t>(K) * (rank + 1) / CS);
   const T* dcol = static_cast<const T*>(p.down) + (c_ok ? c : 0) * V;
   float* clu0 = cluster.map_shared_rank(clu_s, 0);
 
@@ -451,16 +542,23 @@ __global__ void __launch_bounds__(DOWN_THREADS, 2) k_down_rows(const DownArgs p)
 #pragma unroll
       for (int v = 0; v < V; ++v) acc[b][v] = 0.f;
     if (c_ok) {
-      for (int j = lo + rl; j < hi; j += 32 * DOWN_UNROLL) {
+      const int nrl = K > rank ? (K - 1 - rank) / CS + 1 : 0;  // ranks of this CTA: rank + CS*l, l < nrl
+      for (int l0 = rl; l0 < nrl; l0 += 32 * DOWN_UNROLL) {
         uint4 dv[DOWN_UNROLL];
         float av[DOWN_UNROLL][NB];
+        int rows[DOWN_UNROLL];
 #pragma unroll
         for (int u = 0; u < DOWN_UNROLL; ++u) {
-          const int jj = j + 32 * u;
-          dv[u] = make_uint4(0, 0, 0, 0);
-          if (jj < hi) dv[u] = ld_stream16(dcol + static_cast<size_t>(p.row_idx ? p.row_idx[jj] : jj) * H);
+          const int jj = rank + CS * (l0 + 32 * u);
+          rows[u] = (l0 + 32 * u < nrl) ? (p.row_idx ? p.row_idx[jj] : jj) : -1;
+        }
 #pragma unroll
-          for (int b = 0; b < NB; ++b) av[u][b] = (jj < hi && b < nb) ? p.a[static_cast<size_t>(jj) * p.B + b0 + b] : 0.f;
+        for (int u = 0; u < DOWN_UNROLL; ++u) {
+          const int jj = rank + CS * (l0 + 32 * u);
+          dv[u] = make_uint4(0, 0, 0, 0);
+          if (rows[u] >= 0) dv[u] = ld_stream16(dcol + static_cast<size_t>(rows[u]) * H);
+#pragma unroll
+          for (int b = 0; b < NB; ++b) av[u][b] = (rows[u] >= 0 && b < nb) ? p.a[static_cast<size_t>(jj) * p.B + b0 + b] : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < DOWN_UNROLL; ++u) {
@@ -623,7 +721,7 @@ static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const
 // these kernels; the caller then uses the plain-load kernel.
 // scratch: fp32 a[K][B] at offset 256.  parts: bit 0 = gate/up kernel, bit 1 = down kernel.
 int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
-                    const int32_t* K_dev, int64_t K_host, const int32_t* row_idx, void* out, void* combined, int act,
+                    const int32_t* K_dev, int64_t K_host, const GatherSpec* gs, void* out, void* combined, int act,
                     int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s) {
   const size_t es = dtype_size(dtype);
   const int V = static_cast<int>(16 / es);
@@ -645,7 +743,10 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   a.a_out = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256);
   a.status = status;
   a.K_dev = K_dev;
-  a.row_idx = row_idx;
+  a.mask_bits = gs ? gs->mask_bits : nullptr;
+  a.idx_out = gs ? gs->idx : nullptr;
+  a.count_out = gs ? gs->count : nullptr;
+  a.I = gs ? gs->I : 0;
   a.K_host = static_cast<int>(K_host);
   a.B = static_cast<int>(B);
   a.H = static_cast<int>(H);
@@ -654,13 +755,22 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   a.nwarps = nwarps;
   const size_t smem = 256 + x_bytes + static_cast<size_t>(nwarps) * nmat * row_bytes;
   int grid = num_sms();
-  if (!K_dev) grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, K_host)));
+  if (!K_dev && !gs) grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, K_host)));
+  if (gs) {
+    // the in-kernel listing of the mask handles 8 words per thread and 512 rows per CTA
+    const size_t mma_stride = row_bytes + 64;
+    const size_t mma_fixed = 256 + static_cast<size_t>(std::min<int64_t>(B, 8)) * mma_stride;
+    int min_warps = nwarps;
+    if (es == 2 && mma_fixed + 2 * MMA_TILE_ROWS * mma_stride <= TMA_SMEM_BUDGET)
+      min_warps = std::min<int>(min_warps, static_cast<int>((TMA_SMEM_BUDGET - mma_fixed) / (MMA_TILE_ROWS * mma_stride)));
+    if ((gs->I + 31) / 32 > 8 * 32 * min_warps || (gs->I + grid - 1) / grid + 4 > GATHER_MY_CAP) return STX_ERR_UNSUPPORTED;
+  }
   DownArgs d;
   d.a = a.a_out;
   d.down = down;
   d.out = out;
-  d.K_dev = K_dev;
-  d.row_idx = row_idx;
+  d.K_dev = gs ? gs->count : K_dev;
+  d.row_idx = gs ? gs->idx : nullptr;
   d.K_host = static_cast<int>(K_host);
   d.B = static_cast<int>(B);
   d.H = static_cast<int>(H);

@@ -70,68 +70,12 @@ k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t
   }
 }
 
-// Ascending list of the set bits of a mask (and their count), by one block of 256 threads:
-// thread u owns the words u*WPT .. u*WPT+WPT-1; block-wide exclusive scan of the popcounts.
-struct CompactOut {
-  int32_t* idx;        // [I] neuron ids in ascending order (null: no compaction)
-  int32_t* count;      // number of set bits
-  unsigned* ticket;    // zero on entry, zero on exit (last-block detection)
-};
-
-__device__ __forceinline__ void compact_mask_256(const uint32_t* bits, int I, int32_t* idx, int32_t* count) {
-  __shared__ int s_wsum[8];
-  __shared__ int s_total;
-  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  const int W = (I + 31) >> 5;
-  const int WPT = (W + 255) / 256;
-  int cnt = 0;
-  for (int k = 0; k < WPT; ++k) {
-    const int w = tid * WPT + k;
-    if (w < W) cnt += __popc(__ldcg(bits + w));
-  }
-  int inc = cnt;
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const int v = __shfl_up_sync(0xffffffffu, inc, off);
-    if (lane >= off) inc += v;
-  }
-  if (lane == 31) s_wsum[wid] = inc;
-  __syncthreads();
-  if (tid == 0) {
-    int run = 0;
-    for (int q = 0; q < 8; ++q) {
-      const int v = s_wsum[q];
-      s_wsum[q] = run;
-      run += v;
-    }
-    s_total = run;
-  }
-  __syncthreads();
-  int o = s_wsum[wid] + inc - cnt;
-  for (int k = 0; k < WPT; ++k) {
-    const int w = tid * WPT + k;
-    if (w < W) {
-      uint32_t b = __ldcg(bits + w);
-      while (b) {
-        idx[o++] = w * 32 + __ffs(b) - 1;
-        b &= b - 1;
-      }
-    }
-  }
-  if (tid == 0) *count = s_total;
-}
-
-__global__ void __launch_bounds__(256) k_mask_compact(const uint32_t* bits, int I, int32_t* idx, int32_t* count) {
-  compact_mask_256(bits, I, idx, count);
-}
-
 // One block (256 threads) per mask word: 8 lanes cooperate on one neuron, 32 neurons per
-// block.  Dynamic shared memory: t [B,r] fp32.  With `co.idx` set, the last block to finish
-// also lists the set bits (the active neuron ids in ascending order) for the gather kernels.
+// block.  Dynamic shared memory: t [B,r] fp32.
 template <typename T>
 __global__ void __launch_bounds__(256)
 k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* __restrict__ bits,
-              T* __restrict__ scores_out, int B, int r, int I, float tau, int write_bits, CompactOut co) {
+              T* __restrict__ scores_out, int B, int r, int I, float tau, int write_bits) {
   constexpr int V = DT<T>::V;
   extern __shared__ float t_s[];
   __shared__ uint32_t s_nib[8];
@@ -234,25 +178,12 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
     for (int q = 0; q < 8; ++q) word |= s_nib[q] << (4 * q);
     bits[w] = word;
   }
-  if (write_bits && co.idx) {
-    __shared__ int s_last;
-    if (tid == 0) {
-      __threadfence();
-      s_last = (atomicAdd(co.ticket, 1u) == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      compact_mask_256(bits, I, co.idx, co.count);
-      if (tid == 0) *co.ticket = 0u;
-    }
-  }
 }
 
 template <typename T>
 static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
                           int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
-                          int write_bits, CompactOut co, cudaStream_t s) {
+                          int write_bits, cudaStream_t s) {
   k_pred_t<T><<<static_cast<unsigned>(r), pred_t_threads(static_cast<int>(H), DT<T>::V), 0, s>>>(
       static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B), static_cast<int>(H),
       static_cast<int>(r));
@@ -261,7 +192,7 @@ static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, in
   const size_t smem = static_cast<size_t>(B) * r * sizeof(float);
   k_pred_scores<T><<<static_cast<unsigned>(W), 256, smem, s>>>(
       t_scratch, static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
-      static_cast<int>(r), static_cast<int>(I), tau, write_bits, co);
+      static_cast<int>(r), static_cast<int>(I), tau, write_bits);
   STX_LAUNCH_CHECK("k_pred_scores");
   return STX_OK;
 }
@@ -270,33 +201,26 @@ static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, in
 int mask_from_scores(const void* scores, int64_t B, int64_t I, int dtype, int method, float param,
                      uint32_t* bits_out, void* scratch, cudaStream_t s);
 
-// idx_out / count_out / ticket: optional ascending list of the active neuron ids.
 int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
                  int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch,
-                 int32_t* idx_out, int32_t* count_out, unsigned* ticket, cudaStream_t s) {
+                 cudaStream_t s) {
   float* t_scratch = static_cast<float*>(scratch);
   const int write_bits = method == STX_MASK_THRESHOLD ? 1 : 0;
-  CompactOut co{write_bits ? idx_out : nullptr, count_out, ticket};
   int rc;
   switch (dtype) {
     case STX_F32:
-      rc = launch_predict<float>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, co, s);
+      rc = launch_predict<float>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
       break;
     case STX_F16:
-      rc = launch_predict<__half>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, co, s);
+      rc = launch_predict<__half>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
       break;
     default:
-      rc = launch_predict<__nv_bfloat16>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, co, s);
+      rc = launch_predict<__nv_bfloat16>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
       break;
   }
   if (rc != STX_OK || method == STX_MASK_THRESHOLD) return rc;
   void* sel_scratch = static_cast<char*>(scratch) + align_up(static_cast<size_t>(B) * r * sizeof(float), 256);
-  rc = mask_from_scores(scores_out, B, I, dtype, method, param, bits, sel_scratch, s);
-  if (rc == STX_OK && idx_out) {
-    k_mask_compact<<<1, 256, 0, s>>>(bits, static_cast<int>(I), idx_out, count_out);
-    STX_LAUNCH_CHECK("k_mask_compact");
-  }
-  return rc;
+  return mask_from_scores(scores_out, B, I, dtype, method, param, bits, sel_scratch, s);
 }
 
 }  // namespace stx
@@ -330,8 +254,8 @@ int stx_predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t
     set_error("stx_predict_mask: B*r=%lld exceeds the shared-memory tile (12288 values)", static_cast<long long>(B * r));
     return STX_ERR_TOO_LARGE;
   }
-  return predict_mask(x, B, H, A, r, Bm, I, dtype, method, param, mask_bits_out, scores_out, scratch, nullptr, nullptr,
-                      nullptr, static_cast<cudaStream_t>(stream));
+  return predict_mask(x, B, H, A, r, Bm, I, dtype, method, param, mask_bits_out, scores_out, scratch,
+                      static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
