@@ -123,8 +123,12 @@ int stx_cache_concat_weight(stx_cache_t* c, void** ptr_out, int64_t* rows_out, v
  * the reference tensor [H,K] with strides (1,H).  Zero-copy.  SYNCHRONISES `stream`.   */
 int stx_cache_active_down(stx_cache_t* c, void** ptr_out, int64_t* k_out, void* stream);
 
+/* Brings the packed rows up to date when layer steps ran with lazy row copies (see
+ * stx_layer_set_lazy_cache); the getters above do this themselves.  Asynchronous.       */
+int stx_cache_flush(stx_cache_t* c, void* stream);
+
 /* Device addresses of the packed per-matrix pools ([I,H] capacity, first K rows valid)
- * and of the cache's device-resident K.  No synchronisation.                            */
+ * and of the cache's device-resident K.  No synchronisation (and no flush).             */
 int stx_cache_packed_ptrs(stx_cache_t* c, void** gate_out, void** up_out, void** down_out,
                           const int32_t** k_dev_out);
 
@@ -227,6 +231,11 @@ int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_
 #define STX_STAGE_ALL 31u
 int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B,
                           void* out, void* stream, unsigned stages);
+/* lazy != 0: a layer step advances the cache's index plan but defers the packed-row
+ * copies until a cache getter (or stx_cache_flush) asks for the rows; the step's own MLP
+ * gathers its rows from the full pools and never needs them.  Default: 0 (rows are copied
+ * every step, as WeightCache::update_active_weights does).  Set before capturing a stack. */
+int stx_layer_set_lazy_cache(stx_layer_t* l, int lazy);
 /* Device pointer to the layer's current mask bits (ceil(I/32) words), valid after a step. */
 int stx_layer_mask_bits(stx_layer_t* l, const uint32_t** bits_out);
 

@@ -41,6 +41,7 @@ SIGNATURES = {
     "stx_cache_num_active": (_i32, [_vp, _pi64, _vp]),
     "stx_cache_concat_weight": (_i32, [_vp, _pp, _pi64, _vp]),
     "stx_cache_active_down": (_i32, [_vp, _pp, _pi64, _vp]),
+    "stx_cache_flush": (_i32, [_vp, _vp]),
     "stx_cache_packed_ptrs": (_i32, [_vp, _pp, _pp, _pp, _pp]),
     "stx_cache_active_indices": (_i32, [_vp, _vp, _i64, _pi64, _vp]),
     "stx_cache_last_update_stats": (_i32, [_vp, _pi64, _pi64, _pi64, _vp]),
@@ -57,6 +58,7 @@ SIGNATURES = {
     "stx_layer_destroy": (_i32, [_vp]),
     "stx_layer_step": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "stx_layer_step_stages": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _u32]),
+    "stx_layer_set_lazy_cache": (_i32, [_vp, _i32]),
     "stx_layer_mask_bits": (_i32, [_vp, _pp]),
     "stx_layer_step_host": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "stx_stack_create": (_i32, [_pp, _pp, _i64, _i64]),

@@ -74,7 +74,7 @@ __device__ __forceinline__ Int2 block_excl_scan2(Int2 v, Int2* total, Int2* warp
 __global__ void __launch_bounds__(PLAN_THREADS, 1)
 k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_bits,
              int32_t* __restrict__ active, int32_t* __restrict__ pos_of, int32_t* __restrict__ lists,
-             int32_t* __restrict__ jobs, int32_t* __restrict__ state, int I) {
+             int32_t* __restrict__ jobs, int32_t* __restrict__ state, uint32_t* __restrict__ stale, int lazy, int I) {
   extern __shared__ int32_t sm[];
   __shared__ Int2 s_ws[32];
   __shared__ Int2 s_tot;
@@ -288,13 +288,18 @@ k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_b
     __syncthreads();
   }
 
-  // ---- 4. rewritten slots below the new K, ascending
+  // ---- 4. rewritten slots below the new K, ascending.  Lazy mode only remembers them in
+  //         the cache's stale bitmap; the rows are brought up to date when somebody reads them.
   Int2 jc{0, 0};
   uint32_t dw[2] = {0, 0};
   for (int k = 0; k < WPT; ++k) {
     const int w = t * WPT + k;
     if (w < W) {
       uint32_t d = s_dirty[w];
+      if (lazy) {
+        if (d) stale[w] |= d;
+        d = 0u;
+      }
       const int lo = w * 32;
       if (lo >= Knew) d = 0u;
       else if (Knew - lo < 32) d &= (1u << (Knew - lo)) - 1u;
@@ -337,7 +342,7 @@ k_cache_plan(const uint32_t* __restrict__ new_bits, uint32_t* __restrict__ cur_b
 }
 
 // One warp per (job, matrix): packed[m][pos] = pool[m][active[pos]], 16-byte vectors.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 k_cache_copy_rows(const int32_t* __restrict__ jobs, const int32_t* __restrict__ active,
                   const int32_t* __restrict__ state, const void* pool0, const void* pool1,
                   const void* pool2, void* pk0, void* pk1, void* pk2, int nmat, int vec_per_row, int I) {
@@ -424,7 +429,7 @@ static size_t plan_smem_bytes(int64_t I) {
   return static_cast<size_t>(3 * W + 3 * PLAN_LIST_CAP + PLAN_MFAST) * sizeof(int32_t);
 }
 
-int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
+int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s, bool lazy) {
   static bool attr_set[64] = {};
   int dev = 0;
   STX_CUDA(cudaGetDevice(&dev));
@@ -436,23 +441,69 @@ int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
   // two mask words per thread at most; small index spaces use fewer threads (cheaper barriers)
   const int W = static_cast<int>((c->I + 31) / 32);
   const int threads = W <= 256 ? 256 : (W <= 512 ? 512 : PLAN_THREADS);
-  k_cache_plan<<<1, threads, plan_smem_bytes(c->I), s>>>(bits, c->cur_bits, c->active, c->pos_of,
-                                                             c->lists, c->jobs, c->state,
-                                                             static_cast<int>(c->I));
+  k_cache_plan<<<1, threads, plan_smem_bytes(c->I), s>>>(bits, c->cur_bits, c->active, c->pos_of, c->lists, c->jobs,
+                                                        c->state, c->stale, lazy ? 1 : 0, static_cast<int>(c->I));
   STX_LAUNCH_CHECK("k_cache_plan");
+  if (lazy) c->lazy_used = true;
   return STX_OK;
+}
+
+// Turns the stale bitmap into the job list (slots below K, ascending) and clears it.
+__global__ void __launch_bounds__(1024, 1)
+k_stale_to_jobs(uint32_t* __restrict__ stale, int32_t* __restrict__ jobs, int32_t* __restrict__ state, int I) {
+  __shared__ Int2 s_ws[32];
+  __shared__ Int2 s_tot;
+  const int W = (I + 31) >> 5;
+  const int t = threadIdx.x;
+  const int WPT = (W + blockDim.x - 1) / blockDim.x;
+  const int K = state[ST_K];
+  uint32_t dw[2] = {0, 0};
+  Int2 jc{0, 0};
+  for (int k = 0; k < WPT; ++k) {
+    const int w = t * WPT + k;
+    if (w < W) {
+      uint32_t d = stale[w];
+      stale[w] = 0u;
+      const int lo = w * 32;
+      if (lo >= K) d = 0u;
+      else if (K - lo < 32) d &= (1u << (K - lo)) - 1u;
+      dw[k] = d;
+      jc.x += __popc(d);
+    }
+  }
+  Int2 joff = block_excl_scan2(jc, &s_tot, s_ws);
+  for (int k = 0; k < WPT; ++k) {
+    const int w = t * WPT + k;
+    uint32_t d = dw[k];
+    while (d) {
+      jobs[joff.x++] = w * 32 + __ffs(d) - 1;
+      d &= d - 1;
+    }
+  }
+  if (t == 0) state[ST_NJOBS] = s_tot.x;
+}
+
+// Brings the packed rows up to date after lazy plans.  A cache that has ever been planned
+// lazily (possibly inside a captured graph that is replayed later) is flushed on every call.
+int cache_flush(stx_cache* c, cudaStream_t s) {
+  if (!c->lazy_used) return STX_OK;
+  k_stale_to_jobs<<<1, 1024, 0, s>>>(c->stale, c->jobs, c->state, static_cast<int>(c->I));
+  STX_LAUNCH_CHECK("k_stale_to_jobs");
+  return cache_copy_rows(c, s);
 }
 
 int cache_copy_rows(stx_cache* c, cudaStream_t s) {
   const int nmat = c->has_gate ? 3 : 2;
   const int vec = static_cast<int>(c->row_bytes / 16);
+  // small blocks with few registers: they fit next to the MLP kernels' CTAs when the cache is
+  // maintained on a side stream
   const int grid = num_sms() * 4;
   if (c->has_gate) {
-    k_cache_copy_rows<<<grid, 256, 0, s>>>(c->jobs, c->active, c->state, c->pool_gate, c->pool_up,
+    k_cache_copy_rows<<<grid, 128, 0, s>>>(c->jobs, c->active, c->state, c->pool_gate, c->pool_up,
                                           c->pool_down, c->pk_gate, c->pk_up, c->pk_down, nmat, vec,
                                           static_cast<int>(c->I));
   } else {
-    k_cache_copy_rows<<<grid, 256, 0, s>>>(c->jobs, c->active, c->state, c->pool_up, c->pool_down, nullptr,
+    k_cache_copy_rows<<<grid, 128, 0, s>>>(c->jobs, c->active, c->state, c->pool_up, c->pool_down, nullptr,
                                           c->pk_up, c->pk_down, nullptr, nmat, vec, static_cast<int>(c->I));
   }
   STX_LAUNCH_CHECK("k_cache_copy_rows");
@@ -460,7 +511,9 @@ int cache_copy_rows(stx_cache* c, cudaStream_t s) {
 }
 
 int cache_update_bits(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
-  int rc = cache_plan(c, bits, s);
+  int rc = cache_flush(c, s);  // rows left stale by earlier lazy plans come first
+  if (rc != STX_OK) return rc;
+  rc = cache_plan(c, bits, s, false);
   if (rc != STX_OK) return rc;
   return cache_copy_rows(c, s);
 }
@@ -505,6 +558,7 @@ int stx_cache_destroy(stx_cache_t* c) {
   cudaFree(c->jobs);
   cudaFree(c->cur_bits);
   cudaFree(c->tmp_bits);
+  cudaFree(c->stale);
   cudaFree(c->state);
   if (c->host_state) cudaFreeHost(c->host_state);
   delete c;
@@ -575,6 +629,7 @@ int stx_cache_create(stx_cache_t** out, int64_t I, int64_t H, int dtype, int has
   STX_ALLOC(c->jobs, I * sizeof(int32_t));
   STX_ALLOC(c->cur_bits, W * sizeof(uint32_t));
   STX_ALLOC(c->tmp_bits, W * sizeof(uint32_t));
+  STX_ALLOC(c->stale, W * sizeof(uint32_t));
   STX_ALLOC(c->state, ST_COUNT * sizeof(int32_t));
   if (cudaMallocHost(reinterpret_cast<void**>(&c->host_state), ST_COUNT * sizeof(int32_t)) != cudaSuccess) {
     set_error("stx_cache_create: cudaMallocHost failed");
@@ -606,6 +661,7 @@ int stx_cache_create(stx_cache_t** out, int64_t I, int64_t H, int dtype, int has
     e = cudaGetLastError();
   }
   if (e == cudaSuccess) e = cudaMemsetAsync(c->cur_bits, 0, W * sizeof(uint32_t), s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(c->stale, 0, W * sizeof(uint32_t), s);
   if (e == cudaSuccess) e = cudaMemsetAsync(c->state, 0, ST_COUNT * sizeof(int32_t), s);
   if (e == cudaSuccess) e = cudaMemsetAsync(c->pos_of, 0xff, I * sizeof(int32_t), s);  // -1
   if (e == cudaSuccess) e = cudaMemsetAsync(c->active, 0xff, I * sizeof(int32_t), s);
@@ -683,7 +739,9 @@ int stx_cache_num_active(stx_cache_t* c, int64_t* k_out, void* stream) {
 int stx_cache_concat_weight(stx_cache_t* c, void** ptr_out, int64_t* rows_out, void* stream) {
   STX_CHECK_ARG(c && ptr_out && rows_out, "stx_cache_concat_weight: null argument");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int rc = cache_read_state(c, s);
+  int rc = cache_flush(c, s);
+  if (rc != STX_OK) return rc;
+  rc = cache_read_state(c, s);
   if (rc != STX_OK) return rc;
   rc = state_to_status(c);
   if (rc != STX_OK) return rc;
@@ -712,13 +770,20 @@ int stx_cache_concat_weight(stx_cache_t* c, void** ptr_out, int64_t* rows_out, v
 
 int stx_cache_active_down(stx_cache_t* c, void** ptr_out, int64_t* k_out, void* stream) {
   STX_CHECK_ARG(c && ptr_out && k_out, "stx_cache_active_down: null argument");
-  int rc = cache_read_state(c, static_cast<cudaStream_t>(stream));
+  int rc = cache_flush(c, static_cast<cudaStream_t>(stream));
+  if (rc != STX_OK) return rc;
+  rc = cache_read_state(c, static_cast<cudaStream_t>(stream));
   if (rc != STX_OK) return rc;
   rc = state_to_status(c);
   if (rc != STX_OK) return rc;
   *ptr_out = c->pk_down;
   *k_out = c->host_state[ST_K];
   return STX_OK;
+}
+
+int stx_cache_flush(stx_cache_t* c, void* stream) {
+  STX_CHECK_ARG(c, "stx_cache_flush: null cache");
+  return cache_flush(c, static_cast<cudaStream_t>(stream));
 }
 
 int stx_cache_packed_ptrs(stx_cache_t* c, void** gate_out, void** up_out, void** down_out,

@@ -45,6 +45,8 @@ struct stx_cache {
   int32_t* jobs = nullptr;     // [I] packed positions to rewrite from the pool
   uint32_t* cur_bits = nullptr;  // [W] current mask
   uint32_t* tmp_bits = nullptr;  // [W] staging for byte masks
+  uint32_t* stale = nullptr;     // [W] packed slots whose rows lag behind the index plan (lazy mode)
+  bool lazy_used = false;        // host flag: some plan was enqueued (or captured) in lazy mode
   int32_t* state = nullptr;      // [ST_COUNT]
   int32_t* host_state = nullptr; // pinned mirror for read-backs
 };
@@ -53,7 +55,9 @@ namespace stx {
 // Enqueue plan + row copies for a bit-packed mask already on the device.
 int cache_update_bits(stx_cache* c, const uint32_t* bits, cudaStream_t s);
 // Plan only (index arrays, job list, state); the caller moves the rows.
-int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s);
+// lazy: remember the rewritten slots in `stale` instead of queueing them for cache_copy_rows
+int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s, bool lazy = false);
 int cache_copy_rows(stx_cache* c, cudaStream_t s);
+int cache_flush(stx_cache* c, cudaStream_t s);  // rows of all stale slots (no-op when none are pending)
 int cache_read_state(stx_cache* c, cudaStream_t s);  // syncs; fills host_state
 }  // namespace stx

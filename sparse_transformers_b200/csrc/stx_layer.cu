@@ -31,6 +31,7 @@ struct stx_layer {
   int32_t* idx = nullptr;        // [I] active neuron ids in ascending order (set bits of `bits`)
   int32_t* count = nullptr;      // [0] number of active neurons, [1] last-block ticket of the predictor
   bool gather = true;            // MLP gathers rows from the full pools (needs H*elem >= 512 bytes)
+  bool lazy = false;             // gather mode only: defer the packed-row copies until somebody reads them
   void* scores = nullptr;        // [max_batch, I], only for rules that need whole rows
   void* pred_scratch = nullptr;
   void* mlp_scratch = nullptr;
@@ -159,10 +160,10 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
   }
   if (l->gather) {
     if (stages & STX_STAGE_PLAN) {
-      rc = cache_plan(c, l->bits, cs);
+      rc = cache_plan(c, l->bits, cs, l->lazy);
       if (rc != STX_OK) return rc;
     }
-    if (stages & STX_STAGE_COPY) {
+    if ((stages & STX_STAGE_COPY) && !l->lazy) {
       rc = cache_copy_rows(c, cs);
       if (rc != STX_OK) return rc;
     }
@@ -182,6 +183,12 @@ int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp,
 int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, void* stream) {
   STX_CHECK_ARG(l && x_pred && x_mlp && out, "stx_layer_step: null pointer");
   return stx_layer_step_stages(l, x_pred, x_mlp, B, out, stream, STX_STAGE_ALL);
+}
+
+int stx_layer_set_lazy_cache(stx_layer_t* l, int lazy) {
+  STX_CHECK_ARG(l, "stx_layer_set_lazy_cache: null layer");
+  l->lazy = lazy != 0 && l->gather;
+  return STX_OK;
 }
 
 int stx_layer_mask_bits(stx_layer_t* l, const uint32_t** bits_out) {

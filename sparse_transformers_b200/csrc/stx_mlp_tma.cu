@@ -692,7 +692,8 @@ static int launch_both(const GateUpArgs& g, int grid, size_t smem, const DownArg
       if (fixed + 2 * MMA_TILE_ROWS * stride <= TMA_SMEM_BUDGET) {
         GateUpArgs m = g;
         m.nwarps = static_cast<int>(std::min<size_t>(16, (TMA_SMEM_BUDGET - fixed) / (MMA_TILE_ROWS * stride)));
-        rc = launch_gateup_mma<T>(m, num_sms(), fixed + static_cast<size_t>(m.nwarps) * MMA_TILE_ROWS * stride, s);
+        rc = launch_gateup_mma<T>(m, g.mask_bits ? std::max(1, num_sms() - 1) : num_sms(),
+                                  fixed + static_cast<size_t>(m.nwarps) * MMA_TILE_ROWS * stride, s);
       }
     }
     if (rc == STX_ERR_UNSUPPORTED) rc = launch_gateup<T, NB>(g, grid, smem, s);
@@ -754,7 +755,9 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   a.has_gate = has_gate;
   a.nwarps = nwarps;
   const size_t smem = 256 + x_bytes + static_cast<size_t>(nwarps) * nmat * row_bytes;
-  int grid = num_sms();
+  // gather mode runs next to the cache maintenance of the same layer (side stream): leave one
+  // SM free for its single-block index plan instead of making a persistent CTA wait for it
+  int grid = gs ? std::max(1, num_sms() - 1) : num_sms();
   if (!K_dev && !gs) grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, K_host)));
   if (gs) {
     // the in-kernel listing of the mask handles 8 words per thread and 512 rows per CTA

@@ -35,7 +35,7 @@ class SparseLayer:
     """
 
     def __init__(self, gate, up, down, lora_down, lora_up, *, act="silu", method="threshold", param=0.0,
-                 max_batch=1, has_gate=True, alias_gate_up=False, init_all_active=True):
+                 max_batch=1, has_gate=True, alias_gate_up=False, init_all_active=True, lazy_cache=False):
         _need_cuda(up, down, lora_down, lora_up)
         self.dtype = up.dtype
         self.device = up.device
@@ -61,6 +61,8 @@ class SparseLayer:
             C.check(C.lib.stx_layer_create(ctypes.byref(l), self._cache, self.A.data_ptr(), self.r, self.Bm.data_ptr(),
                                            _METHOD[method], float(param), _ACT[act], self.max_batch))
             self._layer = l
+            if lazy_cache:
+                C.check(C.lib.stx_layer_set_lazy_cache(self._layer, 1))
         if not alias_gate_up:
             self._keep = [self.A, self.Bm]
 
@@ -113,6 +115,29 @@ class SparseLayer:
         out = torch.empty(self.I, dtype=torch.bool, device=self.device)
         C.check(C.lib.stx_mask_bits_to_bytes(p, self.I, out.data_ptr(), _stream()))
         return out
+
+    def _dev_view(self, ptr: int, rows: int) -> torch.Tensor:
+        es = torch.empty(0, dtype=self.dtype).element_size()
+        n = rows * self.H * es
+
+        class _Bytes:
+            __cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+        if n == 0:
+            return torch.empty(0, self.H, dtype=self.dtype, device=self.device)
+        return torch.as_tensor(_Bytes(), device=self.device).view(self.dtype).view(rows, self.H)
+
+    def concat_weight(self) -> torch.Tensor:
+        """WeightCache.get_concat_weight() of this layer's cache: [2K,H] (a view of cache memory)."""
+        p, rows = ctypes.c_void_p(), ctypes.c_int64()
+        C.check(C.lib.stx_cache_concat_weight(self._cache, ctypes.byref(p), ctypes.byref(rows), _stream()))
+        return self._dev_view(p.value, rows.value)
+
+    def active_down_weight(self) -> torch.Tensor:
+        """WeightCache.get_active_down_weight(): [H,K] with strides (1,H) (a view of cache memory)."""
+        p, k = ctypes.c_void_p(), ctypes.c_int64()
+        C.check(C.lib.stx_cache_active_down(self._cache, ctypes.byref(p), ctypes.byref(k), _stream()))
+        return self._dev_view(p.value, k.value).t()
 
     def update_stats(self) -> tuple[int, int, int]:
         a, r, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()

@@ -131,3 +131,34 @@ def test_step_host_equals_device_step():
     od = a.step(x.to(DEV)).cpu()
     assert torch.allclose(od, oh, rtol=1e-5, atol=1e-6)
     assert a.active_indices().tolist() == b.active_indices().tolist()
+
+
+@pytest.mark.parametrize("lazy", [False, True])
+def test_packed_cache_current_after_fused_steps(lazy):
+    """The fused step's MLP gathers from the full pools; the packed cache must still be what
+    WeightCache would hold — immediately (eager) or when it is read (lazy row copies)."""
+    from sparse_transformers_b200 import SparseLayer
+    from sparse_transformers_b200.synth import HiddenStream, WORKLOADS, layer_weights
+    from stxgpu import DEV
+
+    w = WORKLOADS["C2"].scaled(I=2048, H=512, layers=1)
+    gen = torch.Generator().manual_seed(5)
+    gate, up, down, A, Bm = layer_weights(w, gen)
+    layer = SparseLayer(gate.to(DEV), up.to(DEV), down.to(DEV), A.to(DEV), Bm.to(DEV), param=w.tau, lazy_cache=lazy)
+    eager = SparseLayer(gate.to(DEV), up.to(DEV), down.to(DEV), A.to(DEV), Bm.to(DEV), param=w.tau)
+    oc = orc.OracleCache(w.I)
+    oc.update(np.ones(w.I, bool))
+    xs = HiddenStream(w, gen)
+    for t in range(7):
+        x = xs.next().to(DEV)
+        out = layer.step(x)
+        ref = eager.step(x)
+        assert torch.equal(out, ref)  # same kernels, same order: identical bits
+        oc.update(layer.mask().cpu().numpy())
+        if t in (2, 6):  # read the cache after a few steps in a row
+            idx = torch.from_numpy(oc.active.astype(np.int64))
+            assert layer.active_indices().tolist() == oc.active.tolist()
+            cw = layer.concat_weight().cpu()
+            K = len(idx)
+            assert torch.equal(cw[:K], gate[idx]) and torch.equal(cw[K:], up[idx])
+            assert torch.equal(layer.active_down_weight().cpu(), down[:, idx])
