@@ -42,7 +42,7 @@ DTYPE_NAME = {"torch.float32": "f32", "torch.float16": "f16", "torch.bfloat16": 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--workload", default="C2")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
@@ -55,7 +55,7 @@ def parse_args():
 # ------------------------------------------------------------------------------ helpers
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed region runs."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -66,7 +66,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -228,6 +228,7 @@ def workload_config(w, n_gpus):
     return {"workload": w.name, "hidden": w.H, "intermediate": w.I, "predictor_rank": w.r, "layers": w.layers,
             "batch": w.B, "density_per_row": w.density, "activation": w.act, "threshold": round(w.tau, 6),
             "parallelism": "single GPU" if n_gpus == 1 else f"intermediate dim sharded over {n_gpus} GPUs + all-reduce per layer",
+            "cache_rows": "copied every step (eager), on a side branch of the step's graph",
             "l2": "distinct weights per layer: one step touches more bytes than the 126 MB L2"}
 
 
@@ -276,7 +277,7 @@ def run_native(args):
     torch.cuda.synchronize()
 
     n_inst = 8  # steps of the stage-timing pass
-    xs_cpu = HiddenStream(w, torch.Generator().manual_seed(1)).take(2 * (W_steps + K_steps) + n_inst + 8)
+    xs_cpu = HiddenStream(w, torch.Generator().manual_seed(1)).take(3 * (W_steps + K_steps) + n_inst + 16)
     xs_dev = xs_cpu.to(dev)
     cursor = 0
 
@@ -333,6 +334,29 @@ def run_native(args):
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_total = float(e2e_s.item())
 
+    # ---- the same steps with lazy packed-row copies (index plan every step, rows on demand)
+    lazy_value = None
+    if world == 1:
+        for l in layers:
+            l.set_lazy_cache(True)
+        lazy_stack = stb.SparseStack(layers, w.B)
+        for _ in range(W_steps):
+            lazy_stack.step(xs_dev[cursor % len(xs_dev)], out_dev)
+            cursor += 1
+        torch.cuda.synchronize()
+        n_lazy = max(8, K_steps // 4)
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record()
+        for _ in range(n_lazy):
+            lazy_stack.step(xs_dev[cursor % len(xs_dev)], out_dev)
+            cursor += 1
+        l1.record()
+        torch.cuda.synchronize()
+        lazy_value = w.B / (l0.elapsed_time(l1) / n_lazy * 1e-3)
+        lazy_stack.close()
+        for l in layers:
+            l.set_lazy_cache(False)
+
     # ---- stage timing pass (single GPU): the dominant kernel's launches timed alone with
     #      CUDA events on the launching stream, all layers back to back in one graph
     roofline, stages_us, k_mean, dk_mean = None, None, None, None
@@ -347,7 +371,7 @@ def run_native(args):
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
         n_warm = 2
         for i in range(n_inst + n_warm):
-            x = xs_dev[cursor]
+            x = xs_dev[cursor % len(xs_dev)]
             cursor += 1
             for v in xin:  # stage the input in the stacks' own buffers, outside the timed brackets
                 v.copy_(x.contiguous().view(torch.uint8).reshape(-1))
@@ -383,10 +407,10 @@ def run_native(args):
         for s_ in st.values():
             s_.close()
 
+    if world > 1:
+        stack.close()
     if rank != 0:
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
+        _finish_distributed(dist, world)
         return
 
     ms_step = ms_total / K_steps
@@ -401,6 +425,8 @@ def run_native(args):
         "gpu_launches": int(stack.launches_per_step * K_steps),
         "clocks": clocks,
     }
+    if lazy_value is not None:
+        line["value_lazy_cache_rows"] = lazy_value
     if roofline:
         line["roofline"] = roofline
         line["stages_us_per_layer"] = stages_us
@@ -418,9 +444,20 @@ def run_native(args):
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
                                     "sample": f"failed: {type(e).__name__}: {e}"}
     print(json.dumps(line), flush=True)
+    _finish_distributed(dist, world)
+
+
+def _finish_distributed(dist, world):
+    """Leave a multi-rank run: barrier, then exit without destroy_process_group(), which was
+    seen to block after NCCL collectives had been captured in CUDA graphs."""
     if world > 1:
+        import torch
+
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 class _DevBytes:

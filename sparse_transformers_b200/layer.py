@@ -80,6 +80,11 @@ class SparseLayer:
         except Exception:
             pass
 
+    def set_lazy_cache(self, lazy: bool) -> None:
+        """Defer (True) or perform every step (False, default) the packed-row copies of the cache;
+        takes effect for steps enqueued, and stacks captured, afterwards."""
+        C.check(C.lib.stx_layer_set_lazy_cache(self._layer, int(bool(lazy))))
+
     def step(self, x_pred: torch.Tensor, x_mlp: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         x_mlp = x_pred if x_mlp is None else x_mlp
         _need_cuda(x_pred, x_mlp)

@@ -74,6 +74,14 @@ class ShardedStack:
         with torch.cuda.graph(self.graph):
             self._eager()
 
+    def close(self) -> None:
+        """Release the captured graph (it holds NCCL work).  Call before tearing down the process
+        group: destroying a process group whose collectives live in a CUDA graph blocked here."""
+        if getattr(self, "graph", None) is not None:
+            torch.cuda.synchronize()
+            self.graph.reset()
+            self.graph = None
+
     def _eager(self):
         for i, l in enumerate(self.layers):
             l.step(self.x_in, self.x_in, self.out[i])
