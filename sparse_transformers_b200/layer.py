@@ -96,6 +96,15 @@ class SparseLayer:
         C.check(C.lib.stx_layer_step(self._layer, xp.data_ptr(), xm.data_ptr(), B, out.data_ptr(), _stream()))
         return out
 
+    def step_stages(self, stages: int, x_pred: torch.Tensor | None = None, x_mlp: torch.Tensor | None = None,
+                    out: torch.Tensor | None = None, batch: int | None = None) -> None:
+        """Run only the given STAGE_* bits of a step on the current stream (tensors must already be
+        contiguous [B,H]); used to put the cache maintenance on a side stream."""
+        B = batch if batch is not None else (x_pred if x_pred is not None else x_mlp).reshape(-1, self.H).shape[0]
+        C.check(C.lib.stx_layer_step_stages(self._layer, x_pred.data_ptr() if x_pred is not None else None,
+                                            x_mlp.data_ptr() if x_mlp is not None else None, B,
+                                            out.data_ptr() if out is not None else None, _stream(), stages))
+
     def step_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> torch.Tensor:
         """x_host/out_host: CPU tensors [B,H] (pinned for speed); blocks until the result is back."""
         B = x_host.reshape(-1, self.H).shape[0]

@@ -16,6 +16,7 @@ from typing import Sequence
 import torch
 import torch.distributed as dist
 
+from . import _capi as C
 from .layer import SparseLayer
 
 
@@ -60,7 +61,8 @@ class ShardedStack:
         self.B, self.L, self.H, self.dtype, self.device = int(batch), len(layers), l0.H, l0.dtype, l0.device
         self.x_in = torch.zeros(self.B, self.H, dtype=self.dtype, device=self.device)
         self.out = torch.zeros(self.L, self.B, self.H, dtype=self.dtype, device=self.device)
-        self.launches_per_step = 6 * self.L  # 5 kernels of this library + 1 NCCL kernel per layer
+        self.launches_per_step = 7 * self.L  # 6 kernels of this library + 1 NCCL kernel per layer
+        self._side = torch.cuda.Stream(device=self.device)
         # eager warm-up on a side stream (NCCL communicators, function attributes), then capture
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
@@ -83,8 +85,19 @@ class ShardedStack:
             self.graph = None
 
     def _eager(self):
+        # critical path on the current stream: predictor -> sparse MLP -> all-reduce, layer after
+        # layer; each layer's cache maintenance (index plan + row copies) forks onto a side stream
+        # after its predictor and joins at the end of the step
+        main = torch.cuda.current_stream()
+        side = self._side
         for i, l in enumerate(self.layers):
-            l.step(self.x_in, self.x_in, self.out[i])
+            l.local.step_stages(C.STAGE_PREDICT, self.x_in, batch=self.B)
+            side.wait_stream(main)  # the side work needs the mask, nothing later
+            l.local.step_stages(C.STAGE_MLP, None, self.x_in, self.out[i], batch=self.B)
+            with torch.cuda.stream(side):
+                l.local.step_stages(C.STAGE_PLAN | C.STAGE_COPY, batch=self.B)
+            dist.all_reduce(self.out[i], op=dist.ReduceOp.SUM, group=l.group)
+        main.wait_stream(side)
 
     def step(self, x: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:
         if x is not None:
