@@ -140,6 +140,31 @@ __device__ __forceinline__ float apply_act(int act, float x) {
   }
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl() may start while its
+// predecessor on the stream is still running; it must call pdl_wait() before it touches
+// anything the predecessor wrote (or still reads), and may do set-up work before that.
+// pdl_wait() returns at once in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();  // STX_PDL=0 turns programmatic dependent launch off (A/B measurements)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Device status word bits (stx_cache state[STATUS]).
 enum : int {
   DEV_OK = 0,

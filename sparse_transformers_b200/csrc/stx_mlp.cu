@@ -241,6 +241,17 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
                     const int32_t* K_dev, int64_t K_host, const GatherSpec* gs, void* out, void* combined, int act,
                     int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s);
 
+size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K);
+bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate);
+int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, const void* down_packed, int64_t K,
+                    void* out, void* combined, int act, int dtype, void* scratch, int* status, cudaStream_t s);
+
+static size_t decode_scratch_bytes(int64_t B, int64_t H, int64_t K) {
+  // [counter | fp32 accumulator B*H (kept zero) | 256 | fp32 a[K][B]]
+  return 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256) + 256 +
+         align_up(static_cast<size_t>(B) * std::max<int64_t>(K, 1) * sizeof(float), 256);
+}
+
 // STX_MLP_KERNEL=plain forces the plain-load kernel (for A/B measurements); default: the
 // TMA-staged kernel wherever the shape fits it.
 static bool use_tma_kernel() {
@@ -313,9 +324,9 @@ extern "C" {
 
 int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out) {
   STX_CHECK_ARG(bytes_out && B > 0 && H > 0 && K >= 0, "stx_mlp_scratch_bytes: bad argument");
-  // [counter | fp32 accumulator B*H (kept zero) | 256 | fp32 a[K][B]]
-  *bytes_out = 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256) + 256 +
-               align_up(static_cast<size_t>(B) * std::max<int64_t>(K, 1) * sizeof(float), 256);
+  // decode kernels' regions, then (row blocks of 64 and more) the tensor-core path's
+  // activation matrix and transposed down weight
+  *bytes_out = decode_scratch_bytes(B, H, K) + (B >= 64 ? prefill_scratch_bytes(B, H, K) : 0);
   return STX_OK;
 }
 
@@ -335,6 +346,12 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
   const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(concat_w) |
                        reinterpret_cast<uintptr_t>(down_packed) | reinterpret_cast<uintptr_t>(scratch);
   STX_CHECK_ARG((al & 15) == 0, "stx_sparse_mlp_forward: x, concat_w, down_packed and scratch must be 16-byte aligned");
+  if (prefill_wanted(B, H, K, dtype, has_gate)) {
+    // hundreds of rows: the gathered weights form a dense contraction -> tcgen05 GEMMs
+    return prefill_forward(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, dtype,
+                           static_cast<char*>(scratch) + decode_scratch_bytes(B, H, K), nullptr,
+                           static_cast<cudaStream_t>(stream));
+  }
   const char* cw = static_cast<const char*>(concat_w);
   const void* gate = has_gate ? cw : nullptr;
   const void* up = has_gate ? cw + static_cast<size_t>(K) * H * es : cw;

@@ -205,6 +205,8 @@ __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
     for (int w = 0; w < NWp; ++w) mbar_init(&bars[w], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  pdl_wait();  // everything above is set-up; from here on the predecessor's results are read
+  pdl_launch_dependents();
   // the list of active rows (gather mode) or K (packed mode); also orders the barrier init
   const int K = gather ? cta_list_active(p.mask_bits, p.I, 1, s_my, p.idx_out, p.count_out)
                        : (p.K_dev ? *p.K_dev : p.K_host);
@@ -383,6 +385,8 @@ __global__ void __launch_bounds__(512, 1) k_gateup_mma(const GateUpArgs p) {
     for (int w = 0; w < NWp; ++w) mbar_init(&bars[w], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  pdl_wait();
+  pdl_launch_dependents();
   const int K = gather ? cta_list_active(p.mask_bits, p.I, TR, s_my, p.idx_out, p.count_out)
                        : (p.K_dev ? *p.K_dev : p.K_host);
   if (!gather) __syncthreads();
@@ -530,6 +534,8 @@ __global__ void __launch_bounds__(DOWN_THREADS, 2) k_down_rows(const DownArgs p)
   const int H = p.H, nchunk = H / V;
   const int c = blockIdx.x * 16 + cl;
   const bool c_ok = c < nchunk;
+  pdl_wait();
+  pdl_launch_dependents();
   const int K = p.K_dev ? *p.K_dev : p.K_host;
   const T* dcol = static_cast<const T*>(p.down) + (c_ok ? c : 0) * V;
   float* clu0 = cluster.map_shared_rank(clu_s, 0);
@@ -614,8 +620,7 @@ static int launch_gateup(const GateUpArgs& a, int grid, size_t smem, cudaStream_
                                   static_cast<int>(TMA_SMEM_BUDGET + 4096)));
     attr_set[dev] = true;
   }
-  k_gateup_tma<T, NB><<<grid, a.nwarps * 32, smem, s>>>(a);
-  STX_LAUNCH_CHECK("k_gateup_tma");
+  STX_CUDA(launch_pdl(k_gateup_tma<T, NB>, dim3(grid), dim3(a.nwarps * 32), smem, s, a));
   return STX_OK;
 }
 
@@ -629,8 +634,7 @@ static int launch_gateup_mma(const GateUpArgs& a, int grid, size_t smem, cudaStr
                                   static_cast<int>(TMA_SMEM_BUDGET + 4096)));
     attr_set[dev] = true;
   }
-  k_gateup_mma<T><<<grid, a.nwarps * 32, smem, s>>>(a);
-  STX_LAUNCH_CHECK("k_gateup_mma");
+  STX_CUDA(launch_pdl(k_gateup_mma<T>, dim3(grid), dim3(a.nwarps * 32), smem, s, a));
   return STX_OK;
 }
 template <>
@@ -670,13 +674,15 @@ static int launch_down(const DownArgs& d, cudaStream_t s) {
   cfg.blockDim = dim3(DOWN_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = cs;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   STX_CUDA(cudaLaunchKernelEx(&cfg, k_down_rows<T, NB>, d));
   return STX_OK;
 }

@@ -35,6 +35,8 @@ k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
   const int k = blockIdx.x;
   const int nchunk = H / V;
+  pdl_wait();
+  pdl_launch_dependents();
   const T* arow = A + static_cast<size_t>(k) * H;
   for (int b0 = 0; b0 < B; b0 += PRED_BT) {
     float acc[PRED_BT];
@@ -88,7 +90,7 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
   const int nchunk = (r + V - 1) / V;
   const T* brow = Bm + static_cast<size_t>(i_ok ? i : 0) * r;
 
-  // weights first (independent of t), then the t tile
+  // weights first (they do not depend on the previous kernel), then the t tile
   constexpr int MAXC = 4;  // chunks held in registers per lane: r <= 8 * MAXC * V on the fast path
   float wv[MAXC][V];
   const bool in_regs = nchunk <= 8 * MAXC;
@@ -108,6 +110,8 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
       }
     }
   }
+  pdl_wait();
+  pdl_launch_dependents();
   for (int k = tid; k < B * r; k += blockDim.x) t_s[k] = t[k];
   __syncthreads();
 
@@ -184,16 +188,15 @@ template <typename T>
 static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
                           int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
                           int write_bits, cudaStream_t s) {
-  k_pred_t<T><<<static_cast<unsigned>(r), pred_t_threads(static_cast<int>(H), DT<T>::V), 0, s>>>(
-      static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B), static_cast<int>(H),
-      static_cast<int>(r));
-  STX_LAUNCH_CHECK("k_pred_t");
+  STX_CUDA(launch_pdl(k_pred_t<T>, dim3(static_cast<unsigned>(r)), dim3(pred_t_threads(static_cast<int>(H), DT<T>::V)), 0,
+                      s, static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B),
+                      static_cast<int>(H), static_cast<int>(r)));
   const int64_t W = (I + 31) / 32;
   const size_t smem = static_cast<size_t>(B) * r * sizeof(float);
-  k_pred_scores<T><<<static_cast<unsigned>(W), 256, smem, s>>>(
-      t_scratch, static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
-      static_cast<int>(r), static_cast<int>(I), tau, write_bits);
-  STX_LAUNCH_CHECK("k_pred_scores");
+  STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W)), dim3(256), smem, s, t_scratch,
+                      static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
+                      static_cast<int>(r), static_cast<int>(I), tau, write_bits));
+  
   return STX_OK;
 }
 
