@@ -465,10 +465,77 @@ class _DevBytes:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
 
+def run_prefill(args):
+    """C4: the op-level prefill path (rows x packed active weights -> tcgen05 GEMMs) over a sweep
+    of active fractions; prints one JSON line with the tensor roofline at K = I."""
+    import ctypes
+
+    import torch
+
+    from sparse_transformers_b200 import _capi as C
+    from sparse_transformers_b200.synth import WORKLOADS
+
+    w = WORKLOADS["C4"]
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    T, H, I = w.B, w.H, w.I
+    x = torch.randn(T, H, generator=gen, device=dev).to(w.dtype)
+    cw_full = (torch.randn(2 * I, H, generator=gen, device=dev) * w.wstd).to(w.dtype)
+    dp_full = (torch.randn(I, H, generator=gen, device=dev) * w.wstd).to(w.dtype)
+    out = torch.empty(T, H, dtype=w.dtype, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        peak_src = "measured (MEASURED_PEAKS.json cuBLAS bf16 burst)"
+    except Exception:
+        peak, peak_src = 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+    sweep = {}
+    for frac in (0.10, 0.25, 0.50, 1.00):
+        K = int(I * frac)
+        cw = torch.cat([cw_full[:K], cw_full[I:I + K]]).contiguous()
+        dp = dp_full[:K].contiguous()
+        comb = torch.empty(T, 2 * K, dtype=w.dtype, device=dev)
+        n = ctypes.c_size_t()
+        C.check(C.lib.stx_mlp_scratch_bytes(T, H, K, ctypes.byref(n)))
+        scratch = torch.zeros(n.value, dtype=torch.uint8, device=dev)
+
+        def call():
+            C.check(C.lib.stx_sparse_mlp_forward(x.data_ptr(), T, H, cw.data_ptr(), dp.data_ptr(), K, out.data_ptr(),
+                                                 comb.data_ptr(), C.ACT_RELU, 1, C.F16, scratch.data_ptr(), stream))
+        for _ in range(max(3, args.warmup)):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = max(4, min(args.steps, 32))
+        e0.record()
+        for _ in range(steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        sweep[f"{frac:.2f}"] = {"K": K, "ms": ms, "tflops": 6.0 * T * H * K / (ms * 1e-3) / 1e12,
+                                "rows_per_s": T / (ms * 1e-3)}
+        del cw, dp, comb, scratch
+    top = sweep["1.00"]
+    line = {"metric": "sparse_mlp_prefill_tflops", "value": top["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": max(4, min(args.steps, 32)), "warmup": max(3, args.warmup), "ms_per_step": top["ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": w.name, "rows": T, "hidden": H, "intermediate": I, "activation": "relu",
+                       "l2": "x (64 MB) + packed weights (270 MB at K = I) exceed the 126 MB L2"},
+            "roofline": {"kernel": "k_umma_gemm", "bound": "tensor", "achieved": top["tflops"], "peak": peak,
+                         "unit": "TFLOP/s", "frac": top["tflops"] / peak, "peak_source": peak_src, "traffic": None,
+                         "flops_per_step": 6.0 * T * H * I},
+            "k_sweep": sweep, "gpu_launches": 3 * max(4, min(args.steps, 32))}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "C4":
+        run_prefill(args)
     else:
         run_native(args)
 

@@ -51,6 +51,8 @@ WORKLOADS = {
     "C2": Workload("C2-llama3b-mlp-stack-fp16", H=3072, I=8192, r=64, B=1, dtype=torch.float16, density=0.20, layers=28, steps=128),
     # Mistral-7B-shaped 32-layer stack, bf16, 8 streams, union of masks ~40-60 %
     "C3": Workload("C3-mistral7b-mlp-stack-bf16-b8", H=4096, I=14336, r=128, B=8, dtype=torch.bfloat16, density=0.15, layers=32, steps=256, alpha=0.7),
+    # ReluLLaMA-7B-shaped sparse MLP on the prefill path: 4 x 2048 rows, ReLU gated, fp16
+    "C4": Workload("C4-relullama7b-prefill-fp16", H=4096, I=11008, r=128, B=8192, dtype=torch.float16, density=0.10, layers=1, steps=16, act="relu"),
     # same shapes, 64 streams, intermediate dimension sharded over the GPUs
     "C5": Workload("C5-mistral7b-mlp-stack-bf16-b64-sharded", H=4096, I=14336, r=128, B=64, dtype=torch.bfloat16, density=0.15, layers=32, steps=512, alpha=0.7),
 }
