@@ -8,7 +8,9 @@
 //            (Wd: the packed down rows, transposed once per call to [H, K8] so that both
 //             operands of both GEMMs are K-major)
 //
-// One kernel, k_umma_gemm<T, MODE>: 128 x 128 output tile per CTA, 64-wide k blocks.
+// One kernel, k_umma_gemm<T, MODE, MH>: per CTA MH (1 or 2) row halves of 128 and two 128-wide
+// B tiles (MODE 0: gate and up rows of the same 128 neurons; MODE 1: 256 output columns), so a
+// 64-wide k block of 64 KB feeds eight 128x128x16 MMAs; 64-wide k blocks.
 //   warp 0      producer: TMA tiled loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the A
 //               tile and one (MODE 1) or two (MODE 0: gate and up rows) B tiles into a ring of
 //               shared-memory stages, completion on mbarriers
@@ -135,14 +137,13 @@ __device__ __forceinline__ void pf_store_row(T* dst, const float* v, int n) {
 
 // Dynamic shared memory (1024-byte aligned): stages x (A tile | B tile [| second B tile]);
 // then full[stages], empty[stages], accum barrier, TMEM base address.
-template <typename T, int MODE>
+template <typename T, int MODE, int MH>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PfArgs p) {
   extern __shared__ unsigned char pf_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pf_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  constexpr int NB_TILES = MODE == 0 ? 2 : 1;
-  constexpr uint32_t STAGE_BYTES = (1 + NB_TILES) * PF_TILE_BYTES;
-  constexpr uint32_t TMEM_COLS = MODE == 0 ? 256 : 128;
+  constexpr uint32_t STAGE_BYTES = (MH + 2) * PF_TILE_BYTES;   // MH A tiles, 2 B tiles
+  constexpr uint32_t TMEM_COLS = MH * 2 * PF_BN;               // accumulator (mh, nt) at column (2*mh + nt) * 128
   const int S = p.stages;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(S) * STAGE_BYTES);
   uint64_t* empty = full + S;
@@ -150,7 +151,7 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * PF_BN, m0 = blockIdx.y * PF_BM;
+  const int n0 = blockIdx.x * (MODE == 0 ? PF_BN : 2 * PF_BN), m0 = blockIdx.y * (MH * PF_BM);
   const int nkb = (p.Kd + PF_BK - 1) / PF_BK;
 
   if (threadIdx.x == 0) {
@@ -180,9 +181,10 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (kb >= S && !pf_wait(&empty[s], ((kb / S) - 1) & 1)) timed_out = true;
         unsigned char* st = smem + static_cast<size_t>(s) * STAGE_BYTES;
         pf_expect_tx(&full[s], STAGE_BYTES);
-        pf_tma_2d(st, &tmA, kb * PF_BK, m0, &full[s]);
-        pf_tma_2d(st + PF_TILE_BYTES, &tmB, kb * PF_BK, n0, &full[s]);
-        if (MODE == 0) pf_tma_2d(st + 2 * PF_TILE_BYTES, &tmB, kb * PF_BK, p.up_off + n0, &full[s]);
+#pragma unroll
+        for (int mh = 0; mh < MH; ++mh) pf_tma_2d(st + mh * PF_TILE_BYTES, &tmA, kb * PF_BK, m0 + mh * PF_BM, &full[s]);
+        pf_tma_2d(st + MH * PF_TILE_BYTES, &tmB, kb * PF_BK, n0, &full[s]);
+        pf_tma_2d(st + (MH + 1) * PF_TILE_BYTES, &tmB, kb * PF_BK, MODE == 0 ? p.up_off + n0 : n0 + PF_BN, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -197,14 +199,17 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!pf_wait(&full[s], (kb / S) & 1)) timed_out = true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned char* st = smem + static_cast<size_t>(s) * STAGE_BYTES;
-        const uint64_t da = pf_smem_desc(st), db0 = pf_smem_desc(st + PF_TILE_BYTES);
-        const uint64_t db1 = pf_smem_desc(st + 2 * PF_TILE_BYTES);
+        const uint64_t db0 = pf_smem_desc(st + MH * PF_TILE_BYTES), db1 = pf_smem_desc(st + (MH + 1) * PF_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < PF_BK / 16; ++kk) {
           const uint32_t acc = (kb | kk) != 0;
           const uint64_t adv = static_cast<uint64_t>(kk * 32 >> 4);  // 16 elements = 32 bytes along k
-          pf_mma(tmem_base, da + adv, db0 + adv, idesc, acc);
-          if (MODE == 0) pf_mma(tmem_base + PF_BN, da + adv, db1 + adv, idesc, acc);
+#pragma unroll
+          for (int mh = 0; mh < MH; ++mh) {
+            const uint64_t da = pf_smem_desc(st + mh * PF_TILE_BYTES) + adv;
+            pf_mma(tmem_base + (2 * mh) * PF_BN, da, db0 + adv, idesc, acc);
+            pf_mma(tmem_base + (2 * mh + 1) * PF_BN, da, db1 + adv, idesc, acc);
+          }
         }
         pf_commit(&empty[s]);  // arrives when the MMAs that read this stage are done
       }
@@ -213,31 +218,41 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..5
     const int lg = warp & 3;                    // TMEM lane group this warp may read
-    const int row = m0 + lg * 32 + lane;
     if (!pf_wait(accum, 0)) timed_out = true;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lg * 32) << 16);
     T* out = static_cast<T*>(p.a_out);
     T* comb = static_cast<T*>(p.combined);
-    for (int c = 0; c < PF_BN; c += 32) {
-      float g[32];
-      pf_ld32(taddr + c, g);
-      const int col = n0 + c;
-      const int n = min(32, p.N - col);
+#pragma unroll 1
+    for (int mh = 0; mh < MH; ++mh) {
+      const int row = m0 + mh * PF_BM + lg * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + (2 * mh) * PF_BN;
       if (MODE == 0) {
-        float u[32];
-        pf_ld32(taddr + PF_BN + c, u);
+#pragma unroll 1
+        for (int c = 0; c < PF_BN; c += 32) {
+          float g[32], u[32];
+          pf_ld32(taddr + c, g);
+          pf_ld32(taddr + PF_BN + c, u);
+          const int col = n0 + c;
+          const int n = min(32, p.N - col);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) g[e] = apply_act(p.act, g[e]) * u[e];
-        if (row < p.M && n > 0) {
-          pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
-          if (comb) {
-            pf_store_row<T>(comb + static_cast<size_t>(row) * (2 * p.N) + col, g, n);
-            pf_store_row<T>(comb + static_cast<size_t>(row) * (2 * p.N) + p.N + col, u, n);
+          for (int e = 0; e < 32; ++e) g[e] = apply_act(p.act, g[e]) * u[e];
+          if (row < p.M && n > 0) {
+            pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
+            if (comb) {
+              pf_store_row<T>(comb + static_cast<size_t>(row) * (2 * p.N) + col, g, n);
+              pf_store_row<T>(comb + static_cast<size_t>(row) * (2 * p.N) + p.N + col, u, n);
+            }
           }
         }
-      } else if (row < p.M && n > 0) {
-        pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 2 * PF_BN; c += 32) {
+          float g[32];
+          pf_ld32(taddr + c, g);
+          const int col = n0 + c;
+          const int n = min(32, p.N - col);
+          if (row < p.M && n > 0) pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
+        }
       }
     }
   }
@@ -306,21 +321,29 @@ static int make_map(CUtensorMap* m, const void* base, int dtype, int64_t rows, i
   return STX_OK;
 }
 
-template <typename T, int MODE>
-static int launch_umma(const CUtensorMap& a, const CUtensorMap& b, const PfArgs& p, cudaStream_t s) {
-  constexpr uint32_t stage_bytes = (MODE == 0 ? 3 : 2) * PF_TILE_BYTES;
+template <typename T, int MODE, int MH>
+static int launch_umma_mh(const CUtensorMap& a, const CUtensorMap& b, PfArgs p, cudaStream_t s) {
+  constexpr uint32_t stage_bytes = (MH + 2) * PF_TILE_BYTES;
+  p.stages = MH == 2 ? 3 : 4;
   const size_t smem = 1024 + static_cast<size_t>(p.stages) * stage_bytes + (2 * p.stages + 1) * sizeof(uint64_t) + 16;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    STX_CUDA(cudaFuncSetAttribute(k_umma_gemm<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    STX_CUDA(cudaFuncSetAttribute(k_umma_gemm<T, MODE, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr_set[dev] = true;
   }
-  dim3 grid((p.N + PF_BN - 1) / PF_BN, (p.M + PF_BM - 1) / PF_BM);
-  k_umma_gemm<T, MODE><<<grid, PF_THREADS, smem, s>>>(a, b, p);
+  const int bn = MODE == 0 ? PF_BN : 2 * PF_BN, bm = MH * PF_BM;
+  dim3 grid((p.N + bn - 1) / bn, (p.M + bm - 1) / bm);
+  k_umma_gemm<T, MODE, MH><<<grid, PF_THREADS, smem, s>>>(a, b, p);
   STX_LAUNCH_CHECK("k_umma_gemm");
   return STX_OK;
+}
+
+template <typename T, int MODE>
+static int launch_umma(const CUtensorMap& a, const CUtensorMap& b, const PfArgs& p, cudaStream_t s) {
+  // one row half for small row counts, two (a 256-row CTA tile) otherwise
+  return p.M > PF_BM ? launch_umma_mh<T, MODE, 2>(a, b, p, s) : launch_umma_mh<T, MODE, 1>(a, b, p, s);
 }
 
 size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K) {
