@@ -151,7 +151,10 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * (MODE == 0 ? PF_BN : 2 * PF_BN), m0 = blockIdx.y * (MH * PF_BM);
+  // MODE 0: row tiles vary fastest, so CTAs in flight share weight tiles and x (which fits L2)
+  // is the re-read operand; MODE 1: column tiles vary fastest (the transposed down weight fits L2)
+  const int n_idx = MODE == 0 ? blockIdx.y : blockIdx.x, m_idx = MODE == 0 ? blockIdx.x : blockIdx.y;
+  const int n0 = n_idx * (MODE == 0 ? PF_BN : 2 * PF_BN), m0 = m_idx * (MH * PF_BM);
   const int nkb = (p.Kd + PF_BK - 1) / PF_BK;
 
   if (threadIdx.x == 0) {
@@ -335,6 +338,7 @@ static int launch_umma_mh(const CUtensorMap& a, const CUtensorMap& b, PfArgs p, 
   }
   const int bn = MODE == 0 ? PF_BN : 2 * PF_BN, bm = MH * PF_BM;
   dim3 grid((p.N + bn - 1) / bn, (p.M + bm - 1) / bm);
+  if (MODE == 0) grid = dim3(grid.y, grid.x);
   k_umma_gemm<T, MODE, MH><<<grid, PF_THREADS, smem, s>>>(a, b, p);
   STX_LAUNCH_CHECK("k_umma_gemm");
   return STX_OK;
