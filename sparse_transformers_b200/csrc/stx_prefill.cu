@@ -240,7 +240,7 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
           for (int e = 0; e < 32; ++e) g[e] = apply_act(p.act, g[e]) * u[e];
           if (row < p.M && n > 0) {
-            pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
+            if (out) pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
             if (comb) {
               pf_store_row<T>(comb + static_cast<size_t>(row) * (2 * p.N) + col, g, n);
               pf_store_row<T>(comb + static_cast<size_t>(row) * (2 * p.N) + p.N + col, u, n);
@@ -383,10 +383,13 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
                                                  static_cast<int>(K), static_cast<int>(H), static_cast<int>(K8));
     STX_LAUNCH_CHECK("k_pf_transpose");
   }
+  // the activations are GEMM 2's A operand: read them straight from combined_buf[:, :K] when its
+  // row stride is TMA-compatible (a multiple of 16 bytes), else from the scratch copy
+  const bool a_in_combined = combined != nullptr && (K % 4) == 0 && (reinterpret_cast<uintptr_t>(combined) & 15) == 0;
   CUtensorMap mx, mw, ma, md;
   int rc = make_map(&mx, x, dtype, B, H, H);
   if (rc == STX_OK) rc = make_map(&mw, concat, dtype, 2 * K, H, H);
-  if (rc == STX_OK) rc = make_map(&ma, a_scr, dtype, B, K, K8);
+  if (rc == STX_OK) rc = a_in_combined ? make_map(&ma, combined, dtype, B, K, 2 * K) : make_map(&ma, a_scr, dtype, B, K, K8);
   if (rc == STX_OK) rc = make_map(&md, dt_scr, dtype, H, K, K8);
   if (rc != STX_OK) return rc;
   PfArgs g1{};
@@ -395,7 +398,7 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
   g1.Kd = static_cast<int>(H);
   g1.up_off = static_cast<int>(K);
   g1.stages = 4;
-  g1.a_out = a_scr;
+  g1.a_out = a_in_combined ? nullptr : a_scr;
   g1.ld_out = static_cast<int>(K8);
   g1.combined = combined;
   g1.act = act;
