@@ -111,10 +111,10 @@ def measured_peak_gbs():
         return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
-def traffic_ratio():
+def traffic_ratio(kernel: str):
     """DRAM bytes / algorithmic bytes of the MLP kernel from the committed ncu capture."""
     try:
-        with open(os.path.join(ROOT, "profiles", "k_gateup_tma_traffic.json")) as f:
+        with open(os.path.join(ROOT, "profiles", f"{kernel}_traffic.json")) as f:
             return float(json.load(f)["dram_over_algorithmic"])
     except Exception:
         return None
@@ -361,11 +361,19 @@ def run_native(args):
     #      CUDA events on the launching stream, all layers back to back in one graph
     roofline, stages_us, k_mean, dk_mean = None, None, None, None
     if world == 1:
-        names = ("predict", "plan", "copy", "gateup", "down")
-        st = {n: stb.SparseStack(layers, w.B, stages=b) for n, b in
-              zip(names, (C.STAGE_PREDICT, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_MLP_GATEUP, C.STAGE_MLP_DOWN))}
+        # one row under the threshold rule: [t = A x] [scores + mask + gather + MLP] [sum of partials];
+        # otherwise: [predictor] [gate/up] [down]
+        fused = layers[0].single_row_fused(w.B)
+        if fused:
+            names = ("predict_t", "plan", "copy", "mlp_b1", "reduce")
+            bits = (C.STAGE_PREDICT_T, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_PREDICT_MASK | C.STAGE_MLP_GATEUP,
+                    C.STAGE_PREDICT_MASK | C.STAGE_MLP_DOWN)
+        else:
+            names = ("predict", "plan", "copy", "gateup", "down")
+            bits = (C.STAGE_PREDICT, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_MLP_GATEUP, C.STAGE_MLP_DOWN)
+        st = {n: stb.SparseStack(layers, w.B, stages=b) for n, b in zip(names, bits)}
         nbytes = w.B * w.H * w.dtype.itemsize
-        xin = [torch.as_tensor(_DevBytes(st[n].buffers()[0], nbytes), device=dev) for n in ("predict", "gateup")]
+        xin = [torch.as_tensor(_DevBytes(st[n].buffers()[0], nbytes), device=dev) for n in (names[0], names[3])]
         acc = dict.fromkeys(names, 0.0)
         ks, dks = [], []
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
@@ -392,18 +400,26 @@ def run_native(args):
         k_mean, dk_mean = statistics.mean(ks), statistics.mean(dks)
         peak, peak_src = measured_peak_gbs()
         es = w.dtype.itemsize
-        alg = es * (2 if w.has_gate else 1) * k_mean * w.H + es * w.B * w.H + 4 * w.B * k_mean      # gate/up rows + x + a
-        alg_down = es * k_mean * w.H + 4 * w.B * k_mean + es * w.B * w.H                            # down rows + a + out
-        achieved = alg / (stages_us["gateup"] * 1e-6) / 1e9
-        ratio = traffic_ratio()
-        roofline = {"kernel": "k_gateup_tma", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        if fused:
+            # k_mlp_b1: active gate/up/down rows + the predictor's up matrix + x + t + mask bytes.  The
+            # per-CTA partial vectors it writes are an artefact of the implementation, not counted.
+            top, second, k1, k2 = "mlp_b1", "reduce", "k_mlp_b1", "k_partial_reduce"
+            alg = (es * (3 if w.has_gate else 2) * k_mean * w.H + es * w.I * w.r + es * w.H + 4 * w.r + w.I / 8)
+            alg2 = 4 * (torch.cuda.get_device_properties(dev).multi_processor_count - 1) * w.H + es * w.H
+        else:
+            top, second, k1, k2 = "gateup", "down", ("k_gateup_mma" if w.B >= 4 else "k_gateup_tma"), "k_down_rows"
+            alg = es * (2 if w.has_gate else 1) * k_mean * w.H + es * w.B * w.H + 4 * w.B * k_mean  # gate/up rows + x + a
+            alg2 = es * k_mean * w.H + 4 * w.B * k_mean + es * w.B * w.H                            # down rows + a + out
+        achieved = alg / (stages_us[top] * 1e-6) / 1e9
+        ratio = traffic_ratio(k1)
+        roofline = {"kernel": k1, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "peak_source": peak_src, "traffic": (ratio * alg if ratio else None),
-                    "algorithmic_bytes_per_launch": alg, "us_per_launch": stages_us["gateup"],
+                    "algorithmic_bytes_per_launch": alg, "us_per_launch": stages_us[top],
                     "launches_timed": n_inst * w.layers,
-                    "second_kernel": {"kernel": "k_down_slab", "algorithmic_bytes_per_launch": alg_down,
-                                      "us_per_launch": stages_us["down"],
-                                      "achieved": alg_down / (stages_us["down"] * 1e-6) / 1e9,
-                                      "frac": alg_down / (stages_us["down"] * 1e-6) / 1e9 / peak}}
+                    "second_kernel": {"kernel": k2, "algorithmic_bytes_per_launch": alg2,
+                                      "us_per_launch": stages_us[second],
+                                      "achieved": alg2 / (stages_us[second] * 1e-6) / 1e9,
+                                      "frac": alg2 / (stages_us[second] * 1e-6) / 1e9 / peak}}
         for s_ in st.values():
             s_.close()
 

@@ -223,14 +223,19 @@ int stx_layer_destroy(stx_layer_t* l);
 int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B,
                    void* out, void* stream);
 /* The same step restricted to some of its stages (bit mask); used to time stages apart.
- * Stages that are skipped leave their outputs as the previous call left them.          */
-#define STX_STAGE_PREDICT 1u /* predictor -> mask bits                    */
+ * Stages that are skipped leave their outputs as the previous call left them.  A single
+ * row (B == 1) under the threshold rule runs PREDICT_MASK and MLP_GATEUP as ONE kernel
+ * when both bits are set (the mask never leaves the chip before the rows are fetched);
+ * MLP_DOWN is then the deterministic sum of that kernel's per-CTA partial outputs.      */
+#define STX_STAGE_PREDICT_T 1u     /* predictor, first half: t = A x            */
+#define STX_STAGE_PREDICT_MASK 32u /* predictor, second half: scores -> mask bits */
+#define STX_STAGE_PREDICT 33u      /* both                                      */
 #define STX_STAGE_PLAN 2u    /* mask diff -> cache index plan             */
 #define STX_STAGE_COPY 4u    /* rewrite the changed packed rows           */
 #define STX_STAGE_MLP_GATEUP 8u  /* sparse gate/up projection + activation  */
 #define STX_STAGE_MLP_DOWN 16u   /* sparse down projection                   */
 #define STX_STAGE_MLP 24u        /* both                                     */
-#define STX_STAGE_ALL 31u
+#define STX_STAGE_ALL 63u
 int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B,
                           void* out, void* stream, unsigned stages);
 /* lazy != 0: a layer step advances the cache's index plan but defers the packed-row
@@ -240,6 +245,10 @@ int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp,
 int stx_layer_set_lazy_cache(stx_layer_t* l, int lazy);
 /* Device pointer to the layer's current mask bits (ceil(I/32) words), valid after a step. */
 int stx_layer_mask_bits(stx_layer_t* l, const uint32_t** bits_out);
+/* *fused_out = 1 when a step of B rows runs PREDICT_MASK and the MLP as the single-row
+ * kernel pair described above (B == 1, threshold rule, shape fits), else 0.  No reference
+ * counterpart; bench and tests use it to name the kernels they time.                    */
+int stx_layer_single_row_fused(stx_layer_t* l, int64_t B, int* fused_out);
 
 /* Same step with HOST buffers: copies x (B*H elements, used for both inputs) to the
  * device, runs the step, copies the result back and SYNCHRONISES the stream.           */

@@ -16,7 +16,8 @@ F32, F16, BF16 = 0, 1, 2
 ACT_RELU, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID, ACT_GELU = range(5)
 MASK_THRESHOLD, MASK_TOPK, MASK_STATISTICAL = range(3)
 CACHE_ALIAS_GATE_UP = 1
-STAGE_PREDICT, STAGE_PLAN, STAGE_COPY, STAGE_MLP_GATEUP, STAGE_MLP_DOWN, STAGE_MLP, STAGE_ALL = 1, 2, 4, 8, 16, 24, 31
+STAGE_PREDICT, STAGE_PLAN, STAGE_COPY, STAGE_MLP_GATEUP, STAGE_MLP_DOWN, STAGE_MLP, STAGE_ALL = 33, 2, 4, 8, 16, 24, 63
+STAGE_PREDICT_T, STAGE_PREDICT_MASK = 1, 32
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -60,6 +61,7 @@ SIGNATURES = {
     "stx_layer_step_stages": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _u32]),
     "stx_layer_set_lazy_cache": (_i32, [_vp, _i32]),
     "stx_layer_mask_bits": (_i32, [_vp, _pp]),
+    "stx_layer_single_row_fused": (_i32, [_vp, _i64, ctypes.POINTER(ctypes.c_int)]),
     "stx_layer_step_host": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "stx_stack_create": (_i32, [_pp, _pp, _i64, _i64]),
     "stx_stack_create_stages": (_i32, [_pp, _pp, _i64, _i64, _u32]),

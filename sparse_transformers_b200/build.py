@@ -50,7 +50,7 @@ def build_libstx(force: bool = False, verbose: bool = False) -> str:
         return LIBSTX
     nvcc = os.path.join(cuda_home(), "bin", "nvcc")
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-Xcompiler", "-fPIC", "-shared", f"-I{INCLUDE}", f"-I{CSRC}", "-Xptxas", "-v"] + srcs + ["-o", LIBSTX]
+           "-Xcompiler", "-fPIC", "-shared", f"-I{INCLUDE}", f"-I{CSRC}", "-Xptxas", "-v"] + shlex.split(os.environ.get("STX_NVCC_FLAGS", "")) + srcs + ["-o", LIBSTX]
     out = _run(cmd, verbose)
     with open(os.path.join(HERE, "ptxas_libstx.log"), "w") as f:  # registers / spills / shared memory per kernel
         f.write(out)

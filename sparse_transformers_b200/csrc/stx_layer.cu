@@ -5,17 +5,25 @@
 // sparse branch of SkipDecoderLayer.forward (src/modeling_skip.py:236-238 and :258).
 #include "stx_cache.cuh"
 
+#include <algorithm>
 #include <new>
 #include <vector>
 
 namespace stx {
 int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
-                 int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch,
+                 int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch, unsigned parts,
                  cudaStream_t s);
+float* b1_partial_region(void* scratch, int64_t H, int64_t K_cap);
+bool layer_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate, const void* up,
+                        const void* down, const void* Bm);
+int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
+                     const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
+                     int has_gate, int dtype, float* partial, int* status, unsigned parts, cudaStream_t s);
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
                 int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts,
-                const uint32_t* mask_bits, int32_t* idx_out, int32_t* count_out, cudaStream_t s);
+                const uint32_t* mask_bits, int32_t* idx_out, int32_t* count_out, bool scratch_has_partial,
+                cudaStream_t s);
 }  // namespace stx
 
 struct stx_layer {
@@ -94,6 +102,11 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   size_t pred_bytes = 0, mlp_bytes = 0;
   stx_predict_scratch_bytes(max_batch, I, r, &pred_bytes);
   stx_mlp_scratch_bytes(max_batch, H, I, &mlp_bytes);
+  if (max_batch > 1) {  // a single row uses a layout of its own (per-CTA partial output vectors)
+    size_t one = 0;
+    stx_mlp_scratch_bytes(1, H, I, &one);
+    mlp_bytes = std::max(mlp_bytes, one);
+  }
   const size_t es = dtype_size(cache->dtype);
   // 16-bit rows narrower than 32 chunks fall back to the packed cache inside the MLP
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&l->bits), ((I + 31) / 32) * sizeof(uint32_t));
@@ -101,6 +114,7 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&l->count), 64);
   if (e == cudaSuccess) e = cudaMemset(l->count, 0, 64);
   if (e == cudaSuccess) e = cudaMemset(l->idx, 0, I * sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMemset(l->bits, 0, ((I + 31) / 32) * sizeof(uint32_t));
   l->gather = (H * es) >= 512 && (H * es) % 16 == 0 && I <= 65536 && (I + 131) / 132 + 4 <= 512;
   if (e == cudaSuccess) e = cudaMalloc(&l->pred_scratch, pred_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&l->mlp_scratch, mlp_bytes);
@@ -115,6 +129,12 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   return STX_OK;
 }
 
+static bool single_row_fusable(const stx_layer* l, int64_t B) {
+  const stx_cache* c = l->cache;
+  return B == 1 && l->gather && l->method == STX_MASK_THRESHOLD && b1_partial_region(l->mlp_scratch, c->H, c->I) &&
+         layer_b1_supported(c->H, c->I, l->r, c->has_gate, c->dtype, c->pool_gate, c->pool_up, c->pool_down, l->Bm);
+}
+
 // One step with the cache maintenance (plan + row copies) optionally on a second stream.
 // With `gather` the MLP reads the active rows straight from the full pools through the list
 // of set mask bits, so it needs neither the index plan nor the copied rows: the differential
@@ -124,17 +144,41 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
                               cudaStream_t side, cudaEvent_t fork_ev, unsigned stages) {
   stx_cache* c = l->cache;
   int rc = STX_OK;
+  // One row under the threshold rule: scores, mask, gather and MLP of a neuron stay in one CTA.
+  float* partial = single_row_fusable(l, B) ? b1_partial_region(l->mlp_scratch, c->H, c->I) : nullptr;
+  const bool fuse = partial && (stages & STX_STAGE_PREDICT_MASK) && (stages & STX_STAGE_MLP) && x_mlp && out;
   if (stages & STX_STAGE_PREDICT) {
     STX_CHECK_ARG(x_pred, "stx_layer_step: x_pred is null");
-    rc = predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
-                      l->pred_scratch, s);
-    if (rc != STX_OK) return rc;
+    const unsigned pparts = ((stages & STX_STAGE_PREDICT_T) ? 1u : 0u) | (((stages & STX_STAGE_PREDICT_MASK) && !fuse) ? 2u : 0u);
+    if (pparts) {
+      rc = predict_mask(x_pred, B, c->H, l->A, l->r, l->Bm, c->I, c->dtype, l->method, l->param, l->bits, l->scores,
+                        l->pred_scratch, pparts, s);
+      if (rc != STX_OK) return rc;
+    }
   }
   const bool forked = side != s && l->gather;
   cudaStream_t cs = forked ? side : s;  // stream of the cache maintenance
-  if (forked && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY))) {
+  const bool fork_needed = forked && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY));
+  if (fork_needed && !fuse) {
     STX_CUDA(cudaEventRecord(fork_ev, s));
     STX_CUDA(cudaStreamWaitEvent(side, fork_ev, 0));
+  }
+  if (fuse) {
+    const float* t = static_cast<const float*>(l->pred_scratch);
+    if (stages & STX_STAGE_MLP_GATEUP) {
+      rc = layer_b1_forward(x_mlp, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
+                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 1u, s);
+      if (rc != STX_OK) return rc;
+    }
+    if (fork_needed) {  // the mask exists once that kernel is done
+      STX_CUDA(cudaEventRecord(fork_ev, s));
+      STX_CUDA(cudaStreamWaitEvent(side, fork_ev, 0));
+    }
+    if (stages & STX_STAGE_MLP_DOWN) {
+      rc = layer_b1_forward(x_mlp, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
+                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 2u, s);
+      if (rc != STX_OK) return rc;
+    }
   }
   if (!l->gather) {
     // the MLP reads the packed cache: plan and copies come first, on the same stream
@@ -147,15 +191,15 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       if (rc != STX_OK) return rc;
     }
   }
-  if (stages & STX_STAGE_MLP) {
+  if ((stages & STX_STAGE_MLP) && !fuse) {
     STX_CHECK_ARG(x_mlp && out, "stx_layer_step: x_mlp/out is null");
     const unsigned parts = ((stages & STX_STAGE_MLP_GATEUP) ? 1u : 0u) | ((stages & STX_STAGE_MLP_DOWN) ? 2u : 0u);
     if (l->gather)
       rc = mlp_forward(x_mlp, B, c->H, c->pool_gate, c->pool_up, c->pool_down, l->count, 0, c->I, 0, out, nullptr, l->act,
-                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, l->bits, l->idx, l->count, s);
+                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, l->bits, l->idx, l->count, true, s);
     else
       rc = mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
-                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, nullptr, nullptr, nullptr, s);
+                       c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, nullptr, nullptr, nullptr, true, s);
     if (rc != STX_OK) return rc;
   }
   if (l->gather) {
@@ -188,6 +232,12 @@ int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_
 int stx_layer_set_lazy_cache(stx_layer_t* l, int lazy) {
   STX_CHECK_ARG(l, "stx_layer_set_lazy_cache: null layer");
   l->lazy = lazy != 0 && l->gather;
+  return STX_OK;
+}
+
+int stx_layer_single_row_fused(stx_layer_t* l, int64_t B, int* fused_out) {
+  STX_CHECK_ARG(l && fused_out, "stx_layer_single_row_fused: null pointer");
+  *fused_out = single_row_fusable(l, B) ? 1 : 0;
   return STX_OK;
 }
 

@@ -239,17 +239,31 @@ struct GatherSpec {
 };
 int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                     const int32_t* K_dev, int64_t K_host, const GatherSpec* gs, void* out, void* combined, int act,
-                    int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s);
+                    int has_gate, int dtype, void* scratch, float* partial, int* status, unsigned parts,
+                    cudaStream_t s);
 
 size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K);
 bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate);
 int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, const void* down_packed, int64_t K,
                     void* out, void* combined, int act, int dtype, void* scratch, int* status, cudaStream_t s);
 
-static size_t decode_scratch_bytes(int64_t B, int64_t H, int64_t K) {
+constexpr int64_t PARTIAL_ROWS = 256;  // per-CTA partial output vectors of the batch-1 kernel (>= SM count)
+
+// without the batch-1 partial vectors: what the built-in scratch of the no-alloc entry point holds
+static size_t decode_scratch_bytes_min(int64_t B, int64_t H, int64_t K) {
   // [counter | fp32 accumulator B*H (kept zero) | 256 | fp32 a[K][B]]
   return 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256) + 256 +
          align_up(static_cast<size_t>(B) * std::max<int64_t>(K, 1) * sizeof(float), 256);
+}
+static size_t decode_scratch_bytes(int64_t B, int64_t H, int64_t K) {
+  return decode_scratch_bytes_min(B, H, K) + (B == 1 ? align_up(static_cast<size_t>(PARTIAL_ROWS) * H * sizeof(float), 256) : 0);
+}
+
+// Per-CTA partial output vectors of the batch-1 kernel inside a scratch buffer that
+// stx_mlp_scratch_bytes(1, H, K_cap) sized; nullptr when the device has too many SMs for it.
+float* b1_partial_region(void* scratch, int64_t H, int64_t K_cap) {
+  if (num_sms() > PARTIAL_ROWS) return nullptr;
+  return reinterpret_cast<float*>(static_cast<char*>(scratch) + decode_scratch_bytes_min(1, H, K_cap));
 }
 
 // STX_MLP_KERNEL=plain forces the plain-load kernel (for A/B measurements); default: the
@@ -269,14 +283,17 @@ static bool use_tma_kernel() {
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
                 int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts,
-                const uint32_t* mask_bits, int32_t* idx_out, int32_t* count_out, cudaStream_t s) {
+                const uint32_t* mask_bits, int32_t* idx_out, int32_t* count_out, bool scratch_has_partial,
+                cudaStream_t s) {
   const bool row_idx = mask_bits != nullptr;
   GatherSpec gs{mask_bits, idx_out, count_out, static_cast<int>(K_cap)};
   if ((use_tma_kernel() || row_idx) && !up_after_gate) {
     // the streaming kernels keep a[K][B] behind the (always zero) accumulator region
     void* a_region = static_cast<char*>(scratch) + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
+    float* partial = nullptr;
+    if (scratch_has_partial && B == 1) partial = b1_partial_region(scratch, H, K_cap);
     const int rc = mlp_forward_tma(x, B, H, gate, up, down, K_dev, K_host, row_idx ? &gs : nullptr, out, combined, act,
-                                   has_gate, dtype, a_region, status, parts, s);
+                                   has_gate, dtype, a_region, partial, status, parts, s);
     if (rc != STX_ERR_UNSUPPORTED) return rc;
   }
   if (row_idx) {
@@ -320,6 +337,12 @@ int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const voi
 
 using namespace stx;
 
+namespace stx {
+int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed,
+                            int64_t K, void* down_buf, void* combined_buf, int act, int has_gate, int dtype,
+                            void* scratch, bool scratch_has_partial, void* stream);
+}
+
 extern "C" {
 
 int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out) {
@@ -333,6 +356,18 @@ int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out) {
 int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed,
                            int64_t K, void* down_buf, void* combined_buf, int act, int has_gate, int dtype,
                            void* scratch, void* stream) {
+  return stx::sparse_mlp_forward_impl(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, has_gate, dtype,
+                                      scratch, true, stream);
+}
+
+}  // extern "C"
+
+namespace stx {
+// scratch_has_partial: the scratch was sized by stx_mlp_scratch_bytes (true) or is the smaller
+// built-in array of the no-alloc entry point (false: batch 1 keeps the two-kernel path).
+int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed,
+                            int64_t K, void* down_buf, void* combined_buf, int act, int has_gate, int dtype,
+                            void* scratch, bool scratch_has_partial, void* stream) {
   STX_CHECK_ARG(x && concat_w && down_packed && down_buf && scratch, "stx_sparse_mlp_forward: null pointer");
   STX_CHECK_ARG(B > 0 && H > 0 && K >= 0, "stx_sparse_mlp_forward: bad sizes B=%lld H=%lld K=%lld",
                 static_cast<long long>(B), static_cast<long long>(H), static_cast<long long>(K));
@@ -356,10 +391,10 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
   const void* gate = has_gate ? cw : nullptr;
   const void* up = has_gate ? cw + static_cast<size_t>(K) * H * es : cw;
   return mlp_forward(x, B, H, gate, up, down_packed, nullptr, K, std::max<int64_t>(K, 1), 0, down_buf, combined_buf, act,
-                     has_gate ? 1 : 0, dtype, scratch, nullptr, 3u, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+                     has_gate ? 1 : 0, dtype, scratch, nullptr, 3u, nullptr, nullptr, nullptr, scratch_has_partial,
+                     static_cast<cudaStream_t>(stream));
 }
-
-}  // extern "C"
+}  // namespace stx
 
 // ---------------------------------------------------------------------------------------
 // Allocation-free variant of stx_sparse_mlp_forward.
@@ -421,8 +456,7 @@ extern "C" int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t 
                                               int act, int has_gate, int dtype, void* stream) {
   STX_CHECK_ARG(B > 0 && H > 0 && K >= 0, "stx_sparse_mlp_forward_noalloc: bad sizes B=%lld H=%lld K=%lld",
                 static_cast<long long>(B), static_cast<long long>(H), static_cast<long long>(K));
-  size_t need = 0;
-  stx_mlp_scratch_bytes(B, H, K, &need);
+  const size_t need = decode_scratch_bytes_min(B, H, K) + (B >= 64 ? prefill_scratch_bytes(B, H, K) : 0);
   if (need > NOALLOC_BYTES) {
     set_error("stx_sparse_mlp_forward_noalloc: B*(H+K) = %lld exceeds the built-in scratch of %lld elements; "
               "use stx_sparse_mlp_forward with a caller-provided scratch buffer",
@@ -435,6 +469,6 @@ extern "C" int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t 
   // the array keeps the previous call's contents: clear the counter and the accumulator
   const size_t used = 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
   STX_CUDA(cudaMemsetAsync(scratch, 0, used, static_cast<cudaStream_t>(stream)));
-  return stx_sparse_mlp_forward(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, has_gate, dtype, scratch,
-                                stream);
+  return stx::sparse_mlp_forward_impl(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, has_gate, dtype,
+                                      scratch, false, stream);
 }

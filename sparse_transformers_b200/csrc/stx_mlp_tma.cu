@@ -608,6 +608,367 @@ __global__ void __launch_bounds__(DOWN_THREADS, 2) k_down_rows(const DownArgs p)
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Batch 1: gate/up, activation and the down projection of a neuron in one pass.
+//
+// k_mlp_b1: a CTA owns S "slots" (one per warp w < S); a slot holds the gate, up and down
+// row of one neuron, fetched by bulk copies the moment the CTA knows its neurons.  With
+// S * gridDim.x >= K (the usual case) every byte the kernel reads is in flight from the start.
+//   phase 1  warp w: gate/up dot products of its neuron against x -> a = act(g) * u -> a_s[w]
+//   phase 2  all threads: thread t owns the 16-byte column chunks t, t + blockDim.x, ... and adds
+//            a_s[slot] * down_row[slot][chunk] over the slots in ascending order (registers)
+// A second round (K > S * gridDim.x) re-fills a slot's gate/up part right after phase 1 and its
+// down part after phase 2.  At the end each thread writes its columns of the CTA's partial
+// output vector; k_partial_reduce adds the per-CTA vectors in ascending CTA order:
+// deterministic, no atomics, nothing to re-zero.  One launch that streams gate, up and down
+// rows pays the launch, listing and first-byte latency once instead of twice.
+// Development aid, compiled out unless STX_B1_TRACE is defined: thread 0 of every CTA stamps
+// the global timer at a few points of k_mlp_b1 (read back with stx_debug_b1_trace).
+#ifdef STX_B1_TRACE
+__device__ unsigned long long g_b1_trace[256][8];
+#define STX_B1_STAMP(i)                                                                 \
+  do {                                                                                  \
+    if (threadIdx.x == 0) {                                                             \
+      unsigned long long t__;                                                           \
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t__));                            \
+      g_b1_trace[blockIdx.x][i] = t__;                                                  \
+    }                                                                                   \
+  } while (0)
+#else
+#define STX_B1_STAMP(i) do { } while (0)
+#endif
+
+constexpr int B1_MAX_SLOTS = 16;
+constexpr int B1_MAX_PASS = 2;    // column chunks per thread: H / V <= 2 * 512
+constexpr int B1_HEADER = 512;    // [0,256) 2 x 16 mbarriers | [256,320) a_s
+
+struct MlpB1Args {
+  GateUpArgs g;          // x, gate, up, combined, gather spec, K, H, act, has_gate; nwarps = slots S
+  const void* down;
+  float* partial;        // [gridDim.x][H]
+  // Predictor back half inside the kernel (Bm != nullptr): scores of the CTA's own neurons from
+  // t = A x (fp32 [r], written by the preceding kernel), threshold, mask bytes to `bits`.
+  const float* t;
+  const void* Bm;        // [I][r]
+  uint32_t* bits;        // mask words of the layer (written bytewise)
+  int r;
+  float tau;
+};
+
+// With the predictor's back half fused in, CTA c owns mask bytes c, c + G, c + 2G, ... (8
+// neurons each): it needs nobody else's scores to know which of its rows to fetch, so the
+// mask never makes a round trip through global memory on the critical path.  The price is
+// balance: the CTAs' active counts differ (binomially) instead of by at most one.
+//
+// Measured alternative, not kept: letting the CTAs publish their counts and hand their excess
+// to lighter CTAs (a deterministic plan from the exchanged counts) balanced the work, but the
+// exchange's small messages queue behind the bulk row traffic of the same SM and the two
+// round trips cost more than the imbalance they removed.
+constexpr int B1_MAX_BYTES = 24;   // mask bytes per CTA: ceil(ceil(I / 8) / G) <= 24 (192 neurons)
+constexpr int B1_LIST_CAP = 192;
+
+template <typename T>
+__global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
+  constexpr int V = DT<T>::V;
+  const GateUpArgs& p = q.g;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int S = p.nwarps;
+  const int H = p.H, nchunk = H / V;
+  const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+  const int ngu = p.has_gate ? 2 : 1;
+
+  uint64_t* bar_gu = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* bar_d = bar_gu + B1_MAX_SLOTS;
+  float* a_s = reinterpret_cast<float*>(smem + 256);
+  // [B1_HEADER, +t_bytes): t of the fused predictor back half
+  const size_t t_bytes = q.Bm ? (static_cast<size_t>(q.r) * sizeof(float) + 127) / 128 * 128 : 0;
+  T* x_s = reinterpret_cast<T*>(smem + B1_HEADER + t_bytes);
+  const size_t x_bytes = (sizeof(T) * H + 127) / 128 * 128;
+  unsigned char* gu_bufs = smem + B1_HEADER + t_bytes + x_bytes;
+  unsigned char* d_bufs = gu_bufs + static_cast<size_t>(S) * ngu * row_bytes;
+  unsigned char* my_gu = gu_bufs + static_cast<size_t>(warp) * ngu * row_bytes;
+
+  __shared__ int32_t s_my[GATHER_MY_CAP];
+  __shared__ uint32_t s_nib[16];
+  __shared__ uint8_t s_bytes[B1_MAX_BYTES];
+  __shared__ int s_nlocal;
+  const char* gsrc = static_cast<const char*>(p.gate);
+  const char* usrc = static_cast<const char*>(p.up);
+  const char* dsrc = static_cast<const char*>(q.down);
+  const bool fused = q.Bm != nullptr;
+  T* combined = fused ? nullptr : static_cast<T*>(p.combined);
+  const bool gather = fused || p.mask_bits != nullptr;
+  const int G = gridDim.x;
+
+  if (tid == 0) {
+    for (int w = 0; w < S; ++w) {
+      mbar_init(&bar_gu[w], 1);
+      mbar_init(&bar_d[w], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  int K = 0, nlocal = 0;
+  STX_B1_STAMP(0);
+  if (fused) {
+    // ---- predictor back half for this CTA's neurons; same arithmetic as k_pred_scores: 8 lanes
+    // per neuron, lane g takes the 16-byte chunks g, g + 8, ... of the r-long row in order, then a
+    // butterfly over the 8 lanes (4, 2, 1).
+    const int r = q.r, rch = r / V;  // rch <= 32
+    const int NBY = (p.I + 7) >> 3;
+    const int nby = NBY > static_cast<int>(blockIdx.x) ? (NBY - 1 - static_cast<int>(blockIdx.x)) / G + 1 : 0;
+    const int g = tid & 7;
+    const T* Bm = static_cast<const T*>(q.Bm);
+    float* t_s = reinterpret_cast<float*>(smem + B1_HEADER);
+    float wv[4][V];
+    auto load_w = [&](int pass) {
+      const int kk = pass * 8 + (tid >> 6);
+      const int n = 8 * (static_cast<int>(blockIdx.x) + G * kk) + ((tid >> 3) & 7);
+      const bool ok = kk < nby && n < p.I;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const int c = g + 8 * c4;
+#pragma unroll
+        for (int v = 0; v < V; ++v) wv[c4][v] = 0.f;
+        if (ok && c < rch) Unpack<T>::run(ld_stream16(Bm + static_cast<size_t>(n) * r + c * V), wv[c4]);
+      }
+      return ok;
+    };
+    bool ok = load_w(0);  // weights do not depend on the preceding kernel
+    pdl_wait();
+    pdl_launch_dependents();
+    STX_B1_STAMP(1);
+    for (int k = tid; k < r; k += blockDim.x) t_s[k] = __ldcg(q.t + k);
+    __syncthreads();
+    const float tau_r = DT<T>::round_f(q.tau);
+    for (int pass = 0; pass * 8 < nby; ++pass) {
+      if (pass > 0) ok = load_w(pass);
+      float sc = 0.f;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const int c = g + 8 * c4;
+        if (c < rch) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) sc = fmaf(t_s[c * V + v], wv[c4][v], sc);
+        }
+      }
+      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+      const bool on = ok && (DT<T>::round_f(sc) >= tau_r);
+      const uint32_t bal = __ballot_sync(0xffffffffu, on && g == 0);
+      if (lane == 0) s_nib[warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
+      __syncthreads();
+      if (tid < 8 && pass * 8 + tid < nby) {
+        const uint32_t byte = s_nib[2 * tid] | (s_nib[2 * tid + 1] << 4);
+        s_bytes[pass * 8 + tid] = static_cast<uint8_t>(byte);
+        reinterpret_cast<uint8_t*>(q.bits)[blockIdx.x + G * (pass * 8 + tid)] = static_cast<uint8_t>(byte);
+      }
+      __syncthreads();
+    }
+    if (warp == 0) {  // the CTA's active neurons in ascending order
+      int carry = 0;
+      for (int base = 0; base < nby; base += 32) {
+        const int kk = base + lane;
+        uint32_t byte = kk < nby ? s_bytes[kk] : 0u;
+        const int cnt = __popc(byte);
+        int inc = cnt;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, inc, off);
+          if (lane >= off) inc += v;
+        }
+        int pos = carry + inc - cnt;
+        while (byte) {
+          const int n = 8 * (static_cast<int>(blockIdx.x) + G * kk) + __ffs(byte) - 1;
+          byte &= byte - 1;
+          if (pos < B1_LIST_CAP) s_my[pos] = n;
+          ++pos;
+        }
+        carry += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) s_nlocal = min(carry, B1_LIST_CAP);
+    }
+    __syncthreads();
+    nlocal = s_nlocal;
+  } else {
+    pdl_wait();
+    pdl_launch_dependents();
+    K = gather ? cta_list_active(p.mask_bits, p.I, 1, s_my, p.idx_out, p.count_out) : (p.K_dev ? *p.K_dev : p.K_host);
+    if (!gather) __syncthreads();
+    nlocal = K > static_cast<int>(blockIdx.x) ? (K - 1 - static_cast<int>(blockIdx.x)) / G + 1 : 0;
+  }
+
+  // local neuron s (rank blockIdx.x + G*s) -> slot s % S; called by lane 0 of warp s % S
+  auto row_of = [&](int s) { return gather ? s_my[s] : static_cast<int>(blockIdx.x) + G * s; };
+  auto issue_gu = [&](int s) {
+    mbar_expect_tx(&bar_gu[warp], row_bytes * ngu);
+    const size_t off = static_cast<size_t>(row_of(s)) * row_bytes;
+    if (p.has_gate) bulk_load(my_gu, gsrc + off, row_bytes, &bar_gu[warp]);
+    bulk_load(my_gu + (p.has_gate ? row_bytes : 0), usrc + off, row_bytes, &bar_gu[warp]);
+  };
+  auto issue_d = [&](int s) {
+    mbar_expect_tx(&bar_d[warp], row_bytes);
+    bulk_load(d_bufs + static_cast<size_t>(warp) * row_bytes, dsrc + static_cast<size_t>(row_of(s)) * row_bytes, row_bytes,
+              &bar_d[warp]);
+  };
+
+  STX_B1_STAMP(2);
+  if (warp < S && lane == 0 && warp < nlocal) {  // the rows stream in while x is staged
+    issue_gu(warp);
+    issue_d(warp);
+  }
+  {
+    const uint4* xg = reinterpret_cast<const uint4*>(p.x);
+    uint4* xs4 = reinterpret_cast<uint4*>(x_s);
+    for (int i = tid; i < nchunk; i += blockDim.x) xs4[i] = xg[i];
+  }
+  __syncthreads();
+  STX_B1_STAMP(3);
+
+  bool timed_out = false;
+  float acc[B1_MAX_PASS][V];
+#pragma unroll
+  for (int k = 0; k < B1_MAX_PASS; ++k)
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[k][v] = 0.f;
+
+  const int nrounds = (nlocal + S - 1) / S;
+  for (int r = 0; r < nrounds; ++r) {
+    const uint32_t parity = static_cast<uint32_t>(r) & 1u;
+    const int s = warp + r * S;
+    if (warp < S && s < nlocal) {
+      const int j = static_cast<int>(blockIdx.x) + G * s;  // rank of this neuron
+      if (!mbar_wait_bounded(&bar_gu[warp], parity)) timed_out = true;
+      const T* grow = reinterpret_cast<const T*>(my_gu);
+      const T* urow = reinterpret_cast<const T*>(my_gu + (p.has_gate ? row_bytes : 0));
+      float ag = 0.f, au = 0.f;
+      int c = lane;
+      for (; c + 32 < nchunk; c += 64) {  // two chunks per iteration: independent chains
+        float wu0[V], wu1[V], wg0[V], wg1[V], x0[V], x1[V];
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(urow + c * V), wu0);
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(urow + (c + 32) * V), wu1);
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + c * V), x0);
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + (c + 32) * V), x1);
+        float su0 = 0.f, su1 = 0.f, sg0 = 0.f, sg1 = 0.f;
+        if (p.has_gate) {
+          Unpack<T>::run(*reinterpret_cast<const uint4*>(grow + c * V), wg0);
+          Unpack<T>::run(*reinterpret_cast<const uint4*>(grow + (c + 32) * V), wg1);
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          su0 = fmaf(x0[v], wu0[v], su0);
+          su1 = fmaf(x1[v], wu1[v], su1);
+          if (p.has_gate) {
+            sg0 = fmaf(x0[v], wg0[v], sg0);
+            sg1 = fmaf(x1[v], wg1[v], sg1);
+          }
+        }
+        au += su0 + su1;
+        ag += sg0 + sg1;
+      }
+      for (; c < nchunk; c += 32) {
+        float wu[V], wg[V], xv[V];
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(urow + c * V), wu);
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(x_s + c * V), xv);
+        if (p.has_gate) Unpack<T>::run(*reinterpret_cast<const uint4*>(grow + c * V), wg);
+        float su = 0.f, sg = 0.f;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          su = fmaf(xv[v], wu[v], su);
+          if (p.has_gate) sg = fmaf(xv[v], wg[v], sg);
+        }
+        au += su;
+        ag += sg;
+      }
+      const float u = warp_sum_xor(au);
+      const float gsum = p.has_gate ? warp_sum_xor(ag) : 0.f;
+      const float a = p.has_gate ? apply_act(p.act, gsum) * u : apply_act(p.act, u);
+      if (lane == 0) {
+        a_s[warp] = a;
+        if (combined) {
+          combined[j] = DT<T>::from_f(a);
+          if (p.has_gate) combined[K + j] = DT<T>::from_f(u);
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && s + S < nlocal) {  // the gate/up part of the slot is free again
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue_gu(s + S);
+      }
+    }
+    __syncthreads();  // a_s of this round complete
+
+    const int nvalid = min(S, nlocal - r * S);
+    if (tid < nchunk) {
+      for (int slot = 0; slot < nvalid; ++slot) {
+        if (!mbar_wait_bounded(&bar_d[slot], parity)) timed_out = true;
+        const float a = a_s[slot];
+        const T* drow = reinterpret_cast<const T*>(d_bufs + static_cast<size_t>(slot) * row_bytes);
+#pragma unroll
+        for (int k = 0; k < B1_MAX_PASS; ++k) {
+          const int cc = tid + k * static_cast<int>(blockDim.x);
+          if (cc < nchunk) {
+            float wd[V];
+            Unpack<T>::run(*reinterpret_cast<const uint4*>(drow + cc * V), wd);
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[k][v] = fmaf(a, wd[v], acc[k][v]);
+          }
+        }
+      }
+    }
+    if (r + 1 < nrounds) {
+      __syncthreads();  // every thread is done with a_s and the down rows of this round
+      if (warp < S && lane == 0 && s + S < nlocal) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue_d(s + S);
+      }
+    }
+  }
+  if (timed_out && p.status) atomicOr(p.status, DEV_TIMEOUT);
+#ifdef STX_B1_TRACE
+  if (tid == 0) g_b1_trace[blockIdx.x][7] = static_cast<unsigned long long>(nlocal);
+#endif
+
+  float* dst = q.partial + static_cast<size_t>(blockIdx.x) * H;
+#pragma unroll
+  for (int k = 0; k < B1_MAX_PASS; ++k) {
+    const int cc = tid + k * static_cast<int>(blockDim.x);
+    if (cc < nchunk) {
+#pragma unroll
+      for (int v = 0; v < V; v += 4)
+        *reinterpret_cast<float4*>(dst + cc * V + v) = make_float4(acc[k][v], acc[k][v + 1], acc[k][v + 2], acc[k][v + 3]);
+    }
+  }
+  STX_B1_STAMP(6);
+}
+
+// out[h] = sum_c partial[c][h], c ascending.  Block: 32 columns x 32 groups of CTAs; a group
+// adds a contiguous range of CTAs in order, then the groups are added in order.
+template <typename T>
+__global__ void __launch_bounds__(1024) k_partial_reduce(const float* __restrict__ partial, int G, int H, T* __restrict__ out) {
+  __shared__ float s_r[32][33];
+  const int hc = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int h = blockIdx.x * 32 + hc;
+  const int per = (G + 31) / 32;
+  const int c0 = grp * per, c1 = min(G, c0 + per);
+  pdl_wait();
+  pdl_launch_dependents();
+  float sum = 0.f;
+  if (h < H) {
+#pragma unroll 8
+    for (int c = c0; c < c1; ++c) sum += __ldcg(partial + static_cast<size_t>(c) * H + h);
+  }
+  s_r[grp][hc] = sum;
+  __syncthreads();
+  if (grp == 0 && h < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < 32; ++g) t += s_r[g][hc];
+    out[h] = DT<T>::from_f(t);
+  }
+}
+
 constexpr size_t TMA_SMEM_BUDGET = 220 * 1024;
 
 template <typename T, int NB>
@@ -713,6 +1074,92 @@ static int launch_both(const GateUpArgs& g, int grid, size_t smem, const DownArg
   return STX_OK;
 }
 
+// Batch-1 fused path: parts bit 0 = k_mlp_b1, bit 1 = k_partial_reduce.
+// Dynamic shared memory a k_mlp_b1 CTA may use: the 227 KB per-block limit less the kernel's
+// static shared memory.
+template <typename T>
+static size_t b1_smem_budget() {
+  static size_t budget = 0;
+  if (!budget) {
+    cudaFuncAttributes fa;
+    size_t stat = 4096;
+    if (cudaFuncGetAttributes(&fa, k_mlp_b1<T>) == cudaSuccess) stat = fa.sharedSizeBytes;
+    budget = 227 * 1024 - (stat + 127) / 128 * 128;
+  }
+  return budget;
+}
+
+// slots per CTA for row length H (r: predictor rank when its back half is fused in, else 0),
+// or 0 when the kernel does not fit the shape
+template <typename T>
+static int b1_slots(int H, int has_gate, int r) {
+  const size_t row_bytes = static_cast<size_t>(H) * sizeof(T);
+  const size_t x_bytes = (row_bytes + 127) / 128 * 128 + (static_cast<size_t>(r) * sizeof(float) + 127) / 128 * 128;
+  const int nmat = has_gate ? 3 : 2;
+  const size_t budget = b1_smem_budget<T>();
+  if (H / DT<T>::V > B1_MAX_PASS * 512 || budget < B1_HEADER + x_bytes) return 0;
+  const size_t sl = (budget - B1_HEADER - x_bytes) / (nmat * row_bytes);
+  return sl < 8 ? 0 : static_cast<int>(std::min<size_t>(B1_MAX_SLOTS, sl));
+}
+
+struct B1Pred {  // predictor back half fused into k_mlp_b1 (Bm == nullptr: not fused)
+  const float* t = nullptr;
+  const void* Bm = nullptr;
+  uint32_t* bits = nullptr;
+  int r = 0;
+  float tau = 0.f;
+};
+
+template <typename T>
+static int launch_b1(const GateUpArgs& g, const void* down, float* partial, void* out, int grid, unsigned parts,
+                     const B1Pred& pr, cudaStream_t s) {
+  const size_t row_bytes = static_cast<size_t>(g.H) * sizeof(T);
+  const int nmat = g.has_gate ? 3 : 2;
+  const size_t x_bytes = (row_bytes + 127) / 128 * 128 + (static_cast<size_t>(pr.r) * sizeof(float) + 127) / 128 * 128;
+  MlpB1Args q;
+  q.g = g;
+  q.g.nwarps = b1_slots<T>(g.H, g.has_gate, pr.r);
+  q.down = down;
+  q.partial = partial;
+  q.t = pr.t;
+  q.Bm = pr.Bm;
+  q.bits = pr.bits;
+  q.r = pr.r;
+  q.tau = pr.tau;
+  const size_t smem = B1_HEADER + x_bytes + static_cast<size_t>(q.g.nwarps) * nmat * row_bytes;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    STX_CUDA(cudaFuncSetAttribute(k_mlp_b1<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(b1_smem_budget<T>())));
+    attr_set[dev] = true;
+  }
+  if (parts & 1u) STX_CUDA(launch_pdl(k_mlp_b1<T>, dim3(grid), dim3(512), smem, s, q));
+  if (parts & 2u)
+    STX_CUDA(launch_pdl(k_partial_reduce<T>, dim3((g.H + 31) / 32), dim3(1024), 0, s, static_cast<const float*>(partial),
+                        grid, g.H, static_cast<T*>(out)));
+  return STX_OK;
+}
+
+static int b1_slots_dt(int H, int has_gate, int dtype, int r) {
+  switch (dtype) {
+    case STX_F32: return b1_slots<float>(H, has_gate, r);
+    case STX_F16: return b1_slots<__half>(H, has_gate, r);
+    default: return b1_slots<__nv_bfloat16>(H, has_gate, r);
+  }
+}
+
+// STX_MLP_B1=split keeps batch 1 on the two-kernel path (A/B measurements).
+static bool use_b1_fused() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("STX_MLP_B1");
+    v = (e && !strcmp(e, "split")) ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <typename T>
 static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const DownArgs& d, unsigned parts,
                        cudaStream_t s) {
@@ -727,9 +1174,62 @@ static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const
 // Returns STX_ERR_UNSUPPORTED (without setting an error text) when the shape does not fit
 // these kernels; the caller then uses the plain-load kernel.
 // scratch: fp32 a[K][B] at offset 256.  parts: bit 0 = gate/up kernel, bit 1 = down kernel.
+// One row through a layer whose mask comes from the threshold rule: the predictor's back half,
+// the gather and the whole MLP in k_mlp_b1, then k_partial_reduce.  parts bit 0 / bit 1 select
+// the two kernels.  `t` holds A x (fp32 [r]) written earlier on the same stream.
+bool layer_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate, const void* up,
+                        const void* down, const void* Bm) {
+  const size_t es = dtype_size(dtype);
+  const int V = static_cast<int>(16 / es);
+  if (!use_b1_fused() || (H * es) % 16 != 0 || H / V < 32 || r % V != 0 || r / V > 32 || H > (1 << 20) || I > (1 << 24))
+    return false;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
+                       reinterpret_cast<uintptr_t>(down) | reinterpret_cast<uintptr_t>(Bm);
+  if (al & 15) return false;
+  const int grid = std::max(1, num_sms() - 1);
+  if (((I + 7) / 8 + grid - 1) / grid > B1_MAX_BYTES) return false;
+  return b1_slots_dt(static_cast<int>(H), has_gate, dtype, static_cast<int>(r)) > 0;
+}
+
+int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
+                     const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
+                     int has_gate, int dtype, float* partial, int* status, unsigned parts, cudaStream_t s) {
+  GateUpArgs a;
+  a.x = x;
+  a.gate = gate;
+  a.up = up;
+  a.combined = nullptr;
+  a.a_out = nullptr;
+  a.status = status;
+  a.K_dev = nullptr;
+  a.mask_bits = nullptr;
+  a.idx_out = nullptr;
+  a.count_out = nullptr;
+  a.I = static_cast<int>(I);
+  a.K_host = 0;
+  a.B = 1;
+  a.H = static_cast<int>(H);
+  a.act = act;
+  a.has_gate = has_gate;
+  a.nwarps = 0;
+  B1Pred pr;
+  pr.t = t;
+  pr.Bm = Bm;
+  pr.bits = bits;
+  pr.r = static_cast<int>(r);
+  pr.tau = tau;
+  const int grid = std::max(1, num_sms() - 1);
+  switch (dtype) {
+    case STX_F32: return launch_b1<float>(a, down, partial, out, grid, parts, pr, s);
+    case STX_F16: return launch_b1<__half>(a, down, partial, out, grid, parts, pr, s);
+    default: return launch_b1<__nv_bfloat16>(a, down, partial, out, grid, parts, pr, s);
+  }
+}
+
 int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                     const int32_t* K_dev, int64_t K_host, const GatherSpec* gs, void* out, void* combined, int act,
-                    int has_gate, int dtype, void* scratch, int* status, unsigned parts, cudaStream_t s) {
+                    int has_gate, int dtype, void* scratch, float* partial, int* status, unsigned parts,
+                    cudaStream_t s) {
   const size_t es = dtype_size(dtype);
   const int V = static_cast<int>(16 / es);
   const int nchunk = static_cast<int>(H / V);
@@ -783,6 +1283,15 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   d.K_host = static_cast<int>(K_host);
   d.B = static_cast<int>(B);
   d.H = static_cast<int>(H);
+  // batch 1 with room for three rows per warp and H within the register accumulators: fused kernel
+  const bool b1 = B == 1 && partial != nullptr && use_b1_fused() && b1_slots_dt(static_cast<int>(H), has_gate, dtype, 0) > 0;
+  if (b1) {
+    switch (dtype) {
+      case STX_F32: return launch_b1<float>(a, down, partial, out, grid, parts, B1Pred(), s);
+      case STX_F16: return launch_b1<__half>(a, down, partial, out, grid, parts, B1Pred(), s);
+      default: return launch_b1<__nv_bfloat16>(a, down, partial, out, grid, parts, B1Pred(), s);
+    }
+  }
   switch (dtype) {
     case STX_F32: return dispatch_nb<float>(a, nb, grid, smem, d, parts, s);
     case STX_F16: return dispatch_nb<__half>(a, nb, grid, smem, d, parts, s);
@@ -791,3 +1300,9 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
 }
 
 }  // namespace stx
+
+#ifdef STX_B1_TRACE
+extern "C" int stx_debug_b1_trace(unsigned long long* out_host) {
+  return cudaMemcpyFromSymbol(out_host, stx::g_b1_trace, sizeof(unsigned long long) * 256 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -187,12 +187,14 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
 template <typename T>
 static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
                           int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
-                          int write_bits, cudaStream_t s) {
+                          int write_bits, unsigned parts, cudaStream_t s) {
+  if (parts & 1u)
   STX_CUDA(launch_pdl(k_pred_t<T>, dim3(static_cast<unsigned>(r)), dim3(pred_t_threads(static_cast<int>(H), DT<T>::V)), 0,
                       s, static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B),
                       static_cast<int>(H), static_cast<int>(r)));
   const int64_t W = (I + 31) / 32;
   const size_t smem = static_cast<size_t>(B) * r * sizeof(float);
+  if (parts & 2u)
   STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W)), dim3(256), smem, s, t_scratch,
                       static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
                       static_cast<int>(r), static_cast<int>(I), tau, write_bits));
@@ -204,24 +206,25 @@ static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, in
 int mask_from_scores(const void* scores, int64_t B, int64_t I, int dtype, int method, float param,
                      uint32_t* bits_out, void* scratch, cudaStream_t s);
 
+// parts: bit 0 = t = A x, bit 1 = scores, threshold/selection and mask
 int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm, int64_t I,
-                 int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch,
+                 int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch, unsigned parts,
                  cudaStream_t s) {
   float* t_scratch = static_cast<float*>(scratch);
   const int write_bits = method == STX_MASK_THRESHOLD ? 1 : 0;
   int rc;
   switch (dtype) {
     case STX_F32:
-      rc = launch_predict<float>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
+      rc = launch_predict<float>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, parts, s);
       break;
     case STX_F16:
-      rc = launch_predict<__half>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
+      rc = launch_predict<__half>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, parts, s);
       break;
     default:
-      rc = launch_predict<__nv_bfloat16>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, s);
+      rc = launch_predict<__nv_bfloat16>(x, B, H, A, r, Bm, I, param, bits, scores_out, t_scratch, write_bits, parts, s);
       break;
   }
-  if (rc != STX_OK || method == STX_MASK_THRESHOLD) return rc;
+  if (rc != STX_OK || method == STX_MASK_THRESHOLD || !(parts & 2u)) return rc;
   void* sel_scratch = static_cast<char*>(scratch) + align_up(static_cast<size_t>(B) * r * sizeof(float), 256);
   return mask_from_scores(scores_out, B, I, dtype, method, param, bits, sel_scratch, s);
 }
@@ -257,7 +260,7 @@ int stx_predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t
     set_error("stx_predict_mask: B*r=%lld exceeds the shared-memory tile (12288 values)", static_cast<long long>(B * r));
     return STX_ERR_TOO_LARGE;
   }
-  return predict_mask(x, B, H, A, r, Bm, I, dtype, method, param, mask_bits_out, scores_out, scratch,
+  return predict_mask(x, B, H, A, r, Bm, I, dtype, method, param, mask_bits_out, scores_out, scratch, 3u,
                       static_cast<cudaStream_t>(stream));
 }
 

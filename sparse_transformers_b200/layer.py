@@ -111,6 +111,13 @@ class SparseLayer:
         C.check(C.lib.stx_layer_step_host(self._layer, x_host.data_ptr(), B, out_host.data_ptr(), _stream()))
         return out_host
 
+    def single_row_fused(self, batch: int = 1) -> bool:
+        """True when a step of `batch` rows runs the predictor's back half, the gather and the MLP as
+        one kernel (k_mlp_b1) followed by the sum of its partial outputs (k_partial_reduce)."""
+        f = ctypes.c_int()
+        C.check(C.lib.stx_layer_single_row_fused(self._layer, batch, ctypes.byref(f)))
+        return bool(f.value)
+
     # ---- introspection (each call synchronises)
     def num_active(self) -> int:
         k = ctypes.c_int64()

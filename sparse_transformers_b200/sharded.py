@@ -61,7 +61,9 @@ class ShardedStack:
         self.B, self.L, self.H, self.dtype, self.device = int(batch), len(layers), l0.H, l0.dtype, l0.device
         self.x_in = torch.zeros(self.B, self.H, dtype=self.dtype, device=self.device)
         self.out = torch.zeros(self.L, self.B, self.H, dtype=self.dtype, device=self.device)
-        self.launches_per_step = 7 * self.L  # 6 kernels of this library + 1 NCCL kernel per layer
+        # kernels of this library per layer (single row: t, fused MLP, partial sum, plan, copy;
+        # else: t, scores, gate/up, down, plan, copy) + 1 NCCL kernel
+        self.launches_per_step = ((5 if l0.single_row_fused(self.B) else 6) + 1) * self.L
         self._side = torch.cuda.Stream(device=self.device)
         # eager warm-up on a side stream (NCCL communicators, function attributes), then capture
         s = torch.cuda.Stream(device=self.device)
@@ -91,9 +93,14 @@ class ShardedStack:
         main = torch.cuda.current_stream()
         side = self._side
         for i, l in enumerate(self.layers):
-            l.local.step_stages(C.STAGE_PREDICT, self.x_in, batch=self.B)
-            side.wait_stream(main)  # the side work needs the mask, nothing later
-            l.local.step_stages(C.STAGE_MLP, None, self.x_in, self.out[i], batch=self.B)
+            if l.local.single_row_fused(self.B):
+                # the mask is made inside the MLP kernel: one call, the side work follows it
+                l.local.step_stages(C.STAGE_PREDICT | C.STAGE_MLP, self.x_in, self.x_in, self.out[i], batch=self.B)
+                side.wait_stream(main)
+            else:
+                l.local.step_stages(C.STAGE_PREDICT, self.x_in, batch=self.B)
+                side.wait_stream(main)  # the side work needs the mask, nothing later
+                l.local.step_stages(C.STAGE_MLP, None, self.x_in, self.out[i], batch=self.B)
             with torch.cuda.stream(side):
                 l.local.step_stages(C.STAGE_PLAN | C.STAGE_COPY, batch=self.B)
             dist.all_reduce(self.out[i], op=dist.ReduceOp.SUM, group=l.group)
