@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = workload default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="N>1: sum of the shards' outputs inside the library's kernels over peer memory, or NCCL")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     return ap.parse_args()
 
@@ -224,10 +226,12 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(w, n_gpus):
+def workload_config(w, n_gpus, allreduce="peer"):
     return {"workload": w.name, "hidden": w.H, "intermediate": w.I, "predictor_rank": w.r, "layers": w.layers,
             "batch": w.B, "density_per_row": w.density, "activation": w.act, "threshold": round(w.tau, 6),
-            "parallelism": "single GPU" if n_gpus == 1 else f"intermediate dim sharded over {n_gpus} GPUs + all-reduce per layer",
+            "parallelism": "single GPU" if n_gpus == 1 else
+            f"intermediate dim sharded over {n_gpus} GPUs + all-reduce per layer ("
+            + ("peer-memory stores inside the step's kernels" if allreduce == "peer" else "NCCL") + ")",
             "cache_rows": "copied every step (eager), on a side branch of the step's graph",
             "l2": "distinct weights per layer: one step touches more bytes than the 126 MB L2"}
 
@@ -240,7 +244,7 @@ def run_native(args):
 
     import sparse_transformers_b200 as stb
     from sparse_transformers_b200 import _capi as C
-    from sparse_transformers_b200.sharded import ShardedLayer, ShardedStack, shard_range
+    from sparse_transformers_b200.sharded import PeerExchange, ShardedLayer, ShardedStack, shard_range
     from sparse_transformers_b200.synth import HiddenStream, WORKLOADS, layer_weights
 
     rank = int(os.environ.get("RANK", "0"))
@@ -262,6 +266,7 @@ def run_native(args):
     # ---- weights: generated on the device (identical on every rank), sliced per rank
     gen = torch.Generator(device=dev).manual_seed(0)
     layers = []
+    peer = PeerExchange(w.B * w.H) if world > 1 and args.allreduce == "peer" else None
     cpu_weights = []  # first layers kept on the host for the CPU baseline sample (fp32)
     for li in range(w.layers):
         gate, up, down, A, Bm = layer_weights(w, gen, device=dev)
@@ -272,7 +277,7 @@ def run_native(args):
             lo, hi = shard_range(w.I, rank, world)
             layers.append(ShardedLayer(gate[lo:hi].contiguous(), up[lo:hi].contiguous(), down[:, lo:hi].contiguous(), A,
                                        Bm[lo:hi].contiguous(), act=w.act, method="threshold", param=w.tau,
-                                       max_batch=w.B, has_gate=w.has_gate))
+                                       max_batch=w.B, has_gate=w.has_gate, peer=peer))
         del gate, up, down
     torch.cuda.synchronize()
 
@@ -425,6 +430,11 @@ def run_native(args):
 
     if world > 1:
         stack.close()
+    if peer is not None:
+        if peer.timed_out():
+            print(f"rank {rank}: a wait for a peer's partial sums timed out; the numbers of this run are invalid",
+                  file=sys.stderr)
+        peer.close()
     if rank != 0:
         _finish_distributed(dist, world)
         return
@@ -435,7 +445,7 @@ def run_native(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K_steps, "warmup": W_steps,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
         "vs_baseline": None, "dtype": DTYPE_NAME[str(w.dtype)], "data": "synthetic",
-        "config": workload_config(w, world),
+        "config": workload_config(w, world, args.allreduce),
         "e2e": {"value": w.B / (e2e_total / K_steps), "unit": UNIT, "ms_per_step": e2e_total / K_steps * 1e3,
                 "h2d_bytes_per_step": w.B * w.H * w.dtype.itemsize, "d2h_bytes_per_step": w.layers * w.B * w.H * w.dtype.itemsize},
         "gpu_launches": int(stack.launches_per_step * K_steps),

@@ -65,6 +65,7 @@ typedef enum {
 typedef struct stx_cache stx_cache_t;   /* differential weight cache (one per MLP layer) */
 typedef struct stx_layer stx_layer_t;   /* predictor + cache + scratch of one sparse layer */
 typedef struct stx_stack stx_stack_t;   /* a sequence of layers replayed as one CUDA graph */
+typedef struct stx_peer stx_peer_t;     /* peer-memory exchange of the GPUs that share a layer */
 
 /* ------------------------------------------------------------------ misc */
 
@@ -272,6 +273,42 @@ int stx_stack_step(stx_stack_t* s, const void* x, void* out, void* stream);
 int stx_stack_step_host(stx_stack_t* s, const void* x_host, void* out_host, void* stream);
 /* Number of kernel launches one stack step replays (for launch accounting).            */
 int stx_stack_launches_per_step(stx_stack_t* s, int64_t* n_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Intermediate-dimension sharding over the GPUs of one node: the sum of the shards' partial
+ * down projections.  The reference has no multi-GPU path; these entries implement the
+ * all-reduce that sharding its MLP (sparse_mlp_op.cpp:66-94, the down projection sums over
+ * neurons) needs.  One process per GPU.  Every rank creates a peer object (it ALLOCATES a
+ * buffer of 16 * world * max_elems bytes on the current device), the host side exchanges the
+ * 64-byte handles by any means (torch.distributed in this package) and connects.  A call of
+ * stx_peer_allreduce - or a layer step after stx_layer_set_peer - is collective: every rank
+ * must make the same calls in the same order.  The sum runs in fp32 in ascending rank order
+ * (bit-identical on all ranks) inside ONE kernel that stores to the peers' memory over
+ * NVLink and polls its own; there is no library collective underneath.  Waits are bounded
+ * (environment STX_PEER_WAIT_ITERS at create time, default 2^22 polls, a few seconds): a
+ * rank that never arrives makes the others finish with a wrong sum and STX_ERR_TIMEOUT in
+ * stx_peer_status, it does not hang them.                                                */
+#define STX_PEER_HANDLE_BYTES 64
+int stx_peer_create(stx_peer_t** out, int rank, int world, int64_t max_elems);
+int stx_peer_destroy(stx_peer_t* p);
+/* Writes the STX_PEER_HANDLE_BYTES-byte interprocess handle of this rank's buffer.       */
+int stx_peer_ipc_handle(stx_peer_t* p, void* handle_out);
+/* handles: world * STX_PEER_HANDLE_BYTES bytes, rank-major (the own entry is ignored).
+ * Every rank must have created its object before any rank connects.                     */
+int stx_peer_connect_ipc(stx_peer_t* p, const void* handles);
+/* Same-process alternative (one process driving several GPUs with peer access enabled):
+ * buffers[q] = stx_peer_local_buffer of rank q's object.                                */
+int stx_peer_connect_ptrs(stx_peer_t* p, void* const* buffers);
+int stx_peer_local_buffer(stx_peer_t* p, void** buffer_out);
+/* data[0..n) <- element-wise sum over ranks, in place; n <= max_elems.  Asynchronous,
+ * allocation-free, graph-capturable.                                                    */
+int stx_peer_allreduce(stx_peer_t* p, void* data, int64_t n, int dtype, void* stream);
+/* SYNCHRONISES the stream; *status_out = STX_OK or STX_ERR_TIMEOUT (sticky).             */
+int stx_peer_status(stx_peer_t* p, int* status_out, void* stream);
+/* After this call a step of the layer ends with the all-reduce of its output over the
+ * peer object's ranks: inside the step's last kernel for the single-row path, as one more
+ * kernel otherwise.  peer == NULL detaches.  Set before capturing a stack.               */
+int stx_layer_set_peer(stx_layer_t* l, stx_peer_t* peer);
 
 #ifdef __cplusplus
 }

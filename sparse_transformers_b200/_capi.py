@@ -16,6 +16,7 @@ F32, F16, BF16 = 0, 1, 2
 ACT_RELU, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID, ACT_GELU = range(5)
 MASK_THRESHOLD, MASK_TOPK, MASK_STATISTICAL = range(3)
 CACHE_ALIAS_GATE_UP = 1
+PEER_HANDLE_BYTES = 64
 STAGE_PREDICT, STAGE_PLAN, STAGE_COPY, STAGE_MLP_GATEUP, STAGE_MLP_DOWN, STAGE_MLP, STAGE_ALL = 33, 2, 4, 8, 16, 24, 63
 STAGE_PREDICT_T, STAGE_PREDICT_MASK = 1, 32
 
@@ -70,6 +71,15 @@ SIGNATURES = {
     "stx_stack_step": (_i32, [_vp, _vp, _vp, _vp]),
     "stx_stack_step_host": (_i32, [_vp, _vp, _vp, _vp]),
     "stx_stack_launches_per_step": (_i32, [_vp, _pi64]),
+    "stx_peer_create": (_i32, [_pp, _i32, _i32, _i64]),
+    "stx_peer_destroy": (_i32, [_vp]),
+    "stx_peer_ipc_handle": (_i32, [_vp, _vp]),
+    "stx_peer_connect_ipc": (_i32, [_vp, _vp]),
+    "stx_peer_connect_ptrs": (_i32, [_vp, _pp]),
+    "stx_peer_local_buffer": (_i32, [_vp, _pp]),
+    "stx_peer_allreduce": (_i32, [_vp, _vp, _i64, _i32, _vp]),
+    "stx_peer_status": (_i32, [_vp, ctypes.POINTER(ctypes.c_int), _vp]),
+    "stx_layer_set_peer": (_i32, [_vp, _vp]),
 }
 
 

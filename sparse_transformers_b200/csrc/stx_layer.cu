@@ -4,6 +4,7 @@
 // one stream with K resident on the device (no host read-back, no allocation), i.e. the
 // sparse branch of SkipDecoderLayer.forward (src/modeling_skip.py:236-238 and :258).
 #include "stx_cache.cuh"
+#include "stx_peer.cuh"
 
 #include <algorithm>
 #include <new>
@@ -18,7 +19,9 @@ bool layer_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype
                         const void* down, const void* Bm);
 int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
                      const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
-                     int has_gate, int dtype, float* partial, int* status, unsigned parts, cudaStream_t s);
+                     int has_gate, int dtype, float* partial, int* status, unsigned parts, const stx_peer* peer,
+                     cudaStream_t s);
+int peer_allreduce(const stx_peer* p, void* data, int64_t n, int dtype, cudaStream_t s);
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
                 int act, int has_gate, int dtype, void* scratch, int* status, unsigned parts,
@@ -43,6 +46,7 @@ struct stx_layer {
   void* scores = nullptr;        // [max_batch, I], only for rules that need whole rows
   void* pred_scratch = nullptr;
   void* mlp_scratch = nullptr;
+  stx_peer* peer = nullptr;  // not owned: the shards' exchange; a step then ends with the all-reduce
   void* x_stage = nullptr;       // [max_batch, H] for the host-buffer entry point
   void* out_stage = nullptr;
 };
@@ -167,7 +171,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
     const float* t = static_cast<const float*>(l->pred_scratch);
     if (stages & STX_STAGE_MLP_GATEUP) {
       rc = layer_b1_forward(x_mlp, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
-                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 1u, s);
+                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 1u, l->peer, s);
       if (rc != STX_OK) return rc;
     }
     if (fork_needed) {  // the mask exists once that kernel is done
@@ -176,7 +180,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
     }
     if (stages & STX_STAGE_MLP_DOWN) {
       rc = layer_b1_forward(x_mlp, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
-                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 2u, s);
+                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 2u, l->peer, s);
       if (rc != STX_OK) return rc;
     }
   }
@@ -201,6 +205,10 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       rc = mlp_forward(x_mlp, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, l->act,
                        c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, nullptr, nullptr, nullptr, true, s);
     if (rc != STX_OK) return rc;
+    if ((stages & STX_STAGE_MLP_DOWN) && l->peer && l->peer->world > 1) {
+      rc = peer_allreduce(l->peer, out, B * c->H, c->dtype, s);
+      if (rc != STX_OK) return rc;
+    }
   }
   if (l->gather) {
     if (stages & STX_STAGE_PLAN) {
@@ -232,6 +240,18 @@ int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_
 int stx_layer_set_lazy_cache(stx_layer_t* l, int lazy) {
   STX_CHECK_ARG(l, "stx_layer_set_lazy_cache: null layer");
   l->lazy = lazy != 0 && l->gather;
+  return STX_OK;
+}
+
+int stx_layer_set_peer(stx_layer_t* l, stx_peer_t* peer) {
+  STX_CHECK_ARG(l, "stx_layer_set_peer: null layer");
+  if (peer) {
+    STX_CHECK_ARG(peer->connected, "stx_layer_set_peer: connect the peer object first");
+    STX_CHECK_ARG(peer->max_elems >= l->max_batch * l->cache->H,
+                  "stx_layer_set_peer: max_elems=%lld is smaller than max_batch*H=%lld", static_cast<long long>(peer->max_elems),
+                  static_cast<long long>(l->max_batch * l->cache->H));
+  }
+  l->peer = peer;
   return STX_OK;
 }
 

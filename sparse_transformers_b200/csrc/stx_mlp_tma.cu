@@ -22,6 +22,7 @@
 // DEV_TIMEOUT in the status word and carries on with the same control flow (the result is
 // then garbage, but no thread is left waiting and the context stays usable).
 #include "stx_common.cuh"
+#include "stx_peer.cuh"
 
 #include <cooperative_groups.h>
 
@@ -944,9 +945,13 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
 }
 
 // out[h] = sum_c partial[c][h], c ascending.  Block: 32 columns x 32 groups of CTAs; a group
-// adds a contiguous range of CTAs in order, then the groups are added in order.
+// adds a contiguous range of CTAs in order, then the groups are added in order.  With peers
+// (pa.world > 1: the layer is one shard of several GPUs) the column sums are then exchanged
+// over peer memory and added in rank order before the output is written: the all-reduce of the
+// sharded down projection costs no extra launch.
 template <typename T>
-__global__ void __launch_bounds__(1024) k_partial_reduce(const float* __restrict__ partial, int G, int H, T* __restrict__ out) {
+__global__ void __launch_bounds__(1024) k_partial_reduce(const float* __restrict__ partial, int G, int H, T* __restrict__ out,
+                                                         const __grid_constant__ PeerArgs pa) {
   __shared__ float s_r[32][33];
   const int hc = threadIdx.x & 31, grp = threadIdx.x >> 5;
   const int h = blockIdx.x * 32 + hc;
@@ -954,6 +959,8 @@ __global__ void __launch_bounds__(1024) k_partial_reduce(const float* __restrict
   const int c0 = grp * per, c1 = min(G, c0 + per);
   pdl_wait();
   pdl_launch_dependents();
+  const bool shared = pa.world > 1;
+  const int epoch = shared ? peer_epoch_begin(pa) : 0;
   float sum = 0.f;
   if (h < H) {
 #pragma unroll 8
@@ -965,8 +972,15 @@ __global__ void __launch_bounds__(1024) k_partial_reduce(const float* __restrict
     float t = 0.f;
 #pragma unroll
     for (int g = 0; g < 32; ++g) t += s_r[g][hc];
+    if (shared) {
+      bool timed_out = false;
+      peer_push(pa, epoch, h, t);
+      t = peer_collect(pa, epoch, h, t, &timed_out);
+      if (timed_out) atomicOr(pa.ctl + 2, DEV_TIMEOUT);
+    }
     out[h] = DT<T>::from_f(t);
   }
+  if (shared) peer_epoch_end(pa, epoch);
 }
 
 constexpr size_t TMA_SMEM_BUDGET = 220 * 1024;
@@ -1103,6 +1117,7 @@ static int b1_slots(int H, int has_gate, int r) {
 }
 
 struct B1Pred {  // predictor back half fused into k_mlp_b1 (Bm == nullptr: not fused)
+  PeerArgs peer = {};  // world > 1: k_partial_reduce ends with the all-reduce over the shards
   const float* t = nullptr;
   const void* Bm = nullptr;
   uint32_t* bits = nullptr;
@@ -1138,7 +1153,7 @@ static int launch_b1(const GateUpArgs& g, const void* down, float* partial, void
   if (parts & 1u) STX_CUDA(launch_pdl(k_mlp_b1<T>, dim3(grid), dim3(512), smem, s, q));
   if (parts & 2u)
     STX_CUDA(launch_pdl(k_partial_reduce<T>, dim3((g.H + 31) / 32), dim3(1024), 0, s, static_cast<const float*>(partial),
-                        grid, g.H, static_cast<T*>(out)));
+                        grid, g.H, static_cast<T*>(out), pr.peer));
   return STX_OK;
 }
 
@@ -1193,7 +1208,8 @@ bool layer_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype
 
 int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
                      const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
-                     int has_gate, int dtype, float* partial, int* status, unsigned parts, cudaStream_t s) {
+                     int has_gate, int dtype, float* partial, int* status, unsigned parts, const stx_peer* peer,
+                     cudaStream_t s) {
   GateUpArgs a;
   a.x = x;
   a.gate = gate;
@@ -1218,6 +1234,16 @@ int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, cons
   pr.bits = bits;
   pr.r = static_cast<int>(r);
   pr.tau = tau;
+  if (peer && peer->world > 1) {
+    if (!peer_args(peer, &pr.peer)) {
+      set_error("stx_layer_step: the layer's peer object is not connected");
+      return STX_ERR_INVALID_ARG;
+    }
+    if (H > peer->max_elems) {
+      set_error("stx_layer_step: H=%lld exceeds the peer object's max_elems", static_cast<long long>(H));
+      return STX_ERR_INVALID_ARG;
+    }
+  }
   const int grid = std::max(1, num_sms() - 1);
   switch (dtype) {
     case STX_F32: return launch_b1<float>(a, down, partial, out, grid, parts, pr, s);

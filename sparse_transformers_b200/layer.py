@@ -85,6 +85,12 @@ class SparseLayer:
         takes effect for steps enqueued, and stacks captured, afterwards."""
         C.check(C.lib.stx_layer_set_lazy_cache(self._layer, int(bool(lazy))))
 
+    def set_peer(self, peer) -> None:
+        """peer: sharded.PeerExchange (or None).  A step then ends with the sum of the shards'
+        outputs over peer memory; every rank must step its shard in the same order."""
+        self._peer = peer  # keep it alive as long as the layer points at it
+        C.check(C.lib.stx_layer_set_peer(self._layer, peer.handle if peer is not None else None))
+
     def step(self, x_pred: torch.Tensor, x_mlp: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
         x_mlp = x_pred if x_mlp is None else x_mlp
         _need_cuda(x_pred, x_mlp)

@@ -5,13 +5,21 @@ contiguous neuron range shard_range(I, g, G): the matching rows of gate / up / t
 predictor's up matrix and the matching columns of down.  The predictor's down matrix A and
 the hidden states are replicated.  Every rank runs its own predictor slice, mask and
 differential weight cache (identical to a single-GPU cache built on the sliced weights) and
-produces a partial [B,H]; one all-reduce(sum) per layer per step combines them (NCCL over
-NVLink).  The per-row rules that need whole-row statistics (topk, statistical_topk) are not
+produces a partial [B,H]; one all-reduce(sum) per layer per step combines them.  Two ways:
+
+  peer  (PeerExchange) the step's own last kernel pushes its fp32 sums into the other GPUs'
+        memory over NVLink and adds what they pushed, in rank order: no extra launch for a
+        single row, one small kernel otherwise; results are bit-identical on all ranks
+  nccl  torch.distributed.all_reduce on the layer's output (model dtype)
+
+The per-row rules that need whole-row statistics (topk, statistical_topk) are not
 shard-local; sharded layers use the explicit-threshold rule.
 """
 from __future__ import annotations
 
 from typing import Sequence
+
+import ctypes
 
 import torch
 import torch.distributed as dist
@@ -33,18 +41,68 @@ def shard_weights(gate, up, down, A, Bm, rank: int, world: int):
     return (gate[lo:hi] if gate is not None else None), up[lo:hi], down[:, lo:hi], A, Bm[lo:hi]
 
 
-class ShardedLayer:
-    """SparseLayer on this rank's shard plus the all-reduce of the partial sums."""
+_DTYPE = {torch.float32: C.F32, torch.float16: C.F16, torch.bfloat16: C.BF16}
 
-    def __init__(self, gate, up, down, lora_down, lora_up, *, group=None, **kw):
+
+class PeerExchange:
+    """This rank's exchange buffer for sums over the process group's GPUs (one node, one process
+    per GPU, current CUDA device).  Construction is collective: the ranks swap the buffers'
+    interprocess handles through torch.distributed and map each other's memory."""
+
+    def __init__(self, max_elems: int, group=None):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        p = ctypes.c_void_p()
+        C.check(C.lib.stx_peer_create(ctypes.byref(p), self.rank, self.world, int(max_elems)))
+        self.handle = p
+        if self.world > 1:
+            h = ctypes.create_string_buffer(C.PEER_HANDLE_BYTES)
+            C.check(C.lib.stx_peer_ipc_handle(p, h))
+            handles: list = [None] * self.world
+            dist.all_gather_object(handles, bytes(h.raw), group=group)
+            blob = ctypes.create_string_buffer(b"".join(handles), C.PEER_HANDLE_BYTES * self.world)
+            C.check(C.lib.stx_peer_connect_ipc(p, blob))
+            dist.barrier(group)  # nobody pushes before everybody has mapped
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum of `t` (contiguous CUDA tensor) over the ranks, on the current stream."""
+        C.check(C.lib.stx_peer_allreduce(self.handle, t.data_ptr(), t.numel(), _DTYPE[t.dtype],
+                                         torch.cuda.current_stream().cuda_stream))
+        return t
+
+    def timed_out(self) -> bool:
+        """True when some wait for a peer gave up since creation (synchronises the stream)."""
+        st = ctypes.c_int()
+        C.check(C.lib.stx_peer_status(self.handle, ctypes.byref(st), torch.cuda.current_stream().cuda_stream))
+        return st.value != C.OK
+
+    def close(self) -> None:
+        """Collective: every rank must be done stepping before anybody unmaps."""
+        if self.handle is not None:
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(self.group)
+            C.lib.stx_peer_destroy(self.handle)
+            self.handle = None
+
+
+class ShardedLayer:
+    """SparseLayer on this rank's shard plus the all-reduce of the partial sums (peer: a
+    PeerExchange shared by the layers of this rank; None: NCCL)."""
+
+    def __init__(self, gate, up, down, lora_down, lora_up, *, group=None, peer: PeerExchange | None = None, **kw):
         if kw.get("method", "threshold") not in ("threshold", "naive"):
             raise ValueError("sharded layers support the explicit-threshold rule only")
         self.group = group
+        self.peer = peer
         self.local = SparseLayer(gate, up, down, lora_down, lora_up, **kw)
+        if peer is not None:
+            self.local.set_peer(peer)
 
     def step(self, x_pred, x_mlp=None, out=None):
         out = self.local.step(x_pred, x_mlp, out)
-        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        if self.peer is None:
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out
 
     def close(self):
@@ -63,7 +121,9 @@ class ShardedStack:
         self.out = torch.zeros(self.L, self.B, self.H, dtype=self.dtype, device=self.device)
         # kernels of this library per layer (single row: t, fused MLP, partial sum, plan, copy;
         # else: t, scores, gate/up, down, plan, copy) + 1 NCCL kernel
-        self.launches_per_step = ((5 if l0.single_row_fused(self.B) else 6) + 1) * self.L
+        # (with a PeerExchange the sum rides in the partial-sum kernel of the single-row path)
+        fused, peer = l0.single_row_fused(self.B), self.layers[0].peer is not None
+        self.launches_per_step = ((5 if fused else 6) + (0 if fused and peer else 1)) * self.L
         self._side = torch.cuda.Stream(device=self.device)
         # eager warm-up on a side stream (NCCL communicators, function attributes), then capture
         s = torch.cuda.Stream(device=self.device)
@@ -103,7 +163,8 @@ class ShardedStack:
                 l.local.step_stages(C.STAGE_MLP, None, self.x_in, self.out[i], batch=self.B)
             with torch.cuda.stream(side):
                 l.local.step_stages(C.STAGE_PLAN | C.STAGE_COPY, batch=self.B)
-            dist.all_reduce(self.out[i], op=dist.ReduceOp.SUM, group=l.group)
+            if l.peer is None:
+                dist.all_reduce(self.out[i], op=dist.ReduceOp.SUM, group=l.group)
         main.wait_stream(side)
 
     def step(self, x: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:

@@ -1,6 +1,7 @@
-"""Intermediate-dimension sharding on real GPUs (NCCL): sharded layers + all-reduce equal the
-single-GPU layer; per-shard masks and cache orders equal the single-GPU ones restricted to
-the shard.  Needs at least two GPUs (skipped otherwise)."""
+"""Intermediate-dimension sharding on real GPUs: sharded layers + all-reduce (through peer
+memory inside the library's own kernels, or NCCL) equal the single-GPU layer; per-shard masks
+and cache orders equal the single-GPU ones restricted to the shard.  The multi-GPU cases need
+at least two GPUs (skipped otherwise); the bounded-wait case runs on one."""
 import os
 import socket
 
@@ -17,29 +18,39 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, out_dir):
+def _rank_main(rank, world, port, out_dir, mode, batch):
     import sys
 
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import torch.distributed as dist
 
     from sparse_transformers_b200 import SparseLayer
-    from sparse_transformers_b200.sharded import ShardedLayer, ShardedStack, shard_range, shard_weights
+    from sparse_transformers_b200.sharded import PeerExchange, ShardedLayer, ShardedStack, shard_range, shard_weights
     from sparse_transformers_b200.synth import HiddenStream, Workload, layer_weights
 
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
-    w = Workload("shard", H=1024, I=4096, r=32, B=4, dtype=torch.bfloat16, density=0.2, alpha=0.5, layers=2)
+    w = Workload("shard", H=1024, I=4096, r=32, B=batch, dtype=torch.bfloat16, density=0.2, alpha=0.5, layers=2)
+    peer = PeerExchange(w.B * w.H) if mode == "peer" else None
+    ok = True
+    if peer is not None:  # the stand-alone collective first: every rank contributes rank + 1
+        for dt in (torch.float32, torch.float16, torch.bfloat16):
+            for n in (1, 777, w.B * w.H):
+                v = (torch.arange(n, device=dev, dtype=torch.float32) % 13 + rank + 1).to(dt)
+                want = sum((torch.arange(n, dtype=torch.float32) % 13 + q + 1) for q in range(world)).to(dt)
+                peer.all_reduce(v)
+                torch.cuda.synchronize()
+                ok &= torch.equal(v.cpu(), want)
     gen = torch.Generator().manual_seed(0)
     ws = [layer_weights(w, gen) for _ in range(w.layers)]
     xs = HiddenStream(w, gen).take(6)
     lo, hi = shard_range(w.I, rank, world)
     sharded = [ShardedLayer(*[t.contiguous().to(dev) for t in shard_weights(*lw, rank, world)], act=w.act, param=w.tau,
-                            max_batch=w.B) for lw in ws]
+                            max_batch=w.B, peer=peer) for lw in ws]
+    assert sharded[0].local.single_row_fused(w.B) == (w.B == 1)
     full = [SparseLayer(*[t.to(dev) for t in lw], act=w.act, param=w.tau, max_batch=w.B) for lw in ws] if rank == 0 else None
     stack = ShardedStack(sharded, w.B, xs[0].to(dev))
-    ok = True
     out = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=dev)
     # the stack's warm-up advanced the shard caches with xs[0] twice; do the same on the full layers
     if rank == 0:
@@ -60,18 +71,71 @@ def _rank_main(rank, world, port, out_dir):
                 ok &= torch.equal(masks[li], l.mask().cpu()[lo:hi])
                 mine = set(orders[li].tolist())
                 ok &= mine == {i for i in l.active_indices().tolist() if lo <= i < hi}
+    if peer is not None:
+        ok &= not peer.timed_out()
+        # all ranks hold the same bits
+        mine = out.float().cpu()
+        both = [None] * world
+        dist.all_gather_object(both, mine)
+        ok &= all(torch.equal(both[0], b) for b in both)
+    oks = [None] * world
+    dist.all_gather_object(oks, ok)
     if rank == 0:
         with open(os.path.join(out_dir, "ok.txt"), "w") as fh:
-            fh.write("1" if ok else "0")
+            fh.write("1" if all(oks) else "0")
     stack.close()
     torch.cuda.synchronize()
     dist.barrier()
+    if peer is not None:
+        peer.close()
     os._exit(0)  # not destroy_process_group(): it blocked after collectives were captured in a graph
 
 
-def test_two_gpu_sharded_stack_matches_single_gpu(tmp_path):
+@pytest.mark.parametrize("mode,batch", [("nccl", 4), ("peer", 4), ("peer", 1), ("nccl", 1)])
+def test_two_gpu_sharded_stack_matches_single_gpu(tmp_path, mode, batch):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     port = _free_port()
-    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path), mode, batch), nprocs=2, join=True)
     assert open(tmp_path / "ok.txt").read() == "1"
+
+
+def test_four_gpu_peer_allreduce(tmp_path):
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    port = _free_port()
+    mp.spawn(_rank_main, args=(4, port, str(tmp_path), "peer", 1), nprocs=4, join=True)
+    assert open(tmp_path / "ok.txt").read() == "1"
+
+
+def test_peer_wait_is_bounded(monkeypatch):
+    """A peer that never sends: the kernel gives up after its poll limit, reports the timeout
+    through the status word and the context stays usable.  World of two with the other rank's
+    buffer played by a second buffer on this GPU that nobody writes."""
+    import ctypes
+
+    from sparse_transformers_b200 import _capi as C
+
+    monkeypatch.setenv("STX_PEER_WAIT_ITERS", "2000")
+    a, b = ctypes.c_void_p(), ctypes.c_void_p()
+    C.check(C.lib.stx_peer_create(ctypes.byref(a), 0, 2, 4096))
+    C.check(C.lib.stx_peer_create(ctypes.byref(b), 1, 2, 4096))  # only its buffer is used
+    try:
+        pa, pb = ctypes.c_void_p(), ctypes.c_void_p()
+        C.check(C.lib.stx_peer_local_buffer(a, ctypes.byref(pa)))
+        C.check(C.lib.stx_peer_local_buffer(b, ctypes.byref(pb)))
+        bufs = (ctypes.c_void_p * 2)(pa.value, pb.value)
+        C.check(C.lib.stx_peer_connect_ptrs(a, bufs))
+        v = torch.ones(1000, device="cuda")
+        st = ctypes.c_int()
+        s = torch.cuda.current_stream().cuda_stream
+        C.check(C.lib.stx_peer_status(a, ctypes.byref(st), s))
+        assert st.value == C.OK
+        C.check(C.lib.stx_peer_allreduce(a, v.data_ptr(), v.numel(), C.F32, s))
+        C.check(C.lib.stx_peer_status(a, ctypes.byref(st), s))
+        assert st.value == C.ERR_TIMEOUT
+        assert torch.equal(v.cpu(), torch.ones(1000))  # the own term only
+        assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0  # context alive
+    finally:
+        C.lib.stx_peer_destroy(a)
+        C.lib.stx_peer_destroy(b)
