@@ -556,10 +556,51 @@ def run_prefill(args):
     print(json.dumps(line), flush=True)
 
 
+def run_llama_skip(args):
+    """`--workload C2-e2e`: the Llama-3.2-3B-shaped LlamaSkip host end to end (random-init weights,
+    512 random prompt ids, 128 greedy tokens): TTFT and output tokens/s as the reference's benchmark
+    defines them.  Attention, norms and lm_head are torch ops; the decode-time MLP is this library."""
+    import torch
+
+    from sparse_transformers_b200.llama_skip import LlamaSkipConfig, LlamaSkipModel
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    dev = torch.device("cuda", 0)
+    cfg = LlamaSkipConfig(layers=args.layers or 28)
+    prompt = torch.randint(0, cfg.vocab, (512,), generator=torch.Generator().manual_seed(0)).to(dev)
+    n_new = 128
+    out = {}
+    for lazy in (False, True):
+        cfg.lazy_cache = lazy
+        m = LlamaSkipModel(cfg, dev, seed=0)
+        m.generate(prompt, 16)  # warm-up: cuBLAS handles, graph capture
+        runs = [m.generate(prompt, n_new) for _ in range(3)]
+        best = max(runs, key=lambda r: r["output_tokens_per_s"])
+        dens = [float(L["sparse"].num_active()) / cfg.intermediate for L in m.layers]
+        out["lazy" if lazy else "eager"] = dict(ttft_s=min(r["ttft_s"] for r in runs), output_tokens_per_s=best["output_tokens_per_s"],
+                                                total_tokens_per_s=best["total_tokens_per_s"], active_fraction=sum(dens) / len(dens))
+        m.close()
+        del m
+        torch.cuda.empty_cache()
+    e = out["eager"]
+    print(json.dumps({
+        "metric": "llamaskip_output_tokens_per_s", "value": e["output_tokens_per_s"], "unit": UNIT, "n_gpus": 1,
+        "higher_is_better": True, "dtype": "f16", "data": "synthetic", "ttft_s": e["ttft_s"],
+        "total_tokens_per_s": e["total_tokens_per_s"], "active_fraction_last_token": e["active_fraction"],
+        "value_lazy_cache_rows": out["lazy"]["output_tokens_per_s"], "vs_baseline": None,
+        "config": {"workload": "C2-llamaskip-3b-e2e-fp16", "layers": cfg.layers, "hidden": cfg.hidden, "intermediate": cfg.intermediate,
+                   "heads": cfg.heads, "kv_heads": cfg.kv_heads, "vocab": cfg.vocab, "rope_theta": cfg.rope_theta,
+                   "predictor_rank": cfg.predictor_rank, "density_target": cfg.density, "prompt_tokens": 512, "new_tokens": n_new,
+                   "decode": "one CUDA graph per token; MLP sparse (this library); attention/norms/lm_head torch",
+                   "prefill": "dense (torch GEMMs), as the reference does for sequences longer than one token"}}), flush=True)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "C2-e2e":
+        run_llama_skip(args)
     elif args.workload == "C4":
         run_prefill(args)
     else:

@@ -1,0 +1,243 @@
+"""Minimal LlamaSkip host: a Llama-architecture decoder whose MLP runs dense in prefill and
+through the sparse layer step (predictor -> mask -> weight cache -> sparse MLP) in decode.
+
+Mirrors the reference's inference model for this path (src/modeling_skip.py:131-266: decoder
+layer with the mask computed from the input-layernorm output and the sparse MLP applied to the
+post-attention-layernorm output, dense for sequences longer than one token;
+src/models/llama/modelling_llama_skip.py:30-66: RMSNorm and layer wiring).  Attention, norms,
+embedding and lm_head are ordinary torch ops: they are the host around the path, not the path.
+Weights are random (N(0, 0.02), seeded): checkpoints are not available offline.
+
+The decode step (all layers, lm_head, greedy argmax, KV-cache append, position advance) is
+captured once into a CUDA graph and replayed per token with no host synchronisation; each
+layer's cache maintenance runs on a side stream inside the same graph.
+"""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass
+from statistics import NormalDist
+
+import torch
+import torch.nn.functional as F
+
+from . import _capi as C
+from .layer import SparseLayer
+
+
+@dataclass
+class LlamaSkipConfig:
+    vocab: int = 128256
+    hidden: int = 3072
+    intermediate: int = 8192
+    layers: int = 28
+    heads: int = 24
+    kv_heads: int = 8
+    head_dim: int = 128
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+    predictor_rank: int = 64
+    density: float = 0.20          # active fraction per token the threshold aims at
+    act: str = "silu"
+    max_len: int = 1024
+    dtype: torch.dtype = torch.float16
+    wstd: float = 0.02             # initializer_range
+    lazy_cache: bool = False
+
+    @property
+    def tau(self) -> float:
+        # scores of a unit-RMS input are ~N(0, wstd^4 H r)
+        return self.wstd ** 2 * math.sqrt(self.hidden * self.predictor_rank) * NormalDist().inv_cdf(1.0 - self.density)
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def rope_tables(cfg: LlamaSkipConfig, device) -> tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device, dtype=torch.float32) / cfg.head_dim))
+    ang = torch.arange(cfg.max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    emb = torch.cat([ang, ang], dim=-1)
+    return emb.cos(), emb.sin()  # [max_len, head_dim] fp32
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [heads, T, hd]; cos/sin [T, hd] (rotate-half convention)."""
+    h = x.shape[-1] // 2
+    rot = torch.cat([-x[..., h:], x[..., :h]], dim=-1)
+    return (x.float() * cos + rot.float() * sin).to(x.dtype)
+
+
+class LlamaSkipModel:
+    def __init__(self, cfg: LlamaSkipConfig, device: torch.device | str = "cuda", seed: int = 0):
+        self.cfg, self.device = cfg, torch.device(device)
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        dt = cfg.dtype
+
+        def rn(*shape):
+            return (torch.randn(*shape, generator=g, device=self.device, dtype=torch.float32) * cfg.wstd).to(dt)
+
+        H, I, hd = cfg.hidden, cfg.intermediate, cfg.head_dim
+        self.embed = rn(cfg.vocab, H)          # tied with lm_head, as Llama-3.2 does
+        self.final_norm = torch.ones(H, dtype=dt, device=self.device)
+        self.layers = []
+        for _ in range(cfg.layers):
+            L = dict(
+                wqkv=rn((cfg.heads + 2 * cfg.kv_heads) * hd, H), wo=rn(H, cfg.heads * hd),
+                ln1=torch.ones(H, dtype=dt, device=self.device), ln2=torch.ones(H, dtype=dt, device=self.device),
+                gate=rn(I, H), up=rn(I, H), down=rn(H, I), A=rn(cfg.predictor_rank, H), Bm=rn(I, cfg.predictor_rank))
+            L["sparse"] = SparseLayer(L["gate"], L["up"], L["down"], L["A"], L["Bm"], act=cfg.act, method="threshold",
+                                      param=cfg.tau, max_batch=1, alias_gate_up=True, init_all_active=True,
+                                      lazy_cache=cfg.lazy_cache)
+            self.layers.append(L)
+        self.cos, self.sin = rope_tables(cfg, self.device)
+        self.k_cache = torch.zeros(cfg.layers, cfg.kv_heads, cfg.max_len, hd, dtype=dt, device=self.device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        # decode state, all on the device so that the captured step needs no host input
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.gen_base = torch.zeros(1, dtype=torch.long, device=self.device)  # prompt length of the current generation
+        self.token = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.generated = torch.zeros(cfg.max_len, dtype=torch.long, device=self.device)
+        self.logits = torch.zeros(cfg.vocab, dtype=torch.float32, device=self.device)
+        self._arange = torch.arange(cfg.max_len, device=self.device)
+        self._side = torch.cuda.Stream(device=self.device)
+        self._graph = None
+        self.trace = None  # when a list: per decode step and layer (x_pred, x_mlp, mlp_out, mask) copies, eager mode only
+
+    # ------------------------------------------------------------------ pieces
+    def _attention(self, li: int, x: torch.Tensor, pos0, T: int, decode: bool) -> torch.Tensor:
+        cfg, L = self.cfg, self.layers[li]
+        hd, nh, nkv = cfg.head_dim, cfg.heads, cfg.kv_heads
+        qkv = x @ L["wqkv"].t()                                                  # [T, (nh+2nkv)*hd]
+        q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
+        q = q.view(T, nh, hd).transpose(0, 1)
+        k = k.view(T, nkv, hd).transpose(0, 1)
+        v = v.view(T, nkv, hd).transpose(0, 1)
+        if decode:
+            idx = self.pos                                                       # device scalar [1]
+            cos, sin = self.cos.index_select(0, idx), self.sin.index_select(0, idx)
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            self.k_cache[li].index_copy_(1, idx, k)
+            self.v_cache[li].index_copy_(1, idx, v)
+            mask = (self._arange <= idx).view(1, 1, cfg.max_len)                  # keys 0..pos
+            o = F.scaled_dot_product_attention(q.unsqueeze(0), self.k_cache[li].unsqueeze(0), self.v_cache[li].unsqueeze(0),
+                                               attn_mask=mask.unsqueeze(0), enable_gqa=True)
+        else:
+            cos, sin = self.cos[pos0:pos0 + T], self.sin[pos0:pos0 + T]
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            self.k_cache[li, :, pos0:pos0 + T] = k
+            self.v_cache[li, :, pos0:pos0 + T] = v
+            o = F.scaled_dot_product_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), is_causal=True, enable_gqa=True)
+        o = o.squeeze(0).transpose(0, 1).reshape(T, nh * hd)
+        return o @ L["wo"].t()
+
+    def _dense_mlp(self, li: int, x: torch.Tensor) -> torch.Tensor:
+        L = self.layers[li]
+        act = {"silu": F.silu, "relu": F.relu, "gelu_pytorch_tanh": lambda t: F.gelu(t, approximate="tanh")}[self.cfg.act]
+        return (act(x @ L["gate"].t()) * (x @ L["up"].t())) @ L["down"].t()
+
+    # ------------------------------------------------------------------ prefill (dense MLP)
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [T] on the device.  Fills the KV cache, returns the greedy next token [1] and leaves
+        the decode state (position, token) ready."""
+        cfg, T = self.cfg, int(ids.numel())
+        h = self.embed.index_select(0, ids)
+        for li, L in enumerate(self.layers):
+            a = self._attention(li, rms_norm(h, L["ln1"], cfg.rms_eps), 0, T, decode=False)
+            h = h + a
+            h = h + self._dense_mlp(li, rms_norm(h, L["ln2"], cfg.rms_eps))
+        last = rms_norm(h[-1:], self.final_norm, cfg.rms_eps)
+        self.logits.copy_((last @ self.embed.t()).float().view(-1))
+        nxt = self.logits.argmax().view(1)
+        self.token.copy_(nxt)
+        self.pos.fill_(T)
+        self.generated.zero_()
+        self.generated[0:1] = nxt
+        self.gen_base.fill_(T)
+        return nxt
+
+    # ------------------------------------------------------------------ one decode token
+    def _decode_body(self) -> None:
+        cfg = self.cfg
+        main = torch.cuda.current_stream()
+        h = self.embed.index_select(0, self.token)                              # [1,H]
+        for li, L in enumerate(self.layers):
+            x_pred = rms_norm(h, L["ln1"], cfg.rms_eps)                          # the predictor's input
+            h = h + self._attention(li, x_pred, None, 1, decode=True)
+            x_mlp = rms_norm(h, L["ln2"], cfg.rms_eps).contiguous()
+            out = torch.empty_like(x_mlp)
+            sp: SparseLayer = L["sparse"]
+            sp.step_stages(C.STAGE_PREDICT | C.STAGE_MLP, x_pred.contiguous(), x_mlp, out, batch=1)
+            self._side.wait_stream(main)                                         # cache upkeep off the critical path
+            with torch.cuda.stream(self._side):
+                sp.step_stages(C.STAGE_PLAN | C.STAGE_COPY, batch=1)
+            if self.trace is not None:
+                self.trace.append((li, x_pred.clone(), x_mlp.clone(), out.clone(), sp.mask().clone()))
+            h = h + out
+        main.wait_stream(self._side)
+        last = rms_norm(h, self.final_norm, cfg.rms_eps)
+        self.logits.copy_((last @ self.embed.t()).float().view(-1))
+        nxt = self.logits.argmax().view(1)
+        self.pos.add_(1)
+        self.token.copy_(nxt)
+        self.generated.index_copy_(0, self.pos - self.gen_base, nxt)
+
+    @torch.no_grad()
+    def decode_step(self, use_graph: bool = True) -> None:
+        """Consumes the current token, appends the greedy next one to `generated`."""
+        if not use_graph:
+            self._decode_body()
+            return
+        if self._graph is None:
+            # warm up eagerly on a side stream (allocator, function attributes), restore the state, capture
+            state = (self.pos.clone(), self.token.clone(), self.generated.clone())
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._decode_body()
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            self._restore(state)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._decode_body()
+            self._graph = g
+            self._restore(state)
+            # the two passes above advanced every layer's weight cache with this token's mask: replaying
+            # the same token reproduces the same mask, which the cache treats as "no change"
+        self._graph.replay()
+
+    def _restore(self, state) -> None:
+        self.pos.copy_(state[0])
+        self.token.copy_(state[1])
+        self.generated.copy_(state[2])
+
+    @torch.no_grad()
+    def generate(self, prompt_ids: torch.Tensor, n_new: int, use_graph: bool = True) -> dict:
+        """Greedy decoding; returns tokens and the reference's two timings (benchmark.py:255-260):
+        ttft = start -> first token available; output tokens/s = (n_new - 1) / (total - ttft)."""
+        assert prompt_ids.numel() + n_new <= self.cfg.max_len
+        if use_graph and self._graph is None:
+            # build the decode graph outside the timed region, on a throw-away state
+            self.prefill(prompt_ids[: min(8, prompt_ids.numel())])
+            self.decode_step(True)
+            torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        self.prefill(prompt_ids)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for _ in range(n_new - 1):
+            self.decode_step(use_graph)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        return {"tokens": self.generated[:n_new].clone(), "ttft_s": t1 - t0, "decode_s": t2 - t1,
+                "output_tokens_per_s": (n_new - 1) / (t2 - t1), "total_tokens_per_s": n_new / (t2 - t0)}
+
+    def close(self) -> None:
+        self._graph = None
+        for L in self.layers:
+            L["sparse"].close()
