@@ -408,9 +408,9 @@ def run_native(args):
         if fused:
             # k_mlp_b1: active gate/up/down rows + the predictor's up matrix + x + t + mask bytes.  The
             # per-CTA partial vectors it writes are an artefact of the implementation, not counted.
-            top, second, k1, k2 = "mlp_b1", "reduce", "k_mlp_b1", "k_partial_reduce"
-            alg = (es * (3 if w.has_gate else 2) * k_mean * w.H + es * w.I * w.r + es * w.H + 4 * w.r + w.I / 8)
-            alg2 = 4 * (torch.cuda.get_device_properties(dev).multi_processor_count - 1) * w.H + es * w.H
+            top, second, k1, k2 = "mlp_b1", "reduce", ("k_mlp_b1" if w.B == 1 else "k_mlp_bn"), "k_partial_reduce"
+            alg = (es * (3 if w.has_gate else 2) * k_mean * w.H + es * w.I * w.r + es * w.B * w.H + 4 * w.B * w.r + w.I / 8)
+            alg2 = (4 * (torch.cuda.get_device_properties(dev).multi_processor_count - 1) + es) * w.B * w.H
         else:
             top, second, k1, k2 = "gateup", "down", ("k_gateup_mma" if w.B >= 4 else "k_gateup_tma"), "k_down_rows"
             alg = es * (2 if w.has_gate else 1) * k_mean * w.H + es * w.B * w.H + 4 * w.B * k_mean  # gate/up rows + x + a

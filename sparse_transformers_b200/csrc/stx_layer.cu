@@ -15,9 +15,9 @@ int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, 
                  int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch, unsigned parts,
                  cudaStream_t s);
 float* b1_partial_region(void* scratch, int64_t H, int64_t K_cap);
-bool layer_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate, const void* up,
-                        const void* down, const void* Bm);
-int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
+bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate,
+                        const void* up, const void* down, const void* Bm);
+int layer_b1_forward(const void* x, int64_t B, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
                      const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
                      int has_gate, int dtype, float* partial, int* status, unsigned parts, const stx_peer* peer,
                      cudaStream_t s);
@@ -46,6 +46,8 @@ struct stx_layer {
   void* scores = nullptr;        // [max_batch, I], only for rules that need whole rows
   void* pred_scratch = nullptr;
   void* mlp_scratch = nullptr;
+  float* partial = nullptr;  // per-CTA partial outputs of the fused kernels: [SMs][partial_rows][H] fp32
+  int64_t partial_rows = 0;
   stx_peer* peer = nullptr;  // not owned: the shards' exchange; a step then ends with the all-reduce
   void* x_stage = nullptr;       // [max_batch, H] for the host-buffer entry point
   void* out_stage = nullptr;
@@ -75,6 +77,7 @@ int stx_layer_destroy(stx_layer_t* l) {
   cudaFree(l->scores);
   cudaFree(l->pred_scratch);
   cudaFree(l->mlp_scratch);
+  cudaFree(l->partial);
   cudaFree(l->x_stage);
   cudaFree(l->out_stage);
   delete l;
@@ -123,6 +126,10 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   if (e == cudaSuccess) e = cudaMalloc(&l->pred_scratch, pred_bytes);
   if (e == cudaSuccess) e = cudaMalloc(&l->mlp_scratch, mlp_bytes);
   if (e == cudaSuccess) e = cudaMemset(l->mlp_scratch, 0, mlp_bytes);
+  if (e == cudaSuccess) {
+    l->partial_rows = std::min<int64_t>(max_batch, 8);
+    e = cudaMalloc(reinterpret_cast<void**>(&l->partial), sizeof(float) * num_sms() * l->partial_rows * H);
+  }
   if (e == cudaSuccess && method != STX_MASK_THRESHOLD) e = cudaMalloc(&l->scores, static_cast<size_t>(max_batch) * I * es);
   if (e != cudaSuccess) {
     set_error("stx_layer_create: device allocation failed: %s", cudaGetErrorString(e));
@@ -133,10 +140,12 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   return STX_OK;
 }
 
+// Up to 8 rows under the threshold rule: scores, mask, gather and MLP of a neuron stay in one CTA
+// (k_mlp_b1 for one row, k_mlp_bn for 2..8), followed by the sum of the per-CTA partials.
 static bool single_row_fusable(const stx_layer* l, int64_t B) {
   const stx_cache* c = l->cache;
-  return B == 1 && l->gather && l->method == STX_MASK_THRESHOLD && b1_partial_region(l->mlp_scratch, c->H, c->I) &&
-         layer_b1_supported(c->H, c->I, l->r, c->has_gate, c->dtype, c->pool_gate, c->pool_up, c->pool_down, l->Bm);
+  return l->partial && B <= l->partial_rows && l->gather && l->method == STX_MASK_THRESHOLD &&
+         layer_b1_supported(B, c->H, c->I, l->r, c->has_gate, c->dtype, c->pool_gate, c->pool_up, c->pool_down, l->Bm);
 }
 
 // One step with the cache maintenance (plan + row copies) optionally on a second stream.
@@ -149,7 +158,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
   stx_cache* c = l->cache;
   int rc = STX_OK;
   // One row under the threshold rule: scores, mask, gather and MLP of a neuron stay in one CTA.
-  float* partial = single_row_fusable(l, B) ? b1_partial_region(l->mlp_scratch, c->H, c->I) : nullptr;
+  float* partial = single_row_fusable(l, B) ? l->partial : nullptr;
   const bool fuse = partial && (stages & STX_STAGE_PREDICT_MASK) && (stages & STX_STAGE_MLP) && x_mlp && out;
   if (stages & STX_STAGE_PREDICT) {
     STX_CHECK_ARG(x_pred, "stx_layer_step: x_pred is null");
@@ -170,7 +179,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
   if (fuse) {
     const float* t = static_cast<const float*>(l->pred_scratch);
     if (stages & STX_STAGE_MLP_GATEUP) {
-      rc = layer_b1_forward(x_mlp, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
+      rc = layer_b1_forward(x_mlp, B, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
                             out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 1u, l->peer, s);
       if (rc != STX_OK) return rc;
     }
@@ -179,7 +188,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       STX_CUDA(cudaStreamWaitEvent(side, fork_ev, 0));
     }
     if (stages & STX_STAGE_MLP_DOWN) {
-      rc = layer_b1_forward(x_mlp, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
+      rc = layer_b1_forward(x_mlp, B, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
                             out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 2u, l->peer, s);
       if (rc != STX_OK) return rc;
     }

@@ -339,6 +339,13 @@ __global__ void __launch_bounds__(512, 1) k_gateup_tma(const GateUpArgs p) {
 // shared memory, which makes the 16-byte fragment loads conflict-free.
 template <typename T> struct MmaOp;
 template <> struct MmaOp<__half> {
+  // all 16 tile rows: a0/a2 = row g (k low/high pair), a1/a3 = row g + 8
+  static __device__ __forceinline__ void run16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
   static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -346,6 +353,12 @@ template <> struct MmaOp<__half> {
   }
 };
 template <> struct MmaOp<__nv_bfloat16> {
+  static __device__ __forceinline__ void run16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
   static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -635,8 +648,10 @@ __device__ unsigned long long g_b1_trace[256][8];
       g_b1_trace[blockIdx.x][i] = t__;                                                  \
     }                                                                                   \
   } while (0)
+#define STX_B1_NOW(var) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(var))
 #else
 #define STX_B1_STAMP(i) do { } while (0)
+#define STX_B1_NOW(var) do { } while (0)
 #endif
 
 constexpr int B1_MAX_SLOTS = 16;
@@ -667,6 +682,121 @@ struct MlpB1Args {
 // round trips cost more than the imbalance they removed.
 constexpr int B1_MAX_BYTES = 24;   // mask bytes per CTA: ceil(ceil(I / 8) / G) <= 24 (192 neurons)
 constexpr int B1_LIST_CAP = 192;
+
+// Predictor back half for the calling CTA's neurons (mask bytes blockIdx.x, + gridDim.x, ...),
+// all 512 threads.  Same arithmetic as k_pred_scores: 8 lanes per neuron, lane g takes the
+// 16-byte chunks g, g + 8, ... of the r-long row in order, then a butterfly over the 8 lanes
+// (4, 2, 1); the mask bit is the OR over the B rows.  The CTA's slice of the up matrix is loaded
+// BEFORE the dependency wait (weights do not depend on the preceding kernel); the function
+// contains the kernel's griddepcontrol wait.  t_s: shared fp32 [B][r].  Writes the mask bytes to
+// `bits` and the CTA's active neurons, ascending, to s_my; returns their number.
+template <typename T>
+__device__ __forceinline__ int cta_scores_and_list(const T* __restrict__ Bm, const float* __restrict__ t_gl, float* t_s, int B,
+                                                   int r, int I, float tau, uint32_t* bits, int32_t* s_my, uint32_t* s_nib,
+                                                   uint8_t* s_bytes, int* s_nlocal) {
+  constexpr int V = DT<T>::V;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = gridDim.x;
+  const int rch = r / V;  // <= 32
+  const int NBY = (I + 7) >> 3;
+  const int nby = NBY > static_cast<int>(blockIdx.x) ? (NBY - 1 - static_cast<int>(blockIdx.x)) / G + 1 : 0;
+  const int g = tid & 7;
+  // Two register sets of weights: a pass computes from one set while the loads of the next pass
+  // into the other set are in flight (the first set is loaded before the dependency wait).
+  float wv0[4][V], wv1[4][V];
+  bool ok0 = false, ok1 = false;
+  auto load_w = [&](int pass, float (&w)[4][V], bool& ok) {
+    const int kk = pass * 8 + (tid >> 6);
+    const int n = 8 * (static_cast<int>(blockIdx.x) + G * kk) + ((tid >> 3) & 7);
+    ok = kk < nby && n < I;
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const int c = g + 8 * c4;
+#pragma unroll
+      for (int v = 0; v < V; ++v) w[c4][v] = 0.f;
+      if (ok && c < rch) Unpack<T>::run(ld_stream16(Bm + static_cast<size_t>(n) * r + c * V), w[c4]);
+    }
+  };
+  load_w(0, wv0, ok0);
+  pdl_wait();
+  pdl_launch_dependents();
+  STX_B1_STAMP(1);
+  if (8 < nby) load_w(1, wv1, ok1);
+  for (int k = tid; k < B * r; k += blockDim.x) t_s[k] = __ldcg(t_gl + k);
+  __syncthreads();
+  const float tau_r = DT<T>::round_f(tau);
+  constexpr int SB = 8;  // batch rows whose chains run side by side (each row's own order is unchanged)
+  auto run_pass = [&](int pass, float (&w)[4][V], bool& ok) {
+    bool on = false;
+    for (int b0 = 0; b0 < B; b0 += SB) {
+      float sc[SB];
+#pragma unroll
+      for (int b = 0; b < SB; ++b) sc[b] = 0.f;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const int c = g + 8 * c4;
+        if (c < rch) {
+#pragma unroll
+          for (int b = 0; b < SB; ++b) {
+            if (b0 + b < B) {
+              const float* tb = t_s + (b0 + b) * r + c * V;
+#pragma unroll
+              for (int v = 0; v < V; ++v) sc[b] = fmaf(tb[v], w[c4][v], sc[b]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < SB; ++b) {
+        float t = sc[b];
+        t += __shfl_xor_sync(0xffffffffu, t, 4);
+        t += __shfl_xor_sync(0xffffffffu, t, 2);
+        t += __shfl_xor_sync(0xffffffffu, t, 1);
+        on = on || (b0 + b < B && DT<T>::round_f(t) >= tau_r);
+      }
+    }
+    on = on && ok;
+    if ((pass + 2) * 8 < nby) load_w(pass + 2, w, ok);  // this set is free again
+    const uint32_t bal = __ballot_sync(0xffffffffu, on && g == 0);
+    if (lane == 0) s_nib[warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
+    __syncthreads();
+    if (tid < 8 && pass * 8 + tid < nby) {
+      const uint32_t byte = s_nib[2 * tid] | (s_nib[2 * tid + 1] << 4);
+      s_bytes[pass * 8 + tid] = static_cast<uint8_t>(byte);
+      reinterpret_cast<uint8_t*>(bits)[blockIdx.x + G * (pass * 8 + tid)] = static_cast<uint8_t>(byte);
+    }
+    __syncthreads();
+  };
+  for (int pass = 0; pass * 8 < nby; pass += 2) {
+    run_pass(pass, wv0, ok0);
+    if ((pass + 1) * 8 < nby) run_pass(pass + 1, wv1, ok1);
+  }
+  if (warp == 0) {  // the CTA's active neurons in ascending order
+    int carry = 0;
+    for (int base = 0; base < nby; base += 32) {
+      const int kk = base + lane;
+      uint32_t byte = kk < nby ? s_bytes[kk] : 0u;
+      const int cnt = __popc(byte);
+      int inc = cnt;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += v;
+      }
+      int pos = carry + inc - cnt;
+      while (byte) {
+        const int n = 8 * (static_cast<int>(blockIdx.x) + G * kk) + __ffs(byte) - 1;
+        byte &= byte - 1;
+        if (pos < B1_LIST_CAP) s_my[pos] = n;
+        ++pos;
+      }
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) *s_nlocal = min(carry, B1_LIST_CAP);
+  }
+  __syncthreads();
+  return *s_nlocal;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
@@ -712,86 +842,8 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
   int K = 0, nlocal = 0;
   STX_B1_STAMP(0);
   if (fused) {
-    // ---- predictor back half for this CTA's neurons; same arithmetic as k_pred_scores: 8 lanes
-    // per neuron, lane g takes the 16-byte chunks g, g + 8, ... of the r-long row in order, then a
-    // butterfly over the 8 lanes (4, 2, 1).
-    const int r = q.r, rch = r / V;  // rch <= 32
-    const int NBY = (p.I + 7) >> 3;
-    const int nby = NBY > static_cast<int>(blockIdx.x) ? (NBY - 1 - static_cast<int>(blockIdx.x)) / G + 1 : 0;
-    const int g = tid & 7;
-    const T* Bm = static_cast<const T*>(q.Bm);
-    float* t_s = reinterpret_cast<float*>(smem + B1_HEADER);
-    float wv[4][V];
-    auto load_w = [&](int pass) {
-      const int kk = pass * 8 + (tid >> 6);
-      const int n = 8 * (static_cast<int>(blockIdx.x) + G * kk) + ((tid >> 3) & 7);
-      const bool ok = kk < nby && n < p.I;
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        const int c = g + 8 * c4;
-#pragma unroll
-        for (int v = 0; v < V; ++v) wv[c4][v] = 0.f;
-        if (ok && c < rch) Unpack<T>::run(ld_stream16(Bm + static_cast<size_t>(n) * r + c * V), wv[c4]);
-      }
-      return ok;
-    };
-    bool ok = load_w(0);  // weights do not depend on the preceding kernel
-    pdl_wait();
-    pdl_launch_dependents();
-    STX_B1_STAMP(1);
-    for (int k = tid; k < r; k += blockDim.x) t_s[k] = __ldcg(q.t + k);
-    __syncthreads();
-    const float tau_r = DT<T>::round_f(q.tau);
-    for (int pass = 0; pass * 8 < nby; ++pass) {
-      if (pass > 0) ok = load_w(pass);
-      float sc = 0.f;
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        const int c = g + 8 * c4;
-        if (c < rch) {
-#pragma unroll
-          for (int v = 0; v < V; ++v) sc = fmaf(t_s[c * V + v], wv[c4][v], sc);
-        }
-      }
-      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
-      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-      const bool on = ok && (DT<T>::round_f(sc) >= tau_r);
-      const uint32_t bal = __ballot_sync(0xffffffffu, on && g == 0);
-      if (lane == 0) s_nib[warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
-      __syncthreads();
-      if (tid < 8 && pass * 8 + tid < nby) {
-        const uint32_t byte = s_nib[2 * tid] | (s_nib[2 * tid + 1] << 4);
-        s_bytes[pass * 8 + tid] = static_cast<uint8_t>(byte);
-        reinterpret_cast<uint8_t*>(q.bits)[blockIdx.x + G * (pass * 8 + tid)] = static_cast<uint8_t>(byte);
-      }
-      __syncthreads();
-    }
-    if (warp == 0) {  // the CTA's active neurons in ascending order
-      int carry = 0;
-      for (int base = 0; base < nby; base += 32) {
-        const int kk = base + lane;
-        uint32_t byte = kk < nby ? s_bytes[kk] : 0u;
-        const int cnt = __popc(byte);
-        int inc = cnt;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-          const int v = __shfl_up_sync(0xffffffffu, inc, off);
-          if (lane >= off) inc += v;
-        }
-        int pos = carry + inc - cnt;
-        while (byte) {
-          const int n = 8 * (static_cast<int>(blockIdx.x) + G * kk) + __ffs(byte) - 1;
-          byte &= byte - 1;
-          if (pos < B1_LIST_CAP) s_my[pos] = n;
-          ++pos;
-        }
-        carry += __shfl_sync(0xffffffffu, inc, 31);
-      }
-      if (lane == 0) s_nlocal = min(carry, B1_LIST_CAP);
-    }
-    __syncthreads();
-    nlocal = s_nlocal;
+    nlocal = cta_scores_and_list<T>(static_cast<const T*>(q.Bm), q.t, reinterpret_cast<float*>(smem + B1_HEADER), 1, q.r, p.I,
+                                    q.tau, q.bits, s_my, s_nib, s_bytes, &s_nlocal);
   } else {
     pdl_wait();
     pdl_launch_dependents();
@@ -944,6 +996,216 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
   STX_B1_STAMP(6);
 }
 
+// ------------------------------------------------------------------------------------------
+// 2..8 rows, 16-bit weights, gated: the same one-kernel structure as k_mlp_b1 (scores of the CTA's
+// own neurons -> mask bytes -> bulk copies of gate/up/down rows -> MLP -> per-CTA partial [B][H]),
+// with the gate/up dot products on the tensor pipe.
+//
+// The CTA walks its neurons TN (<= 8) at a time.  Three shared-memory buffers hold one such tile:
+//   X  the first halves (columns 0 .. H/2) of the TN gate and up rows
+//   Y  their second halves
+//   Z  the TN down rows
+//   phase 1a/1b  A tile of mma.m16n8k16 = the 2*TN gate/up rows (neuron e in tile rows 2e, 2e+1),
+//                B tile = x^T (8 batch columns); each of the 16 warps owns a sixteenth of each half
+//                of H and keeps its accumulators in registers from X to Y; the sixteen partial
+//                sums meet in shared memory and are added in warp order -> a[e][b] = act(g) * u
+//   phase 2      thread t owns the 16-byte column chunk t for all rows: acc[b][v] += a[e][b] * down
+// A buffer is re-filled with the next tile's rows as soon as its phase is over, so two of the three
+// are in flight or ready while the third is being read.  Filling all 16 tile rows matters: the
+// kernel's instruction stream is dominated by the fragment loads of x (64 KB per tile pass) and the
+// mma issue, both per tile, not per neuron.
+// Rows of x and of the weights sit 64 bytes apart from a multiple of 128 so that the fragment
+// loads of different rows fall into different banks.
+constexpr int BN_MAX = 8;
+constexpr int BN_TN_MAX = 8;
+constexpr int BN_HEADER = 1024;                // [0,64) 3 mbarriers | [256,512) a_s [8 neurons][8 rows of the batch]
+constexpr int BN_RED_BYTES = 16 * 16 * 8 * 4;  // [warp][tile row][batch] fp32
+
+template <typename T>
+__global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
+  constexpr int V = DT<T>::V;
+  static_assert(sizeof(T) == 2, "16-bit weights only");
+  const GateUpArgs& p = q.g;
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int TN = p.nwarps, B = p.B;
+  const int H = p.H, nchunk = H / V;
+  const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+  const uint32_t half_bytes = row_bytes / 2;
+  const uint32_t rstride = row_bytes + 64, hstride = half_bytes + 64;
+
+  uint64_t* bar_x = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* bar_y = bar_x + 1;
+  uint64_t* bar_z = bar_x + 2;
+  float* a_s = reinterpret_cast<float*>(smem + 256);  // [neuron of the tile][8]
+  const size_t t_bytes = (static_cast<size_t>(B) * q.r * sizeof(float) + 127) / 128 * 128;
+  float* t_s = reinterpret_cast<float*>(smem + BN_HEADER);
+  float* red_s = reinterpret_cast<float*>(smem + BN_HEADER + t_bytes);
+  unsigned char* x_s = smem + BN_HEADER + t_bytes + BN_RED_BYTES;        // 8 rows of rstride
+  unsigned char* X = x_s + static_cast<size_t>(BN_MAX) * rstride;         // [TN][gate, up] half rows of hstride
+  unsigned char* Y = X + static_cast<size_t>(TN) * 2 * hstride;
+  unsigned char* Z = Y + static_cast<size_t>(TN) * 2 * hstride;           // [TN] rows of rstride
+
+  __shared__ int32_t s_my[GATHER_MY_CAP];
+  __shared__ uint32_t s_nib[16];
+  __shared__ uint8_t s_bytes[B1_MAX_BYTES];
+  __shared__ int s_nlocal;
+  const char* gsrc = static_cast<const char*>(p.gate);
+  const char* usrc = static_cast<const char*>(p.up);
+  const char* dsrc = static_cast<const char*>(q.down);
+
+  if (tid == 0) {
+    mbar_init(bar_x, 1);
+    mbar_init(bar_y, 1);
+    mbar_init(bar_z, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  STX_B1_STAMP(0);
+  const int nlocal = cta_scores_and_list<T>(static_cast<const T*>(q.Bm), q.t, t_s, B, q.r, p.I, q.tau, q.bits, s_my, s_nib,
+                                            s_bytes, &s_nlocal);
+  const int niter = (nlocal + TN - 1) / TN;
+
+  // One thread fills a buffer with the rows of tile j (warp 0: X, warp 1: Y, warp 2: Z).
+  auto fill = [&](int which, int j) {
+    if (j >= niter || warp != which || lane != 0) return;
+    const int nv = min(TN, nlocal - j * TN);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (which < 2) {
+      uint64_t* bar = which == 0 ? bar_x : bar_y;
+      unsigned char* buf = which == 0 ? X : Y;
+      const size_t col = which == 0 ? 0 : half_bytes;
+      mbar_expect_tx(bar, static_cast<uint32_t>(nv) * 2 * half_bytes);
+      for (int e = 0; e < nv; ++e) {
+        const size_t off = static_cast<size_t>(s_my[j * TN + e]) * row_bytes + col;
+        bulk_load(buf + static_cast<size_t>(2 * e) * hstride, gsrc + off, half_bytes, bar);
+        bulk_load(buf + static_cast<size_t>(2 * e + 1) * hstride, usrc + off, half_bytes, bar);
+      }
+    } else {
+      mbar_expect_tx(bar_z, static_cast<uint32_t>(nv) * row_bytes);
+      for (int e = 0; e < nv; ++e)
+        bulk_load(Z + static_cast<size_t>(e) * rstride, dsrc + static_cast<size_t>(s_my[j * TN + e]) * row_bytes, row_bytes, bar_z);
+    }
+  };
+  STX_B1_STAMP(2);
+  fill(0, 0);
+  fill(1, 0);
+  fill(2, 0);
+  for (int i = tid; i < BN_MAX * nchunk; i += blockDim.x) {  // rows beyond B are zero
+    const int b = i / nchunk, c = i - b * nchunk;
+    const uint4 v = b < B ? ld_cached16(static_cast<const T*>(p.x) + static_cast<size_t>(b) * H + c * V) : make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(x_s + static_cast<size_t>(b) * rstride + c * 16) = v;
+  }
+  __syncthreads();
+
+  float acc[BN_MAX][V];
+#pragma unroll
+  for (int b = 0; b < BN_MAX; ++b)
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[b][v] = 0.f;
+
+  bool timed_out = false;
+  const int nwh = H / 64;  // windows (32 consecutive k = 64 bytes) per half row
+  const int w_lo = (nwh * warp) / 16, w_hi = (nwh * (warp + 1)) / 16;  // this warp's share of each half
+  unsigned long long tw0 = 0, tw1 = 0, tw_gu = 0, tw_d = 0, t_loop0 = 0;  // development timeline only
+  (void)tw0; (void)tw1; (void)tw_gu; (void)tw_d; (void)t_loop0;
+  STX_B1_NOW(t_loop0);
+  for (int it = 0; it < niter; ++it) {
+    const uint32_t parity = static_cast<uint32_t>(it) & 1u;
+    const int nv = min(TN, nlocal - it * TN);
+    // tile rows of this lane: gq (neuron gq >> 1) and gq + 8 (neuron 4 + (gq >> 1)); gate even, up odd
+    const bool lo_on = gq < 2 * nv, hi_on = gq + 8 < 2 * nv;
+    float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      STX_B1_NOW(tw0);
+      if (!mbar_wait_bounded(half == 0 ? bar_x : bar_y, parity)) timed_out = true;
+      STX_B1_NOW(tw1);
+      tw_gu += tw1 - tw0;
+      const unsigned char* buf = half == 0 ? X : Y;
+      const unsigned char* arow_lo = buf + static_cast<size_t>(lo_on ? gq : 0) * hstride + tq * 16;
+      const unsigned char* arow_hi = buf + static_cast<size_t>(hi_on ? gq + 8 : 0) * hstride + tq * 16;
+      const unsigned char* xrow = x_s + static_cast<size_t>(gq) * rstride + static_cast<size_t>(half) * half_bytes + tq * 16;
+      for (int w = w_lo; w < w_hi; ++w) {
+        uint4 al = make_uint4(0, 0, 0, 0), ah = al;
+        if (lo_on) al = *reinterpret_cast<const uint4*>(arow_lo + static_cast<size_t>(w) * 64);
+        if (hi_on) ah = *reinterpret_cast<const uint4*>(arow_hi + static_cast<size_t>(w) * 64);
+        const uint4 xv = *reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(w) * 64);
+        MmaOp<T>::run16(d0, al.x, ah.x, al.y, ah.y, xv.x, xv.y);
+        MmaOp<T>::run16(d1, al.z, ah.z, al.w, ah.w, xv.z, xv.w);
+      }
+      if (half == 1) {
+        // lane (gq, tq): tile rows gq and gq + 8, batch columns 2tq and 2tq+1
+        float* dst = red_s + (warp * 16 + gq) * 8 + 2 * tq;  // [warp][tile row][batch]
+        dst[0] = d0[0] + d1[0];
+        dst[1] = d0[1] + d1[1];
+        dst[64] = d0[2] + d1[2];
+        dst[65] = d0[3] + d1[3];
+      }
+      __syncthreads();  // nobody reads this half of the tile any more (half 1: the partial sums are complete)
+      fill(half, it + 1);
+    }
+    if (tid < nv * 8) {
+      const int e = tid >> 3, b = tid & 7;
+      const float* src = red_s + (2 * e) * 8 + b;  // [warp 0][row 2e][b]; the up row follows
+      float g = 0.f, u = 0.f;
+#pragma unroll
+      for (int k16 = 0; k16 < 16; ++k16) {
+        g += src[k16 * 128];
+        u += src[k16 * 128 + 8];
+      }
+      a_s[e * 8 + b] = apply_act(p.act, g) * u;
+    }
+    __syncthreads();  // a_s complete
+    // ---- phase 2
+    STX_B1_NOW(tw0);
+    if (!mbar_wait_bounded(bar_z, parity)) timed_out = true;
+    STX_B1_NOW(tw1);
+    tw_d += tw1 - tw0;
+    if (tid < nchunk) {
+      for (int e = 0; e < nv; ++e) {
+        float wd[V];
+        Unpack<T>::run(*reinterpret_cast<const uint4*>(Z + static_cast<size_t>(e) * rstride + tid * 16), wd);
+        const float4 a_lo = *reinterpret_cast<const float4*>(a_s + e * 8);
+        const float4 a_hi = *reinterpret_cast<const float4*>(a_s + e * 8 + 4);
+        const float av[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+#pragma unroll
+        for (int b = 0; b < BN_MAX; ++b)
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[b][v] = fmaf(av[b], wd[v], acc[b][v]);
+      }
+    }
+    if (it + 1 < niter) {
+      __syncthreads();  // every thread is done with a_s and the down rows of this tile
+      fill(2, it + 1);
+    }
+  }
+  if (timed_out && p.status) atomicOr(p.status, DEV_TIMEOUT);
+#ifdef STX_B1_TRACE
+  if (tid == 0) {
+    g_b1_trace[blockIdx.x][7] = static_cast<unsigned long long>(nlocal);
+    // durations, reported relative to the start stamp: gate/up waits, down waits, whole loop
+    g_b1_trace[blockIdx.x][3] = g_b1_trace[blockIdx.x][0] + tw_gu;
+    g_b1_trace[blockIdx.x][4] = g_b1_trace[blockIdx.x][0] + tw_d;
+    STX_B1_NOW(tw1);
+    g_b1_trace[blockIdx.x][5] = g_b1_trace[blockIdx.x][0] + (tw1 - t_loop0);
+  }
+#endif
+  if (tid < nchunk) {
+    float* dst = q.partial + static_cast<size_t>(blockIdx.x) * B * H + tid * V;
+#pragma unroll
+    for (int b = 0; b < BN_MAX; ++b) {
+      if (b < B) {
+#pragma unroll
+        for (int v = 0; v < V; v += 4)
+          *reinterpret_cast<float4*>(dst + static_cast<size_t>(b) * H + v) =
+              make_float4(acc[b][v], acc[b][v + 1], acc[b][v + 2], acc[b][v + 3]);
+      }
+    }
+  }
+  STX_B1_STAMP(6);
+}
+
 // out[h] = sum_c partial[c][h], c ascending.  Block: 32 columns x 32 groups of CTAs; a group
 // adds a contiguous range of CTAs in order, then the groups are added in order.  With peers
 // (pa.world > 1: the layer is one shard of several GPUs) the column sums are then exchanged
@@ -979,6 +1241,55 @@ __global__ void __launch_bounds__(1024) k_partial_reduce(const float* __restrict
       if (timed_out) atomicOr(pa.ctl + 2, DEV_TIMEOUT);
     }
     out[h] = DT<T>::from_f(t);
+  }
+  if (shared) peer_epoch_end(pa, epoch);
+}
+
+// Same sum for long vectors (several rows): a thread owns 4 consecutive columns (16-byte loads),
+// a block 128 columns x 32 groups of CTAs.  n must be a multiple of 128.
+template <typename T>
+__global__ void __launch_bounds__(1024) k_partial_reduce4(const float* __restrict__ partial, int G, int n, T* __restrict__ out,
+                                                          const __grid_constant__ PeerArgs pa) {
+  __shared__ float4 s_r[32][33];
+  const int qc = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int h = (blockIdx.x * 32 + qc) * 4;
+  const int per = (G + 31) / 32;
+  const int c0 = grp * per, c1 = min(G, c0 + per);
+  pdl_wait();
+  pdl_launch_dependents();
+  const bool shared = pa.world > 1;
+  const int epoch = shared ? peer_epoch_begin(pa) : 0;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+  for (int c = c0; c < c1; ++c) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + static_cast<size_t>(c) * n + h));
+    sum.x += v.x;
+    sum.y += v.y;
+    sum.z += v.z;
+    sum.w += v.w;
+  }
+  s_r[grp][qc] = sum;
+  __syncthreads();
+  if (grp == 0) {
+    float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int g = 0; g < 32; ++g) {
+      const float4 v = s_r[g][qc];
+      t[0] += v.x;
+      t[1] += v.y;
+      t[2] += v.z;
+      t[3] += v.w;
+    }
+    if (shared) {
+      bool timed_out = false;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) peer_push(pa, epoch, h + k, t[k]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) t[k] = peer_collect(pa, epoch, h + k, t[k], &timed_out);
+      if (timed_out) atomicOr(pa.ctl + 2, DEV_TIMEOUT);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) out[h + k] = DT<T>::from_f(t[k]);
   }
   if (shared) peer_epoch_end(pa, epoch);
 }
@@ -1157,6 +1468,69 @@ static int launch_b1(const GateUpArgs& g, const void* down, float* partial, void
   return STX_OK;
 }
 
+// ---- k_mlp_bn (2..8 rows)
+template <typename T>
+static size_t bn_smem_budget() {
+  static size_t budget = 0;
+  if (!budget) {
+    cudaFuncAttributes fa;
+    size_t stat = 4096;
+    if (cudaFuncGetAttributes(&fa, k_mlp_bn<T>) == cudaSuccess) stat = fa.sharedSizeBytes;
+    budget = 227 * 1024 - (stat + 127) / 128 * 128;
+  }
+  return budget;
+}
+
+// bytes in front of the slots / slots per CTA (0: the kernel does not fit the shape)
+static size_t bn_fixed_bytes(int H, int B, int r) {
+  return BN_HEADER + (static_cast<size_t>(B) * r * sizeof(float) + 127) / 128 * 128 + BN_RED_BYTES +
+         static_cast<size_t>(BN_MAX) * (static_cast<size_t>(H) * 2 + 64);
+}
+// shared memory per neuron of a tile: four half rows (gate/up x two halves) and the down row
+static size_t bn_neuron_bytes(int H) { return 4 * (static_cast<size_t>(H) + 64) + static_cast<size_t>(H) * 2 + 64; }
+// neurons per tile (0: the kernel does not fit the shape)
+template <typename T>
+static int bn_slots(int H, int B, int r) {
+  const size_t fixed = bn_fixed_bytes(H, B, r), budget = bn_smem_budget<T>();
+  if (H % 64 != 0 || H / 8 > 512 || budget < fixed + 2 * bn_neuron_bytes(H)) return 0;
+  return static_cast<int>(std::min<size_t>(BN_TN_MAX, (budget - fixed) / bn_neuron_bytes(H)));
+}
+
+template <typename T>
+static int launch_bn(const GateUpArgs& g, const void* down, float* partial, void* out, int grid, unsigned parts,
+                     const B1Pred& pr, cudaStream_t s) {
+  MlpB1Args q;
+  q.g = g;
+  q.g.nwarps = bn_slots<T>(g.H, g.B, pr.r);
+  q.down = down;
+  q.partial = partial;
+  q.t = pr.t;
+  q.Bm = pr.Bm;
+  q.bits = pr.bits;
+  q.r = pr.r;
+  q.tau = pr.tau;
+  const size_t smem = bn_fixed_bytes(g.H, g.B, pr.r) + static_cast<size_t>(q.g.nwarps) * bn_neuron_bytes(g.H);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    STX_CUDA(cudaFuncSetAttribute(k_mlp_bn<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(bn_smem_budget<T>())));
+    attr_set[dev] = true;
+  }
+  if (parts & 1u) STX_CUDA(launch_pdl(k_mlp_bn<T>, dim3(grid), dim3(512), smem, s, q));
+  if (parts & 2u) {
+    const int n = g.B * g.H;  // the partials of a CTA are one vector [B][H]
+    if (n % 128 == 0)
+      STX_CUDA(launch_pdl(k_partial_reduce4<T>, dim3(n / 128), dim3(1024), 0, s, static_cast<const float*>(partial), grid, n,
+                          static_cast<T*>(out), pr.peer));
+    else
+      STX_CUDA(launch_pdl(k_partial_reduce<T>, dim3((n + 31) / 32), dim3(1024), 0, s, static_cast<const float*>(partial), grid,
+                          n, static_cast<T*>(out), pr.peer));
+  }
+  return STX_OK;
+}
+
 static int b1_slots_dt(int H, int has_gate, int dtype, int r) {
   switch (dtype) {
     case STX_F32: return b1_slots<float>(H, has_gate, r);
@@ -1192,8 +1566,9 @@ static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const
 // One row through a layer whose mask comes from the threshold rule: the predictor's back half,
 // the gather and the whole MLP in k_mlp_b1, then k_partial_reduce.  parts bit 0 / bit 1 select
 // the two kernels.  `t` holds A x (fp32 [r]) written earlier on the same stream.
-bool layer_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate, const void* up,
-                        const void* down, const void* Bm) {
+bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate,
+                        const void* up, const void* down, const void* Bm) {
+  if (B < 1 || B > BN_MAX) return false;
   const size_t es = dtype_size(dtype);
   const int V = static_cast<int>(16 / es);
   if (!use_b1_fused() || (H * es) % 16 != 0 || H / V < 32 || r % V != 0 || r / V > 32 || H > (1 << 20) || I > (1 << 24))
@@ -1203,10 +1578,13 @@ bool layer_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype
   if (al & 15) return false;
   const int grid = std::max(1, num_sms() - 1);
   if (((I + 7) / 8 + grid - 1) / grid > B1_MAX_BYTES) return false;
-  return b1_slots_dt(static_cast<int>(H), has_gate, dtype, static_cast<int>(r)) > 0;
+  if (B == 1) return b1_slots_dt(static_cast<int>(H), has_gate, dtype, static_cast<int>(r)) > 0;
+  if (!has_gate || dtype == STX_F32 || B * r * 4 > 16 * 1024) return false;
+  return (dtype == STX_F16 ? bn_slots<__half>(static_cast<int>(H), static_cast<int>(B), static_cast<int>(r))
+                           : bn_slots<__nv_bfloat16>(static_cast<int>(H), static_cast<int>(B), static_cast<int>(r))) >= 2;
 }
 
-int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
+int layer_b1_forward(const void* x, int64_t B, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
                      const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
                      int has_gate, int dtype, float* partial, int* status, unsigned parts, const stx_peer* peer,
                      cudaStream_t s) {
@@ -1223,7 +1601,7 @@ int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, cons
   a.count_out = nullptr;
   a.I = static_cast<int>(I);
   a.K_host = 0;
-  a.B = 1;
+  a.B = static_cast<int>(B);
   a.H = static_cast<int>(H);
   a.act = act;
   a.has_gate = has_gate;
@@ -1239,7 +1617,7 @@ int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, cons
       set_error("stx_layer_step: the layer's peer object is not connected");
       return STX_ERR_INVALID_ARG;
     }
-    if (H > peer->max_elems) {
+    if (B * H > peer->max_elems) {
       set_error("stx_layer_step: H=%lld exceeds the peer object's max_elems", static_cast<long long>(H));
       return STX_ERR_INVALID_ARG;
     }
@@ -1247,8 +1625,12 @@ int layer_b1_forward(const void* x, int64_t H, int64_t I, const void* gate, cons
   const int grid = std::max(1, num_sms() - 1);
   switch (dtype) {
     case STX_F32: return launch_b1<float>(a, down, partial, out, grid, parts, pr, s);
-    case STX_F16: return launch_b1<__half>(a, down, partial, out, grid, parts, pr, s);
-    default: return launch_b1<__nv_bfloat16>(a, down, partial, out, grid, parts, pr, s);
+    case STX_F16:
+      return B == 1 ? launch_b1<__half>(a, down, partial, out, grid, parts, pr, s)
+                    : launch_bn<__half>(a, down, partial, out, grid, parts, pr, s);
+    default:
+      return B == 1 ? launch_b1<__nv_bfloat16>(a, down, partial, out, grid, parts, pr, s)
+                    : launch_bn<__nv_bfloat16>(a, down, partial, out, grid, parts, pr, s);
   }
 }
 
