@@ -366,6 +366,37 @@ template <> struct MmaOp<__nv_bfloat16> {
   }
 };
 
+template <typename T> struct MmaK8;  // m16n8k8: A 16x8 (two registers), B 8x8 (one register)
+template <> struct MmaK8<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+template <> struct MmaK8<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+// Four 8x8 b16 matrices, transposed on the way into registers; lane l supplies the address of
+// row l & 7 of matrix l >> 3.
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row_addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(row_addr)));
+}
+
 constexpr int MMA_TILE_ROWS = 4;
 
 // Shared-memory layout (dynamic): [0,256) mbarriers | x_s [min(B,8)][H*2 + 64] | bufs [nwarps][4][H*2 + 64]
@@ -1009,7 +1040,11 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
 //                B tile = x^T (8 batch columns); each of the 16 warps owns a sixteenth of each half
 //                of H and keeps its accumulators in registers from X to Y; the sixteen partial
 //                sums meet in shared memory and are added in warp order -> a[e][b] = act(g) * u
-//   phase 2      thread t owns the 16-byte column chunk t for all rows: acc[b][v] += a[e][b] * down
+//   phase 2      also an mma: D[h][b] += down^T[h][e] * a[e][b] with m = 16 columns of H, n = the 8
+//                batch rows, k = the (up to) 8 neurons of the tile (m16n8k8).  Warp w owns columns
+//                w*H/16 .. and keeps its H/16 x 8 outputs in registers; the A fragments come
+//                transposed out of the down rows with ldmatrix.trans; a is rounded to the model
+//                dtype for the B fragment (as the reference's own activations are).
 // A buffer is re-filled with the next tile's rows as soon as its phase is over, so two of the three
 // are in flight or ready while the third is being read.  Filling all 16 tile rows matters: the
 // kernel's instruction stream is dominated by the fragment loads of x (64 KB per tile pass) and the
@@ -1018,6 +1053,7 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
 // loads of different rows fall into different banks.
 constexpr int BN_MAX = 8;
 constexpr int BN_TN_MAX = 8;
+constexpr int BN_MT_MAX = 16;  // m-tiles of 16 columns per warp: H <= 16 * 16 * 16
 constexpr int BN_HEADER = 1024;                // [0,64) 3 mbarriers | [256,512) a_s [8 neurons][8 rows of the batch]
 constexpr int BN_RED_BYTES = 16 * 16 * 8 * 4;  // [warp][tile row][batch] fp32
 
@@ -1034,18 +1070,19 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
   const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
   const uint32_t half_bytes = row_bytes / 2;
   const uint32_t rstride = row_bytes + 64, hstride = half_bytes + 64;
+  const uint32_t zstride = row_bytes + 16;  // down rows 16 bytes off a multiple of 128: conflict-free ldmatrix
 
   uint64_t* bar_x = reinterpret_cast<uint64_t*>(smem);
   uint64_t* bar_y = bar_x + 1;
   uint64_t* bar_z = bar_x + 2;
-  float* a_s = reinterpret_cast<float*>(smem + 256);  // [neuron of the tile][8]
+  uint32_t* a_pk = reinterpret_cast<uint32_t*>(smem + 256);  // [neuron pair][batch row]: (a[2k][b], a[2k+1][b]) in the model dtype
   const size_t t_bytes = (static_cast<size_t>(B) * q.r * sizeof(float) + 127) / 128 * 128;
   float* t_s = reinterpret_cast<float*>(smem + BN_HEADER);
   float* red_s = reinterpret_cast<float*>(smem + BN_HEADER + t_bytes);
   unsigned char* x_s = smem + BN_HEADER + t_bytes + BN_RED_BYTES;        // 8 rows of rstride
   unsigned char* X = x_s + static_cast<size_t>(BN_MAX) * rstride;         // [TN][gate, up] half rows of hstride
   unsigned char* Y = X + static_cast<size_t>(TN) * 2 * hstride;
-  unsigned char* Z = Y + static_cast<size_t>(TN) * 2 * hstride;           // [TN] rows of rstride
+  unsigned char* Z = Y + static_cast<size_t>(TN) * 2 * hstride;           // [TN] rows of zstride
 
   __shared__ int32_t s_my[GATHER_MY_CAP];
   __shared__ uint32_t s_nib[16];
@@ -1084,12 +1121,18 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     } else {
       mbar_expect_tx(bar_z, static_cast<uint32_t>(nv) * row_bytes);
       for (int e = 0; e < nv; ++e)
-        bulk_load(Z + static_cast<size_t>(e) * rstride, dsrc + static_cast<size_t>(s_my[j * TN + e]) * row_bytes, row_bytes, bar_z);
+        bulk_load(Z + static_cast<size_t>(e) * zstride, dsrc + static_cast<size_t>(s_my[j * TN + e]) * row_bytes, row_bytes, bar_z);
     }
   };
   STX_B1_STAMP(2);
   fill(0, 0);
   fill(1, 0);
+  if (niter > 0 && nlocal < TN) {
+    // a short only tile: the unused down rows are multiplied by a = 0, so they must hold finite numbers
+    for (int i = tid; i < TN * static_cast<int>(zstride / 16); i += blockDim.x)
+      reinterpret_cast<uint4*>(Z)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+  }
   fill(2, 0);
   for (int i = tid; i < BN_MAX * nchunk; i += blockDim.x) {  // rows beyond B are zero
     const int b = i / nchunk, c = i - b * nchunk;
@@ -1098,11 +1141,13 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
   }
   __syncthreads();
 
-  float acc[BN_MAX][V];
+  // outputs of this warp: m-tile mt = columns warp*H/16 + 16*mt .., fragment rows gq / gq + 8, batch 2tq / 2tq + 1
+  float dacc[BN_MT_MAX][4];
 #pragma unroll
-  for (int b = 0; b < BN_MAX; ++b)
+  for (int mt = 0; mt < BN_MT_MAX; ++mt)
 #pragma unroll
-    for (int v = 0; v < V; ++v) acc[b][v] = 0.f;
+    for (int k = 0; k < 4; ++k) dacc[mt][k] = 0.f;
+  const int MT = H / 256;  // m-tiles per warp (even)
 
   bool timed_out = false;
   const int nwh = H / 64;  // windows (32 consecutive k = 64 bytes) per half row
@@ -1145,38 +1190,43 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
       __syncthreads();  // nobody reads this half of the tile any more (half 1: the partial sums are complete)
       fill(half, it + 1);
     }
-    if (tid < nv * 8) {
+    if (tid < 64) {  // neuron e = tid >> 3 of the tile (a = 0 beyond the tile's last neuron), batch row b
       const int e = tid >> 3, b = tid & 7;
-      const float* src = red_s + (2 * e) * 8 + b;  // [warp 0][row 2e][b]; the up row follows
-      float g = 0.f, u = 0.f;
+      float a = 0.f;
+      if (e < nv) {
+        const float* src = red_s + (2 * e) * 8 + b;  // [warp 0][row 2e][b]; the up row follows
+        float g = 0.f, u = 0.f;
 #pragma unroll
-      for (int k16 = 0; k16 < 16; ++k16) {
-        g += src[k16 * 128];
-        u += src[k16 * 128 + 8];
+        for (int k16 = 0; k16 < 16; ++k16) {
+          g += src[k16 * 128];
+          u += src[k16 * 128 + 8];
+        }
+        a = apply_act(p.act, g) * u;
       }
-      a_s[e * 8 + b] = apply_act(p.act, g) * u;
+      const float a_next = __shfl_down_sync(0xffffffffu, a, 8);  // neuron e + 1, same batch row
+      if ((e & 1) == 0) a_pk[(e >> 1) * 8 + b] = MmaK8<T>::pack(a, a_next);
     }
-    __syncthreads();  // a_s complete
+    __syncthreads();  // a_pk complete
     // ---- phase 2
-    STX_B1_NOW(tw0);
     if (!mbar_wait_bounded(bar_z, parity)) timed_out = true;
-    STX_B1_NOW(tw1);
-    tw_d += tw1 - tw0;
-    if (tid < nchunk) {
-      for (int e = 0; e < nv; ++e) {
-        float wd[V];
-        Unpack<T>::run(*reinterpret_cast<const uint4*>(Z + static_cast<size_t>(e) * rstride + tid * 16), wd);
-        const float4 a_lo = *reinterpret_cast<const float4*>(a_s + e * 8);
-        const float4 a_hi = *reinterpret_cast<const float4*>(a_s + e * 8 + 4);
-        const float av[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+    {
+      const uint32_t bfrag = a_pk[tq * 8 + gq];  // B[k = 2tq, 2tq+1][n = gq]
+      // ldmatrix row of this lane: neuron lane & 7 (a missing row of a short buffer reads row 0, its a is 0),
+      // 8-column group lane >> 3 of the 32 columns of an m-tile pair
+      const int zr = (lane & 7) < TN ? (lane & 7) : 0;
+      const unsigned char* zrow = Z + static_cast<size_t>(zr) * zstride + (static_cast<size_t>(warp) * (H / 16) + (lane >> 3) * 8) * 2;
 #pragma unroll
-        for (int b = 0; b < BN_MAX; ++b)
-#pragma unroll
-          for (int v = 0; v < V; ++v) acc[b][v] = fmaf(av[b], wd[v], acc[b][v]);
+      for (int mp = 0; mp < BN_MT_MAX / 2; ++mp) {
+        if (2 * mp < MT) {
+          uint32_t af[4];
+          ldmatrix_x4_trans(af, zrow + static_cast<size_t>(mp) * 64);
+          MmaK8<T>::run(dacc[2 * mp], af[0], af[1], bfrag);
+          MmaK8<T>::run(dacc[2 * mp + 1], af[2], af[3], bfrag);
+        }
       }
     }
     if (it + 1 < niter) {
-      __syncthreads();  // every thread is done with a_s and the down rows of this tile
+      __syncthreads();  // every thread is done with a_pk and the down rows of this tile
       fill(2, it + 1);
     }
   }
@@ -1191,15 +1241,20 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     g_b1_trace[blockIdx.x][5] = g_b1_trace[blockIdx.x][0] + (tw1 - t_loop0);
   }
 #endif
-  if (tid < nchunk) {
-    float* dst = q.partial + static_cast<size_t>(blockIdx.x) * B * H + tid * V;
+  {
+    float* dst = q.partial + static_cast<size_t>(blockIdx.x) * B * H + static_cast<size_t>(warp) * (H / 16) + gq;
+    const int b0 = 2 * tq, b1 = 2 * tq + 1;
 #pragma unroll
-    for (int b = 0; b < BN_MAX; ++b) {
-      if (b < B) {
-#pragma unroll
-        for (int v = 0; v < V; v += 4)
-          *reinterpret_cast<float4*>(dst + static_cast<size_t>(b) * H + v) =
-              make_float4(acc[b][v], acc[b][v + 1], acc[b][v + 2], acc[b][v + 3]);
+    for (int mt = 0; mt < BN_MT_MAX; ++mt) {
+      if (mt < MT) {
+        if (b0 < B) {
+          dst[static_cast<size_t>(b0) * H + mt * 16] = dacc[mt][0];
+          dst[static_cast<size_t>(b0) * H + mt * 16 + 8] = dacc[mt][2];
+        }
+        if (b1 < B) {
+          dst[static_cast<size_t>(b1) * H + mt * 16] = dacc[mt][1];
+          dst[static_cast<size_t>(b1) * H + mt * 16 + 8] = dacc[mt][3];
+        }
       }
     }
   }
@@ -1487,12 +1542,12 @@ static size_t bn_fixed_bytes(int H, int B, int r) {
          static_cast<size_t>(BN_MAX) * (static_cast<size_t>(H) * 2 + 64);
 }
 // shared memory per neuron of a tile: four half rows (gate/up x two halves) and the down row
-static size_t bn_neuron_bytes(int H) { return 4 * (static_cast<size_t>(H) + 64) + static_cast<size_t>(H) * 2 + 64; }
+static size_t bn_neuron_bytes(int H) { return 4 * (static_cast<size_t>(H) + 64) + static_cast<size_t>(H) * 2 + 16; }
 // neurons per tile (0: the kernel does not fit the shape)
 template <typename T>
 static int bn_slots(int H, int B, int r) {
   const size_t fixed = bn_fixed_bytes(H, B, r), budget = bn_smem_budget<T>();
-  if (H % 64 != 0 || H / 8 > 512 || budget < fixed + 2 * bn_neuron_bytes(H)) return 0;
+  if (H % 512 != 0 || H > 256 * BN_MT_MAX || budget < fixed + 2 * bn_neuron_bytes(H)) return 0;
   return static_cast<int>(std::min<size_t>(BN_TN_MAX, (budget - fixed) / bn_neuron_bytes(H)));
 }
 
