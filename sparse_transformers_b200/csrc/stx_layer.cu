@@ -19,8 +19,9 @@ bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate
                         const void* up, const void* down, const void* Bm);
 int layer_b1_forward(const void* x, int64_t B, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
                      const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
-                     int has_gate, int dtype, float* partial, int* status, unsigned parts, const stx_peer* peer,
+                     int has_gate, int dtype, float* partial, int* xchg, int* status, unsigned parts, const stx_peer* peer,
                      cudaStream_t s);
+size_t layer_bn_xchg_bytes();
 int peer_allreduce(const stx_peer* p, void* data, int64_t n, int dtype, cudaStream_t s);
 int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const void* up, const void* down,
                 const int32_t* K_dev, int64_t K_host, int64_t K_cap, int up_after_gate, void* out, void* combined,
@@ -48,6 +49,7 @@ struct stx_layer {
   void* mlp_scratch = nullptr;
   float* partial = nullptr;  // per-CTA partial outputs of the fused kernels: [SMs][partial_rows][H] fp32
   int64_t partial_rows = 0;
+  int* xchg = nullptr;  // count/id exchange between the CTAs of the 2..8-row kernel
   stx_peer* peer = nullptr;  // not owned: the shards' exchange; a step then ends with the all-reduce
   void* x_stage = nullptr;       // [max_batch, H] for the host-buffer entry point
   void* out_stage = nullptr;
@@ -78,6 +80,7 @@ int stx_layer_destroy(stx_layer_t* l) {
   cudaFree(l->pred_scratch);
   cudaFree(l->mlp_scratch);
   cudaFree(l->partial);
+  cudaFree(l->xchg);
   cudaFree(l->x_stage);
   cudaFree(l->out_stage);
   delete l;
@@ -130,6 +133,10 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
     l->partial_rows = std::min<int64_t>(max_batch, 8);
     e = cudaMalloc(reinterpret_cast<void**>(&l->partial), sizeof(float) * num_sms() * l->partial_rows * H);
   }
+  if (e == cudaSuccess && max_batch > 1) {
+    e = cudaMalloc(reinterpret_cast<void**>(&l->xchg), layer_bn_xchg_bytes());
+    if (e == cudaSuccess) e = cudaMemset(l->xchg, 0, layer_bn_xchg_bytes());
+  }
   if (e == cudaSuccess && method != STX_MASK_THRESHOLD) e = cudaMalloc(&l->scores, static_cast<size_t>(max_batch) * I * es);
   if (e != cudaSuccess) {
     set_error("stx_layer_create: device allocation failed: %s", cudaGetErrorString(e));
@@ -180,7 +187,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
     const float* t = static_cast<const float*>(l->pred_scratch);
     if (stages & STX_STAGE_MLP_GATEUP) {
       rc = layer_b1_forward(x_mlp, B, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
-                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 1u, l->peer, s);
+                            out, l->act, c->has_gate, c->dtype, partial, l->xchg, c->state + ST_STATUS, 1u, l->peer, s);
       if (rc != STX_OK) return rc;
     }
     if (fork_needed) {  // the mask exists once that kernel is done
@@ -189,7 +196,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
     }
     if (stages & STX_STAGE_MLP_DOWN) {
       rc = layer_b1_forward(x_mlp, B, c->H, c->I, c->pool_gate, c->pool_up, c->pool_down, t, l->Bm, l->r, l->param, l->bits,
-                            out, l->act, c->has_gate, c->dtype, partial, c->state + ST_STATUS, 2u, l->peer, s);
+                            out, l->act, c->has_gate, c->dtype, partial, l->xchg, c->state + ST_STATUS, 2u, l->peer, s);
       if (rc != STX_OK) return rc;
     }
   }

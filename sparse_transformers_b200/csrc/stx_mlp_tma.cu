@@ -700,6 +700,7 @@ struct MlpB1Args {
   uint32_t* bits;        // mask words of the layer (written bytewise)
   int r;
   float tau;
+  int* xchg;             // k_mlp_bn: count/id exchange between the CTAs (BN_XCHG_BYTES, zero before the first launch) or null
 };
 
 // With the predictor's back half fused in, CTA c owns mask bytes c, c + G, c + 2G, ... (8
@@ -770,9 +771,15 @@ __device__ __forceinline__ int cta_scores_and_list(const T* __restrict__ Bm, con
 #pragma unroll
           for (int b = 0; b < SB; ++b) {
             if (b0 + b < B) {
-              const float* tb = t_s + (b0 + b) * r + c * V;
+              const float4* tb = reinterpret_cast<const float4*>(t_s + (b0 + b) * r + c * V);  // 16-byte loads, same order
 #pragma unroll
-              for (int v = 0; v < V; ++v) sc[b] = fmaf(tb[v], w[c4][v], sc[b]);
+              for (int v4 = 0; v4 < V / 4; ++v4) {
+                const float4 tv = tb[v4];
+                sc[b] = fmaf(tv.x, w[c4][4 * v4], sc[b]);
+                sc[b] = fmaf(tv.y, w[c4][4 * v4 + 1], sc[b]);
+                sc[b] = fmaf(tv.z, w[c4][4 * v4 + 2], sc[b]);
+                sc[b] = fmaf(tv.w, w[c4][4 * v4 + 3], sc[b]);
+              }
             }
           }
         }
@@ -1051,6 +1058,19 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
 // mma issue, both per tile, not per neuron.
 // Rows of x and of the weights sit 64 bytes apart from a multiple of 128 so that the fragment
 // loads of different rows fall into different banks.
+// Balance.  A CTA's share of the active neurons is binomial; with tens of neurons per CTA the
+// heaviest CTA would finish a quarter later than the mean.  So every CTA publishes its count and
+// its list in global memory right after listing, starts on its first tile, and meanwhile reads
+// everybody's counts: CTAs above the cap Tk = ceil(K / G) hand the tail of their list to CTAs
+// below it, in ascending CTA order.  The plan is a pure function of the counts (deterministic);
+// every published word carries the launch's epoch, so no fence orders the stores and a reader
+// polls the word itself (bounded).  The exchange rides behind the first tile's loads.
+constexpr int BN_XCHG_COUNTS = 64;   // int offsets inside the exchange buffer: [0] epoch
+constexpr int BN_XCHG_IDS = BN_XCHG_COUNTS + 256;
+constexpr size_t BN_XCHG_BYTES = sizeof(int) * BN_XCHG_IDS + sizeof(int2) * 256 * B1_LIST_CAP;
+constexpr int BN_MAX_GRID = 160;
+constexpr uint32_t BN_POLL_LIMIT = 1u << 20;
+
 constexpr int BN_MAX = 8;
 constexpr int BN_TN_MAX = 8;
 constexpr int BN_MT_MAX = 16;  // m-tiles of 16 columns per warp: H <= 16 * 16 * 16
@@ -1099,45 +1119,168 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   STX_B1_STAMP(0);
-  const int nlocal = cta_scores_and_list<T>(static_cast<const T*>(q.Bm), q.t, t_s, B, q.r, p.I, q.tau, q.bits, s_my, s_nib,
-                                            s_bytes, &s_nlocal);
-  const int niter = (nlocal + TN - 1) / TN;
+  int nlocal = cta_scores_and_list<T>(static_cast<const T*>(q.Bm), q.t, t_s, B, q.r, p.I, q.tau, q.bits, s_my, s_nib,
+                                      s_bytes, &s_nlocal);
+  int niter = (nlocal + TN - 1) / TN;
+  const int G = gridDim.x;
+  const bool balance = q.xchg != nullptr && G <= BN_MAX_GRID;
+  __shared__ int s_epoch, s_plan[4];
+  int epoch = 0;
+  const int n_own = nlocal;
+  if (balance) {  // publish the count and the list
+    if (tid == 0) s_epoch = *reinterpret_cast<volatile int*>(q.xchg);
+    __syncthreads();
+    epoch = static_cast<int>(static_cast<unsigned>(s_epoch) + 1u);
+    if (tid == 0)
+      *reinterpret_cast<volatile int*>(q.xchg + BN_XCHG_COUNTS + blockIdx.x) = ((epoch & 0x1fffff) << 10) | n_own;
+    if (tid < n_own) {
+      int2* dst = reinterpret_cast<int2*>(q.xchg + BN_XCHG_IDS) + blockIdx.x * B1_LIST_CAP + tid;
+      asm volatile("st.relaxed.gpu.global.v2.s32 [%0], {%1,%2};" ::"l"(dst), "r"(s_my[tid]), "r"(epoch) : "memory");
+    }
+  }
 
-  // One thread fills a buffer with the rows of tile j (warp 0: X, warp 1: Y, warp 2: Z).
+  // One warp fills a buffer with the rows of tile j (warp 0: X, warp 1: Y, warp 2: Z): lane 0 arms
+  // the barrier with the byte count, then lane e issues the copies of neuron e, so the issue cost
+  // of a dozen bulk copies does not sit on one thread between two block-wide barriers.
   auto fill = [&](int which, int j) {
-    if (j >= niter || warp != which || lane != 0) return;
+    if (j >= niter || warp != which) return;
     const int nv = min(TN, nlocal - j * TN);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (which < 2) {
-      uint64_t* bar = which == 0 ? bar_x : bar_y;
-      unsigned char* buf = which == 0 ? X : Y;
-      const size_t col = which == 0 ? 0 : half_bytes;
-      mbar_expect_tx(bar, static_cast<uint32_t>(nv) * 2 * half_bytes);
-      for (int e = 0; e < nv; ++e) {
-        const size_t off = static_cast<size_t>(s_my[j * TN + e]) * row_bytes + col;
-        bulk_load(buf + static_cast<size_t>(2 * e) * hstride, gsrc + off, half_bytes, bar);
-        bulk_load(buf + static_cast<size_t>(2 * e + 1) * hstride, usrc + off, half_bytes, bar);
+    uint64_t* bar = which == 0 ? bar_x : (which == 1 ? bar_y : bar_z);
+    if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(nv) * (which < 2 ? 2 * half_bytes : row_bytes));
+    __syncwarp();
+    if (lane < nv) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      const int e = lane;
+      const size_t row = static_cast<size_t>(s_my[j * TN + e]) * row_bytes;
+      if (which < 2) {
+        unsigned char* buf = which == 0 ? X : Y;
+        const size_t col = which == 0 ? 0 : half_bytes;
+        bulk_load(buf + static_cast<size_t>(2 * e) * hstride, gsrc + row + col, half_bytes, bar);
+        bulk_load(buf + static_cast<size_t>(2 * e + 1) * hstride, usrc + row + col, half_bytes, bar);
+      } else {
+        bulk_load(Z + static_cast<size_t>(e) * zstride, dsrc + row, row_bytes, bar);
       }
-    } else {
-      mbar_expect_tx(bar_z, static_cast<uint32_t>(nv) * row_bytes);
-      for (int e = 0; e < nv; ++e)
-        bulk_load(Z + static_cast<size_t>(e) * zstride, dsrc + static_cast<size_t>(s_my[j * TN + e]) * row_bytes, row_bytes, bar_z);
     }
   };
   STX_B1_STAMP(2);
-  fill(0, 0);
-  fill(1, 0);
-  if (niter > 0 && nlocal < TN) {
+  // the first tile is this CTA's own in any case when it is full; a short list may still grow
+  const bool early = !balance || n_own >= TN;
+  if (early) {
+    fill(0, 0);
+    fill(1, 0);
+  }
+  if (early && niter > 0 && nlocal < TN) {
     // a short only tile: the unused down rows are multiplied by a = 0, so they must hold finite numbers
     for (int i = tid; i < TN * static_cast<int>(zstride / 16); i += blockDim.x)
       reinterpret_cast<uint4*>(Z)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
   }
-  fill(2, 0);
+  if (early) fill(2, 0);
   for (int i = tid; i < BN_MAX * nchunk; i += blockDim.x) {  // rows beyond B are zero
     const int b = i / nchunk, c = i - b * nchunk;
     const uint4 v = b < B ? ld_cached16(static_cast<const T*>(p.x) + static_cast<size_t>(b) * H + c * V) : make_uint4(0, 0, 0, 0);
     *reinterpret_cast<uint4*>(x_s + static_cast<size_t>(b) * rstride + c * 16) = v;
+  }
+  bool timed_out = false;
+  if (balance) {
+    // ---- everybody's counts (bounded wait; 16-byte loads: one request per line of the count array)
+    int* xc = q.xchg;
+    const int tag = epoch & 0x1fffff;
+    int* s_cnt = s_my + B1_LIST_CAP;        // [BN_MAX_GRID]
+    int* s_exE = s_cnt + BN_MAX_GRID;       // [BN_MAX_GRID] exclusive prefix of the excess counts
+    if (tid * 4 < G) {
+      int v[4] = {0, 0, 0, 0};
+      bool got = false;
+      for (uint32_t it = 0; it < BN_POLL_LIMIT; ++it) {
+        asm volatile("ld.relaxed.gpu.global.v4.s32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                     : "l"(xc + BN_XCHG_COUNTS + tid * 4)
+                     : "memory");
+        got = true;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) got = got && (tid * 4 + i >= G || (v[i] >> 10) == tag);
+        if (got) break;
+        __nanosleep(100);
+      }
+      if (!got) timed_out = true;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (tid * 4 + i < G) s_cnt[tid * 4 + i] = got ? (v[i] & 1023) : 0;
+    }
+    const int any_timeout = __syncthreads_or(timed_out ? 1 : 0);
+    if (warp == 0) {
+      int total = 0;
+      for (int c = lane; c < G; c += 32) total += s_cnt[c];
+      total = __reduce_add_sync(0xffffffffu, total);
+      const int Tk = max(TN, (total + G - 1) / G);  // cap: nobody keeps more than this
+      int E = 0;
+      for (int c = lane; c < G; c += 32) E += max(0, s_cnt[c] - Tk);
+      E = __reduce_add_sync(0xffffffffu, E);
+      // exclusive prefixes over CTAs in ascending order: excess (everybody needs all), room (this CTA's)
+      int carry_e = 0, carry_s = 0, my_P = 0;
+      for (int base = 0; base < G; base += 32) {
+        const int c = base + lane;
+        const int n = c < G ? s_cnt[c] : 0;
+        const int ex = c < G ? max(0, n - Tk) : 0;
+        const int sp = c < G ? max(0, Tk - n) : 0;
+        int ie = ex, is = sp;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int ve = __shfl_up_sync(0xffffffffu, ie, off);
+          const int vs = __shfl_up_sync(0xffffffffu, is, off);
+          if (lane >= off) {
+            ie += ve;
+            is += vs;
+          }
+        }
+        if (c < G) s_exE[c] = carry_e + ie - ex;
+        if (c == static_cast<int>(blockIdx.x)) my_P = carry_s + is - sp;
+        carry_e += __shfl_sync(0xffffffffu, ie, 31);
+        carry_s += __shfl_sync(0xffffffffu, is, 31);
+      }
+      my_P = __reduce_add_sync(0xffffffffu, my_P);  // one lane holds it
+      if (lane == 0) {
+        s_plan[0] = min(n_own, Tk);                        // neurons this CTA keeps
+        s_plan[1] = max(0, min(Tk - n_own, E - my_P));     // neurons it takes over
+        s_plan[2] = my_P;
+        s_plan[3] = Tk;
+      }
+    }
+    __syncthreads();
+    if (!any_timeout) {
+      const int keep = s_plan[0], take = s_plan[1], my_P = s_plan[2], Tk = s_plan[3];
+      if (tid < take) {
+        const int o = my_P + tid;  // index of the excess neuron this thread resolves
+        int src = 0;
+        for (int c = 0; c < G; ++c)
+          if (s_exE[c] <= o) src = c;  // the last CTA whose prefix is <= o owns excess neuron o
+        const int2* idp = reinterpret_cast<const int2*>(xc + BN_XCHG_IDS) + src * B1_LIST_CAP + Tk + (o - s_exE[src]);
+        int id = 0, ep = 0;
+        bool got = false;
+        for (uint32_t it = 0; it < BN_POLL_LIMIT && !got; ++it) {
+          asm volatile("ld.relaxed.gpu.global.v2.s32 {%0,%1}, [%2];" : "=r"(id), "=r"(ep) : "l"(idp) : "memory");
+          got = ep == epoch;
+          if (!got) __nanosleep(100);
+        }
+        if (!got) timed_out = true;
+        s_my[keep + tid] = got ? id : 0;
+      }
+      nlocal = keep + take;
+      niter = (nlocal + TN - 1) / TN;
+    }
+    // every CTA has published, hence read the epoch: advance it for the next launch
+    if (blockIdx.x == 0 && tid == 0) *reinterpret_cast<volatile int*>(xc) = epoch;
+    __syncthreads();
+    if (!early) {
+      if (niter > 0 && nlocal < TN) {  // as above: unused down rows must hold finite numbers
+        for (int i = tid; i < TN * static_cast<int>(zstride / 16); i += blockDim.x)
+          reinterpret_cast<uint4*>(Z)[i] = make_uint4(0, 0, 0, 0);
+        __syncthreads();
+      }
+      fill(0, 0);
+      fill(1, 0);
+      fill(2, 0);
+    }
   }
   __syncthreads();
 
@@ -1149,7 +1292,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     for (int k = 0; k < 4; ++k) dacc[mt][k] = 0.f;
   const int MT = H / 256;  // m-tiles per warp (even)
 
-  bool timed_out = false;
   const int nwh = H / 64;  // windows (32 consecutive k = 64 bytes) per half row
   const int w_lo = (nwh * warp) / 16, w_hi = (nwh * (warp + 1)) / 16;  // this warp's share of each half
   unsigned long long tw0 = 0, tw1 = 0, tw_gu = 0, tw_d = 0, t_loop0 = 0;  // development timeline only
@@ -1484,6 +1626,7 @@ static int b1_slots(int H, int has_gate, int r) {
 
 struct B1Pred {  // predictor back half fused into k_mlp_b1 (Bm == nullptr: not fused)
   PeerArgs peer = {};  // world > 1: k_partial_reduce ends with the all-reduce over the shards
+  int* xchg = nullptr;
   const float* t = nullptr;
   const void* Bm = nullptr;
   uint32_t* bits = nullptr;
@@ -1507,6 +1650,7 @@ static int launch_b1(const GateUpArgs& g, const void* down, float* partial, void
   q.bits = pr.bits;
   q.r = pr.r;
   q.tau = pr.tau;
+  q.xchg = nullptr;
   const size_t smem = B1_HEADER + x_bytes + static_cast<size_t>(q.g.nwarps) * nmat * row_bytes;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -1564,6 +1708,7 @@ static int launch_bn(const GateUpArgs& g, const void* down, float* partial, void
   q.bits = pr.bits;
   q.r = pr.r;
   q.tau = pr.tau;
+  q.xchg = pr.xchg;
   const size_t smem = bn_fixed_bytes(g.H, g.B, pr.r) + static_cast<size_t>(q.g.nwarps) * bn_neuron_bytes(g.H);
   static bool attr_set[64] = {};
   int dev = 0;
@@ -1621,6 +1766,8 @@ static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const
 // One row through a layer whose mask comes from the threshold rule: the predictor's back half,
 // the gather and the whole MLP in k_mlp_b1, then k_partial_reduce.  parts bit 0 / bit 1 select
 // the two kernels.  `t` holds A x (fp32 [r]) written earlier on the same stream.
+size_t layer_bn_xchg_bytes() { return BN_XCHG_BYTES; }
+
 bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate,
                         const void* up, const void* down, const void* Bm) {
   if (B < 1 || B > BN_MAX) return false;
@@ -1641,7 +1788,7 @@ bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate
 
 int layer_b1_forward(const void* x, int64_t B, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
                      const float* t, const void* Bm, int64_t r, float tau, uint32_t* bits, void* out, int act,
-                     int has_gate, int dtype, float* partial, int* status, unsigned parts, const stx_peer* peer,
+                     int has_gate, int dtype, float* partial, int* xchg, int* status, unsigned parts, const stx_peer* peer,
                      cudaStream_t s) {
   GateUpArgs a;
   a.x = x;
@@ -1667,6 +1814,7 @@ int layer_b1_forward(const void* x, int64_t B, int64_t H, int64_t I, const void*
   pr.bits = bits;
   pr.r = static_cast<int>(r);
   pr.tau = tau;
+  pr.xchg = xchg;
   if (peer && peer->world > 1) {
     if (!peer_args(peer, &pr.peer)) {
       set_error("stx_layer_step: the layer's peer object is not connected");
