@@ -548,8 +548,10 @@ int stx_cache_destroy(stx_cache_t* c) {
   cudaFree(c->own_gate);
   cudaFree(c->own_up);
   cudaFree(c->pool_down);
-  cudaFree(c->pk_gate);
-  cudaFree(c->pk_up);
+  if (c->pk_gate)
+    cudaFree(c->pk_gate);  // pk_up lives in the same allocation
+  else
+    cudaFree(c->pk_up);
   cudaFree(c->pk_down);
   cudaFree(c->concat);
   cudaFree(c->active);
@@ -616,9 +618,15 @@ int stx_cache_create(stx_cache_t** out, int64_t I, int64_t H, int dtype, int has
   const size_t W = static_cast<size_t>((I + 31) / 32);
 
   STX_ALLOC(c->pool_down, mat);
-  STX_ALLOC(c->pk_up, mat);
+  // packed gate and up rows share one allocation, gate first: [pk_gate ; pk_up] is the concat
+  // weight of a cache whose I slots are all in use, which the tensor-core path reads directly
+  if (has_gate) {
+    STX_ALLOC(c->pk_gate, 2 * mat);
+    c->pk_up = static_cast<char*>(c->pk_gate) + mat;
+  } else {
+    STX_ALLOC(c->pk_up, mat);
+  }
   STX_ALLOC(c->pk_down, mat);
-  if (has_gate) STX_ALLOC(c->pk_gate, mat);
   if (!alias) {
     STX_ALLOC(c->own_up, mat);
     if (has_gate) STX_ALLOC(c->own_gate, mat);

@@ -15,6 +15,11 @@ int predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t r, 
                  int dtype, int method, float param, uint32_t* bits, void* scores_out, void* scratch, unsigned parts,
                  cudaStream_t s);
 float* b1_partial_region(void* scratch, int64_t H, int64_t K_cap);
+void* mlp_prefill_region(void* scratch, int64_t B, int64_t H, int64_t K);
+bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate);
+int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, const void* down_packed, int64_t K,
+                    void* out, void* combined, int act, int dtype, void* scratch, int* status, const int* k_dev,
+                    cudaStream_t s);
 bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate,
                         const void* up, const void* down, const void* Bm);
 int layer_b1_forward(const void* x, int64_t B, int64_t H, int64_t I, const void* gate, const void* up, const void* down,
@@ -176,7 +181,12 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       if (rc != STX_OK) return rc;
     }
   }
-  const bool forked = side != s && l->gather;
+  // Row blocks of 64 and more (16-bit, gated): the packed cache IS the operand of two tensor-core
+  // GEMMs, so its maintenance comes first, on the same stream; the GEMMs are shaped for all I
+  // slots and follow the device-side K (no host read-back, graph-capturable).
+  const bool big = !fuse && c->pk_gate && prefill_wanted(B, c->H, c->I, c->dtype, c->has_gate);
+  const bool gather = l->gather && !big;
+  const bool forked = side != s && gather;
   cudaStream_t cs = forked ? side : s;  // stream of the cache maintenance
   const bool fork_needed = forked && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY));
   if (fork_needed && !fuse) {
@@ -200,21 +210,32 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       if (rc != STX_OK) return rc;
     }
   }
-  if (!l->gather) {
-    // the MLP reads the packed cache: plan and copies come first, on the same stream
-    if (stages & STX_STAGE_PLAN) {
+  if (!gather) {
+    // the MLP reads the packed cache: plan and copies come first, on the same stream (a big row
+    // block brings the cache up to date as part of its MLP stage if the caller left that for later)
+    if ((stages & STX_STAGE_PLAN) || (big && (stages & STX_STAGE_MLP))) {
       rc = cache_plan(c, l->bits, s);
       if (rc != STX_OK) return rc;
     }
-    if (stages & STX_STAGE_COPY) {
+    if ((stages & STX_STAGE_COPY) || (big && (stages & STX_STAGE_MLP))) {
       rc = cache_copy_rows(c, s);
       if (rc != STX_OK) return rc;
     }
   }
-  if ((stages & STX_STAGE_MLP) && !fuse) {
+  if ((stages & STX_STAGE_MLP) && big) {
+    STX_CHECK_ARG(x_mlp && out, "stx_layer_step: x_mlp/out is null");
+    rc = prefill_forward(x_mlp, B, c->H, c->pk_gate, c->pk_down, c->I, out, nullptr, l->act, c->dtype,
+                         mlp_prefill_region(l->mlp_scratch, B, c->H, c->I), c->state + ST_STATUS, c->state + ST_K, s);
+    if (rc != STX_OK) return rc;
+    if (l->peer && l->peer->world > 1) {
+      rc = peer_allreduce(l->peer, out, B * c->H, c->dtype, s);
+      if (rc != STX_OK) return rc;
+    }
+  }
+  if ((stages & STX_STAGE_MLP) && !fuse && !big) {
     STX_CHECK_ARG(x_mlp && out, "stx_layer_step: x_mlp/out is null");
     const unsigned parts = ((stages & STX_STAGE_MLP_GATEUP) ? 1u : 0u) | ((stages & STX_STAGE_MLP_DOWN) ? 2u : 0u);
-    if (l->gather)
+    if (gather)
       rc = mlp_forward(x_mlp, B, c->H, c->pool_gate, c->pool_up, c->pool_down, l->count, 0, c->I, 0, out, nullptr, l->act,
                        c->has_gate, c->dtype, l->mlp_scratch, c->state + ST_STATUS, parts, l->bits, l->idx, l->count, true, s);
     else
@@ -226,7 +247,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       if (rc != STX_OK) return rc;
     }
   }
-  if (l->gather) {
+  if (gather) {
     if (stages & STX_STAGE_PLAN) {
       rc = cache_plan(c, l->bits, cs, l->lazy);
       if (rc != STX_OK) return rc;
@@ -372,7 +393,9 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
     for (int64_t i = 0; i < L && rc == STX_OK; ++i) {
       stx_layer* l = s->layers[i];
       rc = layer_step_streams(l, s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs, side, s->events[i], stages);
-      forked = forked || (l->gather && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY)));
+      const bool big = l->cache->pk_gate && !single_row_fusable(l, B) &&
+                       prefill_wanted(B, l->cache->H, l->cache->I, l->cache->dtype, l->cache->has_gate);
+      forked = forked || (l->gather && !big && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY)));
     }
     if (rc == STX_OK && forked) {  // join
       cudaError_t ej = cudaEventRecord(s->events[L], side);

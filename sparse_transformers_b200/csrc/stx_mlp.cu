@@ -245,7 +245,8 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
 size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K);
 bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate);
 int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, const void* down_packed, int64_t K,
-                    void* out, void* combined, int act, int dtype, void* scratch, int* status, cudaStream_t s);
+                    void* out, void* combined, int act, int dtype, void* scratch, int* status, const int* k_dev,
+                    cudaStream_t s);
 
 constexpr int64_t PARTIAL_ROWS = 256;  // per-CTA partial output vectors of the batch-1 kernel (>= SM count)
 
@@ -257,6 +258,11 @@ static size_t decode_scratch_bytes_min(int64_t B, int64_t H, int64_t K) {
 }
 static size_t decode_scratch_bytes(int64_t B, int64_t H, int64_t K) {
   return decode_scratch_bytes_min(B, H, K) + (B == 1 ? align_up(static_cast<size_t>(PARTIAL_ROWS) * H * sizeof(float), 256) : 0);
+}
+
+// Scratch of the tensor-core path inside a buffer that stx_mlp_scratch_bytes(B', H, K) sized, B' >= B >= 64.
+void* mlp_prefill_region(void* scratch, int64_t B, int64_t H, int64_t K) {
+  return static_cast<char*>(scratch) + decode_scratch_bytes(B, H, K);
 }
 
 // Per-CTA partial output vectors of the batch-1 kernel inside a scratch buffer that
@@ -381,10 +387,10 @@ int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* con
   const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(concat_w) |
                        reinterpret_cast<uintptr_t>(down_packed) | reinterpret_cast<uintptr_t>(scratch);
   STX_CHECK_ARG((al & 15) == 0, "stx_sparse_mlp_forward: x, concat_w, down_packed and scratch must be 16-byte aligned");
-  if (prefill_wanted(B, H, K, dtype, has_gate)) {
+  if (prefill_wanted(B, H, K, dtype, has_gate)) {  // (mlp_prefill_region below)
     // hundreds of rows: the gathered weights form a dense contraction -> tcgen05 GEMMs
     return prefill_forward(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, dtype,
-                           static_cast<char*>(scratch) + decode_scratch_bytes(B, H, K), nullptr,
+                           static_cast<char*>(scratch) + decode_scratch_bytes(B, H, K), nullptr, nullptr,
                            static_cast<cudaStream_t>(stream));
   }
   const char* cw = static_cast<const char*>(concat_w);

@@ -46,6 +46,10 @@ struct PfArgs {
   void* combined;      // MODE 0, optional: [M, 2K]
   int act;
   int* status;
+  // Optional device-side count of valid rows of the packed weights (a weight cache's K): MODE 0
+  // writes zero activations for columns >= *k_dev and skips tiles wholly beyond it; MODE 1 stops
+  // its contraction at *k_dev (rounded up to a k-block, which MODE 0 filled with zeros).
+  const int* k_dev;
 };
 
 __device__ __forceinline__ uint32_t pf_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -155,7 +159,10 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   // is the re-read operand; MODE 1: column tiles vary fastest (the transposed down weight fits L2)
   const int n_idx = MODE == 0 ? blockIdx.y : blockIdx.x, m_idx = MODE == 0 ? blockIdx.x : blockIdx.y;
   const int n0 = n_idx * (MODE == 0 ? PF_BN : 2 * PF_BN), m0 = m_idx * (MH * PF_BM);
-  const int nkb = (p.Kd + PF_BK - 1) / PF_BK;
+  const int k_valid = p.k_dev ? *p.k_dev : 0x7fffffff;
+  const int k_round = k_valid > 0x7fffff00 ? k_valid : (k_valid + PF_BK - 1) / PF_BK * PF_BK;
+  if (MODE == 0 && n0 >= k_round) return;  // nothing downstream reads these columns (uniform for the CTA)
+  const int nkb = (min(p.Kd, MODE == 1 ? k_valid : p.Kd) + PF_BK - 1) / PF_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -238,7 +245,7 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int col = n0 + c;
           const int n = min(32, p.N - col);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) g[e] = apply_act(p.act, g[e]) * u[e];
+          for (int e = 0; e < 32; ++e) g[e] = col + e < k_valid ? apply_act(p.act, g[e]) * u[e] : 0.f;
           if (row < p.M && n > 0) {
             if (out) pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
             if (comb) {
@@ -252,6 +259,10 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int c = 0; c < 2 * PF_BN; c += 32) {
           float g[32];
           pf_ld32(taddr + c, g);
+          if (nkb == 0) {  // empty contraction: the accumulator was never written
+#pragma unroll
+            for (int e = 0; e < 32; ++e) g[e] = 0.f;
+          }
           const int col = n0 + c;
           const int n = min(32, p.N - col);
           if (row < p.M && n > 0) pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
@@ -269,9 +280,11 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
 // [K, H] -> [H, ldo] (ldo >= K): packed down rows to the K-major B operand of GEMM 2.
 template <typename E>
-__global__ void __launch_bounds__(256) k_pf_transpose(const E* __restrict__ in, E* __restrict__ out, int R, int C, int ldo) {
+__global__ void __launch_bounds__(256) k_pf_transpose(const E* __restrict__ in, E* __restrict__ out, int R, int C, int ldo,
+                                                      const int* __restrict__ r_dev) {
   __shared__ E tile[32][33];
   const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  if (r_dev && r0 >= (*r_dev + PF_BK - 1) / PF_BK * PF_BK) return;  // rows no k-block of the contraction reaches
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   for (int k = ty; k < 32; k += 8) {
     const int r = r0 + k, c = c0 + tx;
@@ -366,8 +379,11 @@ bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate) {
 }
 
 // x [B,H], concat [2K,H] (gate rows then up rows), down_packed [K,H]; scratch: prefill_scratch_bytes().
+// k_dev (optional): device count of valid packed rows, <= K; the work then follows *k_dev while all
+// shapes, tensor maps and grids are built for K, so the call needs no host read-back.
 int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, const void* down_packed, int64_t K,
-                    void* out, void* combined, int act, int dtype, void* scratch, int* status, cudaStream_t s) {
+                    void* out, void* combined, int act, int dtype, void* scratch, int* status, const int* k_dev,
+                    cudaStream_t s) {
   const int64_t K8 = (K + 7) / 8 * 8;
   const uintptr_t base = (reinterpret_cast<uintptr_t>(scratch) + 1023) & ~static_cast<uintptr_t>(1023);
   void* a_scr = reinterpret_cast<void*>(base);                                                   // [B, K8]
@@ -380,7 +396,7 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
   {
     dim3 grid(static_cast<unsigned>((H + 31) / 32), static_cast<unsigned>((K + 31) / 32));
     k_pf_transpose<uint16_t><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(down_packed), static_cast<uint16_t*>(dt_scr),
-                                                 static_cast<int>(K), static_cast<int>(H), static_cast<int>(K8));
+                                                 static_cast<int>(K), static_cast<int>(H), static_cast<int>(K8), k_dev);
     STX_LAUNCH_CHECK("k_pf_transpose");
   }
   // the activations are GEMM 2's A operand: read them straight from combined_buf[:, :K] when its
@@ -403,6 +419,7 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
   g1.combined = combined;
   g1.act = act;
   g1.status = status;
+  g1.k_dev = k_dev;
   PfArgs g2{};
   g2.M = static_cast<int>(B);
   g2.N = static_cast<int>(H);
@@ -412,6 +429,7 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
   g2.ld_out = static_cast<int>(H);
   g2.act = act;
   g2.status = status;
+  g2.k_dev = k_dev;
   if (dtype == STX_F16) {
     rc = launch_umma<__half, 0>(mx, mw, g1, s);
     if (rc == STX_OK) rc = launch_umma<__half, 1>(ma, md, g2, s);

@@ -162,3 +162,14 @@ def test_packed_cache_current_after_fused_steps(lazy):
             K = len(idx)
             assert torch.equal(cw[:K], gate[idx]) and torch.equal(cw[K:], up[idx])
             assert torch.equal(layer.active_down_weight().cpu(), down[:, idx])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_row_block_of_64_runs_on_the_packed_cache(dtype):
+    """64 rows: the layer step brings the packed cache up to date first and runs the two tensor-core
+    GEMMs over it, following the device-side K (the union of 64 masks leaves a changing K)."""
+    from sparse_transformers_b200.synth import Workload
+
+    w = Workload("b64", H=1024, I=2048, r=32, B=64, dtype=dtype, density=0.05, alpha=0.8)
+    ks = _run(w, steps=6, seed=3)
+    assert 64 < min(ks) and max(ks) < 2048 and len(set(ks)) > 1
