@@ -1768,6 +1768,22 @@ static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const
 // the two kernels.  `t` holds A x (fp32 [r]) written earlier on the same stream.
 size_t layer_bn_xchg_bytes() { return BN_XCHG_BYTES; }
 
+// out[i] = sum over g < G of partial[g][i] in ascending g (n a multiple of 128), model dtype.
+int partial_sum(const float* partial, int G, int64_t n, void* out, int dtype, cudaStream_t s) {
+  STX_CHECK_ARG(n % 128 == 0 && n / 128 < (1ll << 31), "partial_sum: n must be a multiple of 128");
+  const PeerArgs none = {};
+  const int nn = static_cast<int>(n);
+  switch (dtype) {
+    case STX_F32: STX_CUDA(launch_pdl(k_partial_reduce4<float>, dim3(nn / 128), dim3(1024), 0, s, partial, G, nn, static_cast<float*>(out), none)); break;
+    case STX_F16: STX_CUDA(launch_pdl(k_partial_reduce4<__half>, dim3(nn / 128), dim3(1024), 0, s, partial, G, nn, static_cast<__half*>(out), none)); break;
+    default:
+      STX_CUDA(launch_pdl(k_partial_reduce4<__nv_bfloat16>, dim3(nn / 128), dim3(1024), 0, s, partial, G, nn,
+                          static_cast<__nv_bfloat16*>(out), none));
+      break;
+  }
+  return STX_OK;
+}
+
 bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate, int dtype, const void* gate,
                         const void* up, const void* down, const void* Bm) {
   if (B < 1 || B > BN_MAX) return false;

@@ -41,6 +41,7 @@ struct PfArgs {
   int M, N, Kd;        // output rows, output columns, contraction length
   int up_off;          // MODE 0: row offset of the up block inside the concat weight (= K)
   int stages;
+  int stages_z;        // MODE 1: number of contraction splits (gridDim.z), 0/1 = none
   void* a_out;         // MODE 0: activations [M, lda] ; MODE 1: output [M, ldo]
   int ld_out;
   void* combined;      // MODE 0, optional: [M, 2K]
@@ -50,6 +51,9 @@ struct PfArgs {
   // writes zero activations for columns >= *k_dev and skips tiles wholly beyond it; MODE 1 stops
   // its contraction at *k_dev (rounded up to a k-block, which MODE 0 filled with zeros).
   const int* k_dev;
+  // MODE 1, optional split of the contraction over gridDim.z CTAs: CTA z takes an equal share of the
+  // k-blocks and writes its fp32 partial tile to part[z][M][ld_out]; the caller adds the partials.
+  float* part;
 };
 
 __device__ __forceinline__ uint32_t pf_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -162,7 +166,11 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int k_valid = p.k_dev ? *p.k_dev : 0x7fffffff;
   const int k_round = k_valid > 0x7fffff00 ? k_valid : (k_valid + PF_BK - 1) / PF_BK * PF_BK;
   if (MODE == 0 && n0 >= k_round) return;  // nothing downstream reads these columns (uniform for the CTA)
-  const int nkb = (min(p.Kd, MODE == 1 ? k_valid : p.Kd) + PF_BK - 1) / PF_BK;
+  const int nkb_all = (min(p.Kd, MODE == 1 ? k_valid : p.Kd) + PF_BK - 1) / PF_BK;
+  // this CTA's k-blocks [kb_lo, kb_lo + nkb)
+  const int nz = MODE == 1 ? static_cast<int>(gridDim.z) : 1, zi = MODE == 1 ? static_cast<int>(blockIdx.z) : 0;
+  const int kb_lo = (nkb_all * zi) / nz;
+  const int nkb = (nkb_all * (zi + 1)) / nz - kb_lo;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -192,9 +200,10 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         unsigned char* st = smem + static_cast<size_t>(s) * STAGE_BYTES;
         pf_expect_tx(&full[s], STAGE_BYTES);
 #pragma unroll
-        for (int mh = 0; mh < MH; ++mh) pf_tma_2d(st + mh * PF_TILE_BYTES, &tmA, kb * PF_BK, m0 + mh * PF_BM, &full[s]);
-        pf_tma_2d(st + MH * PF_TILE_BYTES, &tmB, kb * PF_BK, n0, &full[s]);
-        pf_tma_2d(st + (MH + 1) * PF_TILE_BYTES, &tmB, kb * PF_BK, MODE == 0 ? p.up_off + n0 : n0 + PF_BN, &full[s]);
+        for (int mh = 0; mh < MH; ++mh)
+          pf_tma_2d(st + mh * PF_TILE_BYTES, &tmA, (kb_lo + kb) * PF_BK, m0 + mh * PF_BM, &full[s]);
+        pf_tma_2d(st + MH * PF_TILE_BYTES, &tmB, (kb_lo + kb) * PF_BK, n0, &full[s]);
+        pf_tma_2d(st + (MH + 1) * PF_TILE_BYTES, &tmB, (kb_lo + kb) * PF_BK, MODE == 0 ? p.up_off + n0 : n0 + PF_BN, &full[s]);
       }
     }
   } else if (warp == 1) {
@@ -265,7 +274,14 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           const int col = n0 + c;
           const int n = min(32, p.N - col);
-          if (row < p.M && n > 0) pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
+          if (row < p.M && n > 0) {
+            if (p.part) {
+              float* dst = p.part + (static_cast<size_t>(zi) * p.M + row) * p.ld_out + col;
+              for (int e = 0; e < n; ++e) dst[e] = g[e];
+            } else {
+              pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
+            }
+          }
         }
       }
     }
@@ -350,7 +366,7 @@ static int launch_umma_mh(const CUtensorMap& a, const CUtensorMap& b, PfArgs p, 
     attr_set[dev] = true;
   }
   const int bn = MODE == 0 ? PF_BN : 2 * PF_BN, bm = MH * PF_BM;
-  dim3 grid((p.N + bn - 1) / bn, (p.M + bm - 1) / bm);
+  dim3 grid((p.N + bn - 1) / bn, (p.M + bm - 1) / bm, MODE == 1 ? static_cast<unsigned>(std::max(1, p.stages_z)) : 1u);
   if (MODE == 0) grid = dim3(grid.y, grid.x);
   k_umma_gemm<T, MODE, MH><<<grid, PF_THREADS, smem, s>>>(a, b, p);
   STX_LAUNCH_CHECK("k_umma_gemm");
@@ -363,10 +379,23 @@ static int launch_umma(const CUtensorMap& a, const CUtensorMap& b, const PfArgs&
   return p.M > PF_BM ? launch_umma_mh<T, MODE, 2>(a, b, p, s) : launch_umma_mh<T, MODE, 1>(a, b, p, s);
 }
 
+// GEMM 2 has only ceil(B/128..256) x H/256 output tiles; for few rows the contraction is split so
+// that about one CTA per SM streams the down weight.
+static int gemm2_splits(int64_t B, int64_t H) {
+  const int64_t tiles = ((B + (B > PF_BM ? 2 * PF_BM : PF_BM) - 1) / (B > PF_BM ? 2 * PF_BM : PF_BM)) * ((H + 2 * PF_BN - 1) / (2 * PF_BN));
+  if (tiles * 2 > num_sms()) return 1;
+  return static_cast<int>(std::min<int64_t>(16, std::max<int64_t>(1, num_sms() / tiles)));
+}
+
 size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K) {
   const int64_t K8 = (K + 7) / 8 * 8;
-  return align_up(static_cast<size_t>(B) * K8 * 2, 1024) + align_up(static_cast<size_t>(H) * K8 * 2, 1024) + 1024;
+  const int z = gemm2_splits(B, H);
+  return align_up(static_cast<size_t>(B) * K8 * 2, 1024) + align_up(static_cast<size_t>(H) * K8 * 2, 1024) + 1024 +
+         (z > 1 ? align_up(static_cast<size_t>(z) * B * H * sizeof(float), 1024) : 0);
 }
+
+// Implemented in stx_mlp_tma.cu: out[i] = sum over g < G of partial[g][i], g ascending (n % 128 == 0).
+int partial_sum(const float* partial, int G, int64_t n, void* out, int dtype, cudaStream_t s);
 
 // STX_PREFILL=0 keeps large row counts on the decode kernels (A/B measurements).
 bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate) {
@@ -430,6 +459,13 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
   g2.act = act;
   g2.status = status;
   g2.k_dev = k_dev;
+  const int z = (B * H) % 128 == 0 ? gemm2_splits(B, H) : 1;
+  float* part = nullptr;
+  if (z > 1) {
+    part = reinterpret_cast<float*>(base + align_up(static_cast<size_t>(B) * K8 * 2, 1024) + align_up(static_cast<size_t>(H) * K8 * 2, 1024));
+    g2.part = part;
+    g2.stages_z = z;
+  }
   if (dtype == STX_F16) {
     rc = launch_umma<__half, 0>(mx, mw, g1, s);
     if (rc == STX_OK) rc = launch_umma<__half, 1>(ma, md, g2, s);
@@ -437,6 +473,7 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
     rc = launch_umma<__nv_bfloat16, 0>(mx, mw, g1, s);
     if (rc == STX_OK) rc = launch_umma<__nv_bfloat16, 1>(ma, md, g2, s);
   }
+  if (rc == STX_OK && part) rc = partial_sum(part, z, B * H, out, dtype, s);
   return rc;
 }
 
