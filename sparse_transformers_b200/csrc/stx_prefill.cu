@@ -145,7 +145,9 @@ __device__ __forceinline__ void pf_store_row(T* dst, const float* v, int n) {
 
 // Dynamic shared memory (1024-byte aligned): stages x (A tile | B tile [| second B tile]);
 // then full[stages], empty[stages], accum barrier, TMEM base address.
-template <typename T, int MODE, int MH>
+// DK: the device-side row count and the split of the contraction are compiled in (layer step on the
+// packed cache); the plain operator call uses the variant without them.
+template <typename T, int MODE, int MH, bool DK>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PfArgs p) {
   extern __shared__ unsigned char pf_raw[];
@@ -163,12 +165,12 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   // is the re-read operand; MODE 1: column tiles vary fastest (the transposed down weight fits L2)
   const int n_idx = MODE == 0 ? blockIdx.y : blockIdx.x, m_idx = MODE == 0 ? blockIdx.x : blockIdx.y;
   const int n0 = n_idx * (MODE == 0 ? PF_BN : 2 * PF_BN), m0 = m_idx * (MH * PF_BM);
-  const int k_valid = p.k_dev ? *p.k_dev : 0x7fffffff;
+  const int k_valid = (DK && p.k_dev) ? *p.k_dev : 0x7fffffff;
   const int k_round = k_valid > 0x7fffff00 ? k_valid : (k_valid + PF_BK - 1) / PF_BK * PF_BK;
-  if (MODE == 0 && n0 >= k_round) return;  // nothing downstream reads these columns (uniform for the CTA)
+  if (DK && MODE == 0 && n0 >= k_round) return;  // nothing downstream reads these columns (uniform for the CTA)
   const int nkb_all = (min(p.Kd, MODE == 1 ? k_valid : p.Kd) + PF_BK - 1) / PF_BK;
   // this CTA's k-blocks [kb_lo, kb_lo + nkb)
-  const int nz = MODE == 1 ? static_cast<int>(gridDim.z) : 1, zi = MODE == 1 ? static_cast<int>(blockIdx.z) : 0;
+  const int nz = (DK && MODE == 1) ? static_cast<int>(gridDim.z) : 1, zi = (DK && MODE == 1) ? static_cast<int>(blockIdx.z) : 0;
   const int kb_lo = (nkb_all * zi) / nz;
   const int nkb = (nkb_all * (zi + 1)) / nz - kb_lo;
 
@@ -254,7 +256,7 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int col = n0 + c;
           const int n = min(32, p.N - col);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) g[e] = col + e < k_valid ? apply_act(p.act, g[e]) * u[e] : 0.f;
+          for (int e = 0; e < 32; ++e) g[e] = (!DK || col + e < k_valid) ? apply_act(p.act, g[e]) * u[e] : 0.f;
           if (row < p.M && n > 0) {
             if (out) pf_store_row<T>(out + static_cast<size_t>(row) * p.ld_out + col, g, n);
             if (comb) {
@@ -268,14 +270,14 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int c = 0; c < 2 * PF_BN; c += 32) {
           float g[32];
           pf_ld32(taddr + c, g);
-          if (nkb == 0) {  // empty contraction: the accumulator was never written
+          if (DK && nkb == 0) {  // empty contraction: the accumulator was never written
 #pragma unroll
             for (int e = 0; e < 32; ++e) g[e] = 0.f;
           }
           const int col = n0 + c;
           const int n = min(32, p.N - col);
           if (row < p.M && n > 0) {
-            if (p.part) {
+            if (DK && p.part) {
               float* dst = p.part + (static_cast<size_t>(zi) * p.M + row) * p.ld_out + col;
               for (int e = 0; e < n; ++e) dst[e] = g[e];
             } else {
@@ -294,22 +296,33 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
-// [K, H] -> [H, ldo] (ldo >= K): packed down rows to the K-major B operand of GEMM 2.
-template <typename E>
-__global__ void __launch_bounds__(256) k_pf_transpose(const E* __restrict__ in, E* __restrict__ out, int R, int C, int ldo,
-                                                      const int* __restrict__ r_dev) {
-  __shared__ E tile[32][33];
-  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  if (r_dev && r0 >= (*r_dev + PF_BK - 1) / PF_BK * PF_BK) return;  // rows no k-block of the contraction reaches
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  for (int k = ty; k < 32; k += 8) {
-    const int r = r0 + k, c = c0 + tx;
-    if (r < R && c < C) tile[k][tx] = in[static_cast<size_t>(r) * C + c];
+// [R, C] -> [C, ldo] (ldo >= R): packed down rows to the K-major B operand of GEMM 2.  64 x 64
+// tiles of 16-bit elements, 16-byte global loads and stores on both sides; requires C % 8 == 0 and
+// ldo % 8 == 0.  Rows >= R read as zero.  r_dev (optional): device-side row count, rows beyond its
+// k-block are never reached by the contraction and are skipped.
+__global__ void __launch_bounds__(256) k_pf_transpose(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int R, int C,
+                                                      int ldo, const int* __restrict__ r_dev) {
+  __shared__ uint16_t tile[64][64 + 8];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  if (r_dev && r0 >= (*r_dev + PF_BK - 1) / PF_BK * PF_BK) return;
+  const int t = threadIdx.x;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {  // 64 rows x 8 chunks of 8 elements
+    const int idx = t + 256 * k, rr = idx >> 3, cc = (idx & 7) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r0 + rr < R && c0 + cc < C) v = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r0 + rr) * C + c0 + cc);
+    *reinterpret_cast<uint4*>(&tile[rr][cc]) = v;
   }
   __syncthreads();
-  for (int k = ty; k < 32; k += 8) {
-    const int c = c0 + k, r = r0 + tx;
-    if (r < R && c < C) out[static_cast<size_t>(c) * ldo + r] = tile[tx][k];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {  // 64 output rows (columns of the tile) x 8 chunks of 8 input rows
+    const int idx = t + 256 * k, cc = idx >> 3, rr = (idx & 7) * 8;
+    if (c0 + cc < C && r0 + rr < ldo) {
+      __align__(16) uint16_t v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = tile[rr + e][cc];
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(c0 + cc) * ldo + r0 + rr) = *reinterpret_cast<const uint4*>(v);
+    }
   }
 }
 
@@ -353,8 +366,8 @@ static int make_map(CUtensorMap* m, const void* base, int dtype, int64_t rows, i
   return STX_OK;
 }
 
-template <typename T, int MODE, int MH>
-static int launch_umma_mh(const CUtensorMap& a, const CUtensorMap& b, PfArgs p, cudaStream_t s) {
+template <typename T, int MODE, int MH, bool DK>
+static int launch_umma_dk(const CUtensorMap& a, const CUtensorMap& b, PfArgs p, cudaStream_t s) {
   constexpr uint32_t stage_bytes = (MH + 2) * PF_TILE_BYTES;
   p.stages = MH == 2 ? 3 : 4;
   const size_t smem = 1024 + static_cast<size_t>(p.stages) * stage_bytes + (2 * p.stages + 1) * sizeof(uint64_t) + 16;
@@ -362,15 +375,20 @@ static int launch_umma_mh(const CUtensorMap& a, const CUtensorMap& b, PfArgs p, 
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    STX_CUDA(cudaFuncSetAttribute(k_umma_gemm<T, MODE, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    STX_CUDA(cudaFuncSetAttribute(k_umma_gemm<T, MODE, MH, DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr_set[dev] = true;
   }
   const int bn = MODE == 0 ? PF_BN : 2 * PF_BN, bm = MH * PF_BM;
   dim3 grid((p.N + bn - 1) / bn, (p.M + bm - 1) / bm, MODE == 1 ? static_cast<unsigned>(std::max(1, p.stages_z)) : 1u);
   if (MODE == 0) grid = dim3(grid.y, grid.x);
-  k_umma_gemm<T, MODE, MH><<<grid, PF_THREADS, smem, s>>>(a, b, p);
+  k_umma_gemm<T, MODE, MH, DK><<<grid, PF_THREADS, smem, s>>>(a, b, p);
   STX_LAUNCH_CHECK("k_umma_gemm");
   return STX_OK;
+}
+
+template <typename T, int MODE, int MH>
+static int launch_umma_mh(const CUtensorMap& a, const CUtensorMap& b, const PfArgs& p, cudaStream_t s) {
+  return (p.k_dev || p.part) ? launch_umma_dk<T, MODE, MH, true>(a, b, p, s) : launch_umma_dk<T, MODE, MH, false>(a, b, p, s);
 }
 
 template <typename T, int MODE>
@@ -423,8 +441,8 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
   }
   // down rows -> K-major [H, K8]
   {
-    dim3 grid(static_cast<unsigned>((H + 31) / 32), static_cast<unsigned>((K + 31) / 32));
-    k_pf_transpose<uint16_t><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(down_packed), static_cast<uint16_t*>(dt_scr),
+    dim3 grid(static_cast<unsigned>((H + 63) / 64), static_cast<unsigned>((K + 63) / 64));
+    k_pf_transpose<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(down_packed), static_cast<uint16_t*>(dt_scr),
                                                  static_cast<int>(K), static_cast<int>(H), static_cast<int>(K8), k_dev);
     STX_LAUNCH_CHECK("k_pf_transpose");
   }
