@@ -16,6 +16,8 @@
 // round trip.
 #include "stx_common.cuh"
 
+#include <algorithm>
+
 namespace stx {
 
 constexpr int PRED_BT = 8;  // batch rows accumulated per pass
@@ -26,7 +28,7 @@ __host__ __device__ inline int pred_t_threads(int H, int V) {
   return nt < 1024 ? nt : 1024;
 }
 
-// One block per predictor row k; thread u owns chunks u, u+NT, ...
+// One block per (predictor row k, tile of PRED_BT batch rows); thread u owns chunks u, u+NT, ...
 template <typename T>
 __global__ void __launch_bounds__(1024)
 k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t_out, int B, int H, int r) {
@@ -38,7 +40,8 @@ k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t
   pdl_wait();
   pdl_launch_dependents();
   const T* arow = A + static_cast<size_t>(k) * H;
-  for (int b0 = 0; b0 < B; b0 += PRED_BT) {
+  {
+    const int b0 = blockIdx.y * PRED_BT;
     float acc[PRED_BT];
 #pragma unroll
     for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
@@ -68,12 +71,13 @@ k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t
         if (lane == 0) t_out[static_cast<size_t>(b0 + b) * r + k] = DT<T>::round_f(s);
       }
     }
-    __syncthreads();
   }
 }
 
-// One block (256 threads) per mask word: 8 lanes cooperate on one neuron, 32 neurons per
-// block.  Dynamic shared memory: t [B,r] fp32.
+// One block (256 threads) per (mask word, group of PRED_BT batch rows): 8 lanes cooperate on one
+// neuron, 32 neurons per block.  Dynamic shared memory: the group's rows of t, fp32.  With more
+// than one group the blocks OR their words into `bits` (zeroed by the launcher): the union over
+// the batch does not depend on the order.
 template <typename T>
 __global__ void __launch_bounds__(256)
 k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* __restrict__ bits,
@@ -112,16 +116,19 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
   }
   pdl_wait();
   pdl_launch_dependents();
-  for (int k = tid; k < B * r; k += blockDim.x) t_s[k] = t[k];
+  const int bg0 = blockIdx.y * PRED_BT;          // first batch row of this block's group
+  const int Bg = min(PRED_BT, B - bg0);           // rows in the group
+  for (int k = tid; k < Bg * r; k += blockDim.x) t_s[k] = t[static_cast<size_t>(bg0) * r + k];
   __syncthreads();
 
   const float tau_r = DT<T>::round_f(tau);
   bool on = false;
-  for (int b0 = 0; b0 < B; b0 += PRED_BT) {
+  {
+    const int b0 = 0;  // row index inside the group (t_s holds the group's rows only)
     float acc[PRED_BT];
 #pragma unroll
     for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
-    const int nb = min(PRED_BT, B - b0);
+    const int nb = Bg;
     if (i_ok) {
       if (in_regs) {
 #pragma unroll
@@ -168,7 +175,7 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       if (b < nb) {
         const float sr = DT<T>::round_f(s);
-        if (scores_out && g == 0 && i_ok) scores_out[static_cast<size_t>(b0 + b) * I + i] = DT<T>::from_f(s);
+        if (scores_out && g == 0 && i_ok) scores_out[static_cast<size_t>(bg0 + b) * I + i] = DT<T>::from_f(s);
         on = on || (sr >= tau_r);
       }
     }
@@ -180,7 +187,10 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
     uint32_t word = 0u;
 #pragma unroll
     for (int q = 0; q < 8; ++q) word |= s_nib[q] << (4 * q);
-    bits[w] = word;
+    if (gridDim.y == 1)
+      bits[w] = word;
+    else if (word)
+      atomicOr(&bits[w], word);
   }
 }
 
@@ -188,14 +198,16 @@ template <typename T>
 static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
                           int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
                           int write_bits, unsigned parts, cudaStream_t s) {
+  const unsigned groups = static_cast<unsigned>((B + PRED_BT - 1) / PRED_BT);
   if (parts & 1u)
-  STX_CUDA(launch_pdl(k_pred_t<T>, dim3(static_cast<unsigned>(r)), dim3(pred_t_threads(static_cast<int>(H), DT<T>::V)), 0,
-                      s, static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B),
-                      static_cast<int>(H), static_cast<int>(r)));
+    STX_CUDA(launch_pdl(k_pred_t<T>, dim3(static_cast<unsigned>(r), groups), dim3(pred_t_threads(static_cast<int>(H), DT<T>::V)),
+                        0, s, static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B),
+                        static_cast<int>(H), static_cast<int>(r)));
   const int64_t W = (I + 31) / 32;
-  const size_t smem = static_cast<size_t>(B) * r * sizeof(float);
+  const size_t smem = static_cast<size_t>(std::min<int64_t>(B, PRED_BT)) * r * sizeof(float);
+  if ((parts & 2u) && groups > 1 && write_bits) STX_CUDA(cudaMemsetAsync(bits, 0, W * sizeof(uint32_t), s));
   if (parts & 2u)
-  STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W)), dim3(256), smem, s, t_scratch,
+  STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W), groups), dim3(256), smem, s, t_scratch,
                       static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
                       static_cast<int>(r), static_cast<int>(I), tau, write_bits));
   
@@ -256,8 +268,9 @@ int stx_predict_mask(const void* x, int64_t B, int64_t H, const void* A, int64_t
     set_error("stx_predict_mask: x and A rows must be 16-byte aligned (H*elem %% 16 == 0)");
     return STX_ERR_UNSUPPORTED;
   }
-  if (static_cast<size_t>(B) * r * sizeof(float) > 48 * 1024) {
-    set_error("stx_predict_mask: B*r=%lld exceeds the shared-memory tile (12288 values)", static_cast<long long>(B * r));
+  if (static_cast<size_t>(std::min<int64_t>(B, 8)) * r * sizeof(float) > 48 * 1024) {
+    set_error("stx_predict_mask: min(B,8)*r=%lld exceeds the shared-memory tile (12288 values)",
+              static_cast<long long>(std::min<int64_t>(B, 8) * r));
     return STX_ERR_TOO_LARGE;
   }
   return predict_mask(x, B, H, A, r, Bm, I, dtype, method, param, mask_bits_out, scores_out, scratch, 3u,

@@ -48,9 +48,10 @@ def _rank_main(rank, world, port, out_dir, mode, batch):
     lo, hi = shard_range(w.I, rank, world)
     sharded = [ShardedLayer(*[t.contiguous().to(dev) for t in shard_weights(*lw, rank, world)], act=w.act, param=w.tau,
                             max_batch=w.B, peer=peer) for lw in ws]
-    assert sharded[0].local.single_row_fused(w.B) == (w.B == 1)
+    assert sharded[0].local.single_row_fused(w.B)  # 1 row: k_mlp_b1, 2..8 rows: k_mlp_bn
     full = [SparseLayer(*[t.to(dev) for t in lw], act=w.act, param=w.tau, max_batch=w.B) for lw in ws] if rank == 0 else None
     stack = ShardedStack(sharded, w.B, xs[0].to(dev))
+    why = []
     out = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=dev)
     # the stack's warm-up advanced the shard caches with xs[0] twice; do the same on the full layers
     if rank == 0:
@@ -67,10 +68,12 @@ def _rank_main(rank, world, port, out_dir, mode, batch):
                 ref = l.step(x)
                 torch.cuda.synchronize()
                 err = (out[li].float() - ref.float()).abs().max() / ref.float().abs().max()
-                ok &= bool(err <= 2e-2)
-                ok &= torch.equal(masks[li], l.mask().cpu()[lo:hi])
-                mine = set(orders[li].tolist())
-                ok &= mine == {i for i in l.active_indices().tolist() if lo <= i < hi}
+                checks = {"output": bool(err <= 2e-2), "mask": torch.equal(masks[li], l.mask().cpu()[lo:hi]),
+                          "cache order": set(orders[li].tolist()) == {i for i in l.active_indices().tolist() if lo <= i < hi}}
+                for name, good in checks.items():
+                    if not good:
+                        why.append(f"step {t} layer {li}: {name} differs (rel err {float(err):.3g})")
+                ok &= all(checks.values())
     if peer is not None:
         ok &= not peer.timed_out()
         # all ranks hold the same bits
@@ -82,7 +85,7 @@ def _rank_main(rank, world, port, out_dir, mode, batch):
     dist.all_gather_object(oks, ok)
     if rank == 0:
         with open(os.path.join(out_dir, "ok.txt"), "w") as fh:
-            fh.write("1" if all(oks) else "0")
+            fh.write("1" if all(oks) else "0 " + "; ".join(why[:6]))
     stack.close()
     torch.cuda.synchronize()
     dist.barrier()
