@@ -679,10 +679,8 @@ __device__ unsigned long long g_b1_trace[256][8];
       g_b1_trace[blockIdx.x][i] = t__;                                                  \
     }                                                                                   \
   } while (0)
-#define STX_B1_NOW(var) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(var))
 #else
 #define STX_B1_STAMP(i) do { } while (0)
-#define STX_B1_NOW(var) do { } while (0)
 #endif
 
 constexpr int B1_MAX_SLOTS = 16;
@@ -1294,9 +1292,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
 
   const int nwh = H / 64;  // windows (32 consecutive k = 64 bytes) per half row
   const int w_lo = (nwh * warp) / 16, w_hi = (nwh * (warp + 1)) / 16;  // this warp's share of each half
-  unsigned long long tw0 = 0, tw1 = 0, tw_gu = 0, tw_d = 0, t_loop0 = 0;  // development timeline only
-  (void)tw0; (void)tw1; (void)tw_gu; (void)tw_d; (void)t_loop0;
-  STX_B1_NOW(t_loop0);
   for (int it = 0; it < niter; ++it) {
     const uint32_t parity = static_cast<uint32_t>(it) & 1u;
     const int nv = min(TN, nlocal - it * TN);
@@ -1305,10 +1300,7 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      STX_B1_NOW(tw0);
       if (!mbar_wait_bounded(half == 0 ? bar_x : bar_y, parity)) timed_out = true;
-      STX_B1_NOW(tw1);
-      tw_gu += tw1 - tw0;
       const unsigned char* buf = half == 0 ? X : Y;
       const unsigned char* arow_lo = buf + static_cast<size_t>(lo_on ? gq : 0) * hstride + tq * 16;
       const unsigned char* arow_hi = buf + static_cast<size_t>(hi_on ? gq + 8 : 0) * hstride + tq * 16;
@@ -1374,14 +1366,7 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
   }
   if (timed_out && p.status) atomicOr(p.status, DEV_TIMEOUT);
 #ifdef STX_B1_TRACE
-  if (tid == 0) {
-    g_b1_trace[blockIdx.x][7] = static_cast<unsigned long long>(nlocal);
-    // durations, reported relative to the start stamp: gate/up waits, down waits, whole loop
-    g_b1_trace[blockIdx.x][3] = g_b1_trace[blockIdx.x][0] + tw_gu;
-    g_b1_trace[blockIdx.x][4] = g_b1_trace[blockIdx.x][0] + tw_d;
-    STX_B1_NOW(tw1);
-    g_b1_trace[blockIdx.x][5] = g_b1_trace[blockIdx.x][0] + (tw1 - t_loop0);
-  }
+  if (tid == 0) g_b1_trace[blockIdx.x][7] = static_cast<unsigned long long>(nlocal);
 #endif
   {
     float* dst = q.partial + static_cast<size_t>(blockIdx.x) * B * H + static_cast<size_t>(warp) * (H / 16) + gq;
