@@ -116,11 +116,15 @@ int stx_layer_create(stx_layer_t** out, stx_cache_t* cache, const void* A, int64
   const int64_t I = cache->I, H = cache->H;
   size_t pred_bytes = 0, mlp_bytes = 0;
   stx_predict_scratch_bytes(max_batch, I, r, &pred_bytes);
+  // The scratch layout depends on the row count of a call (a single row keeps per-CTA partial
+  // vectors, few rows on the tensor-core path keep split-contraction partials whose size is not
+  // monotonic in B): size the buffer for the worst case over 1..max_batch.  Within a bucket of
+  // equal output-tile count the need grows with B, so the bucket tops are enough.
   stx_mlp_scratch_bytes(max_batch, H, I, &mlp_bytes);
-  if (max_batch > 1) {  // a single row uses a layout of its own (per-CTA partial output vectors)
-    size_t one = 0;
-    stx_mlp_scratch_bytes(1, H, I, &one);
-    mlp_bytes = std::max(mlp_bytes, one);
+  for (int64_t b = 1; b < max_batch; b = (b < 128 ? 128 : b + 256 - b % 256)) {
+    size_t need = 0;
+    stx_mlp_scratch_bytes(b, H, I, &need);
+    mlp_bytes = std::max(mlp_bytes, need);
   }
   const size_t es = dtype_size(cache->dtype);
   // 16-bit rows narrower than 32 chunks fall back to the packed cache inside the MLP
