@@ -52,8 +52,8 @@ class LlamaSkipConfig:
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+    """RMSNorm of modelling_llama_skip.py:41-47 (normalise in fp32, scale by the weight) as one fused op."""
+    return F.rms_norm(x, (x.shape[-1],), w, eps)
 
 
 def rope_tables(cfg: LlamaSkipConfig, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -117,13 +117,13 @@ class LlamaSkipModel:
         v = v.view(T, nkv, hd).transpose(0, 1)
         if decode:
             idx = self.pos                                                       # device scalar [1]
-            cos, sin = self.cos.index_select(0, idx), self.sin.index_select(0, idx)
-            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            cos, sin, mask = self._step_rope                                     # made once per token in _decode_body
+            qk = apply_rope(torch.cat([q, k], dim=0), cos, sin)                   # one pass over the q and k heads
+            q, k = qk[:nh], qk[nh:]
             self.k_cache[li].index_copy_(1, idx, k)
             self.v_cache[li].index_copy_(1, idx, v)
-            mask = (self._arange <= idx).view(1, 1, cfg.max_len)                  # keys 0..pos
             o = F.scaled_dot_product_attention(q.unsqueeze(0), self.k_cache[li].unsqueeze(0), self.v_cache[li].unsqueeze(0),
-                                               attn_mask=mask.unsqueeze(0), enable_gqa=True)
+                                               attn_mask=mask, enable_gqa=True)
         else:
             cos, sin = self.cos[pos0:pos0 + T], self.sin[pos0:pos0 + T]
             q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
@@ -164,6 +164,8 @@ class LlamaSkipModel:
         cfg = self.cfg
         main = torch.cuda.current_stream()
         h = self.embed.index_select(0, self.token)                              # [1,H]
+        self._step_rope = (self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos),
+                           (self._arange <= self.pos).view(1, 1, 1, cfg.max_len))  # keys 0..pos
         for li, L in enumerate(self.layers):
             x_pred = rms_norm(h, L["ln1"], cfg.rms_eps)                          # the predictor's input
             h = h + self._attention(li, x_pred, None, 1, decode=True)
