@@ -69,7 +69,7 @@ struct stx_stack {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   int64_t kernel_nodes = 0;
-  std::vector<cudaEvent_t> events;  // fork points (one per layer) + the final join
+  std::vector<cudaEvent_t> events;  // [0,L) fork points, [L] join, [L+1, 2L+1) plan-done points, [2L+1] second join
 };
 
 using namespace stx;
@@ -170,7 +170,8 @@ static bool single_row_fusable(const stx_layer* l, int64_t B) {
 // cache is then kept current off the critical path (side stream), which is where a GPU wants
 // it — contiguity of the active rows buys nothing when every row is a multi-KB burst.
 static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_mlp, int64_t B, void* out, cudaStream_t s,
-                              cudaStream_t side, cudaEvent_t fork_ev, unsigned stages) {
+                              cudaStream_t side, cudaEvent_t fork_ev, unsigned stages, cudaStream_t side2 = nullptr,
+                              cudaEvent_t plan_ev = nullptr, bool* used_side2 = nullptr) {
   stx_cache* c = l->cache;
   int rc = STX_OK;
   // One row under the threshold rule: scores, mask, gather and MLP of a neuron stay in one CTA.
@@ -257,7 +258,16 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       if (rc != STX_OK) return rc;
     }
     if ((stages & STX_STAGE_COPY) && !l->lazy) {
-      rc = cache_copy_rows(c, cs);
+      // With a second side stream the row copies of this layer leave the plan's stream, so the next
+      // layer's index plan (a single block, latency-bound) does not queue behind them.
+      cudaStream_t ccs = cs;
+      if (forked && side2 && plan_ev) {
+        STX_CUDA(cudaEventRecord(plan_ev, cs));
+        STX_CUDA(cudaStreamWaitEvent(side2, plan_ev, 0));
+        ccs = side2;
+        if (used_side2) *used_side2 = true;
+      }
+      rc = cache_copy_rows(c, ccs);
       if (rc != STX_OK) return rc;
     }
   }
@@ -376,10 +386,12 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
   // Capture the L steps (nothing executes during capture).  The critical path (predictor ->
   // sparse MLP, layer after layer) stays on one stream; each layer's cache maintenance forks
   // off after its predictor onto a side stream and everything joins at the end of the step.
-  cudaStream_t cs = nullptr, side = nullptr;
+  // The maintenance itself uses two side streams: index plans on one, row copies on the other.
+  cudaStream_t cs = nullptr, side = nullptr, side2 = nullptr;
   e = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking);
-  for (int64_t i = 0; i <= L && e == cudaSuccess; ++i) {
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&side2, cudaStreamNonBlocking);
+  for (int64_t i = 0; i < 2 * L + 2 && e == cudaSuccess; ++i) {
     cudaEvent_t ev = nullptr;
     e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     if (e == cudaSuccess) s->events.push_back(ev);
@@ -387,16 +399,18 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
   if (e != cudaSuccess) {
     if (cs) cudaStreamDestroy(cs);
     if (side) cudaStreamDestroy(side);
+    if (side2) cudaStreamDestroy(side2);
     stx_stack_destroy(s);
     return cuda_fail(e, "stx_stack_create: stream/event creation");
   }
   int rc = STX_OK;
   e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
   if (e == cudaSuccess) {
-    bool forked = false;
+    bool forked = false, used2 = false;
     for (int64_t i = 0; i < L && rc == STX_OK; ++i) {
       stx_layer* l = s->layers[i];
-      rc = layer_step_streams(l, s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs, side, s->events[i], stages);
+      rc = layer_step_streams(l, s->x_in, s->x_in, B, static_cast<char*>(s->out) + i * xbytes, cs, side, s->events[i], stages,
+                              side2, s->events[L + 1 + i], &used2);
       const bool big = l->cache->pk_gate && !single_row_fusable(l, B) &&
                        prefill_wanted(B, l->cache->H, l->cache->I, l->cache->dtype, l->cache->has_gate);
       forked = forked || (l->gather && !big && (stages & (STX_STAGE_PLAN | STX_STAGE_COPY)));
@@ -404,6 +418,10 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
     if (rc == STX_OK && forked) {  // join
       cudaError_t ej = cudaEventRecord(s->events[L], side);
       if (ej == cudaSuccess) ej = cudaStreamWaitEvent(cs, s->events[L], 0);
+      if (ej == cudaSuccess && used2) {
+        ej = cudaEventRecord(s->events[2 * L + 1], side2);
+        if (ej == cudaSuccess) ej = cudaStreamWaitEvent(cs, s->events[2 * L + 1], 0);
+      }
       if (ej != cudaSuccess) e = ej;
     }
     cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
@@ -412,6 +430,7 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
   if (e == cudaSuccess && rc == STX_OK) e = cudaGraphInstantiate(&s->exec, s->graph, 0);
   cudaStreamDestroy(cs);
   cudaStreamDestroy(side);
+  cudaStreamDestroy(side2);
   if (rc != STX_OK) {
     stx_stack_destroy(s);
     return rc;

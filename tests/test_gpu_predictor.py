@@ -19,7 +19,7 @@ def _case(B, H, r, I, dtype, seed):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B,H,r,I", [(1, 2048, 64, 8192), (1, 3072, 64, 8192), (8, 4096, 128, 14336), (3, 256, 24, 1000),
-                                     (2, 64, 327, 333), (9, 128, 7, 70), (1, 64, 8, 31)])
+                                     (2, 64, 327, 333), (9, 128, 7, 70), (1, 64, 8, 31), (20, 512, 32, 1030), (64, 1024, 128, 2048)])
 def test_scores_and_mask_bit_exact(dtype, B, H, r, I):
     from stxgpu import DEV, ODT, predict_mask
 
