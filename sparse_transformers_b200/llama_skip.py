@@ -102,7 +102,8 @@ class LlamaSkipModel:
         self.generated = torch.zeros(cfg.max_len, dtype=torch.long, device=self.device)
         self.logits = torch.zeros(cfg.vocab, dtype=torch.float32, device=self.device)
         self._arange = torch.arange(cfg.max_len, device=self.device)
-        self._side = torch.cuda.Stream(device=self.device)
+        self._side = torch.cuda.Stream(device=self.device)    # cache index plans
+        self._side2 = torch.cuda.Stream(device=self.device)   # cache row copies
         self._graph = None
         self.trace = None  # when a list: per decode step and layer (x_pred, x_mlp, mlp_out, mask) copies, eager mode only
 
@@ -175,11 +176,15 @@ class LlamaSkipModel:
             sp.step_stages(C.STAGE_PREDICT | C.STAGE_MLP, x_pred.contiguous(), x_mlp, out, batch=1)
             self._side.wait_stream(main)                                         # cache upkeep off the critical path
             with torch.cuda.stream(self._side):
-                sp.step_stages(C.STAGE_PLAN | C.STAGE_COPY, batch=1)
+                sp.step_stages(C.STAGE_PLAN, batch=1)
+            self._side2.wait_stream(self._side)
+            with torch.cuda.stream(self._side2):
+                sp.step_stages(C.STAGE_COPY, batch=1)
             if self.trace is not None:
                 self.trace.append((li, x_pred.clone(), x_mlp.clone(), out.clone(), sp.mask().clone()))
             h = h + out
         main.wait_stream(self._side)
+        main.wait_stream(self._side2)
         last = rms_norm(h, self.final_norm, cfg.rms_eps)
         self.logits.copy_((last @ self.embed.t()).float().view(-1))
         nxt = self.logits.argmax().view(1)

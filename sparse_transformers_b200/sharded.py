@@ -124,7 +124,8 @@ class ShardedStack:
         # (with a PeerExchange the sum rides in the partial-sum kernel of the single-row path)
         fused, peer = l0.single_row_fused(self.B), self.layers[0].peer is not None
         self.launches_per_step = ((5 if fused else 6) + (0 if fused and peer else 1)) * self.L
-        self._side = torch.cuda.Stream(device=self.device)
+        self._side = torch.cuda.Stream(device=self.device)    # index plans
+        self._side2 = torch.cuda.Stream(device=self.device)   # row copies (so the next layer's plan does not queue behind them)
         # eager warm-up on a side stream (NCCL communicators, function attributes), then capture
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
@@ -162,10 +163,14 @@ class ShardedStack:
                 side.wait_stream(main)  # the side work needs the mask, nothing later
                 l.local.step_stages(C.STAGE_MLP, None, self.x_in, self.out[i], batch=self.B)
             with torch.cuda.stream(side):
-                l.local.step_stages(C.STAGE_PLAN | C.STAGE_COPY, batch=self.B)
+                l.local.step_stages(C.STAGE_PLAN, batch=self.B)
+            self._side2.wait_stream(side)
+            with torch.cuda.stream(self._side2):
+                l.local.step_stages(C.STAGE_COPY, batch=self.B)
             if l.peer is None:
                 dist.all_reduce(self.out[i], op=dist.ReduceOp.SUM, group=l.group)
         main.wait_stream(side)
+        main.wait_stream(self._side2)
 
     def step(self, x: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:
         if x is not None:
