@@ -10,7 +10,10 @@ layer after layer, strictly serialised on one stream.  Metric: decode tokens/s =
 Default workload (N = 1): "C2", the Llama-3.2-3B-shaped 28-layer stack, fp16, batch 1,
 random-init weights N(0, 0.02), AR(1) hidden states, ~20 % active neurons per token.
 For N > 1 the intermediate dimension is sharded over the ranks (one process per GPU,
-launched by torch.distributed.run) with an NCCL all-reduce of the partial sums per layer.
+launched by torch.distributed.run); the partial sums of a layer are added over peer memory
+inside the step's own kernels (--allreduce nccl selects torch.distributed.all_reduce instead).
+Other workloads: --workload C3 | C5 (batched decode stacks), C4 (prefill, tensor roofline),
+C2-e2e (the LlamaSkip host end to end: TTFT and output tokens/s).
 
 One JSON line is printed by rank 0:
   value      device-timed (CUDA events), inputs resident in HBM, CUDA-graph replay

@@ -173,3 +173,20 @@ def test_row_block_of_64_runs_on_the_packed_cache(dtype):
     w = Workload("b64", H=1024, I=2048, r=32, B=64, dtype=dtype, density=0.05, alpha=0.8)
     ks = _run(w, steps=6, seed=3)
     assert 64 < min(ks) and max(ks) < 2048 and len(set(ks)) > 1
+
+
+@pytest.mark.parametrize("B,dtype,act,H,I", [(2, torch.float16, "silu", 512, 1024), (3, torch.bfloat16, "relu", 1024, 2048),
+                                             (5, torch.float16, "gelu_pytorch_tanh", 512, 4096), (7, torch.bfloat16, "silu", 1536, 1000)])
+def test_two_to_eight_rows_one_kernel_path(B, dtype, act, H, I):
+    """Ragged row counts and every activation through the 2..8-row kernel (k_mlp_bn); I = 1000 leaves a
+    partial mask byte and CTAs without neurons, density 0.3 with shared streams makes some CTAs hand
+    neurons to others."""
+    from sparse_transformers_b200 import SparseLayer
+    from sparse_transformers_b200.synth import Workload, layer_weights
+
+    w = Workload("bn", H=H, I=I, r=32, B=B, dtype=dtype, density=0.3, alpha=0.6, act=act)
+    g = torch.Generator().manual_seed(1)
+    probe = SparseLayer(*[t.to("cuda:0") for t in layer_weights(w, g)], act=act, param=w.tau, max_batch=B)
+    assert probe.single_row_fused(B)
+    probe.close()
+    _run(w, steps=6, seed=11)
