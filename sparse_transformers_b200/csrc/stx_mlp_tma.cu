@@ -1753,9 +1753,42 @@ static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const
 // the two kernels.  `t` holds A x (fp32 [r]) written earlier on the same stream.
 size_t layer_bn_xchg_bytes() { return BN_XCHG_BYTES; }
 
+// Few partial vectors (a split contraction): one thread per 4 columns adds them in order.
+template <typename T>
+__global__ void __launch_bounds__(256) k_partial_sum_few(const float* __restrict__ partial, int G, int n, T* __restrict__ out) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  pdl_wait();
+  pdl_launch_dependents();
+  if (i >= n) return;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int g = 0; g < G; ++g) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + static_cast<size_t>(g) * n + i));
+    s.x += v.x;
+    s.y += v.y;
+    s.z += v.z;
+    s.w += v.w;
+  }
+  out[i] = DT<T>::from_f(s.x);
+  out[i + 1] = DT<T>::from_f(s.y);
+  out[i + 2] = DT<T>::from_f(s.z);
+  out[i + 3] = DT<T>::from_f(s.w);
+}
+
 // out[i] = sum over g < G of partial[g][i] in ascending g (n a multiple of 128), model dtype.
 int partial_sum(const float* partial, int G, int64_t n, void* out, int dtype, cudaStream_t s) {
   STX_CHECK_ARG(n % 128 == 0 && n / 128 < (1ll << 31), "partial_sum: n must be a multiple of 128");
+  if (G <= 16) {
+    const int nn = static_cast<int>(n);
+    const dim3 grid(static_cast<unsigned>((n / 4 + 255) / 256));
+    switch (dtype) {
+      case STX_F32: STX_CUDA(launch_pdl(k_partial_sum_few<float>, grid, dim3(256), 0, s, partial, G, nn, static_cast<float*>(out))); break;
+      case STX_F16: STX_CUDA(launch_pdl(k_partial_sum_few<__half>, grid, dim3(256), 0, s, partial, G, nn, static_cast<__half*>(out))); break;
+      default:
+        STX_CUDA(launch_pdl(k_partial_sum_few<__nv_bfloat16>, grid, dim3(256), 0, s, partial, G, nn, static_cast<__nv_bfloat16*>(out)));
+        break;
+    }
+    return STX_OK;
+  }
   const PeerArgs none = {};
   const int nn = static_cast<int>(n);
   switch (dtype) {

@@ -31,7 +31,8 @@ __host__ __device__ inline int pred_t_threads(int H, int V) {
 // One block per (predictor row k, tile of PRED_BT batch rows); thread u owns chunks u, u+NT, ...
 template <typename T>
 __global__ void __launch_bounds__(1024)
-k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t_out, int B, int H, int r) {
+k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t_out, int B, int H, int r,
+         uint32_t* __restrict__ zero_words, int n_zero) {
   constexpr int V = DT<T>::V;
   __shared__ float s_ws[32][PRED_BT];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
@@ -40,6 +41,9 @@ k_pred_t(const T* __restrict__ x, const T* __restrict__ A, float* __restrict__ t
   pdl_wait();
   pdl_launch_dependents();
   const T* arow = A + static_cast<size_t>(k) * H;
+  // several batch groups OR their mask words together later: clear the words here, one kernel ahead
+  if (zero_words && blockIdx.y == 0)
+    for (int w = k * blockDim.x + tid; w < n_zero; w += r * blockDim.x) zero_words[w] = 0u;
   {
     const int b0 = blockIdx.y * PRED_BT;
     float acc[PRED_BT];
@@ -202,10 +206,11 @@ static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, in
   if (parts & 1u)
     STX_CUDA(launch_pdl(k_pred_t<T>, dim3(static_cast<unsigned>(r), groups), dim3(pred_t_threads(static_cast<int>(H), DT<T>::V)),
                         0, s, static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B),
-                        static_cast<int>(H), static_cast<int>(r)));
+                        static_cast<int>(H), static_cast<int>(r), (groups > 1 && write_bits && (parts & 2u)) ? bits : nullptr,
+                        static_cast<int>((I + 31) / 32)));
   const int64_t W = (I + 31) / 32;
   const size_t smem = static_cast<size_t>(std::min<int64_t>(B, PRED_BT)) * r * sizeof(float);
-  if ((parts & 2u) && groups > 1 && write_bits) STX_CUDA(cudaMemsetAsync(bits, 0, W * sizeof(uint32_t), s));
+  if ((parts & 2u) && !(parts & 1u) && groups > 1 && write_bits) STX_CUDA(cudaMemsetAsync(bits, 0, W * sizeof(uint32_t), s));
   if (parts & 2u)
   STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W), groups), dim3(256), smem, s, t_scratch,
                       static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),

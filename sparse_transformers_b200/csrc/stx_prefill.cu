@@ -41,7 +41,7 @@ struct PfArgs {
   int M, N, Kd;        // output rows, output columns, contraction length
   int up_off;          // MODE 0: row offset of the up block inside the concat weight (= K)
   int stages;
-  int stages_z;        // MODE 1: number of contraction splits (gridDim.z), 0/1 = none
+  int stages_z;        // number of contraction splits (gridDim.z), 0/1 = none
   void* a_out;         // MODE 0: activations [M, lda] ; MODE 1: output [M, ldo]
   int ld_out;
   void* combined;      // MODE 0, optional: [M, 2K]
@@ -51,9 +51,12 @@ struct PfArgs {
   // writes zero activations for columns >= *k_dev and skips tiles wholly beyond it; MODE 1 stops
   // its contraction at *k_dev (rounded up to a k-block, which MODE 0 filled with zeros).
   const int* k_dev;
-  // MODE 1, optional split of the contraction over gridDim.z CTAs: CTA z takes an equal share of the
-  // k-blocks and writes its fp32 partial tile to part[z][M][ld_out]; the caller adds the partials.
+  // Optional split of the contraction over gridDim.z CTAs: CTA z takes an equal share of the k-blocks
+  // and writes its fp32 partial tile; the caller adds the partials.  MODE 1: part[z][M][ld_out].
+  // MODE 0: part[z][M][2*ld_part], gate sums in columns [0, N), up sums in [ld_part, ld_part + N)
+  // (the activation needs the complete sums, so it moves to the kernel that adds the partials).
   float* part;
+  int ld_part;
 };
 
 __device__ __forceinline__ uint32_t pf_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -170,7 +173,7 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (DK && MODE == 0 && n0 >= k_round) return;  // nothing downstream reads these columns (uniform for the CTA)
   const int nkb_all = (min(p.Kd, MODE == 1 ? k_valid : p.Kd) + PF_BK - 1) / PF_BK;
   // this CTA's k-blocks [kb_lo, kb_lo + nkb)
-  const int nz = (DK && MODE == 1) ? static_cast<int>(gridDim.z) : 1, zi = (DK && MODE == 1) ? static_cast<int>(blockIdx.z) : 0;
+  const int nz = DK ? static_cast<int>(gridDim.z) : 1, zi = DK ? static_cast<int>(blockIdx.z) : 0;
   const int kb_lo = (nkb_all * zi) / nz;
   const int nkb = (nkb_all * (zi + 1)) / nz - kb_lo;
 
@@ -255,6 +258,16 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           pf_ld32(taddr + PF_BN + c, u);
           const int col = n0 + c;
           const int n = min(32, p.N - col);
+          if (DK && p.part) {  // split contraction: raw partial sums, the activation follows the sum
+            if (row < p.M && n > 0) {
+              float* dst = p.part + (static_cast<size_t>(zi) * p.M + row) * (2 * static_cast<size_t>(p.ld_part)) + col;
+              for (int e = 0; e < n; ++e) {
+                dst[e] = nkb > 0 ? g[e] : 0.f;
+                dst[p.ld_part + e] = nkb > 0 ? u[e] : 0.f;
+              }
+            }
+            continue;
+          }
 #pragma unroll
           for (int e = 0; e < 32; ++e) g[e] = (!DK || col + e < k_valid) ? apply_act(p.act, g[e]) * u[e] : 0.f;
           if (row < p.M && n > 0) {
@@ -379,8 +392,8 @@ static int launch_umma_dk(const CUtensorMap& a, const CUtensorMap& b, PfArgs p, 
     attr_set[dev] = true;
   }
   const int bn = MODE == 0 ? PF_BN : 2 * PF_BN, bm = MH * PF_BM;
-  dim3 grid((p.N + bn - 1) / bn, (p.M + bm - 1) / bm, MODE == 1 ? static_cast<unsigned>(std::max(1, p.stages_z)) : 1u);
-  if (MODE == 0) grid = dim3(grid.y, grid.x);
+  dim3 grid((p.N + bn - 1) / bn, (p.M + bm - 1) / bm, static_cast<unsigned>(std::max(1, p.stages_z)));
+  if (MODE == 0) grid = dim3(grid.y, grid.x, grid.z);
   k_umma_gemm<T, MODE, MH, DK><<<grid, PF_THREADS, smem, s>>>(a, b, p);
   STX_LAUNCH_CHECK("k_umma_gemm");
   return STX_OK;
@@ -397,6 +410,33 @@ static int launch_umma(const CUtensorMap& a, const CUtensorMap& b, const PfArgs&
   return p.M > PF_BM ? launch_umma_mh<T, MODE, 2>(a, b, p, s) : launch_umma_mh<T, MODE, 1>(a, b, p, s);
 }
 
+// a[b][j] = act(sum_z gate_z[b][j]) * sum_z up_z[b][j] for j < K (zero up to the end of K's k-block),
+// z ascending: the tail of a GEMM 1 whose contraction was split.
+template <typename T>
+__global__ void __launch_bounds__(256) k_pf_act_sum(const float* __restrict__ part, int nz, int M, int N, int ldp,
+                                                    T* __restrict__ a_out, int ld_out, int act, const int* __restrict__ k_dev) {
+  const int k_valid = k_dev ? min(*k_dev, N) : N;
+  const int k_round = min(N, (k_valid + PF_BK - 1) / PF_BK * PF_BK);
+  const int j = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (j >= k_round || b >= M) return;
+  float g = 0.f, u = 0.f;
+  for (int z = 0; z < nz; ++z) {
+    const float* src = part + (static_cast<size_t>(z) * M + b) * (2 * static_cast<size_t>(ldp)) + j;
+    g += __ldcg(src);
+    u += __ldcg(src + ldp);
+  }
+  a_out[static_cast<size_t>(b) * ld_out + j] = DT<T>::from_f(j < k_valid ? apply_act(act, g) * u : 0.f);
+}
+
+// GEMM 1 has ceil(B/128..256) x I/128 output tiles: a shard of the intermediate dimension with few rows
+// leaves most SMs without one, so its contraction (over H) is split too.
+static int gemm1_splits(int64_t B, int64_t H, int64_t K) {
+  const int64_t bm = B > PF_BM ? 2 * PF_BM : PF_BM;
+  const int64_t tiles = ((B + bm - 1) / bm) * ((K + PF_BN - 1) / PF_BN);
+  if (tiles * 2 > num_sms()) return 1;
+  return static_cast<int>(std::min<int64_t>({8, std::max<int64_t>(1, num_sms() / tiles), std::max<int64_t>(1, H / (4 * PF_BK))}));
+}
+
 // GEMM 2 has only ceil(B/128..256) x H/256 output tiles; for few rows the contraction is split so
 // that about one CTA per SM streams the down weight.
 static int gemm2_splits(int64_t B, int64_t H) {
@@ -407,9 +447,10 @@ static int gemm2_splits(int64_t B, int64_t H) {
 
 size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K) {
   const int64_t K8 = (K + 7) / 8 * 8;
-  const int z = gemm2_splits(B, H);
+  const int z = gemm2_splits(B, H), z1 = gemm1_splits(B, H, K);
   return align_up(static_cast<size_t>(B) * K8 * 2, 1024) + align_up(static_cast<size_t>(H) * K8 * 2, 1024) + 1024 +
-         (z > 1 ? align_up(static_cast<size_t>(z) * B * H * sizeof(float), 1024) : 0);
+         (z > 1 ? align_up(static_cast<size_t>(z) * B * H * sizeof(float), 1024) : 0) +
+         (z1 > 1 ? align_up(static_cast<size_t>(z1) * B * 2 * K8 * sizeof(float), 1024) : 0);
 }
 
 // Implemented in stx_mlp_tma.cu: out[i] = sum over g < G of partial[g][i], g ascending (n % 128 == 0).
@@ -477,18 +518,40 @@ int prefill_forward(const void* x, int64_t B, int64_t H, const void* concat, con
   g2.act = act;
   g2.status = status;
   g2.k_dev = k_dev;
-  const int z = (B * H) % 128 == 0 ? gemm2_splits(B, H) : 1;
+  const int z_sized = gemm2_splits(B, H);  // what prefill_scratch_bytes reserved
+  const int z = (B * H) % 128 == 0 ? z_sized : 1;
   float* part = nullptr;
+  const uintptr_t part_base = base + align_up(static_cast<size_t>(B) * K8 * 2, 1024) + align_up(static_cast<size_t>(H) * K8 * 2, 1024);
   if (z > 1) {
-    part = reinterpret_cast<float*>(base + align_up(static_cast<size_t>(B) * K8 * 2, 1024) + align_up(static_cast<size_t>(H) * K8 * 2, 1024));
+    part = reinterpret_cast<float*>(part_base);
     g2.part = part;
     g2.stages_z = z;
   }
+  // GEMM 1 split (only without combined_buf: the activation moves to k_pf_act_sum, which writes a alone)
+  const int z1 = combined == nullptr ? gemm1_splits(B, H, K) : 1;
+  float* part1 = nullptr;
+  if (z1 > 1) {
+    part1 = reinterpret_cast<float*>(part_base + (z_sized > 1 ? align_up(static_cast<size_t>(z_sized) * B * H * sizeof(float), 1024) : 0));
+    g1.part = part1;
+    g1.ld_part = static_cast<int>(K8);
+    g1.stages_z = z1;
+  }
+  const dim3 agrid(static_cast<unsigned>((K + 255) / 256), static_cast<unsigned>(B));
   if (dtype == STX_F16) {
     rc = launch_umma<__half, 0>(mx, mw, g1, s);
+    if (rc == STX_OK && part1) {
+      k_pf_act_sum<__half><<<agrid, 256, 0, s>>>(part1, z1, static_cast<int>(B), static_cast<int>(K), static_cast<int>(K8),
+                                                 static_cast<__half*>(a_scr), static_cast<int>(K8), act, k_dev);
+      STX_LAUNCH_CHECK("k_pf_act_sum");
+    }
     if (rc == STX_OK) rc = launch_umma<__half, 1>(ma, md, g2, s);
   } else {
     rc = launch_umma<__nv_bfloat16, 0>(mx, mw, g1, s);
+    if (rc == STX_OK && part1) {
+      k_pf_act_sum<__nv_bfloat16><<<agrid, 256, 0, s>>>(part1, z1, static_cast<int>(B), static_cast<int>(K), static_cast<int>(K8),
+                                                        static_cast<__nv_bfloat16*>(a_scr), static_cast<int>(K8), act, k_dev);
+      STX_LAUNCH_CHECK("k_pf_act_sum");
+    }
     if (rc == STX_OK) rc = launch_umma<__nv_bfloat16, 1>(ma, md, g2, s);
   }
   if (rc == STX_OK && part) rc = partial_sum(part, z, B * H, out, dtype, s);
