@@ -185,7 +185,7 @@ int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out);
  * down_buf [B,H]: the result.  scratch: stx_mlp_scratch_bytes() bytes, 16-byte aligned,
  * ZERO on the first call; its leading (256 + 4*B*H rounded up to 256) bytes are an fp32
  * accumulator and a counter that every call leaves zeroed again, the rest holds the
- * fp32 activations a[K][B] between the two kernels.  Row blocks of 64 and more in
+ * fp32 activations a[K][B] between the two kernels.  Row blocks of 9 and more in
  * fp16/bf16 (prefill) run as two tcgen05 tensor-core GEMMs instead and keep their
  * activation matrix and a transposed copy of the down rows behind those regions.         */
 int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* concat_w,

@@ -37,6 +37,9 @@ int cuda_fail(cudaError_t e, const char* what);  // records the message, returns
 int num_sms();  // SM count of the current device (cached per device)
 
 inline size_t dtype_size(int dt) { return dt == STX_F32 ? 4 : 2; }
+// Row blocks of at least this many rows (16-bit, gated) run as tensor-core GEMMs over packed weights;
+// fewer rows run the streaming kernels (1 row: k_mlp_b1, 2..8: k_mlp_bn).
+constexpr int64_t STX_GEMM_MIN_ROWS = 9;
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ---------------------------------------------------------------- dtype traits

@@ -186,7 +186,7 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
       if (rc != STX_OK) return rc;
     }
   }
-  // Row blocks of 64 and more (16-bit, gated): the packed cache IS the operand of two tensor-core
+  // Row blocks of 9 and more (16-bit, gated): the packed cache IS the operand of two tensor-core
   // GEMMs, so its maintenance comes first, on the same stream; the GEMMs are shaped for all I
   // slots and follow the device-side K (no host read-back, graph-capturable).
   const bool big = !fuse && c->pk_gate && prefill_wanted(B, c->H, c->I, c->dtype, c->has_gate);

@@ -260,7 +260,7 @@ static size_t decode_scratch_bytes(int64_t B, int64_t H, int64_t K) {
   return decode_scratch_bytes_min(B, H, K) + (B == 1 ? align_up(static_cast<size_t>(PARTIAL_ROWS) * H * sizeof(float), 256) : 0);
 }
 
-// Scratch of the tensor-core path inside a buffer that stx_mlp_scratch_bytes(B', H, K) sized, B' >= B >= 64.
+// Scratch of the tensor-core path inside a buffer that stx_mlp_scratch_bytes(B', H, K) sized, B' >= B >= STX_GEMM_MIN_ROWS.
 void* mlp_prefill_region(void* scratch, int64_t B, int64_t H, int64_t K) {
   return static_cast<char*>(scratch) + decode_scratch_bytes(B, H, K);
 }
@@ -353,9 +353,9 @@ extern "C" {
 
 int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out) {
   STX_CHECK_ARG(bytes_out && B > 0 && H > 0 && K >= 0, "stx_mlp_scratch_bytes: bad argument");
-  // decode kernels' regions, then (row blocks of 64 and more) the tensor-core path's
+  // decode kernels' regions, then (row blocks of 9 and more) the tensor-core path's
   // activation matrix and transposed down weight
-  *bytes_out = decode_scratch_bytes(B, H, K) + (B >= 64 ? prefill_scratch_bytes(B, H, K) : 0);
+  *bytes_out = decode_scratch_bytes(B, H, K) + (B >= STX_GEMM_MIN_ROWS ? prefill_scratch_bytes(B, H, K) : 0);
   return STX_OK;
 }
 
@@ -462,7 +462,7 @@ extern "C" int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t 
                                               int act, int has_gate, int dtype, void* stream) {
   STX_CHECK_ARG(B > 0 && H > 0 && K >= 0, "stx_sparse_mlp_forward_noalloc: bad sizes B=%lld H=%lld K=%lld",
                 static_cast<long long>(B), static_cast<long long>(H), static_cast<long long>(K));
-  const size_t need = decode_scratch_bytes_min(B, H, K) + (B >= 64 ? prefill_scratch_bytes(B, H, K) : 0);
+  const size_t need = decode_scratch_bytes_min(B, H, K) + (B >= STX_GEMM_MIN_ROWS ? prefill_scratch_bytes(B, H, K) : 0);
   if (need > NOALLOC_BYTES) {
     set_error("stx_sparse_mlp_forward_noalloc: B*(H+K) = %lld exceeds the built-in scratch of %lld elements; "
               "use stx_sparse_mlp_forward with a caller-provided scratch buffer",

@@ -463,7 +463,7 @@ bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate) {
     const char* e = getenv("STX_PREFILL");
     v = (e && e[0] == '0') ? 0 : 1;
   }
-  return v == 1 && dtype != STX_F32 && has_gate && B >= 64 && (H % 64) == 0 && K >= 64;
+  return v == 1 && dtype != STX_F32 && has_gate && B >= STX_GEMM_MIN_ROWS && (H % 64) == 0 && K >= 64;
 }
 
 // x [B,H], concat [2K,H] (gate rows then up rows), down_packed [K,H]; scratch: prefill_scratch_bytes().

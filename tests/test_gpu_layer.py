@@ -164,6 +164,16 @@ def test_packed_cache_current_after_fused_steps(lazy):
             assert torch.equal(layer.active_down_weight().cpu(), down[:, idx])
 
 
+@pytest.mark.parametrize("rows", [9, 24, 40])
+def test_row_blocks_from_nine_rows_up_take_the_tensor_core_path(rows):
+    """Any row count above the 8 of the streaming kernels runs as GEMMs over the packed cache (rows beyond the
+    batch are out-of-bounds zeros of the TMA box)."""
+    from sparse_transformers_b200.synth import Workload
+
+    w = Workload("b%d" % rows, H=1024, I=2048, r=32, B=rows, dtype=torch.bfloat16, density=0.08, alpha=0.7)
+    _run(w, steps=5, seed=rows)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_row_block_of_64_runs_on_the_packed_cache(dtype):
     """64 rows: the layer step brings the packed cache up to date first and runs the two tensor-core
