@@ -387,8 +387,10 @@ int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* con
   const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(concat_w) |
                        reinterpret_cast<uintptr_t>(down_packed) | reinterpret_cast<uintptr_t>(scratch);
   STX_CHECK_ARG((al & 15) == 0, "stx_sparse_mlp_forward: x, concat_w, down_packed and scratch must be 16-byte aligned");
-  if (prefill_wanted(B, H, K, dtype, has_gate)) {  // (mlp_prefill_region below)
-    // hundreds of rows: the gathered weights form a dense contraction -> tcgen05 GEMMs
+  // the built-in scratch of the no-alloc entry point (scratch_has_partial == false) has no room for the
+  // tensor-core path's buffers: its row blocks stay on the streaming kernels
+  if (scratch_has_partial && prefill_wanted(B, H, K, dtype, has_gate)) {
+    // row blocks: the gathered weights form a dense contraction -> tcgen05 GEMMs
     return prefill_forward(x, B, H, concat_w, down_packed, K, down_buf, combined_buf, act, dtype,
                            static_cast<char*>(scratch) + decode_scratch_bytes(B, H, K), nullptr, nullptr,
                            static_cast<cudaStream_t>(stream));
@@ -462,7 +464,7 @@ extern "C" int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t 
                                               int act, int has_gate, int dtype, void* stream) {
   STX_CHECK_ARG(B > 0 && H > 0 && K >= 0, "stx_sparse_mlp_forward_noalloc: bad sizes B=%lld H=%lld K=%lld",
                 static_cast<long long>(B), static_cast<long long>(H), static_cast<long long>(K));
-  const size_t need = decode_scratch_bytes_min(B, H, K) + (B >= STX_GEMM_MIN_ROWS ? prefill_scratch_bytes(B, H, K) : 0);
+  const size_t need = decode_scratch_bytes_min(B, H, K);
   if (need > NOALLOC_BYTES) {
     set_error("stx_sparse_mlp_forward_noalloc: B*(H+K) = %lld exceeds the built-in scratch of %lld elements; "
               "use stx_sparse_mlp_forward with a caller-provided scratch buffer",

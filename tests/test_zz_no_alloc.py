@@ -31,7 +31,7 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
 
     g = torch.Generator().manual_seed(123)
     # two different calls in a row: the second one must not see the first one's leftovers
-    for (B, H, K, act) in [(2, 1024, 300, "silu"), (1, 3072, 777, "relu")]:
+    for (B, H, K, act) in [(2, 1024, 300, "silu"), (1, 3072, 777, "relu"), (12, 512, 200, "silu")]:  # 12 rows: streaming kernels here
         x = torch.randn(B, H, generator=g).to(dtype).to(DEV)
         cw = (torch.randn(2 * K, H, generator=g) / H ** 0.5).to(dtype).to(DEV)
         dp = (torch.randn(K, H, generator=g) / H ** 0.5).to(dtype).to(DEV)
