@@ -713,6 +713,13 @@ struct MlpB1Args {
 constexpr int B1_MAX_BYTES = 24;   // mask bytes per CTA: ceil(ceil(I / 8) / G) <= 24 (192 neurons)
 constexpr int B1_LIST_CAP = 192;
 
+// Shared-memory footprint of t for the fused predictor back half: B rows, stored so that the eight
+// lanes of a neuron read one contiguous 128-byte line per load: [b][c4][v4][g][4 floats] for chunk
+// c = g + 8*c4 and elements 4*v4 .. 4*v4+3 of the chunk (V elements per chunk, ceil(r/V/8) groups c4).
+__host__ __device__ inline size_t pred_t_smem_bytes(int B, int r, int V) {
+  return r > 0 ? static_cast<size_t>(B) * ((r / V + 7) / 8) * 8 * V * sizeof(float) : 0;
+}
+
 // Predictor back half for the calling CTA's neurons (mask bytes blockIdx.x, + gridDim.x, ...),
 // all 512 threads.  Same arithmetic as k_pred_scores: 8 lanes per neuron, lane g takes the
 // 16-byte chunks g, g + 8, ... of the r-long row in order, then a butterfly over the 8 lanes
@@ -728,6 +735,7 @@ __device__ __forceinline__ int cta_scores_and_list(const T* __restrict__ Bm, con
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = gridDim.x;
   const int rch = r / V;  // <= 32
+  const int nc4 = (rch + 7) >> 3;
   const int NBY = (I + 7) >> 3;
   const int nby = NBY > static_cast<int>(blockIdx.x) ? (NBY - 1 - static_cast<int>(blockIdx.x)) / G + 1 : 0;
   const int g = tid & 7;
@@ -752,7 +760,10 @@ __device__ __forceinline__ int cta_scores_and_list(const T* __restrict__ Bm, con
   pdl_launch_dependents();
   STX_B1_STAMP(1);
   if (8 < nby) load_w(1, wv1, ok1);
-  for (int k = tid; k < B * r; k += blockDim.x) t_s[k] = __ldcg(t_gl + k);
+  for (int k = tid; k < B * r; k += blockDim.x) {
+    const int b = k / r, e = k - b * r, c = e / V, v = e - c * V;
+    t_s[(((b * nc4 + (c >> 3)) * (V / 4) + (v >> 2)) * 8 + (c & 7)) * 4 + (v & 3)] = __ldcg(t_gl + k);
+  }
   __syncthreads();
   const float tau_r = DT<T>::round_f(tau);
   constexpr int SB = 8;  // batch rows whose chains run side by side (each row's own order is unchanged)
@@ -769,10 +780,11 @@ __device__ __forceinline__ int cta_scores_and_list(const T* __restrict__ Bm, con
 #pragma unroll
           for (int b = 0; b < SB; ++b) {
             if (b0 + b < B) {
-              const float4* tb = reinterpret_cast<const float4*>(t_s + (b0 + b) * r + c * V);  // 16-byte loads, same order
+              // elements 4*v4 .. of chunk c of row b0+b: one 128-byte line per (row, c4, v4) for the 8 lanes of a neuron
+              const float4* tb = reinterpret_cast<const float4*>(t_s) + (((b0 + b) * nc4 + c4) * (V / 4)) * 8 + g;
 #pragma unroll
               for (int v4 = 0; v4 < V / 4; ++v4) {
-                const float4 tv = tb[v4];
+                const float4 tv = tb[v4 * 8];
                 sc[b] = fmaf(tv.x, w[c4][4 * v4], sc[b]);
                 sc[b] = fmaf(tv.y, w[c4][4 * v4 + 1], sc[b]);
                 sc[b] = fmaf(tv.z, w[c4][4 * v4 + 2], sc[b]);
@@ -849,7 +861,7 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
   uint64_t* bar_d = bar_gu + B1_MAX_SLOTS;
   float* a_s = reinterpret_cast<float*>(smem + 256);
   // [B1_HEADER, +t_bytes): t of the fused predictor back half
-  const size_t t_bytes = q.Bm ? (static_cast<size_t>(q.r) * sizeof(float) + 127) / 128 * 128 : 0;
+  const size_t t_bytes = q.Bm ? pred_t_smem_bytes(1, q.r, V) : 0;
   T* x_s = reinterpret_cast<T*>(smem + B1_HEADER + t_bytes);
   const size_t x_bytes = (sizeof(T) * H + 127) / 128 * 128;
   unsigned char* gu_bufs = smem + B1_HEADER + t_bytes + x_bytes;
@@ -1094,7 +1106,7 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
   uint64_t* bar_y = bar_x + 1;
   uint64_t* bar_z = bar_x + 2;
   uint32_t* a_pk = reinterpret_cast<uint32_t*>(smem + 256);  // [neuron pair][batch row]: (a[2k][b], a[2k+1][b]) in the model dtype
-  const size_t t_bytes = (static_cast<size_t>(B) * q.r * sizeof(float) + 127) / 128 * 128;
+  const size_t t_bytes = pred_t_smem_bytes(B, q.r, V);
   float* t_s = reinterpret_cast<float*>(smem + BN_HEADER);
   float* red_s = reinterpret_cast<float*>(smem + BN_HEADER + t_bytes);
   unsigned char* x_s = smem + BN_HEADER + t_bytes + BN_RED_BYTES;        // 8 rows of rstride
@@ -1117,17 +1129,18 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   STX_B1_STAMP(0);
-  int nlocal = cta_scores_and_list<T>(static_cast<const T*>(q.Bm), q.t, t_s, B, q.r, p.I, q.tau, q.bits, s_my, s_nib,
-                                      s_bytes, &s_nlocal);
-  int niter = (nlocal + TN - 1) / TN;
   const int G = gridDim.x;
   const bool balance = q.xchg != nullptr && G <= BN_MAX_GRID;
   __shared__ int s_epoch, s_plan[4];
+  // the exchange's epoch was written by this layer's previous launch: read it ahead of everything
+  // (the barriers inside the front-end make it visible to all threads)
+  if (balance && tid == 0) s_epoch = *reinterpret_cast<volatile int*>(q.xchg);
+  int nlocal = cta_scores_and_list<T>(static_cast<const T*>(q.Bm), q.t, t_s, B, q.r, p.I, q.tau, q.bits, s_my, s_nib,
+                                      s_bytes, &s_nlocal);
+  int niter = (nlocal + TN - 1) / TN;
   int epoch = 0;
   const int n_own = nlocal;
   if (balance) {  // publish the count and the list
-    if (tid == 0) s_epoch = *reinterpret_cast<volatile int*>(q.xchg);
-    __syncthreads();
     epoch = static_cast<int>(static_cast<unsigned>(s_epoch) + 1u);
     if (tid == 0)
       *reinterpret_cast<volatile int*>(q.xchg + BN_XCHG_COUNTS + blockIdx.x) = ((epoch & 0x1fffff) << 10) | n_own;
@@ -1601,7 +1614,7 @@ static size_t b1_smem_budget() {
 template <typename T>
 static int b1_slots(int H, int has_gate, int r) {
   const size_t row_bytes = static_cast<size_t>(H) * sizeof(T);
-  const size_t x_bytes = (row_bytes + 127) / 128 * 128 + (static_cast<size_t>(r) * sizeof(float) + 127) / 128 * 128;
+  const size_t x_bytes = (row_bytes + 127) / 128 * 128 + pred_t_smem_bytes(1, r, DT<T>::V);
   const int nmat = has_gate ? 3 : 2;
   const size_t budget = b1_smem_budget<T>();
   if (H / DT<T>::V > B1_MAX_PASS * 512 || budget < B1_HEADER + x_bytes) return 0;
@@ -1624,7 +1637,7 @@ static int launch_b1(const GateUpArgs& g, const void* down, float* partial, void
                      const B1Pred& pr, cudaStream_t s) {
   const size_t row_bytes = static_cast<size_t>(g.H) * sizeof(T);
   const int nmat = g.has_gate ? 3 : 2;
-  const size_t x_bytes = (row_bytes + 127) / 128 * 128 + (static_cast<size_t>(pr.r) * sizeof(float) + 127) / 128 * 128;
+  const size_t x_bytes = (row_bytes + 127) / 128 * 128 + pred_t_smem_bytes(1, pr.r, DT<T>::V);
   MlpB1Args q;
   q.g = g;
   q.g.nwarps = b1_slots<T>(g.H, g.has_gate, pr.r);
@@ -1667,7 +1680,7 @@ static size_t bn_smem_budget() {
 
 // bytes in front of the slots / slots per CTA (0: the kernel does not fit the shape)
 static size_t bn_fixed_bytes(int H, int B, int r) {
-  return BN_HEADER + (static_cast<size_t>(B) * r * sizeof(float) + 127) / 128 * 128 + BN_RED_BYTES +
+  return BN_HEADER + pred_t_smem_bytes(B, r, 8) + BN_RED_BYTES +
          static_cast<size_t>(BN_MAX) * (static_cast<size_t>(H) * 2 + 64);
 }
 // shared memory per neuron of a tile: four half rows (gate/up x two halves) and the down row
