@@ -433,8 +433,10 @@ __global__ void __launch_bounds__(256) k_pf_act_sum(const float* __restrict__ pa
 static int gemm1_splits(int64_t B, int64_t H, int64_t K) {
   const int64_t bm = B > PF_BM ? 2 * PF_BM : PF_BM;
   const int64_t tiles = ((B + bm - 1) / bm) * ((K + PF_BN - 1) / PF_BN);
-  if (tiles * 2 > num_sms()) return 1;
-  return static_cast<int>(std::min<int64_t>({8, std::max<int64_t>(1, num_sms() / tiles), std::max<int64_t>(1, H / (4 * PF_BK))}));
+  if (tiles > num_sms()) return 1;
+  // round up: the tiles are counted for all K slots, but a cache is rarely full (tiles beyond the
+  // device-side K exit at once), so up to 2x the SM count of CTAs still runs as about one wave
+  return static_cast<int>(std::min<int64_t>({8, (num_sms() + tiles - 1) / tiles, std::max<int64_t>(1, H / (4 * PF_BK))}));
 }
 
 // GEMM 2 has only ceil(B/128..256) x H/256 output tiles; for few rows the contraction is split so
