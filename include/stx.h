@@ -224,10 +224,13 @@ int stx_layer_destroy(stx_layer_t* l);
 int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_t B,
                    void* out, void* stream);
 /* The same step restricted to some of its stages (bit mask); used to time stages apart.
- * Stages that are skipped leave their outputs as the previous call left them.  A single
- * row (B == 1) under the threshold rule runs PREDICT_MASK and MLP_GATEUP as ONE kernel
- * when both bits are set (the mask never leaves the chip before the rows are fetched);
- * MLP_DOWN is then the deterministic sum of that kernel's per-CTA partial outputs.      */
+ * Stages that are skipped leave their outputs as the previous call left them.  Up to 8
+ * rows under the threshold rule (2..8 rows: 16-bit gated weights) run PREDICT_MASK and
+ * MLP_GATEUP as ONE kernel when both bits are set (the mask never leaves the chip before
+ * the rows are fetched); MLP_DOWN is then the deterministic sum of that kernel's per-CTA
+ * partial outputs.  9 rows and more (16-bit, gated) run the MLP stage as tensor-core
+ * GEMMs over the packed cache and bring the cache up to date first if PLAN / COPY have
+ * not run yet in this step.                                                             */
 #define STX_STAGE_PREDICT_T 1u     /* predictor, first half: t = A x            */
 #define STX_STAGE_PREDICT_MASK 32u /* predictor, second half: scores -> mask bits */
 #define STX_STAGE_PREDICT 33u      /* both                                      */
@@ -246,8 +249,8 @@ int stx_layer_step_stages(stx_layer_t* l, const void* x_pred, const void* x_mlp,
 int stx_layer_set_lazy_cache(stx_layer_t* l, int lazy);
 /* Device pointer to the layer's current mask bits (ceil(I/32) words), valid after a step. */
 int stx_layer_mask_bits(stx_layer_t* l, const uint32_t** bits_out);
-/* *fused_out = 1 when a step of B rows runs PREDICT_MASK and the MLP as the single-row
- * kernel pair described above (B == 1, threshold rule, shape fits), else 0.  No reference
+/* *fused_out = 1 when a step of B rows runs PREDICT_MASK and the MLP as the one-kernel
+ * pair described above (B <= 8, threshold rule, shape fits), else 0.  No reference
  * counterpart; bench and tests use it to name the kernels they time.                    */
 int stx_layer_single_row_fused(stx_layer_t* l, int64_t B, int* fused_out);
 
