@@ -315,7 +315,9 @@ k_umma_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // k-block are never reached by the contraction and are skipped.
 __global__ void __launch_bounds__(256) k_pf_transpose(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int R, int C,
                                                       int ldo, const int* __restrict__ r_dev) {
-  __shared__ uint16_t tile[64][64 + 8];
+  // the tile is stored transposed ([column][row], rows of 66 elements: the 8 column groups a warp
+  // scatters into land in 4 different bank quarters) and read back with aligned 32-bit loads
+  __shared__ __align__(16) uint16_t tile[64][66];
   const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
   if (r_dev && r0 >= (*r_dev + PF_BK - 1) / PF_BK * PF_BK) return;
   const int t = threadIdx.x;
@@ -324,17 +326,21 @@ __global__ void __launch_bounds__(256) k_pf_transpose(const uint16_t* __restrict
     const int idx = t + 256 * k, rr = idx >> 3, cc = (idx & 7) * 8;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r0 + rr < R && c0 + cc < C) v = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r0 + rr) * C + c0 + cc);
-    *reinterpret_cast<uint4*>(&tile[rr][cc]) = v;
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      tile[cc + 2 * e][rr] = static_cast<uint16_t>(w[e] & 0xffffu);
+      tile[cc + 2 * e + 1][rr] = static_cast<uint16_t>(w[e] >> 16);
+    }
   }
   __syncthreads();
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {  // 64 output rows (columns of the tile) x 8 chunks of 8 input rows
+  for (int k = 0; k < 2; ++k) {  // 64 output rows (columns of the input tile) x 8 chunks of 8 input rows
     const int idx = t + 256 * k, cc = idx >> 3, rr = (idx & 7) * 8;
     if (c0 + cc < C && r0 + rr < ldo) {
-      __align__(16) uint16_t v[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = tile[rr + e][cc];
-      *reinterpret_cast<uint4*>(out + static_cast<size_t>(c0 + cc) * ldo + r0 + rr) = *reinterpret_cast<const uint4*>(v);
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(&tile[cc][rr]);  // 132-byte rows: 4-byte aligned
+      const uint4 v = make_uint4(src[0], src[1], src[2], src[3]);
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(c0 + cc) * ldo + r0 + rr) = v;
     }
   }
 }
