@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256)
 k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* __restrict__ bits,
               T* __restrict__ scores_out, int B, int r, int I, float tau, int write_bits) {
   constexpr int V = DT<T>::V;
-  extern __shared__ float t_s[];
+  extern __shared__ __align__(16) float t_s[];
   __shared__ uint32_t s_nib[8];
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int g = lane & 7;
@@ -143,9 +143,20 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
             for (int b = 0; b < PRED_BT; ++b) {
               if (b < nb) {
                 const float* tb = t_s + (b0 + b) * r + c * V;
+                if (vec_ok) {  // 16-byte shared-memory loads; the additions keep their order
 #pragma unroll
-                for (int v = 0; v < V; ++v)
-                  if (vec_ok || c * V + v < r) acc[b] = fmaf(tb[v], wv[q][v], acc[b]);
+                  for (int v4 = 0; v4 < V / 4; ++v4) {
+                    const float4 tv = reinterpret_cast<const float4*>(tb)[v4];
+                    acc[b] = fmaf(tv.x, wv[q][4 * v4], acc[b]);
+                    acc[b] = fmaf(tv.y, wv[q][4 * v4 + 1], acc[b]);
+                    acc[b] = fmaf(tv.z, wv[q][4 * v4 + 2], acc[b]);
+                    acc[b] = fmaf(tv.w, wv[q][4 * v4 + 3], acc[b]);
+                  }
+                } else {
+#pragma unroll
+                  for (int v = 0; v < V; ++v)
+                    if (c * V + v < r) acc[b] = fmaf(tb[v], wv[q][v], acc[b]);
+                }
               }
             }
           }
