@@ -1,7 +1,16 @@
-// Sparse gated MLP over packed active rows, decode batches — two streaming kernels.
+// Sparse gated MLP for decode batches: the streaming kernels.
 //
-//   a[j,b]   = act(x[b]·gate[j]) * (x[b]·up[j])            k_gateup_tma   (K neurons)
-//   out[b,:] = sum_j a[j,b] * down[j,:]                    k_down_rows
+//   a[j,b]   = act(x[b]·gate[j]) * (x[b]·up[j])      (K active neurons)
+//   out[b,:] = sum_j a[j,b] * down[j,:]
+//
+// Contents, in file order:
+//   k_gateup_tma / k_gateup_mma + k_down_rows   two kernels over packed rows or a mask-listed gather;
+//                                               any dtype, gated or not (described right below)
+//   k_mlp_b1 + k_partial_reduce                 one row: predictor scores of the CTA's own neurons, mask
+//                                               bytes, row gather and the whole MLP in one kernel
+//   k_mlp_bn + k_partial_reduce4                2..8 rows of 16-bit gated weights, same structure with both
+//                                               projections on the tensor pipe
+//   host dispatch (mlp_forward_tma, layer_b1_forward, partial_sum)
 //
 // k_gateup_tma: one persistent CTA per SM owns a contiguous range of neurons.  Every warp is
 // its own producer and consumer: lane 0 issues two 1-D bulk async copies (cp.async.bulk
