@@ -19,7 +19,7 @@
 //               256 columns); tcgen05.commit releases a stage / publishes the accumulator
 //   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, activation and product
 //               in registers, 16-byte stores
-// Edges are handled by TMA zero fill on loads and by masked stores.  No multicast is used.
+// Edges are handled by TMA zero fill on loads and by masked stores.  Every CTA loads its own tiles.
 // Every mbarrier wait is bounded; on expiry the kernel records DEV_TIMEOUT and continues
 // with the same control flow (the result is then garbage) so that TMEM is always freed.
 #include "stx_common.cuh"
