@@ -73,6 +73,20 @@ def test_half_precision_shapes(name, scale):
     _run(WORKLOADS[name].scaled(layers=1, **scale), steps=8)
 
 
+@pytest.mark.parametrize("dtype,has_gate,density", [(torch.float32, True, 0.9), (torch.float16, True, 0.97),
+                                                    (torch.bfloat16, False, 0.9), (torch.float16, True, 0.4)])
+def test_one_row_with_more_neurons_per_cta_than_row_spaces(dtype, has_gate, density):
+    """Dense masks at one row: a CTA of the one-kernel path owns 20 to 55 neurons, more than the
+    36 (fp32: 27) rows its shared memory holds, so row spaces are re-used within the launch, over
+    one block of neurons and over several."""
+    from sparse_transformers_b200.synth import Workload
+
+    w = Workload("dense-b1", H=2048, I=8192, r=64, B=1, dtype=dtype, density=density, has_gate=has_gate,
+                 act="silu" if has_gate else "relu")
+    ks = _run(w, steps=4)
+    assert np.mean(ks) > 0.3 * 8192
+
+
 def test_no_gate_relu_ragged():
     from sparse_transformers_b200.synth import Workload
 
