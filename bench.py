@@ -421,7 +421,8 @@ def run_native(args):
         achieved = alg / (stages_us[top] * 1e-6) / 1e9
         ratio = traffic_ratio(k1)
         roofline = {"kernel": k1, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_source": peak_src, "traffic": (ratio * alg if ratio else None),
+                    "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000_gbs": achieved / 8000.0,
+                    "traffic": (ratio * alg if ratio else None),
                     "algorithmic_bytes_per_launch": alg, "us_per_launch": stages_us[top],
                     "launches_timed": n_inst * w.layers,
                     "second_kernel": {"kernel": k2, "algorithmic_bytes_per_launch": alg2,
