@@ -313,6 +313,31 @@ int stx_peer_status(stx_peer_t* p, int* status_out, void* stream);
  * kernel otherwise.  peer == NULL detaches.  Set before capturing a stack.               */
 int stx_layer_set_peer(stx_layer_t* l, stx_peer_t* peer);
 
+/* ---- decode-time glue of the decoder layer around the MLP (one token, graph-capturable)
+ * What SkipDecoderLayer.forward does between the predictor's input and the MLP
+ * (src/modeling_skip.py:235-256): input RMSNorm -> self-attention with a KV cache ->
+ * residual -> post-attention RMSNorm.  The projections stay GEMV calls of the caller.
+ *
+ * stx_attn_decode: qkv [ (n_heads + 2 n_kv_heads) * head_dim ] = the token's q, k, v
+ * projections.  Rotates q and k by row *pos_dev of cos/sin [max_len, head_dim] (fp32,
+ * rotate-half layout), stores k and v at position *pos_dev of k_cache / v_cache
+ * [n_kv_heads, max_len, head_dim], attends over the positions 0..*pos_dev with scale
+ * head_dim^-1/2 (grouped-query: n_heads / n_kv_heads query heads per cache head) and writes
+ * out [n_heads * head_dim].  head_dim 64, 128 or 256; max_len <= 8192.  A position outside
+ * 0..max_len-1 leaves everything untouched.  workspace: device memory of
+ * stx_attn_decode_workspace_bytes bytes, zeroed once by the caller and then owned by the calls
+ * (the keys of a head are split over several CTAs, whose partial results meet there); calls
+ * that share a workspace must be ordered on one stream.
+ * stx_add_rmsnorm: h_out = h + a (rounded to dtype; a == NULL: no add, h_out unused),
+ * x_out = round(h_out * rsqrt(mean(h_out^2) + eps)) * w, the operation order of
+ * LlamaSkipRMSNorm (src/models/llama/modelling_llama_skip.py:39-44).  h_out may alias h. */
+int stx_attn_decode(const void* qkv, const float* cos_table, const float* sin_table, const int64_t* pos_dev, void* k_cache,
+                    void* v_cache, void* out, int n_heads, int n_kv_heads, int head_dim, int64_t max_len, int dtype,
+                    void* workspace, void* stream);
+int stx_attn_decode_workspace_bytes(int n_heads, int head_dim, int64_t* bytes_out);
+int stx_add_rmsnorm(const void* h, const void* a, const void* w, float eps, void* h_out, void* x_out, int64_t H, int dtype,
+                    void* stream);
+
 #ifdef __cplusplus
 }
 #endif

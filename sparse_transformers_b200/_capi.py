@@ -80,6 +80,9 @@ SIGNATURES = {
     "stx_peer_allreduce": (_i32, [_vp, _vp, _i64, _i32, _vp]),
     "stx_peer_status": (_i32, [_vp, ctypes.POINTER(ctypes.c_int), _vp]),
     "stx_layer_set_peer": (_i32, [_vp, _vp]),
+    "stx_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
+    "stx_attn_decode_workspace_bytes": (_i32, [_i32, _i32, ctypes.POINTER(_i64)]),
+    "stx_add_rmsnorm": (_i32, [_vp, _vp, _vp, ctypes.c_float, _vp, _vp, _i64, _i32, _vp]),
 }
 
 

@@ -1,0 +1,408 @@
+// Decode-time glue of the LlamaSkip host around the sparse MLP (C ABI: stx_attn_decode,
+// stx_add_rmsnorm): one query token against the KV cache, and residual add + RMSNorm.
+//
+//   k_attn_decode   grid = query heads.  A CTA rotates its q head and the k head of its group
+//                   (rotate-half RoPE in fp32, rounded to the model dtype), appends k and v to
+//                   the cache (the first head of each group writes), scores the keys 0..pos
+//                   a warp per key with eight keys in flight, soft-maxes in fp32 and sums the
+//                   values with 16-byte chunks of the head dimension across threads.  The position is read from device memory, so a
+//                   captured CUDA graph can be replayed token after token.
+//   k_add_rmsnorm   one CTA: h <- h + a (rounded to the model dtype), then
+//                   x = round(h * rsqrt(mean(h^2) + eps)) * w, the order of operations of
+//                   LlamaSkipRMSNorm (src/models/llama/modelling_llama_skip.py:39-44).
+#include "stx_common.cuh"
+
+#include <algorithm>
+
+namespace stx {
+
+constexpr int ATT_THREADS = 512;
+constexpr int NORM_THREADS = 1024;
+
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  static __device__ __forceinline__ void load(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x;
+    b = v.y;
+  }
+};
+template <> struct Pair<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float& a, float& b) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(p));
+    a = v.x;
+    b = v.y;
+  }
+};
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float& a, float& b) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    a = v.x;
+    b = v.y;
+  }
+};
+
+// Block-wide max / sum over the block's threads; `red` has 32 floats.  Every thread gets the result.
+template <bool IS_MAX>
+__device__ __forceinline__ float block_reduce(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float o = __shfl_xor_sync(0xffffffffu, v, off);
+    v = IS_MAX ? fmaxf(v, o) : v + o;
+  }
+  __syncthreads();  // red may still be read from a previous call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = IS_MAX ? -INFINITY : 0.f;
+  for (int w = 0; w < nw; ++w) r = IS_MAX ? fmaxf(r, red[w]) : r + red[w];  // same order in every thread
+  return r;
+}
+
+// `BYTES` consecutive bytes (4, 8, 16 or 32; aligned to min(BYTES, 16)) as 32-bit words.
+template <int BYTES>
+__device__ __forceinline__ void load_words(const void* p, uint32_t (&w)[BYTES / 4]) {
+  if constexpr (BYTES == 4) {
+    w[0] = *reinterpret_cast<const uint32_t*>(p);
+  } else if constexpr (BYTES == 8) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    w[0] = v.x;
+    w[1] = v.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < BYTES / 16; ++i) {
+      const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+      w[4 * i] = v.x;
+      w[4 * i + 1] = v.y;
+      w[4 * i + 2] = v.z;
+      w[4 * i + 3] = v.w;
+    }
+  }
+}
+// Word i of a row of T as floats: one element for fp32, two for the 16-bit types.
+template <typename T> struct Words;
+template <> struct Words<float> {
+  static constexpr int EPW = 1;
+  static __device__ __forceinline__ void run(uint32_t w, float* f) { f[0] = __uint_as_float(w); }
+};
+template <> struct Words<__half> {
+  static constexpr int EPW = 2;
+  static __device__ __forceinline__ void run(uint32_t w, float* f) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    f[0] = t.x;
+    f[1] = t.y;
+  }
+};
+template <> struct Words<__nv_bfloat16> {
+  static constexpr int EPW = 2;
+  static __device__ __forceinline__ void run(uint32_t w, float* f) {
+    f[0] = __uint_as_float(w << 16);
+    f[1] = __uint_as_float(w & 0xffff0000u);
+  }
+};
+
+// Workspace of stx_attn_decode: one arrival counter per head (zero between launches), then per
+// head and split the unnormalised value sum [HD], the split's score maximum and its sum of
+// exponentials.
+constexpr size_t ATT_COUNTER_BYTES = 4096;  // up to 1024 heads
+__host__ __device__ inline int att_part_floats(int hd) { return hd + 2; }
+
+// Grid (heads, splits): split s of a head takes an equal share of the cached keys (the last split
+// also the token's own key), so that one query head is read by several SMs; the split that
+// arrives last at the head's counter merges the partial soft-maxes.
+// Shared memory (floats): q_s[HD] | kn_s[HD] | vn_s[HD] | red[32] | acc_s[NG][HD] | sc[keys of the split + 1]
+template <typename T, int HD>
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict__ qkv, const float* __restrict__ cos_t,
+                                                              const float* __restrict__ sin_t,
+                                                              const long long* __restrict__ pos_dev, T* k_cache, T* v_cache,
+                                                              T* __restrict__ out, int nh, int nkv, long long max_len,
+                                                              float scale, unsigned char* workspace) {
+  constexpr int V = DT<T>::V;              // elements per 16 bytes
+  constexpr int NW = ATT_THREADS / 32;
+  constexpr int E = HD / 32;               // elements of a key row per lane
+  constexpr int KB = E * sizeof(T);        // the same in bytes
+  constexpr int TPR = HD / V;              // threads per value row (16 bytes each)
+  constexpr int NG = ATT_THREADS / TPR;    // key groups of the value sum
+  constexpr int U = 8;                     // keys a warp has in flight
+  extern __shared__ float sm[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float* q_s = sm;
+  float* kn_s = q_s + HD;
+  float* vn_s = kn_s + HD;
+  float* red = vn_s + HD;
+  float* acc_s = red + 32;
+  float* sc = acc_s + NG * HD;
+  const long long pos = *pos_dev;
+  if (pos < 0 || pos >= max_len) return;  // nothing sensible to do; the output is left as it was
+  const int h = blockIdx.x;
+  const int sp = blockIdx.y, NSP = gridDim.y;
+  const int rep = nh / nkv;
+  const int g = h / rep;
+  T* kc = k_cache + static_cast<size_t>(g) * max_len * HD;
+  T* vc = v_cache + static_cast<size_t>(g) * max_len * HD;
+
+  if (tid < HD) {
+    constexpr int half = HD / 2;
+    const int dp = tid < half ? tid + half : tid - half;
+    const float sign = tid < half ? -1.f : 1.f;
+    const float c = cos_t[pos * HD + tid], s = sin_t[pos * HD + tid];
+    const T* qrow = qkv + static_cast<size_t>(h) * HD;
+    const T* krow = qkv + static_cast<size_t>(nh + g) * HD;
+    const T* vrow = qkv + static_cast<size_t>(nh + nkv + g) * HD;
+    // x * cos + rotate_half(x) * sin: two rounded products, one rounded sum, then the model dtype
+    const T qr = DT<T>::from_f(__fadd_rn(__fmul_rn(DT<T>::to_f(qrow[tid]), c), __fmul_rn(sign * DT<T>::to_f(qrow[dp]), s)));
+    const T kr = DT<T>::from_f(__fadd_rn(__fmul_rn(DT<T>::to_f(krow[tid]), c), __fmul_rn(sign * DT<T>::to_f(krow[dp]), s)));
+    const T vr = vrow[tid];
+    q_s[tid] = DT<T>::to_f(qr);
+    kn_s[tid] = DT<T>::to_f(kr);
+    vn_s[tid] = DT<T>::to_f(vr);
+    if (h == g * rep && sp == 0) {  // one writer per group; every head of the group uses its own copy in shared memory
+      kc[pos * HD + tid] = kr;
+      vc[pos * HD + tid] = vr;
+    }
+  }
+  __syncthreads();
+
+  // ---- scores: a warp per key, lane l holds elements [l*E, l*E + E); U keys in flight per warp
+  const int chunk = (static_cast<int>(pos) + NSP - 1) / NSP;  // cached keys per split
+  const int lo = min(sp * chunk, static_cast<int>(pos)), hi = min(lo + chunk, static_cast<int>(pos));
+  const bool own = sp == NSP - 1;   // this split also scores the token's own key
+  kc += static_cast<size_t>(lo) * HD;  // from here on key j of the split is cached key lo + j
+  vc += static_cast<size_t>(lo) * HD;
+  const int n = hi - lo + 1;        // sc[n - 1] is the own key's slot (unused unless `own`)
+  float qf[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) qf[e] = q_s[lane * E + e];
+  float lmax = -INFINITY;
+  for (int j0 = warp; j0 < n - 1; j0 += NW * U) {
+    uint32_t kw[U][KB / 4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + NW * u;
+      if (j < n - 1) load_words<KB>(reinterpret_cast<const char*>(kc + static_cast<size_t>(j) * HD) + lane * KB, kw[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + NW * u;
+      if (j < n - 1) {  // uniform over the warp
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < KB / 4; ++i) {
+          float f[Words<T>::EPW];
+          Words<T>::run(kw[u][i], f);
+#pragma unroll
+          for (int e = 0; e < Words<T>::EPW; ++e) dot = fmaf(qf[i * Words<T>::EPW + e], f[e], dot);
+        }
+        dot = warp_sum_xor(dot) * scale;
+        if (lane == 0) sc[j] = dot;
+        lmax = fmaxf(lmax, dot);
+      }
+    }
+  }
+  if (warp == 0 && own) {  // the key of this token
+    float dot = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) dot = fmaf(qf[e], kn_s[lane * E + e], dot);
+    dot = warp_sum_xor(dot) * scale;
+    if (lane == 0) sc[n - 1] = dot;
+    lmax = fmaxf(lmax, dot);
+  }
+  const float m = block_reduce<true>(lmax, red);  // its barriers also publish sc
+  const int nsc = own ? n : n - 1;
+  float lsum = 0.f;
+  for (int j = tid; j < nsc; j += ATT_THREADS) {
+    const float p = __expf(sc[j] - m);
+    sc[j] = p;
+    lsum += p;
+  }
+  const float denom = block_reduce<false>(lsum, red);
+
+  // ---- values: thread (grp, ch) sums p_j * v_j[16-byte chunk ch] over the keys j = grp, grp + NG, ...
+  const int grp = tid / TPR, ch = tid - grp * TPR;
+  float acc[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) acc[v] = 0.f;
+  for (int j0 = grp; j0 < n - 1; j0 += 4 * NG) {
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + NG * u;
+      if (j < n - 1) raw[u] = *reinterpret_cast<const uint4*>(vc + static_cast<size_t>(j) * HD + ch * V);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + NG * u;
+      if (j < n - 1) {
+        float f[V];
+        Unpack<T>::run(raw[u], f);
+        const float p = sc[j];
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = fmaf(p, f[v], acc[v]);
+      }
+    }
+  }
+  if (grp == 0 && own) {
+    const float p = sc[n - 1];
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = fmaf(p, vn_s[ch * V + v], acc[v]);
+  }
+#pragma unroll
+  for (int v = 0; v < V; ++v) acc_s[grp * HD + ch * V + v] = acc[v];
+  __syncthreads();
+  int* counter = reinterpret_cast<int*>(workspace) + h;
+  float* part = reinterpret_cast<float*>(workspace + ATT_COUNTER_BYTES) + static_cast<size_t>(h) * NSP * att_part_floats(HD);
+  float* mine = part + static_cast<size_t>(sp) * att_part_floats(HD);
+  if (tid < HD) {
+    float s = 0.f;
+    for (int k = 0; k < NG; ++k) s += acc_s[k * HD + tid];
+    if (NSP == 1) {
+      out[static_cast<size_t>(h) * HD + tid] = DT<T>::from_f(s / denom);
+    } else {
+      __stcg(mine + tid, s);
+      if (tid == 0) {
+        __stcg(mine + HD, m);
+        __stcg(mine + HD + 1, denom);
+      }
+    }
+  }
+  if (NSP == 1) return;
+  // ---- the split that arrives last merges: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int t = atomicAdd(counter, 1);
+    s_last = t == NSP - 1;
+    if (s_last) *counter = 0;  // every other split has arrived: ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid < HD) {
+    float M = -INFINITY;
+    for (int k = 0; k < NSP; ++k) M = fmaxf(M, __ldcg(part + k * att_part_floats(HD) + HD));
+    float num = 0.f, den = 0.f;
+    for (int k = 0; k < NSP; ++k) {
+      const float* pk = part + k * att_part_floats(HD);
+      const float wgt = __expf(__ldcg(pk + HD) - M);  // 0 for a split without keys (its maximum is -inf)
+      num = fmaf(wgt, __ldcg(pk + tid), num);
+      den = fmaf(wgt, __ldcg(pk + HD + 1), den);
+    }
+    out[static_cast<size_t>(h) * HD + tid] = DT<T>::from_f(num / den);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(const T* h, const T* __restrict__ a, const T* __restrict__ w,
+                                                               float eps, T* h_out, T* __restrict__ x_out, int H) {
+  __shared__ float red[32];
+  const int tid = threadIdx.x;
+  float ss = 0.f;
+  for (int i = tid; i < H; i += NORM_THREADS) {
+    float v = DT<T>::to_f(h[i]);
+    if (a) {
+      v = DT<T>::round_f(v + DT<T>::to_f(a[i]));
+      h_out[i] = DT<T>::from_f(v);
+    }
+    ss = fmaf(v, v, ss);
+  }
+  const float tot = block_reduce<false>(ss, red);
+  const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
+  const T* src = a ? h_out : h;  // a thread re-reads only what it wrote itself
+  for (int i = tid; i < H; i += NORM_THREADS) {
+    const float nv = DT<T>::round_f(DT<T>::to_f(src[i]) * inv);
+    x_out[i] = DT<T>::from_f(nv * DT<T>::to_f(w[i]));
+  }
+}
+
+// Splits of the keys per head: enough CTAs to cover the SMs once, at most 8.
+static int att_splits(int n_heads) { return std::max(1, std::min(8, (num_sms() + n_heads - 1) / n_heads)); }
+
+}  // namespace stx
+
+using namespace stx;
+
+extern "C" {
+
+int stx_attn_decode_workspace_bytes(int n_heads, int head_dim, int64_t* bytes_out) {
+  STX_CHECK_ARG(bytes_out, "stx_attn_decode_workspace_bytes: null pointer");
+  STX_CHECK_ARG(n_heads > 0 && n_heads <= 1024 && head_dim > 0, "stx_attn_decode_workspace_bytes: bad shape");
+  *bytes_out = static_cast<int64_t>(ATT_COUNTER_BYTES + sizeof(float) * static_cast<size_t>(n_heads) * 8 * att_part_floats(head_dim));
+  return STX_OK;
+}
+
+int stx_attn_decode(const void* qkv, const float* cos_table, const float* sin_table, const int64_t* pos_dev, void* k_cache,
+                    void* v_cache, void* out, int n_heads, int n_kv_heads, int head_dim, int64_t max_len, int dtype,
+                    void* workspace, void* stream) {
+  STX_CHECK_ARG(qkv && cos_table && sin_table && pos_dev && k_cache && v_cache && out && workspace,
+                "stx_attn_decode: null pointer");
+  STX_CHECK_ARG(n_heads <= 1024, "stx_attn_decode: more than 1024 heads");
+  STX_CHECK_ARG(dtype == STX_F32 || dtype == STX_F16 || dtype == STX_BF16, "stx_attn_decode: bad dtype %d", dtype);
+  STX_CHECK_ARG(head_dim == 64 || head_dim == 128 || head_dim == 256, "stx_attn_decode: head_dim %d is not 64, 128 or 256",
+                head_dim);
+  STX_CHECK_ARG(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
+                "stx_attn_decode: %d query heads do not divide into %d key/value heads", n_heads, n_kv_heads);
+  STX_CHECK_ARG(max_len > 0 && max_len <= 8192, "stx_attn_decode: max_len %lld outside 1..8192", static_cast<long long>(max_len));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int V = 16 / static_cast<int>(dtype_size(dtype));
+  const int nsp = att_splits(n_heads);
+  const size_t smem = sizeof(float) * (3 * head_dim + 32 + static_cast<size_t>(ATT_THREADS) * V +
+                                       static_cast<size_t>((max_len + nsp - 1) / nsp + 1));
+  const float scale = 1.0f / sqrtf(static_cast<float>(head_dim));
+  const long long* pos = reinterpret_cast<const long long*>(pos_dev);
+  const long long ml = max_len;
+#define STX_ATT_LAUNCH(T, HD)                                                                                              \
+  do {                                                                                                                     \
+    if (smem > 48 * 1024)                                                                                                  \
+      STX_CUDA(cudaFuncSetAttribute(k_attn_decode<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));        \
+    k_attn_decode<T, HD><<<dim3(n_heads, nsp), ATT_THREADS, smem, s>>>(                                                   \
+        static_cast<const T*>(qkv), cos_table, sin_table, pos, static_cast<T*>(k_cache), static_cast<T*>(v_cache),         \
+        static_cast<T*>(out), n_heads, n_kv_heads, ml, scale, static_cast<unsigned char*>(workspace));                     \
+  } while (0)
+#define STX_ATT_HD(T)                       \
+  do {                                      \
+    if (head_dim == 64) STX_ATT_LAUNCH(T, 64);        \
+    else if (head_dim == 128) STX_ATT_LAUNCH(T, 128); \
+    else STX_ATT_LAUNCH(T, 256);            \
+  } while (0)
+  switch (dtype) {
+    case STX_F32: STX_ATT_HD(float); break;
+    case STX_F16: STX_ATT_HD(__half); break;
+    default: STX_ATT_HD(__nv_bfloat16); break;
+  }
+#undef STX_ATT_HD
+#undef STX_ATT_LAUNCH
+  STX_LAUNCH_CHECK("k_attn_decode");
+  return STX_OK;
+}
+
+int stx_add_rmsnorm(const void* h, const void* a, const void* w, float eps, void* h_out, void* x_out, int64_t H, int dtype,
+                    void* stream) {
+  STX_CHECK_ARG(h && w && x_out, "stx_add_rmsnorm: null pointer");
+  STX_CHECK_ARG(!a || h_out, "stx_add_rmsnorm: h_out is required when a is given");
+  STX_CHECK_ARG(dtype == STX_F32 || dtype == STX_F16 || dtype == STX_BF16, "stx_add_rmsnorm: bad dtype %d", dtype);
+  STX_CHECK_ARG(H > 0 && H <= (1 << 20), "stx_add_rmsnorm: H=%lld out of range", static_cast<long long>(H));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int Hi = static_cast<int>(H);
+  switch (dtype) {
+    case STX_F32:
+      k_add_rmsnorm<float><<<1, NORM_THREADS, 0, s>>>(static_cast<const float*>(h), static_cast<const float*>(a),
+                                                      static_cast<const float*>(w), eps, static_cast<float*>(h_out),
+                                                      static_cast<float*>(x_out), Hi);
+      break;
+    case STX_F16:
+      k_add_rmsnorm<__half><<<1, NORM_THREADS, 0, s>>>(static_cast<const __half*>(h), static_cast<const __half*>(a),
+                                                       static_cast<const __half*>(w), eps, static_cast<__half*>(h_out),
+                                                       static_cast<__half*>(x_out), Hi);
+      break;
+    default:
+      k_add_rmsnorm<__nv_bfloat16><<<1, NORM_THREADS, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(w), eps,
+          static_cast<__nv_bfloat16*>(h_out), static_cast<__nv_bfloat16*>(x_out), Hi);
+      break;
+  }
+  STX_LAUNCH_CHECK("k_add_rmsnorm");
+  return STX_OK;
+}
+
+}  // extern "C"

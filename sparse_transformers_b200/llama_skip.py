@@ -4,8 +4,11 @@ through the sparse layer step (predictor -> mask -> weight cache -> sparse MLP) 
 Mirrors the reference's inference model for this path (src/modeling_skip.py:131-266: decoder
 layer with the mask computed from the input-layernorm output and the sparse MLP applied to the
 post-attention-layernorm output, dense for sequences longer than one token;
-src/models/llama/modelling_llama_skip.py:30-66: RMSNorm and layer wiring).  Attention, norms,
-embedding and lm_head are ordinary torch ops: they are the host around the path, not the path.
+src/models/llama/modelling_llama_skip.py:30-66: RMSNorm and layer wiring).  Prefill, the
+projections, embedding and lm_head are ordinary torch ops: they are the host around the path.
+At decode time the glue between them is the library's own (``native_glue``): residual add +
+RMSNorm as one kernel, and RoPE + KV-cache append + one-query attention as one kernel, which
+takes a decoder layer from about two dozen launches to nine.
 Weights are random (N(0, 0.02), seeded): checkpoints are not available offline.
 
 The decode step (all layers, lm_head, greedy argmax, KV-cache append, position advance) is
@@ -14,6 +17,7 @@ layer's cache maintenance runs on a side stream inside the same graph.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 import time
 from dataclasses import dataclass
@@ -44,6 +48,7 @@ class LlamaSkipConfig:
     dtype: torch.dtype = torch.float16
     wstd: float = 0.02             # initializer_range
     lazy_cache: bool = False
+    native_glue: bool = True       # decode: stx_add_rmsnorm / stx_attn_decode instead of torch ops
 
     @property
     def tau(self) -> float:
@@ -54,6 +59,35 @@ class LlamaSkipConfig:
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     """RMSNorm of modelling_llama_skip.py:41-47 (normalise in fp32, scale by the weight) as one fused op."""
     return F.rms_norm(x, (x.shape[-1],), w, eps)
+
+
+_DT = {torch.float32: C.F32, torch.float16: C.F16, torch.bfloat16: C.BF16}
+
+
+def add_rmsnorm(h: torch.Tensor, a: torch.Tensor | None, w: torch.Tensor, eps: float, x_out: torch.Tensor) -> torch.Tensor:
+    """h <- h + a in place (a may be None), x_out <- RMSNorm(h) * w; all [1,H] contiguous on the device."""
+    C.check(C.lib.stx_add_rmsnorm(h.data_ptr(), a.data_ptr() if a is not None else None, w.data_ptr(), float(eps),
+                                  h.data_ptr(), x_out.data_ptr(), h.numel(), _DT[h.dtype],
+                                  torch.cuda.current_stream().cuda_stream))
+    return x_out
+
+
+def attn_workspace(heads: int, head_dim: int, device) -> torch.Tensor:
+    """Zeroed scratch of stx_attn_decode for one stream of calls."""
+    n = ctypes.c_int64()
+    C.check(C.lib.stx_attn_decode_workspace_bytes(heads, head_dim, ctypes.byref(n)))
+    return torch.zeros(n.value, dtype=torch.uint8, device=device)
+
+
+def attn_decode(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor,
+                v_cache: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                workspace: torch.Tensor) -> torch.Tensor:
+    """RoPE at position pos[0] (device int64), append k/v to the caches [kv_heads, max_len, head_dim] of one layer,
+    attend over positions 0..pos; qkv [(heads + 2 kv_heads) * head_dim] -> out [heads * head_dim]."""
+    C.check(C.lib.stx_attn_decode(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(), k_cache.data_ptr(),
+                                  v_cache.data_ptr(), out.data_ptr(), heads, kv_heads, head_dim, k_cache.shape[1],
+                                  _DT[qkv.dtype], workspace.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return out
 
 
 def rope_tables(cfg: LlamaSkipConfig, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -104,6 +138,7 @@ class LlamaSkipModel:
         self._arange = torch.arange(cfg.max_len, device=self.device)
         self._side = torch.cuda.Stream(device=self.device)    # cache index plans
         self._side2 = torch.cuda.Stream(device=self.device)   # cache row copies
+        self._attn_ws = attn_workspace(cfg.heads, cfg.head_dim, self.device)
         self._graph = None
         self.trace = None  # when a list: per decode step and layer (x_pred, x_mlp, mlp_out, mask) copies, eager mode only
 
@@ -161,8 +196,50 @@ class LlamaSkipModel:
         return nxt
 
     # ------------------------------------------------------------------ one decode token
+    def _mlp_decode(self, li: int, x_pred: torch.Tensor, x_mlp: torch.Tensor) -> torch.Tensor:
+        """Sparse MLP of layer li on the current stream, its cache upkeep on the side streams."""
+        main = torch.cuda.current_stream()
+        sp: SparseLayer = self.layers[li]["sparse"]
+        out = torch.empty_like(x_mlp)
+        sp.step_stages(C.STAGE_PREDICT | C.STAGE_MLP, x_pred, x_mlp, out, batch=1)
+        self._side.wait_stream(main)                                             # cache upkeep off the critical path
+        with torch.cuda.stream(self._side):
+            sp.step_stages(C.STAGE_PLAN, batch=1)
+        self._side2.wait_stream(self._side)
+        with torch.cuda.stream(self._side2):
+            sp.step_stages(C.STAGE_COPY, batch=1)
+        if self.trace is not None:
+            self.trace.append((li, x_pred.clone(), x_mlp.clone(), out.clone(), sp.mask().clone()))
+        return out
+
+    def _finish_token(self, last: torch.Tensor) -> None:
+        self.logits.copy_((last @ self.embed.t()).float().view(-1))
+        nxt = self.logits.argmax().view(1)
+        self.pos.add_(1)
+        self.token.copy_(nxt)
+        self.generated.index_copy_(0, self.pos - self.gen_base, nxt)
+
+    def _decode_body_native(self) -> None:
+        cfg = self.cfg
+        main = torch.cuda.current_stream()
+        h = self.embed.index_select(0, self.token)                              # [1,H], updated in place below
+        pending = None                                                          # MLP output not yet added to h
+        for li, L in enumerate(self.layers):
+            x_pred = add_rmsnorm(h, pending, L["ln1"], cfg.rms_eps, torch.empty_like(h))   # the predictor's input
+            qkv = x_pred @ L["wqkv"].t()
+            o = attn_decode(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li],
+                            torch.empty(1, cfg.heads * cfg.head_dim, dtype=h.dtype, device=h.device),
+                            cfg.heads, cfg.kv_heads, cfg.head_dim, self._attn_ws)
+            x_mlp = add_rmsnorm(h, o @ L["wo"].t(), L["ln2"], cfg.rms_eps, torch.empty_like(h))
+            pending = self._mlp_decode(li, x_pred, x_mlp)
+        main.wait_stream(self._side)
+        main.wait_stream(self._side2)
+        self._finish_token(add_rmsnorm(h, pending, self.final_norm, cfg.rms_eps, torch.empty_like(h)))
+
     def _decode_body(self) -> None:
         cfg = self.cfg
+        if cfg.native_glue and cfg.head_dim in (64, 128, 256) and cfg.max_len <= 8192:
+            return self._decode_body_native()
         main = torch.cuda.current_stream()
         h = self.embed.index_select(0, self.token)                              # [1,H]
         self._step_rope = (self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos),
@@ -171,26 +248,10 @@ class LlamaSkipModel:
             x_pred = rms_norm(h, L["ln1"], cfg.rms_eps)                          # the predictor's input
             h = h + self._attention(li, x_pred, None, 1, decode=True)
             x_mlp = rms_norm(h, L["ln2"], cfg.rms_eps).contiguous()
-            out = torch.empty_like(x_mlp)
-            sp: SparseLayer = L["sparse"]
-            sp.step_stages(C.STAGE_PREDICT | C.STAGE_MLP, x_pred.contiguous(), x_mlp, out, batch=1)
-            self._side.wait_stream(main)                                         # cache upkeep off the critical path
-            with torch.cuda.stream(self._side):
-                sp.step_stages(C.STAGE_PLAN, batch=1)
-            self._side2.wait_stream(self._side)
-            with torch.cuda.stream(self._side2):
-                sp.step_stages(C.STAGE_COPY, batch=1)
-            if self.trace is not None:
-                self.trace.append((li, x_pred.clone(), x_mlp.clone(), out.clone(), sp.mask().clone()))
-            h = h + out
+            h = h + self._mlp_decode(li, x_pred.contiguous(), x_mlp)
         main.wait_stream(self._side)
         main.wait_stream(self._side2)
-        last = rms_norm(h, self.final_norm, cfg.rms_eps)
-        self.logits.copy_((last @ self.embed.t()).float().view(-1))
-        nxt = self.logits.argmax().view(1)
-        self.pos.add_(1)
-        self.token.copy_(nxt)
-        self.generated.index_copy_(0, self.pos - self.gen_base, nxt)
+        self._finish_token(rms_norm(h, self.final_norm, cfg.rms_eps))
 
     @torch.no_grad()
     def decode_step(self, use_graph: bool = True) -> None:

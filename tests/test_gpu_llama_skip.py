@@ -88,3 +88,85 @@ def test_decode_continues_prefill():
     err = (full - step).abs().max() / full.abs().max()
     assert err < 3e-2, float(err)
     m.close()
+
+
+@pytest.mark.parametrize("dtype,hd,heads,kv,pos", [(torch.float16, 128, 6, 2, 300), (torch.bfloat16, 64, 4, 4, 0),
+                                                   (torch.float32, 64, 8, 2, 77), (torch.float16, 256, 2, 1, 513),
+                                                   (torch.float16, 128, 24, 8, 3), (torch.bfloat16, 128, 24, 8, 639)])
+def test_attn_decode_matches_torch(dtype, hd, heads, kv, pos):
+    """RoPE + cache append + one-query attention in one kernel against the torch ops it replaces
+    (rotate-half RoPE in fp32, scaled_dot_product_attention in fp32 on the rounded operands)."""
+    from sparse_transformers_b200.llama_skip import LlamaSkipConfig, apply_rope, attn_decode, attn_workspace, rope_tables
+    from stxgpu import rel_err
+
+    dev, max_len = "cuda:0", 640
+    cfg = LlamaSkipConfig(heads=heads, kv_heads=kv, head_dim=hd, max_len=max_len)
+    cos, sin = rope_tables(cfg, dev)
+    g = torch.Generator(device=dev).manual_seed(pos + hd)
+    qkv = torch.randn(1, (heads + 2 * kv) * hd, generator=g, device=dev).to(dtype)
+    kc = torch.randn(kv, max_len, hd, generator=g, device=dev).to(dtype)
+    vc = torch.randn(kv, max_len, hd, generator=g, device=dev).to(dtype)
+    kc0, vc0 = kc.clone(), vc.clone()
+    p = torch.tensor([pos], dtype=torch.long, device=dev)
+    ws = attn_workspace(heads, hd, dev)
+    for _ in range(2):   # the second call finds the workspace as the first left it
+        kc.copy_(kc0)
+        vc.copy_(vc0)
+        out = attn_decode(qkv, cos, sin, p, kc, vc, torch.zeros(1, heads * hd, dtype=dtype, device=dev), heads, kv, hd, ws)
+    torch.cuda.synchronize()
+
+    q, k, v = qkv.view(-1).split([heads * hd, kv * hd, kv * hd])
+    q = apply_rope(q.view(heads, 1, hd), cos[pos:pos + 1], sin[pos:pos + 1])
+    k = apply_rope(k.view(kv, 1, hd), cos[pos:pos + 1], sin[pos:pos + 1])
+    # the cache: position pos holds the rotated key and the value, everything else is untouched
+    assert torch.equal(kc[:, pos], k[:, 0]) and torch.equal(vc[:, pos], v.view(kv, hd))
+    keep = torch.ones(max_len, dtype=torch.bool, device=dev)
+    keep[pos] = False
+    assert torch.equal(kc[:, keep], kc0[:, keep]) and torch.equal(vc[:, keep], vc0[:, keep])
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q.float().unsqueeze(0), kc[:, :pos + 1].float().unsqueeze(0), vc[:, :pos + 1].float().unsqueeze(0), enable_gqa=True)
+    ref = ref.squeeze(0).transpose(0, 1).reshape(1, heads * hd)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert rel_err(out.float().cpu().numpy(), ref.cpu().numpy()) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("with_add", [True, False])
+def test_add_rmsnorm_follows_the_reference_order(dtype, with_add):
+    from sparse_transformers_b200.llama_skip import add_rmsnorm
+
+    dev, H, eps = "cuda:0", 3072, 1e-5
+    g = torch.Generator(device=dev).manual_seed(4)
+    h = torch.randn(1, H, generator=g, device=dev).to(dtype)
+    a = torch.randn(1, H, generator=g, device=dev).to(dtype) if with_add else None
+    w = (1 + 0.1 * torch.randn(H, generator=g, device=dev)).to(dtype)
+    hs = h + a if with_add else h.clone()
+    x = hs.float()
+    ref = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)).to(dtype) * w   # LlamaSkipRMSNorm
+    hh = h.clone()
+    out = add_rmsnorm(hh, a, w, eps, torch.empty_like(h))
+    torch.cuda.synchronize()
+    assert torch.equal(hh, hs)
+    ulp = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7, torch.float32: 1e-6}[dtype]
+    assert ((out.float() - ref.float()).abs() <= 2 * ulp * ref.float().abs() + 1e-7).all()
+
+
+def test_native_glue_matches_torch_glue():
+    """The same model decoded with the library's glue kernels and with torch ops: logits agree
+    within the half-precision tolerance step after step (same prompt, eager steps)."""
+    from sparse_transformers_b200.llama_skip import LlamaSkipModel
+    from stxgpu import rel_err
+
+    prompt = torch.randint(0, 1000, (20,), generator=torch.Generator().manual_seed(2)).to("cuda:0")
+    a = LlamaSkipModel(_cfg(native_glue=True), "cuda:0", seed=7)
+    b = LlamaSkipModel(_cfg(native_glue=False), "cuda:0", seed=7)
+    a.prefill(prompt)
+    b.prefill(prompt)
+    for step in range(6):
+        b.token.copy_(a.token)   # keep both on the same token even if an argmax tie breaks differently
+        a.decode_step(use_graph=False)
+        b.decode_step(use_graph=False)
+        torch.cuda.synchronize()
+        assert rel_err(a.logits.cpu().numpy(), b.logits.cpu().numpy()) <= 2e-2, step
+    a.close()
+    b.close()
