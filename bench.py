@@ -563,7 +563,8 @@ def run_prefill(args):
 def run_llama_skip(args):
     """`--workload C2-e2e`: the Llama-3.2-3B-shaped LlamaSkip host end to end (random-init weights,
     512 random prompt ids, 128 greedy tokens): TTFT and output tokens/s as the reference's benchmark
-    defines them.  Attention, norms and lm_head are torch ops; the decode-time MLP is this library."""
+    defines them.  Prefill, the q/k/v projection and lm_head are torch ops; the decode-time MLP, norms,
+    attention and output projection are this library."""
     import torch
 
     from sparse_transformers_b200.llama_skip import LlamaSkipConfig, LlamaSkipModel
@@ -595,7 +596,7 @@ def run_llama_skip(args):
         "config": {"workload": "C2-llamaskip-3b-e2e-fp16", "layers": cfg.layers, "hidden": cfg.hidden, "intermediate": cfg.intermediate,
                    "heads": cfg.heads, "kv_heads": cfg.kv_heads, "vocab": cfg.vocab, "rope_theta": cfg.rope_theta,
                    "predictor_rank": cfg.predictor_rank, "density_target": cfg.density, "prompt_tokens": 512, "new_tokens": n_new,
-                   "decode": "one CUDA graph per token; MLP sparse (this library); attention/norms/lm_head torch",
+                   "decode": "one CUDA graph per token; sparse MLP, add+RMSNorm, RoPE+KV append+attention and the output projection are this library's kernels; q/k/v projection and lm_head are torch matmuls",
                    "prefill": "dense (torch GEMMs), as the reference does for sequences longer than one token"}}), flush=True)
 
 

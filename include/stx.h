@@ -330,13 +330,23 @@ int stx_layer_set_peer(stx_layer_t* l, stx_peer_t* peer);
  * that share a workspace must be ordered on one stream.
  * stx_add_rmsnorm: h_out = h + a (rounded to dtype; a == NULL: no add, h_out unused),
  * x_out = round(h_out * rsqrt(mean(h_out^2) + eps)) * w, the operation order of
- * LlamaSkipRMSNorm (src/models/llama/modelling_llama_skip.py:39-44).  h_out may alias h. */
+ * LlamaSkipRMSNorm (src/models/llama/modelling_llama_skip.py:39-44).  h_out may alias h;
+ * H <= 8192.                                                                               */
 int stx_attn_decode(const void* qkv, const float* cos_table, const float* sin_table, const int64_t* pos_dev, void* k_cache,
                     void* v_cache, void* out, int n_heads, int n_kv_heads, int head_dim, int64_t max_len, int dtype,
                     void* workspace, void* stream);
 int stx_attn_decode_workspace_bytes(int n_heads, int head_dim, int64_t* bytes_out);
 int stx_add_rmsnorm(const void* h, const void* a, const void* w, float eps, void* h_out, void* x_out, int64_t H, int dtype,
                     void* stream);
+/* y [N] = W [N,H] (row-major) times x, where x = h when w_norm == NULL, else
+ * x = RMSNorm(h + a) * w_norm as in stx_add_rmsnorm, computed inside the same kernel (a may be
+ * NULL).  With w_norm, h + a is also written to h_out and x to x_out when those are given;
+ * h_out must not alias h.  H <= 8192, a multiple of the 16-byte vector; fp32 accumulation,
+ * one rounding of y (NaN if a row's bulk copy did not arrive within the bounded wait).  The
+ * projection in front of which SkipDecoderLayer.forward applies its
+ * input RMSNorm (src/modeling_skip.py:235-241).                                            */
+int stx_norm_gemv(const void* h, const void* a, const void* w_norm, float eps, const void* W, void* y, void* h_out,
+                  void* x_out, int64_t H, int64_t N, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -83,6 +83,7 @@ SIGNATURES = {
     "stx_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp, _vp]),
     "stx_attn_decode_workspace_bytes": (_i32, [_i32, _i32, ctypes.POINTER(_i64)]),
     "stx_add_rmsnorm": (_i32, [_vp, _vp, _vp, ctypes.c_float, _vp, _vp, _i64, _i32, _vp]),
+    "stx_norm_gemv": (_i32, [_vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp]),
 }
 
 

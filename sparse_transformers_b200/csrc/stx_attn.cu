@@ -11,6 +11,7 @@
 //                   x = round(h * rsqrt(mean(h^2) + eps)) * w, the order of operations of
 //                   LlamaSkipRMSNorm (src/models/llama/modelling_llama_skip.py:39-44).
 #include "stx_common.cuh"
+#include "stx_tma.cuh"
 
 #include <algorithm>
 
@@ -140,6 +141,22 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict
   const int g = h / rep;
   T* kc = k_cache + static_cast<size_t>(g) * max_len * HD;
   T* vc = v_cache + static_cast<size_t>(g) * max_len * HD;
+  const int chunk = (static_cast<int>(pos) + NSP - 1) / NSP;  // cached keys per split
+  const int lo = min(sp * chunk, static_cast<int>(pos)), hi = min(lo + chunk, static_cast<int>(pos));
+  const bool own = sp == NSP - 1;   // this split also scores the token's own key
+  const T* ks = kc + static_cast<size_t>(lo) * HD;  // key j of the split is cached key lo + j
+  const T* vs = vc + static_cast<size_t>(lo) * HD;
+  const int n = hi - lo + 1;        // sc[n - 1] is the own key's slot (unused unless `own`)
+  // The first batch of keys is requested before the rotation: it depends on the position only.
+  uint32_t kw[U][KB / 4];
+  auto load_keys = [&](int j0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + NW * u;
+      if (j < n - 1) load_words<KB>(reinterpret_cast<const char*>(ks + static_cast<size_t>(j) * HD) + lane * KB, kw[u]);
+    }
+  };
+  load_keys(warp);
 
   if (tid < HD) {
     constexpr int half = HD / 2;
@@ -164,23 +181,23 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict
   __syncthreads();
 
   // ---- scores: a warp per key, lane l holds elements [l*E, l*E + E); U keys in flight per warp
-  const int chunk = (static_cast<int>(pos) + NSP - 1) / NSP;  // cached keys per split
-  const int lo = min(sp * chunk, static_cast<int>(pos)), hi = min(lo + chunk, static_cast<int>(pos));
-  const bool own = sp == NSP - 1;   // this split also scores the token's own key
-  kc += static_cast<size_t>(lo) * HD;  // from here on key j of the split is cached key lo + j
-  vc += static_cast<size_t>(lo) * HD;
-  const int n = hi - lo + 1;        // sc[n - 1] is the own key's slot (unused unless `own`)
   float qf[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) qf[e] = q_s[lane * E + e];
   float lmax = -INFINITY;
-  for (int j0 = warp; j0 < n - 1; j0 += NW * U) {
-    uint32_t kw[U][KB / 4];
+  // the first batch of values, requested before the soft-max needs anything
+  const int grp = tid / TPR, ch = tid - grp * TPR;
+  uint4 raw[4];
+  auto load_values = [&](int j0) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int j = j0 + NW * u;
-      if (j < n - 1) load_words<KB>(reinterpret_cast<const char*>(kc + static_cast<size_t>(j) * HD) + lane * KB, kw[u]);
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + NG * u;
+      if (j < n - 1) raw[u] = *reinterpret_cast<const uint4*>(vs + static_cast<size_t>(j) * HD + ch * V);
     }
+  };
+  load_values(grp);
+  for (int j0 = warp; j0 < n - 1; j0 += NW * U) {
+    if (j0 != warp) load_keys(j0);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int j = j0 + NW * u;
@@ -218,17 +235,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict
   const float denom = block_reduce<false>(lsum, red);
 
   // ---- values: thread (grp, ch) sums p_j * v_j[16-byte chunk ch] over the keys j = grp, grp + NG, ...
-  const int grp = tid / TPR, ch = tid - grp * TPR;
   float acc[V];
 #pragma unroll
   for (int v = 0; v < V; ++v) acc[v] = 0.f;
   for (int j0 = grp; j0 < n - 1; j0 += 4 * NG) {
-    uint4 raw[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + NG * u;
-      if (j < n - 1) raw[u] = *reinterpret_cast<const uint4*>(vc + static_cast<size_t>(j) * HD + ch * V);
-    }
+    if (j0 != grp) load_values(j0);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int j = j0 + NG * u;
@@ -279,16 +290,66 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict
   if (!s_last) return;
   __threadfence();
   if (tid < HD) {
+    float pm[8], pl[8], pa[8];  // all loads in flight together (at most 8 splits)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k < NSP) {
+        const float* pk = part + k * att_part_floats(HD);
+        pm[k] = __ldcg(pk + HD);
+        pl[k] = __ldcg(pk + HD + 1);
+        pa[k] = __ldcg(pk + tid);
+      }
+    }
     float M = -INFINITY;
-    for (int k = 0; k < NSP; ++k) M = fmaxf(M, __ldcg(part + k * att_part_floats(HD) + HD));
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < NSP) M = fmaxf(M, pm[k]);
     float num = 0.f, den = 0.f;
-    for (int k = 0; k < NSP; ++k) {
-      const float* pk = part + k * att_part_floats(HD);
-      const float wgt = __expf(__ldcg(pk + HD) - M);  // 0 for a split without keys (its maximum is -inf)
-      num = fmaf(wgt, __ldcg(pk + tid), num);
-      den = fmaf(wgt, __ldcg(pk + HD + 1), den);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k < NSP) {
+        const float wgt = __expf(pm[k] - M);  // 0 for a split without keys (its maximum is -inf)
+        num = fmaf(wgt, pa[k], num);
+        den = fmaf(wgt, pl[k], den);
+      }
     }
     out[static_cast<size_t>(h) * HD + tid] = DT<T>::from_f(num / den);
+  }
+}
+
+// h_out = round(h + a) (a may be null: h_out = h, nothing written unless write_h), then
+// x = round(h_out * rsqrt(mean(h_out^2) + eps)) * w.  Thread t owns elements t, t + blockDim.x, ...
+// (at most MAXPT of them, kept in registers).  `store_x(i, value)` receives x.
+constexpr int NORM_MAX_H = 8192;
+template <typename T, int MAXPT, typename StoreX>
+__device__ __forceinline__ void add_rmsnorm_block(const T* h, const T* __restrict__ a, const T* __restrict__ w, float eps,
+                                                  T* h_out, int H, float* red, StoreX store_x) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  float v[MAXPT], wv[MAXPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXPT; ++k) {
+    const int i = tid + k * nt;
+    v[k] = 0.f;
+    wv[k] = 0.f;
+    if (i < H) {
+      v[k] = DT<T>::to_f(h[i]);
+      if (a) v[k] = DT<T>::round_f(v[k] + DT<T>::to_f(a[i]));
+      wv[k] = DT<T>::to_f(w[i]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < MAXPT; ++k) {
+    const int i = tid + k * nt;
+    if (i < H && h_out) h_out[i] = DT<T>::from_f(v[k]);
+    ss = fmaf(v[k], v[k], ss);
+  }
+  const float tot = block_reduce<false>(ss, red);
+  const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
+#pragma unroll
+  for (int k = 0; k < MAXPT; ++k) {
+    const int i = tid + k * nt;
+    if (i < H) store_x(i, DT<T>::from_f(DT<T>::round_f(v[k] * inv) * wv[k]));
   }
 }
 
@@ -296,23 +357,199 @@ template <typename T>
 __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(const T* h, const T* __restrict__ a, const T* __restrict__ w,
                                                                float eps, T* h_out, T* __restrict__ x_out, int H) {
   __shared__ float red[32];
-  const int tid = threadIdx.x;
-  float ss = 0.f;
-  for (int i = tid; i < H; i += NORM_THREADS) {
-    float v = DT<T>::to_f(h[i]);
-    if (a) {
-      v = DT<T>::round_f(v + DT<T>::to_f(a[i]));
-      h_out[i] = DT<T>::from_f(v);
+  add_rmsnorm_block<T, NORM_MAX_H / NORM_THREADS>(h, a, w, eps, a ? h_out : nullptr, H, red, [&](int i, T x) { x_out[i] = x; });
+}
+
+// y[n] = W[n,:] . x for a row-major W [N,H], with x either given (w_norm == null: x = h) or made
+// on the fly as x = RMSNorm(h + a) * w_norm in every CTA (the vector is a few KB; recomputing it
+// costs less than a kernel boundary).  CTA 0 also writes h + a to h_out and x to x_out (either
+// may be null).  h_out must not alias h: other CTAs still read h.  A warp per output row, 16-byte
+// loads, two batches of eight per lane in flight, the first of them while the norm is computed.
+constexpr int GEMV_THREADS = 512;
+constexpr int GEMV_BATCH = 8;  // 16-byte loads per lane and item
+template <typename T>
+__global__ void __launch_bounds__(GEMV_THREADS) k_norm_gemv(const T* __restrict__ h, const T* __restrict__ a,
+                                                             const T* __restrict__ w_norm, float eps,
+                                                             const T* __restrict__ W, T* __restrict__ y, T* h_out,
+                                                             T* x_out, int H, int N) {
+  constexpr int V = DT<T>::V;
+  extern __shared__ __align__(16) unsigned char gsm[];
+  T* x_s = reinterpret_cast<T*>(gsm);
+  __shared__ float red[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nchunk = H / V;
+  const int wpg = (GEMV_THREADS / 32) * gridDim.x;  // warps in the grid
+  const int row0 = blockIdx.x * (GEMV_THREADS / 32) + warp;
+  // A warp's work is a sequence of items: item it = (its row number it / nb, batch it % nb of that
+  // row), a batch being GEMV_BATCH x 32 consecutive 16-byte chunks.  Two items are in flight.
+  const int nb = (nchunk + 32 * GEMV_BATCH - 1) / (32 * GEMV_BATCH);
+  const int nrows = row0 < N ? (N - 1 - row0) / wpg + 1 : 0;
+  const int nitems = nrows * nb;
+  auto load_item = [&](int it, uint4 (&buf)[GEMV_BATCH]) {
+    const int r = it / nb, bi = it - r * nb;
+    const uint4* wr = reinterpret_cast<const uint4*>(W + static_cast<size_t>(row0 + r * wpg) * H) + bi * 32 * GEMV_BATCH + lane;
+    const int left = nchunk - bi * 32 * GEMV_BATCH - lane;
+#pragma unroll
+    for (int i = 0; i < GEMV_BATCH; ++i)
+      if (32 * i < left) buf[i] = ld_stream16(wr + 32 * i);
+  };
+  float acc0 = 0.f, acc1 = 0.f;
+  auto compute_item = [&](int it, const uint4 (&buf)[GEMV_BATCH]) {
+    const int r = it / nb, bi = it - r * nb;
+    const uint4* xs = reinterpret_cast<const uint4*>(x_s) + bi * 32 * GEMV_BATCH + lane;
+    const int left = nchunk - bi * 32 * GEMV_BATCH - lane;
+#pragma unroll
+    for (int i = 0; i < GEMV_BATCH; ++i) {
+      if (32 * i < left) {
+        float wf[V], xf[V];
+        Unpack<T>::run(buf[i], wf);
+        Unpack<T>::run(xs[32 * i], xf);
+        float t = 0.f;
+#pragma unroll
+        for (int v = 0; v < V; ++v) t = fmaf(xf[v], wf[v], t);
+        if (i & 1) acc1 += t; else acc0 += t;
+      }
     }
-    ss = fmaf(v, v, ss);
+    if (bi == nb - 1) {  // the row is complete
+      const float dot = warp_sum_xor(acc0 + acc1);
+      if (lane == 0) y[row0 + r * wpg] = DT<T>::from_f(dot);
+      acc0 = 0.f;
+      acc1 = 0.f;
+    }
+  };
+  uint4 bufa[GEMV_BATCH], bufb[GEMV_BATCH];
+  if (nitems > 0) load_item(0, bufa);  // in flight while the norm is computed
+  if (w_norm) {
+    const bool first = blockIdx.x == 0;
+    add_rmsnorm_block<T, NORM_MAX_H / GEMV_THREADS>(h, a, w_norm, eps, first ? h_out : nullptr, H, red, [&](int i, T x) {
+      x_s[i] = x;
+      if (first && x_out) x_out[i] = x;
+    });
+  } else {
+    for (int i = tid; i < nchunk; i += GEMV_THREADS) reinterpret_cast<uint4*>(x_s)[i] = reinterpret_cast<const uint4*>(h)[i];
   }
-  const float tot = block_reduce<false>(ss, red);
-  const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
-  const T* src = a ? h_out : h;  // a thread re-reads only what it wrote itself
-  for (int i = tid; i < H; i += NORM_THREADS) {
-    const float nv = DT<T>::round_f(DT<T>::to_f(src[i]) * inv);
-    x_out[i] = DT<T>::from_f(nv * DT<T>::to_f(w[i]));
+  __syncthreads();
+  for (int it = 0; it < nitems; it += 2) {
+    if (it + 1 < nitems) load_item(it + 1, bufb);
+    compute_item(it, bufa);
+    if (it + 2 < nitems) load_item(it + 2, bufa);
+    if (it + 1 < nitems) compute_item(it + 1, bufb);
   }
+}
+
+// The same product when the CTA's share of W fits in shared memory (N * H elements over one CTA
+// per SM, e.g. a 5120 x 3072 fp16 projection: 35 rows, 215 KB): every row is requested by a bulk
+// copy before anything else happens, so the whole matrix is in flight while the norm is
+// computed, and each warp then reads its rows from shared memory.
+// Dynamic shared memory: [0,128) one mbarrier per warp | x_s [H] | rows [rows_per_cta][H].
+template <typename T>
+__global__ void __launch_bounds__(GEMV_THREADS) k_norm_gemv_tma(const T* __restrict__ h, const T* __restrict__ a,
+                                                                 const T* __restrict__ w_norm, float eps,
+                                                                 const T* __restrict__ W, T* __restrict__ y, T* h_out,
+                                                                 T* x_out, int H, int N, int rows_per_cta) {
+  constexpr int V = DT<T>::V;
+  constexpr int NW = GEMV_THREADS / 32;
+  extern __shared__ __align__(128) unsigned char gsm[];
+  __shared__ float red[32];
+  uint64_t* bar = reinterpret_cast<uint64_t*>(gsm);
+  T* x_s = reinterpret_cast<T*>(gsm + 128);
+  const size_t row_bytes = static_cast<size_t>(H) * sizeof(T);
+  unsigned char* rows = gsm + 128 + (row_bytes + 127) / 128 * 128;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nchunk = H / V;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int nr = max(0, min(rows_per_cta, N - r0));
+  const int mine = warp < nr ? (nr - 1 - warp) / NW + 1 : 0;  // local rows warp, warp + NW, ...
+  if (tid == 0) {
+    for (int w = 0; w < NW; ++w) mbar_init(&bar[w], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (mine > 0) {
+    if (lane == 0) mbar_expect_tx(&bar[warp], static_cast<uint32_t>(mine * row_bytes));
+    __syncwarp();
+    for (int k = lane; k < mine; k += 32) {
+      const int lr = warp + k * NW;
+      bulk_load(rows + static_cast<size_t>(lr) * row_bytes, W + static_cast<size_t>(r0 + lr) * H, static_cast<uint32_t>(row_bytes),
+                &bar[warp]);
+    }
+  }
+  if (w_norm) {
+    const bool first = blockIdx.x == 0;
+    add_rmsnorm_block<T, NORM_MAX_H / GEMV_THREADS>(h, a, w_norm, eps, first ? h_out : nullptr, H, red, [&](int i, T x) {
+      x_s[i] = x;
+      if (first && x_out) x_out[i] = x;
+    });
+  } else {
+    for (int i = tid; i < nchunk; i += GEMV_THREADS) reinterpret_cast<uint4*>(x_s)[i] = reinterpret_cast<const uint4*>(h)[i];
+  }
+  __syncthreads();
+  if (mine == 0) return;
+  const bool ok = mbar_wait_bounded(&bar[warp], 0);
+  for (int k = 0; k < mine; ++k) {
+    const int lr = warp + k * NW;
+    const uint4* wr = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(lr) * row_bytes);
+    float acc0 = 0.f, acc1 = 0.f;
+    int c = lane;
+    for (; c + 32 < nchunk; c += 64) {
+      float w0[V], w1[V], x0[V], x1[V];
+      Unpack<T>::run(wr[c], w0);
+      Unpack<T>::run(wr[c + 32], w1);
+      Unpack<T>::run(reinterpret_cast<const uint4*>(x_s)[c], x0);
+      Unpack<T>::run(reinterpret_cast<const uint4*>(x_s)[c + 32], x1);
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        acc0 = fmaf(x0[v], w0[v], acc0);
+        acc1 = fmaf(x1[v], w1[v], acc1);
+      }
+    }
+    for (; c < nchunk; c += 32) {
+      float w0[V], x0[V];
+      Unpack<T>::run(wr[c], w0);
+      Unpack<T>::run(reinterpret_cast<const uint4*>(x_s)[c], x0);
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc0 = fmaf(x0[v], w0[v], acc0);
+    }
+    const float dot = warp_sum_xor(acc0 + acc1);
+    // a copy that did not arrive within the wait limit must not pass for a result
+    if (lane == 0) y[r0 + lr] = DT<T>::from_f(ok ? dot : __int_as_float(0x7fc00000));
+  }
+}
+
+template <typename T>
+static int launch_norm_gemv(const void* h, const void* a, const void* w_norm, float eps, const void* W, void* y, void* h_out,
+                            void* x_out, int H, int N, cudaStream_t s) {
+  const int warps = GEMV_THREADS / 32;
+  const int sms = num_sms();
+  // A CTA of this size needs an SM to itself; a few SMs are left to kernels that run beside it on
+  // other streams (the weight cache's upkeep), or one CTA would wait for a second wave.
+  const int target = std::max(1, sms - 4);
+  const int rows_per_cta = (N + target - 1) / target;
+  const size_t row_bytes = static_cast<size_t>(H) * sizeof(T);
+  const size_t smem_tma = 128 + (row_bytes + 127) / 128 * 128 + static_cast<size_t>(rows_per_cta) * row_bytes;
+  const size_t budget = 227 * 1024 - 1024;  // per-block limit less the kernel's static shared memory
+  if (smem_tma <= budget) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      STX_CUDA(cudaFuncSetAttribute(k_norm_gemv_tma<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(budget)));
+      attr_set[dev] = true;
+    }
+    const unsigned grid = static_cast<unsigned>((N + rows_per_cta - 1) / rows_per_cta);
+    k_norm_gemv_tma<T><<<grid, GEMV_THREADS, smem_tma, s>>>(static_cast<const T*>(h), static_cast<const T*>(a),
+                                                            static_cast<const T*>(w_norm), eps, static_cast<const T*>(W),
+                                                            static_cast<T*>(y), static_cast<T*>(h_out), static_cast<T*>(x_out), H,
+                                                            N, rows_per_cta);
+  } else {
+    const int want = (N + warps - 1) / warps;
+    const unsigned grid = static_cast<unsigned>(std::min(want, sms));  // one CTA per SM: the norm is made once per CTA
+    k_norm_gemv<T><<<grid, GEMV_THREADS, row_bytes, s>>>(static_cast<const T*>(h), static_cast<const T*>(a),
+                                                         static_cast<const T*>(w_norm), eps, static_cast<const T*>(W),
+                                                         static_cast<T*>(y), static_cast<T*>(h_out), static_cast<T*>(x_out), H, N);
+  }
+  STX_LAUNCH_CHECK("k_norm_gemv");
+  return STX_OK;
 }
 
 // Splits of the keys per head: enough CTAs to cover the SMs once, at most 8.
@@ -381,7 +618,7 @@ int stx_add_rmsnorm(const void* h, const void* a, const void* w, float eps, void
   STX_CHECK_ARG(h && w && x_out, "stx_add_rmsnorm: null pointer");
   STX_CHECK_ARG(!a || h_out, "stx_add_rmsnorm: h_out is required when a is given");
   STX_CHECK_ARG(dtype == STX_F32 || dtype == STX_F16 || dtype == STX_BF16, "stx_add_rmsnorm: bad dtype %d", dtype);
-  STX_CHECK_ARG(H > 0 && H <= (1 << 20), "stx_add_rmsnorm: H=%lld out of range", static_cast<long long>(H));
+  STX_CHECK_ARG(H > 0 && H <= NORM_MAX_H, "stx_add_rmsnorm: H=%lld outside 1..%d", static_cast<long long>(H), NORM_MAX_H);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int Hi = static_cast<int>(H);
   switch (dtype) {
@@ -403,6 +640,25 @@ int stx_add_rmsnorm(const void* h, const void* a, const void* w, float eps, void
   }
   STX_LAUNCH_CHECK("k_add_rmsnorm");
   return STX_OK;
+}
+
+int stx_norm_gemv(const void* h, const void* a, const void* w_norm, float eps, const void* W, void* y, void* h_out,
+                  void* x_out, int64_t H, int64_t N, int dtype, void* stream) {
+  STX_CHECK_ARG(h && W && y, "stx_norm_gemv: null pointer");
+  STX_CHECK_ARG(w_norm || (!a && !h_out && !x_out), "stx_norm_gemv: a, h_out and x_out need w_norm");
+  STX_CHECK_ARG(!h_out || h_out != h, "stx_norm_gemv: h_out must not alias h");
+  STX_CHECK_ARG(dtype == STX_F32 || dtype == STX_F16 || dtype == STX_BF16, "stx_norm_gemv: bad dtype %d", dtype);
+  const int64_t V = 16 / static_cast<int64_t>(dtype_size(dtype));
+  STX_CHECK_ARG(H > 0 && H <= NORM_MAX_H && H % V == 0, "stx_norm_gemv: H=%lld must be a multiple of %lld, at most %d",
+                static_cast<long long>(H), static_cast<long long>(V), NORM_MAX_H);
+  STX_CHECK_ARG(N > 0 && N <= (1 << 30), "stx_norm_gemv: N=%lld out of range", static_cast<long long>(N));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int Hi = static_cast<int>(H), Ni = static_cast<int>(N);
+  switch (dtype) {
+    case STX_F32: return launch_norm_gemv<float>(h, a, w_norm, eps, W, y, h_out, x_out, Hi, Ni, s);
+    case STX_F16: return launch_norm_gemv<__half>(h, a, w_norm, eps, W, y, h_out, x_out, Hi, Ni, s);
+    default: return launch_norm_gemv<__nv_bfloat16>(h, a, w_norm, eps, W, y, h_out, x_out, Hi, Ni, s);
+  }
 }
 
 }  // extern "C"

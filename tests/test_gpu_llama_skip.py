@@ -151,14 +151,15 @@ def test_add_rmsnorm_follows_the_reference_order(dtype, with_add):
     assert ((out.float() - ref.float()).abs() <= 2 * ulp * ref.float().abs() + 1e-7).all()
 
 
-def test_native_glue_matches_torch_glue():
+@pytest.mark.parametrize("own_qkv,own_wo", [(False, True), (True, True), (True, False), (False, False)])
+def test_native_glue_matches_torch_glue(own_qkv, own_wo):
     """The same model decoded with the library's glue kernels and with torch ops: logits agree
     within the half-precision tolerance step after step (same prompt, eager steps)."""
     from sparse_transformers_b200.llama_skip import LlamaSkipModel
     from stxgpu import rel_err
 
     prompt = torch.randint(0, 1000, (20,), generator=torch.Generator().manual_seed(2)).to("cuda:0")
-    a = LlamaSkipModel(_cfg(native_glue=True), "cuda:0", seed=7)
+    a = LlamaSkipModel(_cfg(native_glue=True, own_qkv=own_qkv, own_wo=own_wo), "cuda:0", seed=7)
     b = LlamaSkipModel(_cfg(native_glue=False), "cuda:0", seed=7)
     a.prefill(prompt)
     b.prefill(prompt)
@@ -170,3 +171,36 @@ def test_native_glue_matches_torch_glue():
         assert rel_err(a.logits.cpu().numpy(), b.logits.cpu().numpy()) <= 2e-2, step
     a.close()
     b.close()
+
+
+@pytest.mark.parametrize("dtype,H,N,mode", [(torch.float16, 3072, 5120, "norm+add"), (torch.bfloat16, 512, 200, "norm"),
+                                            (torch.float32, 1024, 333, "norm+add"), (torch.float16, 3072, 3072, "plain"),
+                                            (torch.bfloat16, 8192, 64, "norm+add"),
+                                            # a share of W larger than shared memory: the register-pipelined kernel
+                                            (torch.float16, 3072, 6000, "norm+add"), (torch.float32, 2048, 4500, "plain")])
+def test_norm_gemv_matches_add_rmsnorm_then_matmul(dtype, H, N, mode):
+    from sparse_transformers_b200.llama_skip import add_rmsnorm, norm_gemv
+    from stxgpu import rel_err
+
+    dev, eps = "cuda:0", 1e-5
+    g = torch.Generator(device=dev).manual_seed(H + N)
+    h = torch.randn(1, H, generator=g, device=dev).to(dtype)
+    a = torch.randn(1, H, generator=g, device=dev).to(dtype) if mode == "norm+add" else None
+    w = (1 + 0.1 * torch.randn(H, generator=g, device=dev)).to(dtype) if mode != "plain" else None
+    W = (torch.randn(N, H, generator=g, device=dev) * 0.02).to(dtype)
+    if mode == "plain":
+        y = norm_gemv(h, None, None, 0.0, W)
+        ref = h.float() @ W.float().t()
+    else:
+        h_out, x_out = torch.empty_like(h), torch.empty_like(h)
+        y = norm_gemv(h, a, w, eps, W, h_out=h_out, x_out=x_out)
+        h2 = h.clone()
+        x_ref = add_rmsnorm(h2, a, w, eps, torch.empty_like(h))
+        torch.cuda.synchronize()
+        assert torch.equal(h_out, h2)
+        ulp = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7, torch.float32: 1e-6}[dtype]
+        # same arithmetic as the stand-alone kernel up to the order of the sum of squares
+        assert ((x_out.float() - x_ref.float()).abs() <= 2 * ulp * x_ref.float().abs() + 1e-7).all()
+        ref = x_ref.float() @ W.float().t()
+    torch.cuda.synchronize()
+    assert rel_err(y.float().cpu().numpy(), ref.cpu().numpy()) <= (1e-5 if dtype == torch.float32 else 4e-3)
