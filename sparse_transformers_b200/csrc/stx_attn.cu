@@ -321,36 +321,53 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict
 // x = round(h_out * rsqrt(mean(h_out^2) + eps)) * w.  Thread t owns elements t, t + blockDim.x, ...
 // (at most MAXPT of them, kept in registers).  `store_x(i, value)` receives x.
 constexpr int NORM_MAX_H = 8192;
-template <typename T, int MAXPT, typename StoreX>
-__device__ __forceinline__ void add_rmsnorm_block(const T* h, const T* __restrict__ a, const T* __restrict__ w, float eps,
-                                                  T* h_out, int H, float* red, StoreX store_x) {
-  const int tid = threadIdx.x, nt = blockDim.x;
+template <int MAXPT> struct NormRegs {
   float v[MAXPT], wv[MAXPT];
+};
+// Part 1: the loads (and the add).  Kernels that also stream bulk copies call this BEFORE they
+// request the copies: small loads issued behind hundreds of KB of bulk traffic of the same SM
+// come back only when that traffic has drained.
+template <typename T, int MAXPT>
+__device__ __forceinline__ void norm_load(const T* h, const T* __restrict__ a, const T* __restrict__ w, int H,
+                                          NormRegs<MAXPT>& r) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+#pragma unroll
+  for (int k = 0; k < MAXPT; ++k) {
+    const int i = tid + k * nt;
+    r.v[k] = 0.f;
+    r.wv[k] = 0.f;
+    if (i < H) {
+      r.v[k] = DT<T>::to_f(h[i]);
+      if (a) r.v[k] = DT<T>::round_f(r.v[k] + DT<T>::to_f(a[i]));
+      r.wv[k] = DT<T>::to_f(w[i]);
+    }
+  }
+}
+// Part 2: h_out, the sum of squares, x.
+template <typename T, int MAXPT, typename StoreX>
+__device__ __forceinline__ void norm_finish(const NormRegs<MAXPT>& r, float eps, T* h_out, int H, float* red, StoreX store_x) {
+  const int tid = threadIdx.x, nt = blockDim.x;
   float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < MAXPT; ++k) {
     const int i = tid + k * nt;
-    v[k] = 0.f;
-    wv[k] = 0.f;
-    if (i < H) {
-      v[k] = DT<T>::to_f(h[i]);
-      if (a) v[k] = DT<T>::round_f(v[k] + DT<T>::to_f(a[i]));
-      wv[k] = DT<T>::to_f(w[i]);
-    }
-  }
-#pragma unroll
-  for (int k = 0; k < MAXPT; ++k) {
-    const int i = tid + k * nt;
-    if (i < H && h_out) h_out[i] = DT<T>::from_f(v[k]);
-    ss = fmaf(v[k], v[k], ss);
+    if (i < H && h_out) h_out[i] = DT<T>::from_f(r.v[k]);
+    ss = fmaf(r.v[k], r.v[k], ss);
   }
   const float tot = block_reduce<false>(ss, red);
   const float inv = rsqrtf(tot / static_cast<float>(H) + eps);
 #pragma unroll
   for (int k = 0; k < MAXPT; ++k) {
     const int i = tid + k * nt;
-    if (i < H) store_x(i, DT<T>::from_f(DT<T>::round_f(v[k] * inv) * wv[k]));
+    if (i < H) store_x(i, DT<T>::from_f(DT<T>::round_f(r.v[k] * inv) * r.wv[k]));
   }
+}
+template <typename T, int MAXPT, typename StoreX>
+__device__ __forceinline__ void add_rmsnorm_block(const T* h, const T* __restrict__ a, const T* __restrict__ w, float eps,
+                                                  T* h_out, int H, float* red, StoreX store_x) {
+  NormRegs<MAXPT> r;
+  norm_load<T, MAXPT>(h, a, w, H, r);
+  norm_finish<T, MAXPT>(r, eps, h_out, H, red, store_x);
 }
 
 template <typename T>
@@ -465,6 +482,17 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_norm_gemv_tma(const T* __restr
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // the small loads of the prologue go first: behind the bulk copies they would come back last
+  constexpr int MAXPT = NORM_MAX_H / GEMV_THREADS;
+  NormRegs<MAXPT> nr_regs;
+  uint4 xr[MAXPT / 4 + 1];
+  if (w_norm) {
+    norm_load<T, MAXPT>(h, a, w_norm, H, nr_regs);
+  } else {
+#pragma unroll
+    for (int k = 0; k < MAXPT / 4 + 1; ++k)
+      if (tid + k * GEMV_THREADS < nchunk) xr[k] = reinterpret_cast<const uint4*>(h)[tid + k * GEMV_THREADS];
+  }
   if (mine > 0) {
     if (lane == 0) mbar_expect_tx(&bar[warp], static_cast<uint32_t>(mine * row_bytes));
     __syncwarp();
@@ -476,12 +504,14 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_norm_gemv_tma(const T* __restr
   }
   if (w_norm) {
     const bool first = blockIdx.x == 0;
-    add_rmsnorm_block<T, NORM_MAX_H / GEMV_THREADS>(h, a, w_norm, eps, first ? h_out : nullptr, H, red, [&](int i, T x) {
+    norm_finish<T, MAXPT>(nr_regs, eps, first ? h_out : nullptr, H, red, [&](int i, T x) {
       x_s[i] = x;
       if (first && x_out) x_out[i] = x;
     });
   } else {
-    for (int i = tid; i < nchunk; i += GEMV_THREADS) reinterpret_cast<uint4*>(x_s)[i] = reinterpret_cast<const uint4*>(h)[i];
+#pragma unroll
+    for (int k = 0; k < MAXPT / 4 + 1; ++k)
+      if (tid + k * GEMV_THREADS < nchunk) reinterpret_cast<uint4*>(x_s)[tid + k * GEMV_THREADS] = xr[k];
   }
   __syncthreads();
   if (mine == 0) return;

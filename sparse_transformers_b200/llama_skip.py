@@ -53,7 +53,7 @@ class LlamaSkipConfig:
     # decode projections: the output projection runs through stx_norm_gemv (measured 6 % more tokens/s than the
     # torch matmul at the 3B shape); add + RMSNorm + q/k/v projection as ONE stx_norm_gemv is available but
     # measured 7 % slower there than stx_add_rmsnorm followed by the torch matmul, so it is off by default
-    own_qkv: bool = False
+    qkv_proj: str = "torch"        # "torch" | "gemv" (stx_add_rmsnorm, then stx_norm_gemv without norm) | "fused"
     own_wo: bool = True
 
     @property
@@ -245,9 +245,11 @@ class LlamaSkipModel:
         for li, L in enumerate(self.layers):
             # residual add + input RMSNorm + q/k/v projection in one kernel; x_pred is the predictor's input
             x_pred = torch.empty_like(h)
-            if cfg.own_qkv:
+            if cfg.qkv_proj == "fused":
                 qkv = norm_gemv(h, pending, L["ln1"], cfg.rms_eps, L["wqkv"], h_out=h_next, x_out=x_pred)
                 h, h_next = h_next, h
+            elif cfg.qkv_proj == "gemv":
+                qkv = norm_gemv(add_rmsnorm(h, pending, L["ln1"], cfg.rms_eps, x_pred), None, None, 0.0, L["wqkv"])
             else:
                 qkv = add_rmsnorm(h, pending, L["ln1"], cfg.rms_eps, x_pred) @ L["wqkv"].t()
             o = attn_decode(qkv, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li],

@@ -151,15 +151,15 @@ def test_add_rmsnorm_follows_the_reference_order(dtype, with_add):
     assert ((out.float() - ref.float()).abs() <= 2 * ulp * ref.float().abs() + 1e-7).all()
 
 
-@pytest.mark.parametrize("own_qkv,own_wo", [(False, True), (True, True), (True, False), (False, False)])
-def test_native_glue_matches_torch_glue(own_qkv, own_wo):
+@pytest.mark.parametrize("qkv_proj,own_wo", [("torch", True), ("fused", True), ("gemv", False), ("torch", False)])
+def test_native_glue_matches_torch_glue(qkv_proj, own_wo):
     """The same model decoded with the library's glue kernels and with torch ops: logits agree
     within the half-precision tolerance step after step (same prompt, eager steps)."""
     from sparse_transformers_b200.llama_skip import LlamaSkipModel
     from stxgpu import rel_err
 
     prompt = torch.randint(0, 1000, (20,), generator=torch.Generator().manual_seed(2)).to("cuda:0")
-    a = LlamaSkipModel(_cfg(native_glue=True, own_qkv=own_qkv, own_wo=own_wo), "cuda:0", seed=7)
+    a = LlamaSkipModel(_cfg(native_glue=True, qkv_proj=qkv_proj, own_wo=own_wo), "cuda:0", seed=7)
     b = LlamaSkipModel(_cfg(native_glue=False), "cuda:0", seed=7)
     a.prefill(prompt)
     b.prefill(prompt)
