@@ -14,8 +14,14 @@
 #include "stx_tma.cuh"
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include <cooperative_groups.h>
 
 namespace stx {
+
+namespace cg = cooperative_groups;
 
 constexpr int ATT_THREADS = 512;
 constexpr int NORM_THREADS = 1024;
@@ -109,10 +115,12 @@ constexpr size_t ATT_COUNTER_BYTES = 4096;  // up to 1024 heads
 __host__ __device__ inline int att_part_floats(int hd) { return hd + 2; }
 
 // Grid (heads, splits): split s of a head takes an equal share of the cached keys (the last split
-// also the token's own key), so that one query head is read by several SMs; the split that
-// arrives last at the head's counter merges the partial soft-maxes.
+// also the token's own key), so that one query head is read by several SMs.  CL: the splits of a
+// head form a thread-block cluster and split 0 merges the partial soft-maxes out of the others'
+// shared memory; otherwise they meet in the workspace and the split that arrives last at the
+// head's counter merges (a store, a fence, an atomic and a load more on the critical path).
 // Shared memory (floats): q_s[HD] | kn_s[HD] | vn_s[HD] | red[32] | acc_s[NG][HD] | sc[keys of the split + 1]
-template <typename T, int HD>
+template <typename T, int HD, bool CL>
 __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict__ qkv, const float* __restrict__ cos_t,
                                                               const float* __restrict__ sin_t,
                                                               const long long* __restrict__ pos_dev, T* k_cache, T* v_cache,
@@ -260,6 +268,49 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn_decode(const T* __restrict
 #pragma unroll
   for (int v = 0; v < V; ++v) acc_s[grp * HD + ch * V + v] = acc[v];
   __syncthreads();
+  if constexpr (CL) {
+    // this split's unnormalised sum, maximum and sum of exponentials, where the cluster can read them
+    if (tid < HD) {
+      float s = 0.f;
+      for (int k = 0; k < NG; ++k) s += acc_s[k * HD + tid];
+      q_s[tid] = s;  // the query is not needed any more
+    }
+    if (tid == 0) {
+      red[0] = m;
+      red[1] = denom;
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (sp == 0 && tid < HD) {
+      float pm[8], pl[8], pa[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (k < NSP) {
+          const float* rq = cluster.map_shared_rank(q_s, k);
+          const float* rr = cluster.map_shared_rank(red, k);
+          pm[k] = rr[0];
+          pl[k] = rr[1];
+          pa[k] = rq[tid];
+        }
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k < NSP) M = fmaxf(M, pm[k]);
+      float num = 0.f, den = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (k < NSP) {
+          const float wgt = __expf(pm[k] - M);  // 0 for a split without keys (its maximum is -inf)
+          num = fmaf(wgt, pa[k], num);
+          den = fmaf(wgt, pl[k], den);
+        }
+      }
+      out[static_cast<size_t>(h) * HD + tid] = DT<T>::from_f(num / den);
+    }
+    cluster.sync();  // nobody leaves while split 0 may still read its shared memory
+    return;
+  }
   int* counter = reinterpret_cast<int*>(workspace) + h;
   float* part = reinterpret_cast<float*>(workspace + ATT_COUNTER_BYTES) + static_cast<size_t>(h) * NSP * att_part_floats(HD);
   float* mine = part + static_cast<size_t>(sp) * att_part_floats(HD);
@@ -390,7 +441,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_norm_gemv(const T* __restrict_
                                                              const T* __restrict__ W, T* __restrict__ y, T* h_out,
                                                              T* x_out, int H, int N) {
   constexpr int V = DT<T>::V;
-  extern __shared__ __align__(16) unsigned char gsm[];
+  extern __shared__ __align__(128) unsigned char gsm[];
   T* x_s = reinterpret_cast<T*>(gsm);
   __shared__ float red[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -618,13 +669,35 @@ int stx_attn_decode(const void* qkv, const float* cos_table, const float* sin_ta
   const float scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   const long long* pos = reinterpret_cast<const long long*>(pos_dev);
   const long long ml = max_len;
-#define STX_ATT_LAUNCH(T, HD)                                                                                              \
+  static int use_cluster = -1;  // STX_ATTN_MERGE=cluster selects the merge through distributed shared memory
+  if (use_cluster < 0) {
+    const char* e = getenv("STX_ATTN_MERGE");
+    use_cluster = (e && !strcmp(e, "cluster")) ? 1 : 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_heads, nsp, 1);
+  cfg.blockDim = dim3(ATT_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = static_cast<unsigned>(nsp);
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (use_cluster && nsp > 1) ? 1 : 0;
+#define STX_ATT_LAUNCH_CL(T, HD, CL)                                                                                       \
   do {                                                                                                                     \
     if (smem > 48 * 1024)                                                                                                  \
-      STX_CUDA(cudaFuncSetAttribute(k_attn_decode<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));        \
-    k_attn_decode<T, HD><<<dim3(n_heads, nsp), ATT_THREADS, smem, s>>>(                                                   \
-        static_cast<const T*>(qkv), cos_table, sin_table, pos, static_cast<T*>(k_cache), static_cast<T*>(v_cache),         \
-        static_cast<T*>(out), n_heads, n_kv_heads, ml, scale, static_cast<unsigned char*>(workspace));                     \
+      STX_CUDA(cudaFuncSetAttribute(k_attn_decode<T, HD, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));    \
+    STX_CUDA(cudaLaunchKernelEx(&cfg, k_attn_decode<T, HD, CL>, static_cast<const T*>(qkv), cos_table, sin_table, pos,     \
+                                static_cast<T*>(k_cache), static_cast<T*>(v_cache), static_cast<T*>(out), n_heads,         \
+                                n_kv_heads, ml, scale, static_cast<unsigned char*>(workspace)));                           \
+  } while (0)
+#define STX_ATT_LAUNCH(T, HD)                                   \
+  do {                                                          \
+    if (cfg.numAttrs) STX_ATT_LAUNCH_CL(T, HD, true);           \
+    else STX_ATT_LAUNCH_CL(T, HD, false);                       \
   } while (0)
 #define STX_ATT_HD(T)                       \
   do {                                      \
@@ -639,6 +712,7 @@ int stx_attn_decode(const void* qkv, const float* cos_table, const float* sin_ta
   }
 #undef STX_ATT_HD
 #undef STX_ATT_LAUNCH
+#undef STX_ATT_LAUNCH_CL
   STX_LAUNCH_CHECK("k_attn_decode");
   return STX_OK;
 }
