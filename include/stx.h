@@ -326,8 +326,9 @@ int stx_layer_set_peer(stx_layer_t* l, stx_peer_t* peer);
  * out [n_heads * head_dim].  head_dim 64, 128 or 256; max_len <= 8192.  A position outside
  * 0..max_len-1 leaves everything untouched.  workspace: device memory of
  * stx_attn_decode_workspace_bytes bytes, zeroed once by the caller and then owned by the calls
- * (the keys of a head are split over several CTAs, whose partial results meet there); calls
- * that share a workspace must be ordered on one stream.
+ * (the keys of a head are split over several CTAs; their partial results meet in shared
+ * memory of the CTAs' cluster, or in the workspace with STX_ATTN_MERGE=workspace in the
+ * environment); calls that share a workspace must be ordered on one stream.
  * stx_add_rmsnorm: h_out = h + a (rounded to dtype; a == NULL: no add, h_out unused),
  * x_out = round(h_out * rsqrt(mean(h_out^2) + eps)) * w, the operation order of
  * LlamaSkipRMSNorm (src/models/llama/modelling_llama_skip.py:39-44).  h_out may alias h;

@@ -669,10 +669,10 @@ int stx_attn_decode(const void* qkv, const float* cos_table, const float* sin_ta
   const float scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   const long long* pos = reinterpret_cast<const long long*>(pos_dev);
   const long long ml = max_len;
-  static int use_cluster = -1;  // STX_ATTN_MERGE=cluster selects the merge through distributed shared memory
+  static int use_cluster = -1;  // STX_ATTN_MERGE=workspace selects the merge through global memory (A/B measurements)
   if (use_cluster < 0) {
     const char* e = getenv("STX_ATTN_MERGE");
-    use_cluster = (e && !strcmp(e, "cluster")) ? 1 : 0;
+    use_cluster = (e && !strcmp(e, "workspace")) ? 0 : 1;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_heads, nsp, 1);
