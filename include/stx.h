@@ -185,7 +185,9 @@ int stx_mlp_scratch_bytes(int64_t B, int64_t H, int64_t K, size_t* bytes_out);
  * down_buf [B,H]: the result.  scratch: stx_mlp_scratch_bytes() bytes, 16-byte aligned,
  * ZERO on the first call; its leading (256 + 4*B*H rounded up to 256) bytes are an fp32
  * accumulator and a counter that every call leaves zeroed again, the rest holds the
- * fp32 activations a[K][B] between the two kernels.  Row blocks of 9 and more in
+ * fp32 activations a[K][B] between the two kernels.  The extent of that leading region
+ * depends on B and H: a buffer that is reused for a call with a different B or H must have
+ * the new call's leading region zeroed again first (cudaMemsetAsync on the same stream).  Row blocks of 9 and more in
  * fp16/bf16 (prefill) run as two tcgen05 tensor-core GEMMs instead and keep their
  * activation matrix and a transposed copy of the down rows behind those regions.         */
 int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* concat_w,
@@ -229,8 +231,10 @@ int stx_layer_step(stx_layer_t* l, const void* x_pred, const void* x_mlp, int64_
  * MLP_GATEUP as ONE kernel when both bits are set (the mask never leaves the chip before
  * the rows are fetched); MLP_DOWN is then the deterministic sum of that kernel's per-CTA
  * partial outputs.  9 rows and more (16-bit, gated) run the MLP stage as tensor-core
- * GEMMs over the packed cache and bring the cache up to date first if PLAN / COPY have
- * not run yet in this step.                                                             */
+ * GEMMs over the packed cache; for such a row block the MLP stage owns the cache upkeep:
+ * it runs the index plan and the row copies itself, on its own stream, and a call that
+ * names PLAN and/or COPY without MLP does nothing (so upkeep issued on a side stream can
+ * never run concurrently with the upkeep of the MLP stage).                             */
 #define STX_STAGE_PREDICT_T 1u     /* predictor, first half: t = A x            */
 #define STX_STAGE_PREDICT_MASK 32u /* predictor, second half: scores -> mask bits */
 #define STX_STAGE_PREDICT 33u      /* both                                      */

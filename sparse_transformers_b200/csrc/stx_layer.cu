@@ -5,6 +5,9 @@
 // sparse branch of SkipDecoderLayer.forward (src/modeling_skip.py:236-238 and :258).
 #include "stx_cache.cuh"
 #include "stx_peer.cuh"
+#include "stx_stack_b1.cuh"
+
+#include <cstdlib>
 
 #include <algorithm>
 #include <new>
@@ -70,6 +73,8 @@ struct stx_stack {
   cudaGraphExec_t exec = nullptr;
   int64_t kernel_nodes = 0;
   std::vector<cudaEvent_t> events;  // [0,L) fork points, [L] join, [L+1, 2L+1) plan-done points, [2L+1] second join
+  std::vector<void*> b1_scratch;    // persistent single-row kernel: counters, t and pair partials per group of layers
+  bool persistent = false;
 };
 
 using namespace stx;
@@ -216,13 +221,17 @@ static int layer_step_streams(stx_layer* l, const void* x_pred, const void* x_ml
     }
   }
   if (!gather) {
-    // the MLP reads the packed cache: plan and copies come first, on the same stream (a big row
-    // block brings the cache up to date as part of its MLP stage if the caller left that for later)
-    if ((stages & STX_STAGE_PLAN) || (big && (stages & STX_STAGE_MLP))) {
+    // The MLP reads the packed cache: plan and copies come first, on the same stream.  For a big row
+    // block the MLP stage OWNS the maintenance: a call that asks for PLAN and/or COPY without the MLP
+    // stage does nothing, so a caller that issues those stages on side streams (as it must for the
+    // gathering kernels) can never run a second plan concurrently with the one of the MLP stage.
+    const bool plan_here = big ? (stages & STX_STAGE_MLP) != 0 : (stages & STX_STAGE_PLAN) != 0;
+    const bool copy_here = big ? (stages & STX_STAGE_MLP) != 0 : (stages & STX_STAGE_COPY) != 0;
+    if (plan_here) {
       rc = cache_plan(c, l->bits, s);
       if (rc != STX_OK) return rc;
     }
-    if ((stages & STX_STAGE_COPY) || (big && (stages & STX_STAGE_MLP))) {
+    if (copy_here) {
       rc = cache_copy_rows(c, s);
       if (rc != STX_OK) return rc;
     }
@@ -345,9 +354,100 @@ int stx_stack_destroy(stx_stack_t* s) {
   if (s->exec) cudaGraphExecDestroy(s->exec);
   if (s->graph) cudaGraphDestroy(s->graph);
   for (cudaEvent_t ev : s->events) cudaEventDestroy(ev);
+  for (void* p : s->b1_scratch) cudaFree(p);
   cudaFree(s->x_in);
   cudaFree(s->out);
   delete s;
+  return STX_OK;
+}
+
+// A single row through layers that all take the one-kernel path of the threshold rule and share
+// their shapes: the whole stack runs as ONE persistent kernel per group of layers
+// (stx_stack_b1.cu); the cache upkeep of every layer (index plan, row copies) forks off behind the
+// group's kernel, one branch per layer, and joins at the end of the step.
+static bool stack_persistent_wanted(const stx_stack* s, unsigned stages) {
+  const unsigned need = STX_STAGE_PREDICT | STX_STAGE_MLP;
+  if (s->B != 1 || (stages & need) != need) return false;
+  const stx_layer* l0 = s->layers[0];
+  const stx_cache* c0 = l0->cache;
+  if (!stack_b1_supported(c0->H, c0->I, l0->r, c0->has_gate, c0->dtype)) return false;
+  for (const stx_layer* l : s->layers) {
+    const stx_cache* c = l->cache;
+    if (!single_row_fusable(l, 1) || l->peer || c->I != c0->I || c->has_gate != c0->has_gate || l->r != l0->r) return false;
+  }
+  return true;
+}
+
+// Layers per launch of the persistent kernel: STX_STACK_GROUP in the environment (1..40), default
+// all layers in one launch.  Smaller groups let the cache upkeep of a group overlap the next group.
+static int64_t stack_group_size(int64_t L) {
+  int64_t g = std::min<int64_t>(L, STACK_B1_MAX_LAYERS);
+  if (const char* e = getenv("STX_STACK_GROUP")) {
+    const long v = strtol(e, nullptr, 10);
+    if (v >= 1 && v <= STACK_B1_MAX_LAYERS) g = std::min<int64_t>(g, v);
+  }
+  return g;
+}
+
+static int capture_persistent(stx_stack* s, unsigned stages, cudaStream_t cs, std::vector<cudaStream_t>& sides) {
+  const int64_t L = static_cast<int64_t>(s->layers.size());
+  const size_t xbytes = static_cast<size_t>(s->H) * s->es;
+  const stx_layer* l0 = s->layers[0];
+  const int64_t gsz = stack_group_size(L);
+  const bool strict = getenv("STX_STACK_STRICT") && atoi(getenv("STX_STACK_STRICT")) != 0;
+  const bool upkeep = (stages & (STX_STAGE_PLAN | STX_STAGE_COPY)) != 0;
+  size_t ev = 0;
+  for (int64_t g0 = 0, gi = 0; g0 < L; g0 += gsz, ++gi) {
+    const int64_t n = std::min<int64_t>(gsz, L - g0);
+    StackB1Args a = {};
+    for (int64_t i = 0; i < n; ++i) {
+      stx_layer* l = s->layers[g0 + i];
+      stx_cache* c = l->cache;
+      StackLayerDesc& d = a.layer[i];
+      d.gate = c->pool_gate;
+      d.up = c->pool_up;
+      d.down = c->pool_down;
+      d.A = l->A;
+      d.Bm = l->Bm;
+      d.bits = l->bits;
+      d.out = static_cast<char*>(s->out) + (g0 + i) * xbytes;
+      d.status = c->state + ST_STATUS;
+      d.tau = l->param;
+      d.act = l->act;
+    }
+    a.x = s->x_in;
+    a.L = static_cast<int>(n);
+    a.H = static_cast<int>(s->H);
+    a.I = static_cast<int>(l0->cache->I);
+    a.r = static_cast<int>(l0->r);
+    a.has_gate = l0->cache->has_gate;
+    a.strict = strict ? 1 : 0;
+    int rc = stack_b1_forward(a, s->b1_scratch[gi], l0->cache->dtype, cs);
+    if (rc != STX_OK) return rc;
+    if (!upkeep) continue;
+    // the masks of the group exist now: one branch per layer
+    STX_CUDA(cudaEventRecord(s->events[ev], cs));
+    const cudaEvent_t fork_ev = s->events[ev++];
+    for (int64_t i = 0; i < n; ++i) {
+      stx_layer* l = s->layers[g0 + i];
+      cudaStream_t side = sides[g0 + i];
+      STX_CUDA(cudaStreamWaitEvent(side, fork_ev, 0));
+      if (stages & STX_STAGE_PLAN) {
+        rc = cache_plan(l->cache, l->bits, side, l->lazy);
+        if (rc != STX_OK) return rc;
+      }
+      if ((stages & STX_STAGE_COPY) && !l->lazy) {
+        rc = cache_copy_rows(l->cache, side);
+        if (rc != STX_OK) return rc;
+      }
+    }
+  }
+  if (upkeep) {
+    for (int64_t i = 0; i < L; ++i) {  // join
+      STX_CUDA(cudaEventRecord(s->events[ev], sides[i]));
+      STX_CUDA(cudaStreamWaitEvent(cs, s->events[ev++], 0));
+    }
+  }
   return STX_OK;
 }
 
@@ -404,6 +504,33 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
     return cuda_fail(e, "stx_stack_create: stream/event creation");
   }
   int rc = STX_OK;
+  s->persistent = stack_persistent_wanted(s, stages);
+  std::vector<cudaStream_t> sides;
+  if (s->persistent) {
+    const int64_t gsz = stack_group_size(L);
+    for (int64_t g0 = 0; g0 < L && e == cudaSuccess; g0 += gsz) {
+      const size_t bytes = stack_b1_scratch_bytes(std::min<int64_t>(gsz, L - g0), s->H, s->layers[0]->r);
+      void* p = nullptr;
+      e = cudaMalloc(&p, bytes);
+      if (e == cudaSuccess) {
+        s->b1_scratch.push_back(p);
+        e = cudaMemset(p, 0, bytes);
+      }
+    }
+    for (int64_t i = 0; i < L && e == cudaSuccess; ++i) {
+      cudaStream_t st = nullptr;
+      e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+      if (e == cudaSuccess) sides.push_back(st);
+    }
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the cleared counters are in place before the first launch
+    if (e == cudaSuccess) e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
+    if (e == cudaSuccess) {
+      rc = capture_persistent(s, stages, cs, sides);
+      cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
+      if (rc == STX_OK && e2 != cudaSuccess) e = e2;
+    }
+    for (cudaStream_t st : sides) cudaStreamDestroy(st);
+  } else {
   e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
   if (e == cudaSuccess) {
     bool forked = false, used2 = false;
@@ -426,6 +553,7 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
     }
     cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
     if (rc == STX_OK && e == cudaSuccess && e2 != cudaSuccess) e = e2;
+  }
   }
   if (e == cudaSuccess && rc == STX_OK) e = cudaGraphInstantiate(&s->exec, s->graph, 0);
   cudaStreamDestroy(cs);

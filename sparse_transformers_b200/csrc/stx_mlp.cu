@@ -18,6 +18,7 @@
 #include "stx_common.cuh"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -344,6 +345,8 @@ int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const voi
 using namespace stx;
 
 namespace stx {
+int sparse_mlp_forward_check(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed, int64_t K,
+                             void* down_buf, int act, int dtype, const void* scratch);
 int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed,
                             int64_t K, void* down_buf, void* combined_buf, int act, int has_gate, int dtype,
                             void* scratch, bool scratch_has_partial, void* stream);
@@ -369,11 +372,9 @@ int stx_sparse_mlp_forward(const void* x, int64_t B, int64_t H, const void* conc
 }  // extern "C"
 
 namespace stx {
-// scratch_has_partial: the scratch was sized by stx_mlp_scratch_bytes (true) or is the smaller
-// built-in array of the no-alloc entry point (false: batch 1 keeps the two-kernel path).
-int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed,
-                            int64_t K, void* down_buf, void* combined_buf, int act, int has_gate, int dtype,
-                            void* scratch, bool scratch_has_partial, void* stream) {
+// Argument checks shared by the two entry points (nothing is enqueued before they pass).
+int sparse_mlp_forward_check(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed, int64_t K,
+                             void* down_buf, int act, int dtype, const void* scratch) {
   STX_CHECK_ARG(x && concat_w && down_packed && down_buf && scratch, "stx_sparse_mlp_forward: null pointer");
   STX_CHECK_ARG(B > 0 && H > 0 && K >= 0, "stx_sparse_mlp_forward: bad sizes B=%lld H=%lld K=%lld",
                 static_cast<long long>(B), static_cast<long long>(H), static_cast<long long>(K));
@@ -387,6 +388,17 @@ int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* con
   const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(concat_w) |
                        reinterpret_cast<uintptr_t>(down_packed) | reinterpret_cast<uintptr_t>(scratch);
   STX_CHECK_ARG((al & 15) == 0, "stx_sparse_mlp_forward: x, concat_w, down_packed and scratch must be 16-byte aligned");
+  return STX_OK;
+}
+
+// scratch_has_partial: the scratch was sized by stx_mlp_scratch_bytes (true) or is the smaller
+// built-in array of the no-alloc entry point (false: batch 1 keeps the two-kernel path).
+int sparse_mlp_forward_impl(const void* x, int64_t B, int64_t H, const void* concat_w, const void* down_packed,
+                            int64_t K, void* down_buf, void* combined_buf, int act, int has_gate, int dtype,
+                            void* scratch, bool scratch_has_partial, void* stream) {
+  const int chk = sparse_mlp_forward_check(x, B, H, concat_w, down_packed, K, down_buf, act, dtype, scratch);
+  if (chk != STX_OK) return chk;
+  const size_t es = dtype_size(dtype);
   // the built-in scratch of the no-alloc entry point (scratch_has_partial == false) has no room for the
   // tensor-core path's buffers: its row blocks stay on the streaming kernels
   if (scratch_has_partial && prefill_wanted(B, H, K, dtype, has_gate)) {
@@ -432,28 +444,33 @@ constexpr size_t NOALLOC_BYTES = 1024 + static_cast<size_t>(STX_NOALLOC_MAX_ELEM
 // In host code this name is only a handle for the runtime, never a device address: the
 // address a kernel can use comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+// stands in for the scratch pointer in the argument checks that run before the array's address is looked up
+alignas(256) static const unsigned char g_noalloc_host_tag[16] = {};
 
 namespace stx {
 
+// Device address of the array on the current device; looked up once per device.  The table is read
+// and written with atomics, so host threads that race on a device's first call all end up with the
+// same value (the lookup is idempotent).
 static int noalloc_scratch_ptr(void** out) {
-  static void* ptrs[64] = {};
+  static std::atomic<void*> ptrs[64] = {};
   int dev = 0;
   STX_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) {
     set_error("stx_sparse_mlp_forward_noalloc: device index %d not supported", dev);
     return STX_ERR_UNSUPPORTED;
   }
-  if (!ptrs[dev]) {
-    void* p = nullptr;
+  void* p = ptrs[dev].load(std::memory_order_acquire);
+  if (!p) {
     cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
     if (!p) {
       set_error("stx_sparse_mlp_forward_noalloc: the scratch array has no device address");
       return STX_ERR_CUDA;
     }
-    ptrs[dev] = p;
+    ptrs[dev].store(p, std::memory_order_release);
   }
-  *out = ptrs[dev];
+  *out = p;
   return STX_OK;
 }
 
@@ -471,8 +488,11 @@ extern "C" int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t 
               static_cast<long long>(B * (H + K)), static_cast<long long>(STX_NOALLOC_MAX_ELEMS));
     return STX_ERR_TOO_LARGE;
   }
+  // every argument check comes before the shared array is touched: a refused call enqueues nothing
+  int rc = stx::sparse_mlp_forward_check(x, B, H, concat_w, down_packed, K, down_buf, act, dtype, g_noalloc_host_tag);
+  if (rc != STX_OK) return rc;
   void* scratch = nullptr;
-  int rc = noalloc_scratch_ptr(&scratch);
+  rc = noalloc_scratch_ptr(&scratch);
   if (rc != STX_OK) return rc;
   // the array keeps the previous call's contents: clear the counter and the accumulator
   const size_t used = 256 + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);

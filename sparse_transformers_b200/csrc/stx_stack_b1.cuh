@@ -1,0 +1,38 @@
+// Arguments of the persistent single-row stack kernel (stx_stack_b1.cu).
+#pragma once
+
+#include "stx_common.cuh"
+
+namespace stx {
+
+constexpr int STACK_B1_MAX_LAYERS = 40;  // layers per launch: the descriptors travel as kernel parameters
+
+struct StackLayerDesc {
+  const void* gate;  // full pools [I,H]
+  const void* up;
+  const void* down;  // transposed: [I,H]
+  const void* A;     // [r,H]
+  const void* Bm;    // [I,r]
+  uint32_t* bits;    // the layer's mask words (written bytewise)
+  void* out;         // [H] in the model dtype
+  int* status;       // device status word of the layer's cache
+  float tau;
+  int act;
+};
+
+struct StackB1Args {
+  StackLayerDesc layer[STACK_B1_MAX_LAYERS];
+  const void* x;     // [H]
+  float* t_buf;      // [L][r]
+  float* partial;    // [2][G/2][H] pair partials, double-buffered by layer parity
+  uint32_t* sync;    // counters (see the kernel)
+  int L, H, I, r, has_gate, nslot, strict;
+};
+
+bool stack_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype);
+size_t stack_b1_scratch_bytes(int64_t L, int64_t H, int64_t r);
+// One launch for layers [0, a.L), a.L <= STACK_B1_MAX_LAYERS.  scratch: stack_b1_scratch_bytes(a.L, ..)
+// bytes, zeroed once at allocation and then owned by the launches of this group of layers.
+int stack_b1_forward(StackB1Args& a, void* scratch, int dtype, cudaStream_t s);
+
+}  // namespace stx

@@ -11,6 +11,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <cuda_runtime.h>
+
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <string>
@@ -142,19 +145,30 @@ class WeightCache : public torch::CustomClassHolder {
   c10::Device device_ = c10::Device(c10::kCUDA, 0);
 };
 
-// Zero-initialised scratch per (device, stream); the kernels leave it zeroed.
-static void* mlp_scratch(const c10::Device& dev, void* stream, size_t bytes) {
+// Zero-initialised scratch per (device, stream).  A call leaves the leading counter and fp32
+// accumulator (256 + 4*B*H bytes, rounded up to 256) zeroed again, but that region's extent
+// depends on B and H and the bytes behind it hold activations and partial sums of the last call:
+// when a call's (B,H) differs from the previous one on the same buffer, the leading region of the
+// new shape is cleared on the stream first.
+static void* mlp_scratch(const c10::Device& dev, void* stream, size_t bytes, int64_t B, int64_t H) {
+  struct Entry {
+    torch::Tensor buf;
+    int64_t B = 0, H = 0;
+  };
   static std::mutex mu;
-  static std::map<std::pair<int, void*>, torch::Tensor> cache;
+  static std::map<std::pair<int, void*>, Entry> cache;
   std::lock_guard<std::mutex> lock(mu);
-  auto key = std::make_pair(static_cast<int>(dev.index()), stream);
-  auto it = cache.find(key);
-  if (it == cache.end() || static_cast<size_t>(it->second.numel()) < bytes) {
-    auto t = torch::zeros({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
-    cache[key] = t;
-    return t.data_ptr();
+  Entry& e = cache[std::make_pair(static_cast<int>(dev.index()), stream)];
+  if (!e.buf.defined() || static_cast<size_t>(e.buf.numel()) < bytes) {
+    e.buf = torch::zeros({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+  } else if (e.B != B || e.H != H) {
+    const size_t lead = std::min<size_t>(256 + (static_cast<size_t>(B) * H * 4 + 255) / 256 * 256, e.buf.numel());
+    const cudaError_t err = cudaMemsetAsync(e.buf.data_ptr(), 0, lead, static_cast<cudaStream_t>(stream));
+    TORCH_CHECK(err == cudaSuccess, "sparse_mlp.forward: clearing the scratch buffer failed: ", cudaGetErrorString(err));
   }
-  return it->second.data_ptr();
+  e.B = B;
+  e.H = H;
+  return e.buf.data_ptr();
 }
 
 // sparse_mlp_forward (sparse_mlp_op.cpp:53-76): same positional signature, so the inferred
@@ -205,7 +219,7 @@ torch::Tensor sparse_mlp_forward(const torch::Tensor& input, const torch::Tensor
   void* stream = cur_stream(input.device());
   size_t sbytes = 0;
   check(stx_mlp_scratch_bytes(B, H, K, &sbytes), "forward");
-  void* scratch = mlp_scratch(input.device(), stream, sbytes);
+  void* scratch = mlp_scratch(input.device(), stream, sbytes, B, H);
   check(stx_sparse_mlp_forward(x.data_ptr(), B, H, wcat.data_ptr(), wdown.data_ptr(), K, down_proj_buffer.data_ptr(),
                                combined_proj_buffer.data_ptr(), act, has_gate ? 1 : 0, to_stx_dtype(dtype), scratch, stream),
         "forward");

@@ -162,6 +162,8 @@ class ShardedStack:
                 l.local.step_stages(C.STAGE_PREDICT, self.x_in, batch=self.B)
                 side.wait_stream(main)  # the side work needs the mask, nothing later
                 l.local.step_stages(C.STAGE_MLP, None, self.x_in, self.out[i], batch=self.B)
+            # (row blocks of 9 and more keep their cache upkeep inside STAGE_MLP on the main stream;
+            # for them the two calls below enqueue nothing)
             with torch.cuda.stream(side):
                 l.local.step_stages(C.STAGE_PLAN, batch=self.B)
             self._side2.wait_stream(side)

@@ -1,0 +1,113 @@
+"""A single row through a stack of layers as ONE persistent kernel (stx_stack_step on a batch-1
+stack) vs the oracle pipeline run layer by layer on the same seeded inputs: masks and cache orders
+bit-exact, outputs within tolerance (1e-5 fp32, 2e-2 fp16/bf16 as max|a-b|/max|b|).  Also the same
+stack on the per-layer kernels (STX_STACK_KERNEL=layers) and with the strict layer order
+(STX_STACK_STRICT=1): identical masks, outputs within tolerance of each other."""
+import numpy as np
+import pytest
+import torch
+
+from test_gpu_layer import ODT, TOL, OracleLayer
+
+pytestmark = pytest.mark.gpu
+
+
+def _stack_vs_oracle(w, steps, seed=0, check_every=1):
+    from sparse_transformers_b200 import SparseLayer, SparseStack
+    from sparse_transformers_b200.synth import HiddenStream, layer_weights
+    from stxgpu import DEV, rel_err
+
+    gen = torch.Generator().manual_seed(seed)
+    ws = [layer_weights(w, gen) for _ in range(w.layers)]
+    xs = HiddenStream(w, gen)
+    layers = [SparseLayer(*[t.to(DEV) for t in lw], act=w.act, method="threshold", param=w.tau, max_batch=1,
+                          has_gate=w.has_gate) for lw in ws]
+    ols = [OracleLayer(w, *lw) for lw in ws]
+    stack = SparseStack(layers, 1)
+    out = torch.empty(w.layers, 1, w.H, dtype=w.dtype, device=DEV)
+    worst, ks = 0.0, []
+    for t in range(steps):
+        x = xs.next()
+        stack.step(x.to(DEV), out)
+        torch.cuda.synchronize()
+        got = out.float().cpu().numpy()
+        for li, (l, ol) in enumerate(zip(layers, ols)):
+            mask, ref = ol.step(x)
+            if t % check_every:
+                continue
+            assert np.array_equal(l.mask().cpu().numpy(), mask), f"mask differs at step {t} layer {li}"
+            assert l.active_indices().tolist() == ol.cache.active.tolist(), f"cache order differs at step {t} layer {li}"
+            worst = max(worst, rel_err(got[li], ref))
+            ks.append(l.num_active())
+    assert worst <= TOL[w.dtype], worst
+    n_launch = stack.launches_per_step
+    stack.close()
+    for l in layers:
+        l.close()
+    return ks, n_launch
+
+
+@pytest.mark.parametrize("dtype,H,I,r,has_gate,act,density,layers", [
+    (torch.float16, 512, 2048, 64, True, "silu", 0.2, 3),
+    (torch.bfloat16, 1024, 4096, 32, True, "gelu_pytorch_tanh", 0.2, 5),
+    (torch.float32, 512, 2048, 16, True, "relu", 0.2, 2),
+    (torch.float16, 1024, 3000, 128, False, "relu", 0.3, 4),      # no gate, ragged I (partial mask byte, CTAs without neurons)
+    (torch.float16, 2048, 8192, 64, True, "silu", 0.9, 2),        # dense mask: several rounds of row spaces per pair
+    (torch.bfloat16, 512, 1024, 64, True, "silu", 0.02, 3),       # nearly empty: pairs without neurons
+])
+def test_persistent_stack_matches_oracle(dtype, H, I, r, has_gate, act, density, layers):
+    from sparse_transformers_b200.synth import Workload
+
+    w = Workload("stack", H=H, I=I, r=r, B=1, dtype=dtype, density=density, layers=layers, act=act, has_gate=has_gate)
+    ks, n_launch = _stack_vs_oracle(w, steps=6, seed=layers)
+    assert n_launch == 1 + 2 * layers  # the persistent kernel + index plan and row copies per layer
+
+
+def test_c2_full_shape_16_steps():
+    """Llama-3.2-3B shape (H 3072, I 8192, r 64, fp16), 4 layers, 16 steps of AR(1) hidden states."""
+    from sparse_transformers_b200.synth import WORKLOADS
+
+    w = WORKLOADS["C2"].scaled(layers=4)
+    ks, _ = _stack_vs_oracle(w, steps=16, check_every=3)
+    assert 0.15 * w.I < np.mean(ks[4:]) < 0.25 * w.I
+
+
+@pytest.mark.parametrize("env", [{"STX_STACK_STRICT": "1"}, {"STX_STACK_KERNEL": "layers"}, {"STX_STACK_GROUP": "2"}])
+def test_stack_variants_agree(monkeypatch, env):
+    """Strict layer order, groups of two layers per launch and the per-layer kernels give the same
+    masks and cache orders as the oracle, outputs within tolerance."""
+    from sparse_transformers_b200.synth import WORKLOADS
+
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    w = WORKLOADS["C2"].scaled(I=4096, H=1024, layers=5)
+    _, n_launch = _stack_vs_oracle(w, steps=5, seed=9)
+    if "STX_STACK_KERNEL" in env:
+        assert n_launch == 5 * w.layers
+    elif "STX_STACK_GROUP" in env:
+        assert n_launch == 3 + 2 * w.layers
+
+
+def test_stack_replay_is_deterministic():
+    """Two stacks over the same weights fed the same inputs produce identical bits (fixed summation
+    order: pair partials are added in ascending pair order)."""
+    from sparse_transformers_b200 import SparseLayer, SparseStack
+    from sparse_transformers_b200.synth import HiddenStream, WORKLOADS, layer_weights
+    from stxgpu import DEV
+
+    w = WORKLOADS["C2"].scaled(I=4096, H=1024, layers=3)
+    gen = torch.Generator().manual_seed(4)
+    ws = [layer_weights(w, gen) for _ in range(w.layers)]
+    mk = lambda: [SparseLayer(*[t.to(DEV) for t in lw], act=w.act, param=w.tau, max_batch=1) for lw in ws]
+    a, b = mk(), mk()
+    sa, sb = SparseStack(a, 1), SparseStack(b, 1)
+    xs = HiddenStream(w, gen)
+    oa = torch.empty(w.layers, 1, w.H, dtype=w.dtype, device=DEV)
+    ob = torch.empty_like(oa)
+    for _ in range(5):
+        x = xs.next().to(DEV)
+        sa.step(x, oa)
+        sb.step(x, ob)
+        torch.cuda.synchronize()
+        assert torch.equal(oa, ob)
+    sa.close(); sb.close()

@@ -43,6 +43,51 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
         assert rel_err(out2.float().cpu().numpy(), ref.float().cpu().numpy()) <= TOL[dtype]
 
 
+def test_noalloc_clears_what_the_fallback_kernel_accumulates_into():
+    """Rows narrower than 512 bytes take the kernel that accumulates into the head of the scratch and
+    expects it zero.  A streaming-kernel call first leaves activations right where the next, narrower
+    call keeps its accumulator: only the per-call clear makes the second result right.  Checked
+    against the regular entry point (fresh scratch) and against the CPU oracle; also K = 0."""
+    from oracle import oracle as orc
+    from stxgpu import DEV, mlp_forward, rel_err
+
+    g = torch.Generator().manual_seed(7)
+    dtype = torch.float32
+    for (B, H, K) in [(1, 128, 200), (8, 64, 150), (1, 128, 90), (3, 32, 40)]:
+        x = torch.randn(B, H, generator=g).to(dtype).to(DEV)
+        cw = (torch.randn(2 * K, H, generator=g) / H ** 0.5).to(dtype).to(DEV)
+        dp = (torch.randn(K, H, generator=g) / H ** 0.5).to(dtype).to(DEV)
+        ref, _ = mlp_forward(x, cw, dp, "silu")
+        out, _ = _noalloc(x, cw, dp, "silu")
+        assert rel_err(out.cpu().numpy(), ref.cpu().numpy()) <= 1e-5
+        want, _ = orc.sparse_mlp(x.cpu().numpy(), cw.cpu().numpy(), dp.cpu().numpy(), "silu", True)
+        assert rel_err(out.cpu().numpy(), want) <= 1e-5
+    # no active neuron: the output is zero, as the regular entry point gives
+    x = torch.randn(2, 64, generator=g).to(DEV)
+    cw = torch.zeros(0, 64, device=DEV)
+    dp = torch.zeros(0, 64, device=DEV)
+    pad = torch.zeros(16, device=DEV)  # a valid, aligned address for the empty operands
+    from sparse_transformers_b200 import _capi as C
+    from stxgpu import ACT, DT, stream
+
+    out = torch.full((2, 64), float("nan"), device=DEV)
+    C.check(C.lib.stx_sparse_mlp_forward_noalloc(x.data_ptr(), 2, 64, pad.data_ptr(), pad.data_ptr(), 0, out.data_ptr(),
+                                                 pad.data_ptr(), ACT["silu"], 1, DT[torch.float32], stream()))
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(out) == 0
+
+
+def test_noalloc_refused_call_enqueues_nothing():
+    """A call with a bad argument is refused before the shared array is touched."""
+    from sparse_transformers_b200 import _capi as C
+    from stxgpu import DEV, stream
+
+    x = torch.zeros(64, device=DEV)
+    rc = C.lib.stx_sparse_mlp_forward_noalloc(x.data_ptr(), 1, 64, x.data_ptr(), x.data_ptr(), 1, x.data_ptr(), None,
+                                              99, 1, C.F32, stream())
+    assert rc == C.ERR_INVALID_ARG and "bad activation" in C.last_error()
+
+
 def test_noalloc_rejects_sizes_beyond_the_builtin_scratch():
     from sparse_transformers_b200 import _capi as C
     from stxgpu import DEV, stream
