@@ -518,6 +518,41 @@ int cache_update_bits(stx_cache* c, const uint32_t* bits, cudaStream_t s) {
   return cache_copy_rows(c, s);
 }
 
+// cat[n] = [gate[n] | up[n] | down[n]] (nmat rows of vec 16-byte vectors each)
+__global__ void __launch_bounds__(256)
+k_interleave_rows(const uint4* __restrict__ p0, const uint4* __restrict__ p1, const uint4* __restrict__ p2,
+                  uint4* __restrict__ cat, int nmat, int vec, size_t total) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t rec = static_cast<size_t>(nmat) * vec;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t n = i / rec, o = i - n * rec;
+    const int m = static_cast<int>(o / vec);
+    const size_t v = o - static_cast<size_t>(m) * vec;
+    const uint4* src = m == 0 ? p0 : (m == 1 ? p1 : p2);
+    cat[i] = ld_stream16(src + n * vec + v);
+  }
+}
+
+int cache_ensure_cat(stx_cache* c, cudaStream_t s) {
+  if (c->pool_cat) return STX_OK;
+  const int nmat = c->has_gate ? 3 : 2;
+  const size_t bytes = static_cast<size_t>(c->I) * nmat * c->row_bytes;
+  cudaError_t e = cudaMalloc(&c->pool_cat, bytes);
+  if (e != cudaSuccess) {
+    c->pool_cat = nullptr;
+    set_error("weight cache: allocating the per-neuron pool (%zu bytes) failed: %s", bytes, cudaGetErrorString(e));
+    return STX_ERR_ALLOC;
+  }
+  const int vec = static_cast<int>(c->row_bytes / 16);
+  const size_t total = static_cast<size_t>(c->I) * nmat * vec;
+  const uint4* p0 = static_cast<const uint4*>(c->has_gate ? c->pool_gate : c->pool_up);
+  const uint4* p1 = static_cast<const uint4*>(c->has_gate ? c->pool_up : c->pool_down);
+  const uint4* p2 = static_cast<const uint4*>(c->has_gate ? c->pool_down : nullptr);
+  k_interleave_rows<<<num_sms() * 8, 256, 0, s>>>(p0, p1, p2, static_cast<uint4*>(c->pool_cat), nmat, vec, total);
+  STX_LAUNCH_CHECK("k_interleave_rows");
+  return STX_OK;
+}
+
 int cache_read_state(stx_cache* c, cudaStream_t s) {
   STX_CUDA(cudaMemcpyAsync(c->host_state, c->state, ST_COUNT * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
   STX_CUDA(cudaStreamSynchronize(s));
@@ -547,6 +582,7 @@ int stx_cache_destroy(stx_cache_t* c) {
   if (!c) return STX_OK;
   cudaFree(c->own_gate);
   cudaFree(c->own_up);
+  cudaFree(c->pool_cat);
   cudaFree(c->pool_down);
   if (c->pk_gate)
     cudaFree(c->pk_gate);  // pk_up lives in the same allocation

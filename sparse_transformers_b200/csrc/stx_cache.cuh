@@ -29,6 +29,10 @@ struct stx_cache {
   void* pool_down = nullptr;
   void* own_gate = nullptr;  // non-null when the cache owns copies of gate/up
   void* own_up = nullptr;
+  // optional second copy of the pools, one record per neuron: [I][gate row | up row | down row]
+  // ([I][up row | down row] without a gate), so that a neuron's weights are ONE contiguous read.
+  // Built on demand (cache_ensure_cat) for the persistent single-row stack kernel.
+  void* pool_cat = nullptr;
 
   // packed pools ([I,H] capacity; rows 0..K-1 valid): row j belongs to neuron active[j]
   void* pk_gate = nullptr;
@@ -60,4 +64,5 @@ int cache_plan(stx_cache* c, const uint32_t* bits, cudaStream_t s, bool lazy = f
 int cache_copy_rows(stx_cache* c, cudaStream_t s);
 int cache_flush(stx_cache* c, cudaStream_t s);  // rows of all stale slots (no-op when none are pending)
 int cache_read_state(stx_cache* c, cudaStream_t s);  // syncs; fills host_state
+int cache_ensure_cat(stx_cache* c, cudaStream_t s);  // allocates and fills pool_cat once (asynchronous fill)
 }  // namespace stx

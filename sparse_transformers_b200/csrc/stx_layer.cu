@@ -404,9 +404,7 @@ static int capture_persistent(stx_stack* s, unsigned stages, cudaStream_t cs, st
       stx_layer* l = s->layers[g0 + i];
       stx_cache* c = l->cache;
       StackLayerDesc& d = a.layer[i];
-      d.gate = c->pool_gate;
-      d.up = c->pool_up;
-      d.down = c->pool_down;
+      d.cat = c->pool_cat;
       d.A = l->A;
       d.Bm = l->Bm;
       d.bits = l->bits;
@@ -522,9 +520,10 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
       e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
       if (e == cudaSuccess) sides.push_back(st);
     }
-    if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the cleared counters are in place before the first launch
-    if (e == cudaSuccess) e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
-    if (e == cudaSuccess) {
+    for (int64_t i = 0; i < L && e == cudaSuccess && rc == STX_OK; ++i) rc = cache_ensure_cat(s->layers[i]->cache, nullptr);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();  // cleared counters and per-neuron pools are in place before the first launch
+    if (e == cudaSuccess && rc == STX_OK) e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
+    if (e == cudaSuccess && rc == STX_OK) {
       rc = capture_persistent(s, stages, cs, sides);
       cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
       if (rc == STX_OK && e2 != cudaSuccess) e = e2;

@@ -8,9 +8,7 @@ namespace stx {
 constexpr int STACK_B1_MAX_LAYERS = 40;  // layers per launch: the descriptors travel as kernel parameters
 
 struct StackLayerDesc {
-  const void* gate;  // full pools [I,H]
-  const void* up;
-  const void* down;  // transposed: [I,H]
+  const void* cat;   // per-neuron records [I][gate row | up row | down row] ([I][up | down] without a gate)
   const void* A;     // [r,H]
   const void* Bm;    // [I,r]
   uint32_t* bits;    // the layer's mask words (written bytewise)
@@ -24,7 +22,7 @@ struct StackB1Args {
   StackLayerDesc layer[STACK_B1_MAX_LAYERS];
   const void* x;     // [H]
   float* t_buf;      // [L][r]
-  float* partial;    // [2][G/2][H] pair partials, double-buffered by layer parity
+  float* partial;    // [2][G][H] per-CTA partial outputs, double-buffered by layer parity
   uint32_t* sync;    // counters (see the kernel)
   int L, H, I, r, has_gate, nslot, strict;
 };
