@@ -5,27 +5,37 @@
 
 A *step* is one decode token through every layer of the workload's sparse-MLP stack:
 predictor -> mask -> differential weight-cache update -> sparse gate/up/down projection,
-layer after layer, strictly serialised on one stream.  Metric: decode tokens/s = B / t_step.
+layer after layer.  Metric: decode tokens/s = B / t_step.
 
-Default workload (N = 1): "C2", the Llama-3.2-3B-shaped 28-layer stack, fp16, batch 1,
-random-init weights N(0, 0.02), AR(1) hidden states, ~20 % active neurons per token.
-For N > 1 the intermediate dimension is sharded over the ranks (one process per GPU,
-launched by torch.distributed.run); the partial sums of a layer are added over peer memory
-inside the step's own kernels (--allreduce nccl selects torch.distributed.all_reduce instead).
-Other workloads: --workload C3 | C5 (batched decode stacks), C4 (prefill, tensor roofline),
-C2-e2e (the LlamaSkip host end to end: TTFT and output tokens/s).
+Default workload (headline at every N): "C2", the Llama-3.2-3B-shaped 28-layer stack, fp16,
+batch 1, random-init weights N(0, 0.02), AR(1) hidden states, ~20 % active neurons per token.
+Weights and hidden states are generated ONCE ON THE CPU from fixed seeds and uploaded, so the
+GPU arm, the CPU reference arm and the parity check all see identical bits.
+For N > 1 the intermediate dimension is sharded over the ranks (one process per GPU, launched
+by torch.distributed.run); the partial sums of a layer are added over peer memory inside the
+step's own kernels (--allreduce nccl selects torch.distributed.all_reduce instead).
 
 One JSON line is printed by rank 0:
-  value      device-timed (CUDA events), inputs resident in HBM, CUDA-graph replay
-  e2e        the same steps through the host-buffer C-ABI call (pinned host x in, result out)
-  roofline   dominant kernel (the sparse MLP): algorithmic bytes / measured launch time
-  cpu_baseline  the reference's own CPU implementation on this box's host cores, bounded sample
-`--impl reference` times only that CPU implementation on the same workload definition.
+  value        device-timed (CUDA events) median over `blocks` timed blocks of exactly K steps
+               each, inputs resident in HBM, CUDA-graph replay; value_spread = min / max block
+  e2e          the same steps through the host-buffer C-ABI call (pinned host x in, result out)
+  roofline     dominant kernel: algorithmic bytes per launch / measured launch time
+  parity       2 sampled layers x 4 steps against the reference's own compiled CPU code on
+               the same bits, outside the timed region (also at N > 1: summed output, per-shard
+               cache orders)
+  cpu_baseline the reference's own CPU implementation on this box's host cores, bounded sample
+  extra keys   (N = 1) c1, c3, c4, c5, c2_e2e, dropin: the other configurations, bounded;
+               (N > 1) c5: the sharded 64-row stack
+`--impl reference` times only the reference CPU implementation on the same workload definition.
+Other single-workload runs: --workload C3 | C5 (batched decode stacks), C4 (prefill, tensor
+roofline), C2-e2e (the LlamaSkip host end to end: TTFT and output tokens/s).
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -40,21 +50,35 @@ if ROOT not in sys.path:
 METRIC = "sparse_mlp_decode_tokens_per_s"
 UNIT = "tokens/s"
 DTYPE_NAME = {"torch.float32": "f32", "torch.float16": "f16", "torch.bfloat16": "bf16"}
+PARITY_STEPS = 4
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--workload", default="C2")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = workload default)")
+    ap.add_argument("--blocks", type=int, default=0, help="timed blocks of --steps steps (0 = 25, bounded by 8192 steps in total)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only (no c1/c3/c4/c5/c2_e2e/dropin keys)")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
                     help="N>1: sum of the shards' outputs inside the library's kernels over peer memory, or NCCL")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
     return ap.parse_args()
+
+
+def load_synth():
+    """sparse_transformers_b200/synth.py loaded by path: the workload definitions need torch only,
+    and the reference arm must not load the native libraries."""
+    spec = importlib.util.spec_from_file_location("stx_synth", os.path.join(ROOT, "sparse_transformers_b200", "synth.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["stx_synth"] = mod
+    spec.loader.exec_module(mod)
+    return mod
 
 
 # ------------------------------------------------------------------------------ helpers
@@ -107,29 +131,24 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def measured_peak_gbs():
+def measured_peak(key: str, fallback: float, what: str):
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json copy bandwidth)"
+            return float(json.load(f)[key]), f"measured (MEASURED_PEAKS.json {what})"
     except Exception:
-        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return fallback, f"fallback ({fallback:g}, an earlier measurement of the same GPU type)"
 
 
 def traffic_ratio(kernel: str):
-    """DRAM bytes / algorithmic bytes of the MLP kernel from the committed ncu capture."""
+    """(DRAM bytes / algorithmic bytes, source) of a kernel from the committed ncu capture."""
+    path = os.path.join("profiles", f"{kernel}_traffic.json")
     try:
-        with open(os.path.join(ROOT, "profiles", f"{kernel}_traffic.json")) as f:
-            return float(json.load(f)["dram_over_algorithmic"])
+        with open(os.path.join(ROOT, path)) as f:
+            d = json.load(f)
+        return float(d["dram_over_algorithmic"]), f"{path} ({d.get('source', 'ncu capture of a smaller case, scaled by units')})"
     except Exception:
-        return None
-
-
-def mlp_algorithmic_bytes(w, K: float) -> float:
-    """Sparse-MLP launch: active gate/up/down rows read once + x, a and the output."""
-    s = w.dtype.itemsize if hasattr(w.dtype, "itemsize") else 2
-    nmat = 3 if w.has_gate else 2
-    return s * nmat * K * w.H + s * w.B * 2 * w.H + 4 * w.B * K
+        return None, None
 
 
 def layer_step_algorithmic_bytes(w, K: float, dK: float) -> float:
@@ -141,22 +160,35 @@ def layer_step_algorithmic_bytes(w, K: float, dK: float) -> float:
             + s * w.B * (2 * w.H + w.r + 2 * K) + w.B * w.I * s + 2 * w.I / 8)
 
 
+def gen_layers(synth, w, n_layers: int, seed: int = 0):
+    """Yields (gate, up, down, A, Bm) CPU tensors in the workload dtype, layer after layer, all
+    drawn from ONE CPU generator: both arms and the parity check use this function."""
+    import torch
+
+    gen = torch.Generator().manual_seed(seed)
+    for _ in range(n_layers):
+        yield synth.layer_weights(w, gen)
+
+
+def hidden_states(synth, w, n: int, seed: int = 1):
+    import torch
+
+    return synth.HiddenStream(w, torch.Generator().manual_seed(seed)).take(n)  # [n,B,H] CPU, workload dtype
+
+
 # ------------------------------------------------------------------------------ CPU arm
 
-def cpu_reference_run(w, n_layers: int, steps: int, warmup: int, seed: int = 0):
-    """Times the reference's CPU path (compiled unmodified, oracle/_ref; else the C oracle) on
-    `n_layers` layers of the workload in fp32 (the reference cache is fp32-only).
+def cpu_reference_run(synth, w, n_layers: int, steps: int, warmup: int):
+    """Times the reference's CPU path (compiled unmodified, oracle/_ref; else the C oracle) on the
+    first `n_layers` layers of the workload, fp32 arithmetic on the SAME bits the GPU arm holds
+    (the workload-dtype weights and hidden states, upcast: the reference cache is fp32-only).
     Returns dict(value tokens/s for the full stack, kind, cores, sample, split)."""
     import torch
 
-    from sparse_transformers_b200.synth import HiddenStream, layer_weights
-
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    gen = torch.Generator().manual_seed(seed)
-    w32 = w.scaled(dtype=torch.float32)
-    weights = [layer_weights(w32, gen) for _ in range(n_layers)]
-    xs = HiddenStream(w32, gen).take(warmup + steps)
+    weights = [tuple(t.float() for t in lw) for lw in gen_layers(synth, w, n_layers)]
+    xs = hidden_states(synth, w, warmup + steps).float()
     kind = "reference"
     try:
         from oracle import ref_python as rp
@@ -201,7 +233,7 @@ def cpu_reference_run(w, n_layers: int, steps: int, warmup: int, seed: int = 0):
     total = sum(times)
     t_layer = total / (steps * n_layers)
     t_token = t_layer * w.layers
-    sample = (f"{n_layers} of {w.layers} layers x {steps} decode steps of {w.name} in fp32 "
+    sample = (f"{n_layers} of {w.layers} layers x {steps} decode steps of {w.name} in fp32 on the GPU arm's bits "
               f"(predictor + WeightCache.update_active_weights + sparse_mlp forward), scaled to {w.layers} layers")
     return {"value": w.B / t_token, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample,
             "ms_per_layer_step": t_layer * 1e3, "ms_per_step": total / steps * 1e3 * w.layers / n_layers}
@@ -211,15 +243,15 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from sparse_transformers_b200.synth import WORKLOADS
-
-    w = WORKLOADS[args.workload]
+    synth = load_synth()
+    w = synth.WORKLOADS[args.workload]
     if args.layers:
         w = w.scaled(layers=args.layers)
-    r = cpu_reference_run(w, min(args.cpu_layers, w.layers), args.steps, args.warmup)
+    steps = max(1, min(args.steps, 512))  # a step is a bounded sample (cpu-layers of the stack): the run ends within minutes
+    r = cpu_reference_run(synth, w, min(args.cpu_layers, w.layers), steps, min(args.warmup, 4))
     line = {
-        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 4), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(w, args.gpus),
         "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -235,65 +267,237 @@ def workload_config(w, n_gpus, allreduce="peer"):
             "parallelism": "single GPU" if n_gpus == 1 else
             f"intermediate dim sharded over {n_gpus} GPUs + all-reduce per layer ("
             + ("peer-memory stores inside the step's kernels" if allreduce == "peer" else "NCCL") + ")",
-            "cache_rows": "copied every step (eager), on a side branch of the step's graph",
+            "inputs": "weights (seed 0) and AR(1) hidden states (seed 1) generated on the CPU and uploaded",
+            "cache_rows": "copied every step (eager), on side branches of the step's graph",
+            "layer_order": "every layer reads the same x; t of layer l+1 and the output sum of layer l overlap the "
+                           "row stream (value_strict_layer_order: nothing of layer l+1 starts before out[l] is complete)"
+                           if n_gpus == 1 and w.B == 1 else "layer after layer on one stream",
             "l2": "distinct weights per layer: one step touches more bytes than the 126 MB L2"}
 
 
 # ------------------------------------------------------------------------------ GPU arm
 
-def run_native(args):
+class _DevBytes:
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class Built:
+    """Layers + stack of one workload on this rank."""
+
+    def __init__(self, layers, stack, peer, kept):
+        self.layers, self.stack, self.peer, self.kept = layers, stack, peer, kept
+
+    def close(self):
+        import torch
+
+        torch.cuda.synchronize()
+        self.stack.close()
+        for l in self.layers:
+            l.close()
+        self.layers = []
+
+
+def build_workload(synth, w, dev, rank, world, allreduce, peer, warm_x, keep=()):
+    """Uploads the CPU-generated weights (sliced per rank) and builds the step object.  `keep`:
+    layer indices whose CPU weights are returned (for the parity check)."""
+    import sparse_transformers_b200 as stb
+    from sparse_transformers_b200.sharded import ShardedLayer, ShardedStack, shard_range
+
+    layers, kept = [], {}
+    for li, (gate, up, down, A, Bm) in enumerate(gen_layers(synth, w, w.layers)):
+        if li in keep:
+            kept[li] = (gate, up, down, A, Bm)
+        if world == 1:
+            layers.append(stb.SparseLayer(gate.to(dev), up.to(dev), down.to(dev), A.to(dev), Bm.to(dev), act=w.act,
+                                          method="threshold", param=w.tau, max_batch=w.B, has_gate=w.has_gate, alias_gate_up=True))
+        else:
+            lo, hi = shard_range(w.I, rank, world)
+            layers.append(ShardedLayer(gate[lo:hi].contiguous().to(dev), up[lo:hi].contiguous().to(dev),
+                                       down[:, lo:hi].contiguous().to(dev), A.to(dev), Bm[lo:hi].contiguous().to(dev), act=w.act,
+                                       method="threshold", param=w.tau, max_batch=w.B, has_gate=w.has_gate,
+                                       peer=peer if allreduce == "peer" else None))
+        del gate, up, down
+    stack = stb.SparseStack(layers, w.B) if world == 1 else ShardedStack(layers, w.B, warm_x)
+    return Built(layers, stack, peer, kept)
+
+
+def time_blocks(stack, xs_dev, cursor, K, blocks, out_dev, barrier, dist, world, dev):
+    """`blocks` timed blocks of exactly K steps each (CUDA events on the launching stream, max over
+    ranks per block).  Returns (list of ms per block, cursor)."""
     import torch
-    import torch.distributed as dist
+
+    ms = []
+    for _ in range(blocks):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            stack.step(xs_dev[cursor % len(xs_dev)], out_dev)
+            cursor += 1
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms.append(float(t.item()))
+    return ms, cursor
+
+
+def parity_check(synth, w, kept, dev, rank, world, allreduce, peer, dist):
+    """2 sampled layers x PARITY_STEPS steps on fresh caches, outside any timed region: the GPU step
+    (all-reduced output at N > 1) against the reference's compiled CPU code (oracle/_ref; the C
+    restatement if that is absent) in fp32 on the same bits.
+      mask_flips        GPU mask bits that differ from the reference's own fp32 nn.Linear pair + threshold
+                        (the GPU rounds t and the scores to the model dtype like the reference would in that
+                        dtype, the fp32 reference arm does not: flips can only sit within rounding distance of tau)
+      max_flip_margin   largest |score - tau| among flipped neurons (fp32 reference score)
+      mask_equal_fixed_order   GPU mask == the CPU restatement with the kernels' documented summation order
+      cache_order_equal every shard's cache order == the reference index plan fed the same masks
+      cache_rows_equal  (N = 1) packed gate/up rows == the compiled reference cache's concat weight
+      out_rel_err       max |out - ref| / max |ref| over layers and steps"""
+    import numpy as np
+    import torch
+
+    import sparse_transformers_b200 as stb
+    from sparse_transformers_b200.sharded import ShardedLayer, ShardedStack, shard_range
+
+    ids = sorted(kept)
+    wp = w.scaled(layers=len(ids))
+    xs = hidden_states(synth, w, PARITY_STEPS + 1, seed=7)
+    lo, hi = shard_range(w.I, rank, world)
+    layers = []
+    for li in ids:
+        gate, up, down, A, Bm = kept[li]
+        if world == 1:
+            layers.append(stb.SparseLayer(gate.to(dev), up.to(dev), down.to(dev), A.to(dev), Bm.to(dev), act=w.act,
+                                          method="threshold", param=w.tau, max_batch=w.B, has_gate=w.has_gate))
+        else:
+            layers.append(ShardedLayer(gate[lo:hi].contiguous().to(dev), up[lo:hi].contiguous().to(dev),
+                                       down[:, lo:hi].contiguous().to(dev), A.to(dev), Bm[lo:hi].contiguous().to(dev), act=w.act,
+                                       method="threshold", param=w.tau, max_batch=w.B, has_gate=w.has_gate,
+                                       peer=peer if allreduce == "peer" else None))
+    # ShardedStack warms up with two eager steps of its warm-up input: the reference side replays them
+    stack = stb.SparseStack(layers, w.B) if world == 1 else ShardedStack(layers, w.B, xs[0].to(dev))
+    warm = [] if world == 1 else [xs[0], xs[0]]
+    local = [l if world == 1 else l.local for l in layers]
+
+    ref = None
+    if rank == 0:
+        from oracle import oracle as orc
+        from oracle import ref_python as rp
+
+        kind = "reference" if rp.have_reference() else "port"
+        ref = []
+        for li in ids:
+            g32, u32, d32, A32, B32 = (t.float() for t in kept[li])
+            rl = rp.RefLayer(g32, u32, d32, A32, B32, act=w.act, tau=w.tau, has_gate=w.has_gate) if kind == "reference" else None
+            ocs = []
+            for q in range(world):
+                oc = orc.OracleCache(shard_range(w.I, q, world)[1] - shard_range(w.I, q, world)[0])
+                oc.update(np.ones(oc.I, bool))
+                ocs.append(oc)
+            ref.append((rl, ocs, (g32, u32, d32, A32, B32)))
+    stats = {"mask_flips": 0, "mask_bits_compared": 0, "max_flip_margin": 0.0, "mask_equal_fixed_order": True,
+             "cache_order_equal": True, "cache_rows_equal": True if world == 1 else None, "out_rel_err": 0.0}
+    odt = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[w.dtype]
+    out = torch.empty(len(ids), w.B, w.H, dtype=w.dtype, device=dev)
+
+    def gather(obj):
+        if world == 1:
+            return [obj]
+        got = [None] * world if rank == 0 else None
+        dist.gather_object(obj, got, dst=0)
+        return got
+
+    def reference_step(k, x, masks, orders, got, check):
+        rl, ocs, (g32, u32, d32, A32, B32) = ref[k]
+        m_gpu = torch.cat(masks)
+        x32 = x.float()
+        if check:
+            s_ref = torch.nn.functional.linear(torch.nn.functional.linear(x32, A32), B32)  # modeling_skip.py:52-53
+            m_ref = (s_ref >= w.tau).any(dim=0)
+            flip = m_gpu != m_ref
+            stats["mask_flips"] += int(flip.sum())
+            stats["mask_bits_compared"] += int(m_gpu.numel())
+            if flip.any():
+                stats["max_flip_margin"] = max(stats["max_flip_margin"], float((s_ref - w.tau).abs().min(dim=0).values[flip].max()))
+            _, s_fix = orc.predictor(x32.numpy(), A32.numpy(), B32.numpy(), odt)
+            _, m_fix = orc.mask_threshold(s_fix, odt, w.tau)
+            stats["mask_equal_fixed_order"] &= bool(np.array_equal(m_fix, m_gpu.numpy()))
+        for q in range(world):
+            qlo, qhi = shard_range(w.I, q, world)
+            ocs[q].update(m_gpu[qlo:qhi].numpy())
+            if check:
+                stats["cache_order_equal"] &= (ocs[q].active + qlo).tolist() == orders[q]
+        if rl is not None:
+            rl.wc.update_active_weights(m_gpu)
+            if check:
+                cw, dw = rl.wc.get_concat_weight(), rl.wc.get_active_down_weight()
+                want = rp.skip_mlp_sparse(x32, cw, dw, w.act, w.has_gate)
+                err = float((got.float() - want).abs().max() / want.abs().max())
+                stats["out_rel_err"] = max(stats["out_rel_err"], err)
+                if world == 1:
+                    stats["cache_rows_equal"] &= bool(torch.equal(local[k].concat_weight().float().cpu(), cw))
+        elif check:
+            act = torch.cat([torch.from_numpy(ocs[q].active.astype(np.int64)) + shard_range(w.I, q, world)[0] for q in range(world)])
+            gg, uu, dd = g32[act], u32[act], d32[:, act]
+            want = rp.skip_mlp_sparse(x32, torch.cat([gg, uu]) if w.has_gate else uu, dd, w.act, w.has_gate)
+            stats["out_rel_err"] = max(stats["out_rel_err"], float((got.float() - want).abs().max() / want.abs().max()))
+
+    # the sharded stack's warm-up steps advanced the shard caches with xs[0]: bring the reference side along
+    if warm:
+        for k in range(len(ids)):
+            masks = gather(local[k].mask().cpu())
+            if rank == 0:
+                reference_step(k, xs[0], masks, None, None, check=False)
+    for t in range(1, PARITY_STEPS + 1):
+        x = xs[t]
+        stack.step(x.to(dev), out)
+        torch.cuda.synchronize()
+        got = out.cpu()
+        for k in range(len(ids)):
+            masks = gather(local[k].mask().cpu())
+            orders = gather((local[k].active_indices() + lo).tolist())
+            if rank == 0:
+                reference_step(k, x, masks, orders, got[k], check=True)
+    if peer is not None and allreduce == "peer":
+        stats["peer_wait_timed_out"] = bool(peer.timed_out())
+    stack.close()
+    for l in layers:
+        l.close()
+    if rank != 0:
+        return None
+    stats.update({"layers": ids, "steps": PARITY_STEPS, "reference": kind, "rows": w.B,
+                  "score_rounding_step_at_tau": (0.0 if w.dtype == torch.float32 else
+                                                 2.0 ** (math.floor(math.log2(abs(w.tau))) - (10 if w.dtype == torch.float16 else 7))),
+                  "tolerance_out_rel_err": 1e-5 if w.dtype == torch.float32 else 2e-2})
+    return stats
+
+
+def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=False):
+    """Builds the workload on this rank, times it, checks parity.  Returns the result dict (rank 0)
+    or None.  extras_mode: bounded run for an extra key (fewer blocks, no CPU baseline, no stage pass)."""
+    import torch
 
     import sparse_transformers_b200 as stb
     from sparse_transformers_b200 import _capi as C
-    from sparse_transformers_b200.sharded import PeerExchange, ShardedLayer, ShardedStack, shard_range
-    from sparse_transformers_b200.synth import HiddenStream, WORKLOADS, layer_weights
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    if world != args.gpus and rank == 0:
-        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
-
-    w = WORKLOADS[args.workload]
-    if args.layers:
-        w = w.scaled(layers=args.layers)
-    K_steps, W_steps = args.steps, max(args.warmup, 0)
-
-    # ---- weights: generated on the device (identical on every rank), sliced per rank
-    gen = torch.Generator(device=dev).manual_seed(0)
-    layers = []
-    peer = PeerExchange(w.B * w.H) if world > 1 and args.allreduce == "peer" else None
-    cpu_weights = []  # first layers kept on the host for the CPU baseline sample (fp32)
-    for li in range(w.layers):
-        gate, up, down, A, Bm = layer_weights(w, gen, device=dev)
-        if world == 1:
-            layers.append(stb.SparseLayer(gate, up, down, A, Bm, act=w.act, method="threshold", param=w.tau,
-                                          max_batch=w.B, has_gate=w.has_gate, alias_gate_up=True))
-        else:
-            lo, hi = shard_range(w.I, rank, world)
-            layers.append(ShardedLayer(gate[lo:hi].contiguous(), up[lo:hi].contiguous(), down[:, lo:hi].contiguous(), A,
-                                       Bm[lo:hi].contiguous(), act=w.act, method="threshold", param=w.tau,
-                                       max_batch=w.B, has_gate=w.has_gate, peer=peer))
-        del gate, up, down
-    torch.cuda.synchronize()
-
-    n_inst = 8  # steps of the stage-timing pass
-    xs_cpu = HiddenStream(w, torch.Generator().manual_seed(1)).take(3 * (W_steps + K_steps) + n_inst + 16)
+    K_steps = args.steps if not extras_mode else min(args.steps, 16)
+    W_steps = max(args.warmup, 3)
+    blocks = args.blocks or 25
+    blocks = max(3, min(blocks, 8192 // max(K_steps, 1)))
+    if extras_mode:
+        blocks = 3
+    n_e2e_blocks = 1 if extras_mode else 3
+    n_x = min(4096, W_steps * 4 + K_steps * (blocks + n_e2e_blocks + 3) + 64)
+    xs_cpu = hidden_states(synth, w, n_x)
     xs_dev = xs_cpu.to(dev)
-    cursor = 0
-
-    if world == 1:
-        stack = stb.SparseStack(layers, w.B)
-    else:
-        stack = ShardedStack(layers, w.B, xs_dev[0])
-        cursor = 1
+    keep = (0, w.layers - 1) if not args.no_parity else ()
+    built = build_workload(synth, w, dev, rank, world, args.allreduce, peer, xs_dev[0], keep=keep)
+    layers, stack = built.layers, built.stack
+    local = [l if world == 1 else l.local for l in layers]
+    torch.cuda.synchronize()
 
     def barrier():
         if world > 1:
@@ -301,78 +505,87 @@ def run_native(args):
         torch.cuda.synchronize()
 
     out_dev = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=dev)
-
-    # ---- device-timed region (inputs resident in HBM)
+    cursor = 1
     for _ in range(W_steps):
-        stack.step(xs_dev[cursor], out_dev)
+        stack.step(xs_dev[cursor % n_x], out_dev)
         cursor += 1
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(dev.index)
     if rank == 0:
         sampler.start()
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(K_steps):
-        stack.step(xs_dev[cursor], out_dev)
-        cursor += 1
-    ev1.record()
-    barrier()
-    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_total = float(ms.item())
+    ms_blocks, cursor = time_blocks(stack, xs_dev, cursor, K_steps, blocks, out_dev, barrier, dist, world, dev)
     clocks = sampler.stop() if rank == 0 else None
+    ms_med = statistics.median(ms_blocks)
 
     # ---- end to end through the host-buffer call (pinned host in, result back to host)
     x_pin = torch.empty(w.B, w.H, dtype=w.dtype).pin_memory()
     o_pin = torch.empty(w.layers, w.B, w.H, dtype=w.dtype).pin_memory()
     for _ in range(W_steps):
-        x_pin.copy_(xs_cpu[cursor])
+        x_pin.copy_(xs_cpu[cursor % n_x])
         stack.step_host(x_pin, o_pin)
         cursor += 1
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K_steps):
-        x_pin.copy_(xs_cpu[cursor])
-        stack.step_host(x_pin, o_pin)
-        cursor += 1
-    barrier()
-    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-    e2e_total = float(e2e_s.item())
+    e2e_blocks = []
+    for _ in range(n_e2e_blocks):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(K_steps):
+            x_pin.copy_(xs_cpu[cursor % n_x])
+            stack.step_host(x_pin, o_pin)
+            cursor += 1
+        barrier()
+        t = torch.tensor([time.perf_counter() - t0], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_blocks.append(float(t.item()))
+    e2e_s = statistics.median(e2e_blocks)
 
-    # ---- the same steps with lazy packed-row copies (index plan every step, rows on demand)
-    lazy_value = None
-    if world == 1:
+    res = {"ms_blocks": ms_blocks, "ms_per_step": ms_med / K_steps, "value": w.B / (ms_med / K_steps * 1e-3),
+           "e2e_value": w.B / (e2e_s / K_steps), "e2e_ms_per_step": e2e_s / K_steps * 1e3,
+           "launches_per_step": int(stack.launches_per_step), "steps": K_steps, "warmup": W_steps, "blocks": blocks,
+           "clocks": clocks}
+    ks = [l.num_active() for l in local]
+    dks = [l.update_stats()[2] for l in local]
+    res["active_neurons_mean"] = float(sum(ks)) * (world if world > 1 else 1) / len(ks)
+    res["rows_rewritten_mean"] = float(sum(dks)) * (world if world > 1 else 1) / len(dks)
+
+    # ---- variants of the same steps (single GPU): other layer order / kernels / lazy cache rows
+    def variant(env=None, lazy=False):
+        old = {}
+        for k, v in (env or {}).items():
+            old[k] = os.environ.get(k)
+            os.environ[k] = v
         for l in layers:
-            l.set_lazy_cache(True)
-        lazy_stack = stb.SparseStack(layers, w.B)
+            l.set_lazy_cache(lazy)
+        st = stb.SparseStack(layers, w.B)
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+        c = cursor
         for _ in range(W_steps):
-            lazy_stack.step(xs_dev[cursor % len(xs_dev)], out_dev)
-            cursor += 1
-        torch.cuda.synchronize()
-        n_lazy = max(8, K_steps // 4)
-        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0.record()
-        for _ in range(n_lazy):
-            lazy_stack.step(xs_dev[cursor % len(xs_dev)], out_dev)
-            cursor += 1
-        l1.record()
-        torch.cuda.synchronize()
-        lazy_value = w.B / (l0.elapsed_time(l1) / n_lazy * 1e-3)
-        lazy_stack.close()
+            st.step(xs_dev[c % n_x], out_dev)
+            c += 1
+        ms, _ = time_blocks(st, xs_dev, c, min(K_steps, 64), 3, out_dev, barrier, dist, world, dev)
+        st.close()
         for l in layers:
             l.set_lazy_cache(False)
+        return w.B / (statistics.median(ms) / min(K_steps, 64) * 1e-3)
 
-    # ---- stage timing pass (single GPU): the dominant kernel's launches timed alone with
-    #      CUDA events on the launching stream, all layers back to back in one graph
-    roofline, stages_us, k_mean, dk_mean = None, None, None, None
-    if world == 1:
-        # one row under the threshold rule: [t = A x] [scores + mask + gather + MLP] [sum of partials];
-        # otherwise: [predictor] [gate/up] [down]
+    if world == 1 and not extras_mode:
+        res["value_lazy_cache_rows"] = variant(lazy=True)
+        if w.B == 1:
+            res["value_strict_layer_order"] = variant({"STX_STACK_STRICT": "1"})
+            res["value_per_layer_kernels"] = variant({"STX_STACK_KERNEL": "layers"})
+
+    # ---- stage timing pass (single GPU): the dominant kernel's launches timed alone with CUDA
+    #      events on the launching stream
+    if world == 1 and not extras_mode:
+        persistent = w.B == 1 and stack.launches_per_step <= 1 + 2 * w.layers
         fused = layers[0].single_row_fused(w.B)
-        if fused:
+        if persistent:
+            names = ("stack_kernel", "plan", "copy")
+            bits = (C.STAGE_PREDICT | C.STAGE_MLP, C.STAGE_PLAN, C.STAGE_COPY)
+        elif fused:
             names = ("predict_t", "plan", "copy", "mlp_b1", "reduce")
             bits = (C.STAGE_PREDICT_T, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_PREDICT_MASK | C.STAGE_MLP_GATEUP,
                     C.STAGE_PREDICT_MASK | C.STAGE_MLP_DOWN)
@@ -381,13 +594,12 @@ def run_native(args):
             bits = (C.STAGE_PREDICT, C.STAGE_PLAN, C.STAGE_COPY, C.STAGE_MLP_GATEUP, C.STAGE_MLP_DOWN)
         st = {n: stb.SparseStack(layers, w.B, stages=b) for n, b in zip(names, bits)}
         nbytes = w.B * w.H * w.dtype.itemsize
-        xin = [torch.as_tensor(_DevBytes(st[n].buffers()[0], nbytes), device=dev) for n in (names[0], names[3])]
+        xin = [torch.as_tensor(_DevBytes(s_.buffers()[0], nbytes), device=dev) for s_ in st.values()]
         acc = dict.fromkeys(names, 0.0)
-        ks, dks = [], []
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
-        n_warm = 2
+        n_inst, n_warm = 16, 3
         for i in range(n_inst + n_warm):
-            x = xs_dev[cursor % len(xs_dev)]
+            x = xs_dev[cursor % n_x]
             cursor += 1
             for v in xin:  # stage the input in the stacks' own buffers, outside the timed brackets
                 v.copy_(x.contiguous().view(torch.uint8).reshape(-1))
@@ -401,74 +613,141 @@ def run_native(args):
                 continue
             for n, a, b in zip(names, evs[:-1], evs[1:]):
                 acc[n] += a.elapsed_time(b) * 1e3 / w.layers  # microseconds per layer
-            for l in layers:
-                ks.append(l.num_active())
-                dks.append(l.update_stats()[2])
         stages_us = {k: v / n_inst for k, v in acc.items()}
-        k_mean, dk_mean = statistics.mean(ks), statistics.mean(dks)
-        peak, peak_src = measured_peak_gbs()
+        k_mean = statistics.mean(l.num_active() for l in layers)
+        dk_mean = statistics.mean(l.update_stats()[2] for l in layers)
+        peak, peak_src = measured_peak("hbm_gbs", 6650.0, "copy bandwidth")
         es = w.dtype.itemsize
-        if fused:
-            # k_mlp_b1: active gate/up/down rows + the predictor's up matrix + x + t + mask bytes.  The
-            # per-CTA partial vectors it writes are an artefact of the implementation, not counted.
-            top, second, k1, k2 = "mlp_b1", "reduce", ("k_mlp_b1" if w.B == 1 else "k_mlp_bn"), "k_partial_reduce"
-            alg = (es * (3 if w.has_gate else 2) * k_mean * w.H + es * w.I * w.r + es * w.B * w.H + 4 * w.B * w.r + w.I / 8)
-            alg2 = (4 * (torch.cuda.get_device_properties(dev).multi_processor_count - 1) + es) * w.B * w.H
+        nmat = 3 if w.has_gate else 2
+        if persistent:
+            # one launch = all layers: per layer the active gate/up/down rows + both predictor matrices + x + t + mask
+            # bytes (read and written).  The per-CTA partial vectors are an artefact of the implementation, not counted.
+            top, k1, launches = "stack_kernel", "k_stack_b1", 1
+            alg_layer = es * nmat * k_mean * w.H + es * (w.I * w.r + w.r * w.H) + 2 * es * w.H + 8 * w.r + 2 * w.I / 8
+            alg = alg_layer * w.layers
+            us = stages_us[top] * w.layers
+            second = ("k_cache_copy_rows", "copy", 2 * nmat * dk_mean * w.H * es)
+        elif fused:
+            top, k1, launches = "mlp_b1", ("k_mlp_b1" if w.B == 1 else "k_mlp_bn"), w.layers
+            alg = es * nmat * k_mean * w.H + es * w.I * w.r + es * w.B * w.H + 4 * w.B * w.r + w.I / 8
+            us = stages_us[top]
+            second = ("k_partial_reduce", "reduce", (4 * (torch.cuda.get_device_properties(dev).multi_processor_count - 1) + es) * w.B * w.H)
         else:
-            top, second, k1, k2 = "gateup", "down", ("k_gateup_mma" if w.B >= 4 else "k_gateup_tma"), "k_down_rows"
-            alg = es * (2 if w.has_gate else 1) * k_mean * w.H + es * w.B * w.H + 4 * w.B * k_mean  # gate/up rows + x + a
-            alg2 = es * k_mean * w.H + 4 * w.B * k_mean + es * w.B * w.H                            # down rows + a + out
-        achieved = alg / (stages_us[top] * 1e-6) / 1e9
-        ratio = traffic_ratio(k1)
-        roofline = {"kernel": k1, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000_gbs": achieved / 8000.0,
-                    "traffic": (ratio * alg if ratio else None),
-                    "algorithmic_bytes_per_launch": alg, "us_per_launch": stages_us[top],
-                    "launches_timed": n_inst * w.layers,
-                    "second_kernel": {"kernel": k2, "algorithmic_bytes_per_launch": alg2,
-                                      "us_per_launch": stages_us[second],
-                                      "achieved": alg2 / (stages_us[second] * 1e-6) / 1e9,
-                                      "frac": alg2 / (stages_us[second] * 1e-6) / 1e9 / peak}}
+            top, k1, launches = "gateup", ("k_gateup_mma" if w.B >= 4 else "k_gateup_tma"), w.layers
+            alg = es * (2 if w.has_gate else 1) * k_mean * w.H + es * w.B * w.H + 4 * w.B * k_mean
+            us = stages_us[top]
+            second = ("k_down_rows", "down", es * k_mean * w.H + 4 * w.B * k_mean + es * w.B * w.H)
+        achieved = alg / (us * 1e-6) / 1e9
+        ratio, tsrc = traffic_ratio(k1)
+        res["roofline"] = {"kernel": k1, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                           "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000_gbs": achieved / 8000.0,
+                           "traffic": (ratio * alg if ratio else None), "traffic_source": tsrc,
+                           "algorithmic_bytes_per_launch": alg, "us_per_launch": us,
+                           "launches_timed": n_inst * launches, "layers_per_launch": w.layers if persistent else 1,
+                           "second_kernel": {"kernel": second[0], "algorithmic_bytes_per_launch": second[2],
+                                             "us_per_launch": stages_us[second[1]],
+                                             "achieved": second[2] / (stages_us[second[1]] * 1e-6) / 1e9,
+                                             "frac": second[2] / (stages_us[second[1]] * 1e-6) / 1e9 / peak}}
+        res["stages_us_per_layer"] = stages_us
+        res["active_neurons_mean"], res["rows_rewritten_mean"] = k_mean, dk_mean
+        step_alg = layer_step_algorithmic_bytes(w, k_mean, dk_mean) * w.layers
+        res["step_algorithmic_gbs"] = step_alg / (res["ms_per_step"] * 1e-3) / 1e9
+        res["step_frac_of_peak"] = res["step_algorithmic_gbs"] / peak
         for s_ in st.values():
             s_.close()
 
+    built.close()
+    if world > 1 and peer is not None and args.allreduce == "peer" and peer.timed_out():
+        print(f"rank {rank}: a wait for a peer's partial sums timed out; the numbers of this run are invalid", file=sys.stderr)
+        res["peer_wait_timed_out"] = True
+    torch.cuda.empty_cache()
+    if not args.no_parity:
+        res["parity"] = parity_check(synth, w, built.kept, dev, rank, world, args.allreduce, peer, dist)
+    built.kept = {}
+    return res if rank == 0 else None
+
+
+def run_native(args):
+    import torch
+    import torch.distributed as dist
+
+    from sparse_transformers_b200.sharded import PeerExchange
+
+    synth = load_synth()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     if world > 1:
-        stack.close()
+        dist.init_process_group("nccl", device_id=dev)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+
+    w = synth.WORKLOADS[args.workload]
+    if args.layers:
+        w = w.scaled(layers=args.layers)
+    wc5 = synth.WORKLOADS["C5"]
+    peer = None
+    if world > 1 and args.allreduce == "peer":
+        peer = PeerExchange(max(w.B * w.H, wc5.B * wc5.H))
+
+    r = stack_measure(synth, w, args, dev, rank, world, dist, peer)
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": world, "steps": r["steps"], "warmup": r["warmup"],
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
+            "vs_baseline": None, "dtype": DTYPE_NAME[str(w.dtype)], "data": "synthetic",
+            "config": workload_config(w, world, args.allreduce),
+            "blocks": r["blocks"],
+            "value_spread": {"min": w.B / (max(r["ms_blocks"]) / r["steps"] * 1e-3), "max": w.B / (min(r["ms_blocks"]) / r["steps"] * 1e-3),
+                             "what": f"tokens/s of the slowest and fastest of {r['blocks']} timed blocks of {r['steps']} steps; value is the median block"},
+            "e2e": {"value": r["e2e_value"], "unit": UNIT, "ms_per_step": r["e2e_ms_per_step"],
+                    "h2d_bytes_per_step": w.B * w.H * w.dtype.itemsize, "d2h_bytes_per_step": w.layers * w.B * w.H * w.dtype.itemsize},
+            "gpu_launches": r["launches_per_step"] * r["steps"],
+            "gpu_launches_per_step": r["launches_per_step"],
+            "clocks": r["clocks"],
+        }
+        for k in ("value_lazy_cache_rows", "value_strict_layer_order", "value_per_layer_kernels", "roofline", "stages_us_per_layer",
+                  "active_neurons_mean", "rows_rewritten_mean", "step_algorithmic_gbs", "step_frac_of_peak", "parity", "peer_wait_timed_out"):
+            if k in r:
+                line[k] = r[k]
+
+    # ---- extra keys: the other configurations, bounded
+    if not args.no_extras and args.workload == "C2":
+        ex = argparse.Namespace(**vars(args))
+        ex.steps, ex.warmup, ex.blocks = 16, 3, 3
+        try:
+            c5 = stack_measure(synth, wc5, ex, dev, rank, world, dist, peer, extras_mode=True)
+            if rank == 0:
+                line["c5"] = extra_summary(wc5, c5, world, args.allreduce)
+        except Exception as e:  # an extra key never costs the headline
+            if rank == 0:
+                line["c5"] = {"error": f"{type(e).__name__}: {e}"}
+        if world == 1:
+            for key, fn in (("c3", lambda: extra_summary(synth.WORKLOADS["C3"],
+                                                         stack_measure(synth, synth.WORKLOADS["C3"], ex, dev, 0, 1, dist, None, extras_mode=True), 1, "peer")),
+                            ("c1", lambda: extra_summary(synth.WORKLOADS["C1"],
+                                                         stack_measure(synth, synth.WORKLOADS["C1"], ex, dev, 0, 1, dist, None, extras_mode=True), 1, "peer")),
+                            ("c4", lambda: prefill_measure(args, dev)),
+                            ("dropin", lambda: dropin_measure(synth, w, dev)),
+                            ("c2_e2e", lambda: llama_skip_measure(args, dev, runs=2))):
+                try:
+                    line[key] = fn()
+                except Exception as e:
+                    line[key] = {"error": f"{type(e).__name__}: {e}"}
+                torch.cuda.empty_cache()
+
     if peer is not None:
-        if peer.timed_out():
-            print(f"rank {rank}: a wait for a peer's partial sums timed out; the numbers of this run are invalid",
-                  file=sys.stderr)
         peer.close()
     if rank != 0:
         _finish_distributed(dist, world)
         return
-
-    ms_step = ms_total / K_steps
-    value = w.B / (ms_step * 1e-3)
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K_steps, "warmup": W_steps,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
-        "vs_baseline": None, "dtype": DTYPE_NAME[str(w.dtype)], "data": "synthetic",
-        "config": workload_config(w, world, args.allreduce),
-        "e2e": {"value": w.B / (e2e_total / K_steps), "unit": UNIT, "ms_per_step": e2e_total / K_steps * 1e3,
-                "h2d_bytes_per_step": w.B * w.H * w.dtype.itemsize, "d2h_bytes_per_step": w.layers * w.B * w.H * w.dtype.itemsize},
-        "gpu_launches": int(stack.launches_per_step * K_steps),
-        "clocks": clocks,
-    }
-    if lazy_value is not None:
-        line["value_lazy_cache_rows"] = lazy_value
-    if roofline:
-        line["roofline"] = roofline
-        line["stages_us_per_layer"] = stages_us
-        line["active_neurons_mean"] = k_mean
-        line["rows_rewritten_mean"] = dk_mean
-        step_alg = layer_step_algorithmic_bytes(w, k_mean, dk_mean) * w.layers
-        line["step_algorithmic_gbs"] = step_alg / (ms_step * 1e-3) / 1e9
-        line["step_frac_of_peak"] = line["step_algorithmic_gbs"] / roofline["peak"]
     if world == 1 and not args.no_cpu_baseline:
-        # free the device side first? not needed: the CPU sample uses its own host copies
         try:
-            cb = cpu_reference_run(w, min(args.cpu_layers, w.layers), steps=24, warmup=2)
+            cb = cpu_reference_run(synth, w, min(args.cpu_layers, w.layers), steps=24, warmup=2)
             line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
         except Exception as e:  # the baseline is a reported extra, never a reason to lose the line
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
@@ -477,9 +756,26 @@ def run_native(args):
     _finish_distributed(dist, world)
 
 
+def extra_summary(w, r, world, allreduce):
+    if r is None:
+        return None
+    out = {"workload": w.name, "tokens_per_s": r["value"], "ms_per_step": r["ms_per_step"], "e2e_tokens_per_s": r["e2e_value"],
+           "steps": r["steps"], "blocks": r["blocks"], "n_gpus": world, "rows": w.B, "layers": w.layers,
+           "active_neurons_mean": r["active_neurons_mean"], "rows_rewritten_mean": r["rows_rewritten_mean"],
+           "gpu_launches_per_step": r["launches_per_step"]}
+    peak, _ = measured_peak("hbm_gbs", 6650.0, "copy bandwidth")
+    alg = layer_step_algorithmic_bytes(w, r["active_neurons_mean"], r["rows_rewritten_mean"]) * w.layers
+    out["step_algorithmic_gbs"] = alg / (r["ms_per_step"] * 1e-3) / 1e9
+    out["step_frac_of_hbm_peak"] = out["step_algorithmic_gbs"] / peak / world
+    if "parity" in r:
+        out["parity"] = r["parity"]
+    return out
+
+
 def _finish_distributed(dist, world):
-    """Leave a multi-rank run: barrier, then exit without destroy_process_group(), which was
-    seen to block after NCCL collectives had been captured in CUDA graphs."""
+    """Leave a multi-rank run: the peer objects are closed and every captured graph is released before
+    this point; the ranks meet once more and exit without destroy_process_group(), which was seen to
+    block at the end of such runs."""
     if world > 1:
         import torch
 
@@ -490,37 +786,29 @@ def _finish_distributed(dist, world):
         os._exit(0)
 
 
-class _DevBytes:
-    def __init__(self, ptr: int, nbytes: int):
-        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+# ------------------------------------------------------------------------------ other workloads
 
-
-def run_prefill(args):
-    """C4: the op-level prefill path (rows x packed active weights -> tcgen05 GEMMs) over a sweep
-    of active fractions; prints one JSON line with the tensor roofline at K = I."""
+def prefill_measure(args, dev):
+    """C4: the op-level prefill path (rows x packed active weights -> tcgen05 GEMMs) over a sweep of
+    active fractions."""
     import ctypes
 
     import torch
 
     from sparse_transformers_b200 import _capi as C
-    from sparse_transformers_b200.synth import WORKLOADS
 
-    w = WORKLOADS["C4"]
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    gen = torch.Generator(device=dev).manual_seed(0)
+    synth = load_synth()
+    w = synth.WORKLOADS["C4"]
+    gen = torch.Generator().manual_seed(0)
     T, H, I = w.B, w.H, w.I
-    x = torch.randn(T, H, generator=gen, device=dev).to(w.dtype)
-    cw_full = (torch.randn(2 * I, H, generator=gen, device=dev) * w.wstd).to(w.dtype)
-    dp_full = (torch.randn(I, H, generator=gen, device=dev) * w.wstd).to(w.dtype)
+    x = torch.randn(T, H, generator=gen).to(w.dtype).to(dev)
+    cw_full = (torch.randn(2 * I, H, generator=gen) * w.wstd).to(w.dtype).to(dev)
+    dp_full = (torch.randn(I, H, generator=gen) * w.wstd).to(w.dtype).to(dev)
     out = torch.empty(T, H, dtype=w.dtype, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
-    try:
-        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
-        peak_src = "measured (MEASURED_PEAKS.json cuBLAS bf16 burst)"
-    except Exception:
-        peak, peak_src = 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+    peak, peak_src = measured_peak("bf16_tflops", 1590.0, "cuBLAS bf16 burst")
     sweep = {}
+    steps = max(4, min(args.steps, 16))
     for frac in (0.10, 0.25, 0.50, 1.00):
         K = int(I * frac)
         cw = torch.cat([cw_full[:K], cw_full[I:I + K]]).contiguous()
@@ -537,7 +825,6 @@ def run_prefill(args):
             call()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        steps = max(4, min(args.steps, 32))
         e0.record()
         for _ in range(steps):
             call()
@@ -548,29 +835,70 @@ def run_prefill(args):
                                 "rows_per_s": T / (ms * 1e-3)}
         del cw, dp, comb, scratch
     top = sweep["1.00"]
-    line = {"metric": "sparse_mlp_prefill_tflops", "value": top["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
-            "steps": max(4, min(args.steps, 32)), "warmup": max(3, args.warmup), "ms_per_step": top["ms"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": w.name, "rows": T, "hidden": H, "intermediate": I, "activation": "relu",
-                       "l2": "x (64 MB) + packed weights (270 MB at K = I) exceed the 126 MB L2"},
+    return {"workload": w.name, "tflops": top["tflops"], "ms_per_step": top["ms"], "rows": T, "steps": steps,
             "roofline": {"kernel": "k_umma_gemm", "bound": "tensor", "achieved": top["tflops"], "peak": peak,
                          "unit": "TFLOP/s", "frac": top["tflops"] / peak, "peak_source": peak_src, "traffic": None,
                          "flops_per_step": 6.0 * T * H * I},
-            "k_sweep": sweep, "gpu_launches": 3 * max(4, min(args.steps, 32))}
+            "k_sweep": sweep, "gpu_launches": 3 * steps,
+            "l2": "x (64 MB) + packed weights (270 MB at K = I) exceed the 126 MB L2"}
+
+
+def run_prefill(args):
+    import torch
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    r = prefill_measure(args, dev)
+    line = {"metric": "sparse_mlp_prefill_tflops", "value": r["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": r["steps"], "warmup": max(3, args.warmup), "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": r["workload"], "rows": r["rows"], "activation": "relu", "l2": r["l2"]},
+            "roofline": r["roofline"], "k_sweep": r["k_sweep"], "gpu_launches": r["gpu_launches"]}
     print(json.dumps(line), flush=True)
 
 
-def run_llama_skip(args):
-    """`--workload C2-e2e`: the Llama-3.2-3B-shaped LlamaSkip host end to end (random-init weights,
-    512 random prompt ids, 128 greedy tokens): TTFT and output tokens/s as the reference's benchmark
-    defines them.  Prefill, the q/k/v projection and lm_head are torch ops; the decode-time MLP, norms,
-    attention and output projection are this library."""
+def dropin_measure(synth, w, dev, steps: int = 24):
+    """C2 through the reference-named API only, as src/modeling_skip.py:204-217,114-117 calls it:
+    predict_mask -> WeightCache.update_active_weights -> get_concat_weight / get_active_down_weight ->
+    sparse_mlp.forward, layer after layer from Python (each getter reads K back from the device)."""
+    import torch
+
+    import sparse_transformers_b200 as stb
+
+    n_layers = w.layers
+    caches, preds = [], []
+    for (gate, up, down, A, Bm) in gen_layers(synth, w, n_layers):
+        caches.append(stb.WeightCache(torch.ones(w.I, dtype=torch.bool, device=dev), w.H, gate.to(dev), up.to(dev), down.to(dev), True))
+        preds.append((A.to(dev), Bm.to(dev)))
+    xs = hidden_states(synth, w, steps + 4).to(dev)
+    down_buf = torch.zeros(1, w.H, dtype=w.dtype, device=dev)
+    comb_buf = torch.zeros(1, 2, dtype=w.dtype, device=dev)
+
+    def token(x):
+        for wc, (A, Bm) in zip(caches, preds):
+            mask = torch.ops.sparse_mlp.predict_mask(x, A, Bm, "threshold", w.tau)
+            wc.update_active_weights(mask)
+            stb.sparse_mlp_forward(x, wc.get_concat_weight(), wc.get_active_down_weight(), down_buf, comb_buf, w.act)
+    for i in range(4):
+        token(xs[i])
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(4, 4 + steps):
+        token(xs[i])
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    del caches, preds
+    return {"tokens_per_s": w.B / dt, "ms_per_step": dt * 1e3, "steps": steps,
+            "path": "torch.ops.sparse_mlp.predict_mask -> WeightCache.update_active_weights -> get_concat_weight -> "
+                    "get_active_down_weight -> torch.ops.sparse_mlp.forward per layer, called from Python (wall clock)",
+            "host_syncs_per_layer": 2}
+
+
+def llama_skip_measure(args, dev, runs: int = 3):
     import torch
 
     from sparse_transformers_b200.llama_skip import LlamaSkipConfig, LlamaSkipModel
 
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
-    dev = torch.device("cuda", 0)
     cfg = LlamaSkipConfig(layers=args.layers or 28)
     prompt = torch.randint(0, cfg.vocab, (512,), generator=torch.Generator().manual_seed(0)).to(dev)
     n_new = 128
@@ -579,25 +907,37 @@ def run_llama_skip(args):
         cfg.lazy_cache = lazy
         m = LlamaSkipModel(cfg, dev, seed=0)
         m.generate(prompt, 16)  # warm-up: cuBLAS handles, graph capture
-        runs = [m.generate(prompt, n_new) for _ in range(3)]
-        best = max(runs, key=lambda r: r["output_tokens_per_s"])
+        rs = [m.generate(prompt, n_new) for _ in range(runs)]
+        best = max(rs, key=lambda r: r["output_tokens_per_s"])
         dens = [float(L["sparse"].num_active()) / cfg.intermediate for L in m.layers]
-        out["lazy" if lazy else "eager"] = dict(ttft_s=min(r["ttft_s"] for r in runs), output_tokens_per_s=best["output_tokens_per_s"],
+        out["lazy" if lazy else "eager"] = dict(ttft_s=min(r["ttft_s"] for r in rs), output_tokens_per_s=best["output_tokens_per_s"],
                                                 total_tokens_per_s=best["total_tokens_per_s"], active_fraction=sum(dens) / len(dens))
         m.close()
         del m
         torch.cuda.empty_cache()
     e = out["eager"]
+    return {"output_tokens_per_s": e["output_tokens_per_s"], "ttft_s": e["ttft_s"], "total_tokens_per_s": e["total_tokens_per_s"],
+            "active_fraction_last_token": e["active_fraction"], "output_tokens_per_s_lazy_cache_rows": out["lazy"]["output_tokens_per_s"],
+            "config": {"workload": "C2-llamaskip-3b-e2e-fp16", "layers": cfg.layers, "hidden": cfg.hidden, "intermediate": cfg.intermediate,
+                       "heads": cfg.heads, "kv_heads": cfg.kv_heads, "vocab": cfg.vocab, "rope_theta": cfg.rope_theta,
+                       "predictor_rank": cfg.predictor_rank, "density_target": cfg.density, "prompt_tokens": 512, "new_tokens": n_new,
+                       "decode": "one CUDA graph per token; sparse MLP, add+RMSNorm, RoPE+KV append+attention and the output projection are this library's kernels; q/k/v projection and lm_head are torch matmuls",
+                       "prefill": "dense (torch GEMMs), as the reference does for sequences longer than one token"}}
+
+
+def run_llama_skip(args):
+    """`--workload C2-e2e`: the Llama-3.2-3B-shaped LlamaSkip host end to end (random-init weights,
+    512 random prompt ids, 128 greedy tokens): TTFT and output tokens/s as the reference's benchmark
+    defines them."""
+    import torch
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    r = llama_skip_measure(args, torch.device("cuda", 0))
     print(json.dumps({
-        "metric": "llamaskip_output_tokens_per_s", "value": e["output_tokens_per_s"], "unit": UNIT, "n_gpus": 1,
-        "higher_is_better": True, "dtype": "f16", "data": "synthetic", "ttft_s": e["ttft_s"],
-        "total_tokens_per_s": e["total_tokens_per_s"], "active_fraction_last_token": e["active_fraction"],
-        "value_lazy_cache_rows": out["lazy"]["output_tokens_per_s"], "vs_baseline": None,
-        "config": {"workload": "C2-llamaskip-3b-e2e-fp16", "layers": cfg.layers, "hidden": cfg.hidden, "intermediate": cfg.intermediate,
-                   "heads": cfg.heads, "kv_heads": cfg.kv_heads, "vocab": cfg.vocab, "rope_theta": cfg.rope_theta,
-                   "predictor_rank": cfg.predictor_rank, "density_target": cfg.density, "prompt_tokens": 512, "new_tokens": n_new,
-                   "decode": "one CUDA graph per token; sparse MLP, add+RMSNorm, RoPE+KV append+attention and the output projection are this library's kernels; q/k/v projection and lm_head are torch matmuls",
-                   "prefill": "dense (torch GEMMs), as the reference does for sequences longer than one token"}}), flush=True)
+        "metric": "llamaskip_output_tokens_per_s", "value": r["output_tokens_per_s"], "unit": UNIT, "n_gpus": 1,
+        "higher_is_better": True, "dtype": "f16", "data": "synthetic", "ttft_s": r["ttft_s"],
+        "total_tokens_per_s": r["total_tokens_per_s"], "active_fraction_last_token": r["active_fraction_last_token"],
+        "value_lazy_cache_rows": r["output_tokens_per_s_lazy_cache_rows"], "vs_baseline": None, "config": r["config"]}), flush=True)
 
 
 def main():
