@@ -65,6 +65,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (no c1/c3/c4/c5/c2_e2e/dropin keys)")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-variants", action="store_true",
+                    help="skip the variant stacks (lazy rows, strict order, per-layer kernels) and the stage timing pass: few launches, for profiler captures")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
                     help="N>1: sum of the shards' outputs inside the library's kernels over peer memory, or NCCL")
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers in the CPU baseline sample")
@@ -486,7 +488,7 @@ def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=Fals
     K_steps = args.steps if not extras_mode else min(args.steps, 16)
     W_steps = max(args.warmup, 3)
     blocks = args.blocks or 25
-    blocks = max(3, min(blocks, 8192 // max(K_steps, 1)))
+    blocks = max(1, min(blocks, 8192 // max(K_steps, 1)))
     if extras_mode:
         blocks = 3
     n_e2e_blocks = 1 if extras_mode else 3
@@ -571,7 +573,7 @@ def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=Fals
             l.set_lazy_cache(False)
         return w.B / (statistics.median(ms) / min(K_steps, 64) * 1e-3)
 
-    if world == 1 and not extras_mode:
+    if world == 1 and not extras_mode and not args.no_variants:
         res["value_lazy_cache_rows"] = variant(lazy=True)
         if w.B == 1:
             res["value_strict_layer_order"] = variant({"STX_STACK_STRICT": "1"})
@@ -579,7 +581,7 @@ def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=Fals
 
     # ---- stage timing pass (single GPU): the dominant kernel's launches timed alone with CUDA
     #      events on the launching stream
-    if world == 1 and not extras_mode:
+    if world == 1 and not extras_mode and not args.no_variants:
         persistent = w.B == 1 and stack.launches_per_step <= 1 + 2 * w.layers
         fused = layers[0].single_row_fused(w.B)
         if persistent:

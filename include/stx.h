@@ -263,8 +263,22 @@ int stx_layer_single_row_fused(stx_layer_t* l, int64_t B, int* fused_out);
 int stx_layer_step_host(stx_layer_t* l, const void* x_host, int64_t B, void* out_host, void* stream);
 
 /* A stack of L layers, every layer fed the same x [B,H]; out [L,B,H].  The L steps are
- * captured once into a CUDA graph and replayed, strictly serialised on one stream.
- * stx_stack_create ALLOCATES and runs one capture; the layers stay owned by the caller. */
+ * captured once into a CUDA graph and replayed.  stx_stack_create ALLOCATES and runs one
+ * capture; the layers stay owned by the caller.
+ *
+ * One row (B == 1) under the threshold rule, all layers of one shape: the whole stack runs
+ * as ONE persistent, cooperatively launched kernel (k_stack_b1) whose CTAs meet at grid-wide
+ * barriers between the links of a layer; each cache then gets a second copy of its pools
+ * with one contiguous record per neuron (ALLOCATED at create time), and the index plans and
+ * row copies of all layers follow the kernel on parallel branches of the graph.  Because
+ * every layer reads the same x, t = A x of layer l+1 and the output sum of layer l are
+ * formed while rows stream.  Environment, read when a stack is created:
+ *   STX_STACK_STRICT=1      nothing of layer l+1 starts before out[l] is complete (the order a
+ *                           model needs that feeds a layer's output forward)
+ *   STX_STACK_KERNEL=layers keep the per-layer kernels (k_pred_t, k_mlp_b1, k_partial_reduce)
+ *   STX_STACK_GROUP=n       at most n layers per launch of the persistent kernel (1..36)
+ * Other shapes and batch sizes: the per-layer kernels, serialised on one stream, each layer's
+ * cache upkeep on side branches.                                                         */
 int stx_stack_create(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B);
 /* Same, capturing only the given STX_STAGE_* bits of every layer step.                  */
 int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B,

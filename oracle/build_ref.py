@@ -28,7 +28,9 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT_SO = os.path.join(OUT_DIR, "sparse_mlp_ref.so")
-DEFAULT_REFERENCE = os.environ.get("STX_REFERENCE_DIR", "/root/reference")
+# where the reference project's checkout lies: $STX_REFERENCE_DIR, else a directory named "reference" beside
+# this repository (absent on machines that only run the prebuilt oracle/_ref)
+DEFAULT_REFERENCE = os.environ.get("STX_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def ref_so_path() -> str:

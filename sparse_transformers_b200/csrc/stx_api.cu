@@ -22,15 +22,6 @@ int cuda_fail(cudaError_t e, const char* what) {
   return STX_ERR_CUDA;
 }
 
-bool pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("STX_PDL");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1;
-}
-
 int num_sms() {
   static int cached[64] = {};
   int dev = 0;

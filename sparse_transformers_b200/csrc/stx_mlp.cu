@@ -273,17 +273,6 @@ float* b1_partial_region(void* scratch, int64_t H, int64_t K_cap) {
   return reinterpret_cast<float*>(static_cast<char*>(scratch) + decode_scratch_bytes_min(1, H, K_cap));
 }
 
-// STX_MLP_KERNEL=plain forces the plain-load kernel (for A/B measurements); default: the
-// TMA-staged kernel wherever the shape fits it.
-static bool use_tma_kernel() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("STX_MLP_KERNEL");
-    v = (e && !strcmp(e, "plain")) ? 0 : 1;
-  }
-  return v == 1;
-}
-
 // Shared by the op entry point and the fused layer step.  Gather mode (mask_bits != null,
 // streaming kernels only): gate/up/down are full [I,H] pools and the rows are those of the set
 // mask bits; idx_out [I] / count_out receive the list of active neuron ids and its length.
@@ -294,7 +283,7 @@ int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const voi
                 cudaStream_t s) {
   const bool row_idx = mask_bits != nullptr;
   GatherSpec gs{mask_bits, idx_out, count_out, static_cast<int>(K_cap)};
-  if ((use_tma_kernel() || row_idx) && !up_after_gate) {
+  if (!up_after_gate) {
     // the streaming kernels keep a[K][B] behind the (always zero) accumulator region
     void* a_region = static_cast<char*>(scratch) + align_up(static_cast<size_t>(B) * H * sizeof(float), 256);
     float* partial = nullptr;

@@ -640,22 +640,6 @@ __global__ void __launch_bounds__(DOWN_THREADS, 2) k_down_rows(const DownArgs p)
 // output vector; k_partial_reduce adds the per-CTA vectors in ascending CTA order:
 // deterministic, no atomics, nothing to re-zero.  One launch that streams gate, up and down
 // rows pays the launch, listing and first-byte latency once instead of twice.
-// Development aid, compiled out unless STX_B1_TRACE is defined: thread 0 of every CTA stamps
-// the global timer at a few points of k_mlp_b1 (read back with stx_debug_b1_trace).
-#ifdef STX_B1_TRACE
-__device__ unsigned long long g_b1_trace[256][8];
-#define STX_B1_STAMP(i)                                                                 \
-  do {                                                                                  \
-    if (threadIdx.x == 0) {                                                             \
-      unsigned long long t__;                                                           \
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t__));                            \
-      g_b1_trace[blockIdx.x][i] = t__;                                                  \
-    }                                                                                   \
-  } while (0)
-#else
-#define STX_B1_STAMP(i) do { } while (0)
-#endif
-
 constexpr int B1_MAX_SLOTS = 16;
 constexpr int B1_MAX_PASS = 2;    // column chunks per thread: H / V <= 2 * 512
 constexpr int B1_HEADER = 512;    // [0,256) 2 x 16 mbarriers | [256,320) a_s
@@ -731,7 +715,6 @@ __device__ __forceinline__ int cta_scores_and_list(const T* __restrict__ Bm, con
   load_w(0, wv0, ok0);
   pdl_wait();
   pdl_launch_dependents();
-  STX_B1_STAMP(1);
   if (8 < nby) load_w(1, wv1, ok1);
   for (int k = tid; k < B * r; k += blockDim.x) {
     const int b = k / r, e = k - b * r, c = e / V, v = e - c * V;
@@ -861,7 +844,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   int K = 0, nlocal = 0;
-  STX_B1_STAMP(0);
   if (fused) {
     nlocal = cta_scores_and_list<T>(static_cast<const T*>(q.Bm), q.t, reinterpret_cast<float*>(smem + B1_HEADER), 1, q.r, p.I,
                                     q.tau, q.bits, s_my, s_nib, s_bytes, &s_nlocal);
@@ -886,8 +868,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
     bulk_load(d_bufs + static_cast<size_t>(warp) * row_bytes, dsrc + static_cast<size_t>(row_of(s)) * row_bytes, row_bytes,
               &bar_d[warp]);
   };
-
-  STX_B1_STAMP(2);
   if (warp < S && lane == 0 && warp < nlocal) {  // the rows stream in while x is staged
     issue_gu(warp);
     issue_d(warp);
@@ -898,7 +878,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
     for (int i = tid; i < nchunk; i += blockDim.x) xs4[i] = xg[i];
   }
   __syncthreads();
-  STX_B1_STAMP(3);
 
   bool timed_out = false;
   float acc[B1_MAX_PASS][V];
@@ -1000,9 +979,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
     }
   }
   if (timed_out && p.status) atomicOr(p.status, DEV_TIMEOUT);
-#ifdef STX_B1_TRACE
-  if (tid == 0) g_b1_trace[blockIdx.x][7] = static_cast<unsigned long long>(nlocal);
-#endif
 
   float* dst = q.partial + static_cast<size_t>(blockIdx.x) * H;
 #pragma unroll
@@ -1014,7 +990,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_b1(const MlpB1Args q) {
         *reinterpret_cast<float4*>(dst + cc * V + v) = make_float4(acc[k][v], acc[k][v + 1], acc[k][v + 2], acc[k][v + 3]);
     }
   }
-  STX_B1_STAMP(6);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1101,7 +1076,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     mbar_init(bar_z, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  STX_B1_STAMP(0);
   const int G = gridDim.x;
   const bool balance = q.xchg != nullptr && G <= BN_MAX_GRID;
   __shared__ int s_epoch, s_plan[4];
@@ -1146,7 +1120,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
       }
     }
   };
-  STX_B1_STAMP(2);
   // the first tile is this CTA's own in any case when it is full; a short list may still grow
   const bool early = !balance || n_own >= TN;
   if (early) {
@@ -1351,9 +1324,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
     }
   }
   if (timed_out && p.status) atomicOr(p.status, DEV_TIMEOUT);
-#ifdef STX_B1_TRACE
-  if (tid == 0) g_b1_trace[blockIdx.x][7] = static_cast<unsigned long long>(nlocal);
-#endif
   {
     float* dst = q.partial + static_cast<size_t>(blockIdx.x) * B * H + static_cast<size_t>(warp) * (H / 16) + gq;
     const int b0 = 2 * tq, b1 = 2 * tq + 1;
@@ -1371,7 +1341,6 @@ __global__ void __launch_bounds__(512, 1) k_mlp_bn(const MlpB1Args q) {
       }
     }
   }
-  STX_B1_STAMP(6);
 }
 
 // out[h] = sum_c partial[c][h], c ascending.  Block: 32 columns x 32 groups of CTAs; a group
@@ -1497,16 +1466,8 @@ int launch_gateup_mma<float>(const GateUpArgs&, int, size_t, cudaStream_t) {
 }
 
 // The tensor-pipe kernel pays off once several batch rows share one pass over the weights;
-// at batch 1-3 the FMA-pipe kernel measured faster.  STX_GATEUP=fma / mma forces one of them
-// (A/B measurements).
-static bool use_mma_path(int B) {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("STX_GATEUP");
-    v = !e ? 2 : (!strcmp(e, "fma") ? 0 : (!strcmp(e, "mma") ? 1 : 2));
-  }
-  return v == 2 ? B >= 4 : v == 1;
-}
+// at batch 1-3 the FMA-pipe kernel measured faster.
+static bool use_mma_path(int B) { return B >= 4; }
 
 template <typename T, int NB>
 static int launch_down(const DownArgs& d, cudaStream_t s) {
@@ -1536,7 +1497,7 @@ static int launch_down(const DownArgs& d, cudaStream_t s) {
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = 2;
   STX_CUDA(cudaLaunchKernelEx(&cfg, k_down_rows<T, NB>, d));
   return STX_OK;
 }
@@ -1710,16 +1671,6 @@ static int b1_slots_dt(int H, int has_gate, int dtype, int r) {
   }
 }
 
-// STX_MLP_B1=split keeps batch 1 on the two-kernel path (A/B measurements).
-static bool use_b1_fused() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("STX_MLP_B1");
-    v = (e && !strcmp(e, "split")) ? 0 : 1;
-  }
-  return v == 1;
-}
-
 template <typename T>
 static int dispatch_nb(const GateUpArgs& g, int nb, int grid, size_t smem, const DownArgs& d, unsigned parts,
                        cudaStream_t s) {
@@ -1793,7 +1744,7 @@ bool layer_b1_supported(int64_t B, int64_t H, int64_t I, int64_t r, int has_gate
   if (B < 1 || B > BN_MAX) return false;
   const size_t es = dtype_size(dtype);
   const int V = static_cast<int>(16 / es);
-  if (!use_b1_fused() || (H * es) % 16 != 0 || H / V < 32 || r % V != 0 || r / V > 32 || H > (1 << 20) || I > (1 << 24))
+  if ((H * es) % 16 != 0 || H / V < 32 || r % V != 0 || r / V > 32 || H > (1 << 20) || I > (1 << 24))
     return false;
   const uintptr_t al = reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
                        reinterpret_cast<uintptr_t>(down) | reinterpret_cast<uintptr_t>(Bm);
@@ -1915,7 +1866,7 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
   d.B = static_cast<int>(B);
   d.H = static_cast<int>(H);
   // batch 1 with room for three rows per warp and H within the register accumulators: fused kernel
-  const bool b1 = B == 1 && partial != nullptr && use_b1_fused() && b1_slots_dt(static_cast<int>(H), has_gate, dtype, 0) > 0;
+  const bool b1 = B == 1 && partial != nullptr && b1_slots_dt(static_cast<int>(H), has_gate, dtype, 0) > 0;
   if (b1) {
     switch (dtype) {
       case STX_F32: return launch_b1<float>(a, down, partial, out, grid, parts, B1Pred(), s);
@@ -1932,8 +1883,3 @@ int mlp_forward_tma(const void* x, int64_t B, int64_t H, const void* gate, const
 
 }  // namespace stx
 
-#ifdef STX_B1_TRACE
-extern "C" int stx_debug_b1_trace(unsigned long long* out_host) {
-  return cudaMemcpyFromSymbol(out_host, stx::g_b1_trace, sizeof(unsigned long long) * 256 * 8) == cudaSuccess ? 0 : 1;
-}
-#endif

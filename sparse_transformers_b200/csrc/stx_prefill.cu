@@ -464,14 +464,9 @@ size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K) {
 // Implemented in stx_mlp_tma.cu: out[i] = sum over g < G of partial[g][i], g ascending (n % 128 == 0).
 int partial_sum(const float* partial, int G, int64_t n, void* out, int dtype, cudaStream_t s);
 
-// STX_PREFILL=0 keeps large row counts on the decode kernels (A/B measurements).
+// Row blocks of STX_GEMM_MIN_ROWS and more (16-bit, gated) run as tensor-core GEMMs.
 bool prefill_wanted(int64_t B, int64_t H, int64_t K, int dtype, int has_gate) {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("STX_PREFILL");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1 && dtype != STX_F32 && has_gate && B >= STX_GEMM_MIN_ROWS && (H % 64) == 0 && K >= 64;
+  return dtype != STX_F32 && has_gate && B >= STX_GEMM_MIN_ROWS && (H % 64) == 0 && K >= 64;
 }
 
 // x [B,H], concat [2K,H] (gate rows then up rows), down_packed [K,H]; scratch: prefill_scratch_bytes().

@@ -5,7 +5,7 @@
 
 namespace stx {
 
-constexpr int STACK_B1_MAX_LAYERS = 40;  // layers per launch: the descriptors travel as kernel parameters
+constexpr int STACK_B1_MAX_LAYERS = 36;  // layers per launch: the descriptors travel as kernel parameters
 
 struct StackLayerDesc {
   const void* cat;   // per-neuron records [I][gate row | up row | down row] ([I][up | down] without a gate)
