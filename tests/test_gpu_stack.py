@@ -37,6 +37,13 @@ def _stack_vs_oracle(w, steps, seed=0, check_every=1):
                 continue
             assert np.array_equal(l.mask().cpu().numpy(), mask), f"mask differs at step {t} layer {li}"
             assert l.active_indices().tolist() == ol.cache.active.tolist(), f"cache order differs at step {t} layer {li}"
+            if t in (1, steps - 1):  # the packed rows themselves
+                idx = torch.from_numpy(ol.cache.active.astype(np.int64))
+                gate, up, down = ws[li][0], ws[li][1], ws[li][2]
+                cw = l.concat_weight().cpu()
+                want = torch.cat([gate[idx], up[idx]]) if w.has_gate else up[idx]
+                assert torch.equal(cw, want), f"packed gate/up rows differ at step {t} layer {li}"
+                assert torch.equal(l.active_down_weight().cpu(), down[:, idx]), f"packed down rows differ at step {t} layer {li}"
             worst = max(worst, rel_err(got[li], ref))
             ks.append(l.num_active())
     assert worst <= TOL[w.dtype], worst
