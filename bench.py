@@ -381,7 +381,7 @@ def parity_check(synth, w, kept, dev, rank, world, allreduce, peer, dist):
                                        peer=peer if allreduce == "peer" else None))
     # ShardedStack warms up with two eager steps of its warm-up input: the reference side replays them
     stack = stb.SparseStack(layers, w.B) if world == 1 else ShardedStack(layers, w.B, xs[0].to(dev))
-    warm = [] if world == 1 else [xs[0], xs[0]]
+    warm = [xs[0]] * getattr(stack, "warmup_steps", 0)
     local = [l if world == 1 else l.local for l in layers]
 
     ref = None

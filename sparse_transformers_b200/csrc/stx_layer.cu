@@ -373,7 +373,7 @@ static bool stack_persistent_wanted(const stx_stack* s, unsigned stages) {
   if (!stack_b1_supported(c0->H, c0->I, l0->r, c0->has_gate, c0->dtype)) return false;
   for (const stx_layer* l : s->layers) {
     const stx_cache* c = l->cache;
-    if (!single_row_fusable(l, 1) || l->peer || c->I != c0->I || c->has_gate != c0->has_gate || l->r != l0->r) return false;
+    if (!single_row_fusable(l, 1) || l->peer != l0->peer || c->I != c0->I || c->has_gate != c0->has_gate || l->r != l0->r) return false;
   }
   return true;
 }
@@ -420,6 +420,18 @@ static int capture_persistent(stx_stack* s, unsigned stages, cudaStream_t cs, st
     a.r = static_cast<int>(l0->r);
     a.has_gate = l0->cache->has_gate;
     a.strict = strict ? 1 : 0;
+    a.peer = PeerArgs{};
+    a.peer.world = 1;
+    if (l0->peer && l0->peer->world > 1) {
+      if (!peer_args(l0->peer, &a.peer)) {
+        set_error("stx_stack_create: the layers' peer object is not connected");
+        return STX_ERR_INVALID_ARG;
+      }
+      if (s->H > l0->peer->max_elems) {
+        set_error("stx_stack_create: H=%lld exceeds the peer object's max_elems", static_cast<long long>(s->H));
+        return STX_ERR_INVALID_ARG;
+      }
+    }
     int rc = stack_b1_forward(a, s->b1_scratch[gi], l0->cache->dtype, cs);
     if (rc != STX_OK) return rc;
     if (!upkeep) continue;

@@ -35,6 +35,12 @@
 // out[l] is complete - B(l), sum, barrier C, t(l+1), barrier A, scores(l+1) ... : the order a model
 // needs that feeds a layer's output forward; four barriers per layer.
 //
+// Sharded over several GPUs (every rank owns a slice of the neurons and runs this kernel on it), the output
+// sum of a layer ends with the all-reduce over the ranks through peer memory (stx_peer.cuh): each CTA pushes
+// the fp32 sums of its few columns into every peer's exchange buffer, adds what the peers pushed in rank
+// order and writes the columns.  In the default order this sits behind the next layer's row stream, so the
+// NVLink round trip is off the critical path.
+//
 // Every wait is bounded.  A grid barrier that expires sets DEV_TIMEOUT in the layer's status word
 // and the CTA stops waiting on grid barriers for the rest of the launch (it falls through them), so
 // the kernel always terminates.  The counters only grow; a launch derives its targets from a
@@ -166,6 +172,8 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_b1(const __grid_consta
     for (int i = tid; i < nchunk; i += SB1_THREADS) xs4[i] = __ldcg(xg + i);
   }
   const uint32_t gen = __ldcg(q.sync + SB1_SYNC_GEN);
+  // exchange number of the peer object before this launch; layer l is exchange peer_epoch0 + l + 1
+  const int peer_epoch0 = q.peer.world > 1 ? *reinterpret_cast<volatile int*>(q.peer.ctl) : 0;
   __syncthreads();
   // phase 1: warp w always works on quarter w & 3 of a row; its lanes' chunks of x stay in registers
   const int sub = warp & 3;
@@ -282,6 +290,13 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_b1(const __grid_consta
       float t = 0.f;
 #pragma unroll
       for (int w = 0; w < SB1_WARPS; ++w) t += s_part[w][tid];
+      if (q.peer.world > 1) {  // sum over the shards: push to every peer, add what they pushed, in rank order
+        const int epoch = peer_epoch0 + l + 1;
+        bool lost = false;
+        peer_push(q.peer, epoch, col0 * 4 + tid, t);
+        t = peer_collect(q.peer, epoch, col0 * 4 + tid, t, &lost);
+        if (lost) atomicOr(q.peer.ctl + 2, DEV_TIMEOUT);
+      }
       static_cast<T*>(q.layer[l].out)[col0 * 4 + tid] = DT<T>::from_f(t);
     }
   };
@@ -541,6 +556,15 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_b1(const __grid_consta
   }
   if (timed_out && q.layer[0].status) atomicOr(q.layer[0].status, DEV_TIMEOUT);
   if (c == 0 && tid == 0) q.sync[SB1_SYNC_GEN] = gen + 1u;
+  if (q.peer.world > 1) {
+    // the launch's last CTA advances the peer object's exchange number (every CTA read it at the start, and
+    // every CTA is past its last exchange when it arrives here)
+    __syncthreads();
+    if (tid == 0 && atomicAdd(reinterpret_cast<unsigned*>(q.peer.ctl + 1), 1u) == gridDim.x - 1) {
+      q.peer.ctl[1] = 0;
+      *reinterpret_cast<volatile int*>(q.peer.ctl) = peer_epoch0 + L;
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------ host

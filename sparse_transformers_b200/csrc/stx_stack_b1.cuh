@@ -2,6 +2,7 @@
 #pragma once
 
 #include "stx_common.cuh"
+#include "stx_peer.cuh"
 
 namespace stx {
 
@@ -25,6 +26,7 @@ struct StackB1Args {
   float* partial;    // [2][G][H] per-CTA partial outputs, double-buffered by layer parity
   uint32_t* sync;    // counters (see the kernel)
   int L, H, I, r, has_gate, nslot, strict;
+  PeerArgs peer;     // world > 1: the output sum of a layer ends with the all-reduce over the shards
 };
 
 bool stack_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype);

@@ -111,12 +111,28 @@ class ShardedLayer:
 
 class ShardedStack:
     """L sharded layers fed the same x [B,H]; the whole step (kernels + L all-reduces) is
-    captured once in a CUDA graph on this rank and replayed.  out: [L,B,H]."""
+    captured once in a CUDA graph on this rank and replayed.  out: [L,B,H].
+    ``warmup_steps``: eager steps with ``warmup_x`` taken at construction (they advance the caches)."""
 
     def __init__(self, layers: Sequence[ShardedLayer], batch: int, warmup_x: torch.Tensor):
         self.layers = list(layers)
         l0 = self.layers[0].local
         self.B, self.L, self.H, self.dtype, self.device = int(batch), len(layers), l0.H, l0.dtype, l0.device
+        # A single row with the sum over peer memory: the library's own stack object runs the shard as ONE
+        # persistent kernel per step, the all-reduce of a layer inside it (stx_stack_create).  No warm-up
+        # steps are taken then.
+        self._native = None
+        self.warmup_steps = 0
+        if self.B == 1 and all(l.peer is not None and l.peer is self.layers[0].peer for l in self.layers):
+            from .layer import SparseStack
+
+            st = SparseStack([l.local for l in self.layers], 1)
+            if st.launches_per_step <= 1 + 2 * self.L:
+                self._native = st
+                self.launches_per_step = st.launches_per_step
+                return
+            st.close()
+        self.warmup_steps = 2
         self.x_in = torch.zeros(self.B, self.H, dtype=self.dtype, device=self.device)
         self.out = torch.zeros(self.L, self.B, self.H, dtype=self.dtype, device=self.device)
         # kernels of this library per layer (single row: t, fused MLP, partial sum, plan, copy;
@@ -142,6 +158,10 @@ class ShardedStack:
     def close(self) -> None:
         """Release the captured graph (it holds NCCL work).  Call before tearing down the process
         group: destroying a process group whose collectives live in a CUDA graph blocked here."""
+        if getattr(self, "_native", None) is not None:
+            torch.cuda.synchronize()
+            self._native.close()
+            self._native = None
         if getattr(self, "graph", None) is not None:
             torch.cuda.synchronize()
             self.graph.reset()
@@ -175,6 +195,8 @@ class ShardedStack:
         main.wait_stream(self._side2)
 
     def step(self, x: torch.Tensor | None = None, out: torch.Tensor | None = None) -> None:
+        if self._native is not None:
+            return self._native.step(x, out)
         if x is not None:
             self.x_in.copy_(x, non_blocking=True)
         self.graph.replay()
@@ -182,6 +204,8 @@ class ShardedStack:
             out.copy_(self.out, non_blocking=True)
 
     def step_host(self, x_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        if self._native is not None:
+            return self._native.step_host(x_host, out_host)
         self.x_in.copy_(x_host, non_blocking=True)
         self.graph.replay()
         out_host.copy_(self.out, non_blocking=True)

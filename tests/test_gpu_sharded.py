@@ -53,10 +53,11 @@ def _rank_main(rank, world, port, out_dir, mode, batch):
     stack = ShardedStack(sharded, w.B, xs[0].to(dev))
     why = []
     out = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=dev)
-    # the stack's warm-up advanced the shard caches with xs[0] twice; do the same on the full layers
+    # the stack's warm-up steps (if it took any) advanced the shard caches with xs[0]; do the same on the full layers
     if rank == 0:
         for l in full:
-            l.step(xs[0].to(dev)); l.step(xs[0].to(dev))
+            for _ in range(stack.warmup_steps):
+                l.step(xs[0].to(dev))
     for t in range(1, 6):
         x = xs[t].to(dev)
         stack.step(x, out)
