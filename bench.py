@@ -582,7 +582,7 @@ def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=Fals
     # ---- stage timing pass (single GPU): the dominant kernel's launches timed alone with CUDA
     #      events on the launching stream
     if world == 1 and not extras_mode and not args.no_variants:
-        persistent = w.B == 1 and stack.launches_per_step <= 1 + 2 * w.layers
+        persistent = w.B == 1 and stack.launches_per_step <= 2 + 2 * w.layers
         fused = layers[0].single_row_fused(w.B)
         if persistent:
             names = ("stack_kernel", "plan", "copy")
@@ -889,11 +889,46 @@ def dropin_measure(synth, w, dev, steps: int = 24):
         token(xs[i])
     torch.cuda.synchronize()
     dt = (time.perf_counter() - t0) / steps
-    del caches, preds
+
+    # the same calls without the two getters (WeightCache.sparse_forward keeps K on the device): nothing
+    # synchronises, so a whole token is captured in one CUDA graph and replayed
+    x_static = xs[0].clone()
+    bufs = [torch.zeros(1, w.H, dtype=w.dtype, device=dev) for _ in range(n_layers)]
+
+    def token_nosync():
+        for wc, (A, Bm), b in zip(caches, preds, bufs):
+            wc.update_active_weights(torch.ops.sparse_mlp.predict_mask(x_static, A, Bm, "threshold", w.tau))
+            wc.sparse_forward(x_static, b, w.act)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            token_nosync()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        token_nosync()
+    for i in range(4):
+        x_static.copy_(xs[i])
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(4, 4 + steps):
+        x_static.copy_(xs[i])
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    dt_graph = e0.elapsed_time(e1) * 1e-3 / steps
+    del graph, caches, preds
     return {"tokens_per_s": w.B / dt, "ms_per_step": dt * 1e3, "steps": steps,
             "path": "torch.ops.sparse_mlp.predict_mask -> WeightCache.update_active_weights -> get_concat_weight -> "
                     "get_active_down_weight -> torch.ops.sparse_mlp.forward per layer, called from Python (wall clock)",
-            "host_syncs_per_layer": 2}
+            "host_syncs_per_layer": 2,
+            "no_sync": {"tokens_per_s": w.B / dt_graph, "ms_per_step": dt_graph * 1e3,
+                        "path": "predict_mask -> update_active_weights -> WeightCache.sparse_forward per layer (K stays on the "
+                                "device, no host synchronisation), one CUDA graph per token, device-timed"}}
 
 
 def llama_skip_measure(args, dev, runs: int = 3):

@@ -208,6 +208,15 @@ int stx_sparse_mlp_forward_noalloc(const void* x, int64_t B, int64_t H, const vo
                                    void* combined_buf, int act, int has_gate, int dtype,
                                    void* stream);
 
+/* SkipMLP._forward_sparse_weight_cache (src/modeling_skip.py:114-117) WITHOUT the two getters:
+ * the sparse MLP of x [B,H] over the cache's packed rows, the number of active neurons read
+ * on the device.  What get_concat_weight + get_active_down_weight + sparse_mlp_forward compute,
+ * but asynchronous: no host read-back of K, no allocation, graph-capturable.  out [B,H].
+ * scratch: stx_mlp_scratch_bytes(B, H, I) bytes, zeroed once (see stx_sparse_mlp_forward for the
+ * reuse rule).  Row blocks of 9 and more (16-bit, gated) take the tensor-core path.  Rows that
+ * lazy layer steps left stale are brought up to date first.                                  */
+int stx_cache_mlp_forward(stx_cache_t* c, const void* x, int64_t B, void* out, int act, void* scratch, void* stream);
+
 /* ------------------------------------------------------------------ fused layer step
  * One decode step of one sparse layer: predictor -> mask -> cache update -> sparse MLP
  * (SkipDecoderLayer.forward's sparse branch, src/modeling_skip.py:236-238,258, with K
@@ -290,6 +299,11 @@ int stx_stack_buffers(stx_stack_t* s, void** x_in_out, void** out_out);
 /* x: device [B,H], copied into the stack's input buffer first (NULL or the buffer itself:
  * use what is already there).  out: device [L,B,H] to copy the result to (NULL or the
  * stack's own buffer: leave it in place).                                              */
+/* Every step ends by collecting the layers' device error bits (a bounded wait that expired,
+ * a bounds check that skipped an access) into pinned host memory; a later call of
+ * stx_stack_step / stx_stack_step_host that finds them set returns STX_ERR_TIMEOUT /
+ * STX_ERR_INVALID_ARG instead of stepping (no synchronisation: the error surfaces one or
+ * two calls late).  The bits are sticky in the caches' status words.                     */
 int stx_stack_step(stx_stack_t* s, const void* x, void* out, void* stream);
 int stx_stack_step_host(stx_stack_t* s, const void* x_host, void* out_host, void* stream);
 /* Number of kernel launches one stack step replays (for launch accounting).            */

@@ -56,6 +56,7 @@ SIGNATURES = {
     "stx_mlp_scratch_bytes": (_i32, [_i64, _i64, _i64, _psz]),
     "stx_sparse_mlp_forward": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "stx_sparse_mlp_forward_noalloc": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "stx_cache_mlp_forward": (_i32, [_vp, _vp, _i64, _vp, _i32, _vp, _vp]),
     "stx_layer_create": (_i32, [_pp, _vp, _vp, _i64, _vp, _i32, _f32, _i32, _i64]),
     "stx_layer_destroy": (_i32, [_vp]),
     "stx_layer_step": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),

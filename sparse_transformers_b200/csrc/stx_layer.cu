@@ -73,13 +73,41 @@ struct stx_stack {
   cudaGraphExec_t exec = nullptr;
   int64_t kernel_nodes = 0;
   std::vector<cudaEvent_t> events;  // [0,L) fork points, [L] join, [L+1, 2L+1) plan-done points, [2L+1] second join
-  std::vector<void*> b1_scratch;    // persistent single-row kernel: counters, t and pair partials per group of layers
+  std::vector<void*> b1_scratch;    // persistent single-row kernel: counters, t and partial vectors per group of layers
   bool persistent = false;
+  // Device status of the step (bounded waits that expired, bounds checks that skipped an access): the last
+  // node of the graph ORs the layers' status words into status_dev and copies it to the pinned status_host,
+  // which the NEXT stx_stack_step call reads without synchronising.
+  int** status_ptrs = nullptr;  // device [L]
+  int* status_dev = nullptr;
+  int* status_host = nullptr;
 };
 
 using namespace stx;
 
+// ORs the layers' device status words into one (error bits only).
+__global__ void k_stack_status(int* const* __restrict__ ptrs, int n, int* __restrict__ out) {
+  int v = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) v |= *ptrs[i] & (DEV_TIMEOUT | DEV_BAD_INDEX);
+  v = __reduce_or_sync(0xffffffffu, v);
+  if (threadIdx.x == 0) *out = v;
+}
+
 extern "C" {
+
+int stx_cache_mlp_forward(stx_cache_t* c, const void* x, int64_t B, void* out, int act, void* scratch, void* stream) {
+  STX_CHECK_ARG(c && x && out && scratch, "stx_cache_mlp_forward: null pointer");
+  STX_CHECK_ARG(B > 0, "stx_cache_mlp_forward: B must be positive");
+  STX_CHECK_ARG(act >= STX_ACT_RELU && act <= STX_ACT_GELU, "stx_cache_mlp_forward: bad activation %d", act);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = cache_flush(c, s);
+  if (rc != STX_OK) return rc;
+  if (c->pk_gate && prefill_wanted(B, c->H, c->I, c->dtype, c->has_gate))
+    return prefill_forward(x, B, c->H, c->pk_gate, c->pk_down, c->I, out, nullptr, act, c->dtype,
+                           mlp_prefill_region(scratch, B, c->H, c->I), c->state + ST_STATUS, c->state + ST_K, s);
+  return mlp_forward(x, B, c->H, c->pk_gate, c->pk_up, c->pk_down, c->state + ST_K, 0, c->I, 0, out, nullptr, act, c->has_gate,
+                     c->dtype, scratch, c->state + ST_STATUS, 3u, nullptr, nullptr, nullptr, true, s);
+}
 
 int stx_layer_destroy(stx_layer_t* l) {
   if (!l) return STX_OK;
@@ -355,6 +383,9 @@ int stx_stack_destroy(stx_stack_t* s) {
   if (s->graph) cudaGraphDestroy(s->graph);
   for (cudaEvent_t ev : s->events) cudaEventDestroy(ev);
   for (void* p : s->b1_scratch) cudaFree(p);
+  cudaFree(s->status_ptrs);
+  cudaFree(s->status_dev);
+  if (s->status_host) cudaFreeHost(s->status_host);
   cudaFree(s->x_in);
   cudaFree(s->out);
   delete s;
@@ -387,6 +418,14 @@ static int64_t stack_group_size(int64_t L) {
     if (v >= 1 && v <= STACK_B1_MAX_LAYERS) g = std::min<int64_t>(g, v);
   }
   return g;
+}
+
+// Last nodes of a step's graph: the layers' error bits -> one word -> pinned host memory.
+static int capture_status(stx_stack* s, cudaStream_t cs) {
+  k_stack_status<<<1, 32, 0, cs>>>(s->status_ptrs, static_cast<int>(s->layers.size()), s->status_dev);
+  STX_LAUNCH_CHECK("k_stack_status");
+  STX_CUDA(cudaMemcpyAsync(s->status_host, s->status_dev, sizeof(int), cudaMemcpyDeviceToHost, cs));
+  return STX_OK;
 }
 
 static int capture_persistent(stx_stack* s, unsigned stages, cudaStream_t cs, std::vector<cudaStream_t>& sides) {
@@ -488,6 +527,16 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
   cudaError_t e = cudaMalloc(&s->x_in, xbytes);
   if (e == cudaSuccess) e = cudaMalloc(&s->out, xbytes * L);
   if (e == cudaSuccess) e = cudaMemset(s->x_in, 0, xbytes);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&s->status_ptrs), sizeof(int*) * L);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&s->status_dev), sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(s->status_dev, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&s->status_host), sizeof(int));
+  if (e == cudaSuccess) {
+    *s->status_host = 0;
+    std::vector<int*> hp(L);
+    for (int64_t i = 0; i < L; ++i) hp[i] = layers[i]->cache->state + ST_STATUS;
+    e = cudaMemcpy(s->status_ptrs, hp.data(), sizeof(int*) * L, cudaMemcpyHostToDevice);
+  }
   if (e != cudaSuccess) {
     set_error("stx_stack_create: device allocation failed: %s", cudaGetErrorString(e));
     stx_stack_destroy(s);
@@ -537,6 +586,7 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
     if (e == cudaSuccess && rc == STX_OK) e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
     if (e == cudaSuccess && rc == STX_OK) {
       rc = capture_persistent(s, stages, cs, sides);
+      if (rc == STX_OK) rc = capture_status(s, cs);
       cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
       if (rc == STX_OK && e2 != cudaSuccess) e = e2;
     }
@@ -562,6 +612,7 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
       }
       if (ej != cudaSuccess) e = ej;
     }
+    if (rc == STX_OK && e == cudaSuccess) rc = capture_status(s, cs);
     cudaError_t e2 = cudaStreamEndCapture(cs, &s->graph);
     if (rc == STX_OK && e == cudaSuccess && e2 != cudaSuccess) e = e2;
   }
@@ -599,8 +650,25 @@ int stx_stack_buffers(stx_stack_t* s, void** x_in_out, void** out_out) {
   return STX_OK;
 }
 
+// A step whose kernels gave up on a bounded wait (or skipped an access after a failed bounds check) has
+// produced garbage.  The graph's last node leaves the error bits in pinned memory; the next call sees them
+// without synchronising and refuses to go on.
+static int stack_check_status(const stx_stack* s) {
+  const int st = *reinterpret_cast<volatile int*>(s->status_host);
+  if (st & DEV_TIMEOUT) {
+    set_error("stx_stack_step: a bounded wait expired in an earlier step of this stack (device status 0x%x); its outputs are invalid", st);
+    return STX_ERR_TIMEOUT;
+  }
+  if (st & DEV_BAD_INDEX) {
+    set_error("stx_stack_step: a device bounds check failed in an earlier step of this stack (device status 0x%x)", st);
+    return STX_ERR_INVALID_ARG;
+  }
+  return STX_OK;
+}
+
 int stx_stack_step(stx_stack_t* s, const void* x, void* out, void* stream) {
   STX_CHECK_ARG(s, "stx_stack_step: null stack");
+  if (int rc = stack_check_status(s)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t xbytes = static_cast<size_t>(s->B) * s->H * s->es;
   if (x && x != s->x_in) STX_CUDA(cudaMemcpyAsync(s->x_in, x, xbytes, cudaMemcpyDeviceToDevice, st));
@@ -612,6 +680,7 @@ int stx_stack_step(stx_stack_t* s, const void* x, void* out, void* stream) {
 
 int stx_stack_step_host(stx_stack_t* s, const void* x_host, void* out_host, void* stream) {
   STX_CHECK_ARG(s && x_host && out_host, "stx_stack_step_host: null pointer");
+  if (int rc = stack_check_status(s)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t xbytes = static_cast<size_t>(s->B) * s->H * s->es;
   STX_CUDA(cudaMemcpyAsync(s->x_in, x_host, xbytes, cudaMemcpyHostToDevice, st));

@@ -295,7 +295,10 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_b1(const __grid_consta
         bool lost = false;
         peer_push(q.peer, epoch, col0 * 4 + tid, t);
         t = peer_collect(q.peer, epoch, col0 * 4 + tid, t, &lost);
-        if (lost) atomicOr(q.peer.ctl + 2, DEV_TIMEOUT);
+        if (lost) {
+          atomicOr(q.peer.ctl + 2, DEV_TIMEOUT);
+          if (q.layer[l].status) atomicOr(q.layer[l].status, DEV_TIMEOUT);
+        }
       }
       static_cast<T*>(q.layer[l].out)[col0 * 4 + tid] = DT<T>::from_f(t);
     }

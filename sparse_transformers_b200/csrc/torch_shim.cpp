@@ -128,6 +128,37 @@ class WeightCache : public torch::CustomClassHolder {
     return out32.narrow(0, 0, k).to(torch::kInt64);
   }
 
+  // SkipMLP._forward_sparse_weight_cache (modeling_skip.py:114-117) over this cache without the two
+  // getters: K stays on the device, nothing synchronises, so the call can be captured in a CUDA graph.
+  // Returns down_proj_buffer (resized to the input's rows like sparse_mlp_op.cpp:107-112 does).
+  torch::Tensor sparse_forward(const torch::Tensor& input, torch::Tensor down_proj_buffer, const std::string& activation_fn) {
+    TORCH_CHECK(input.is_cuda() && down_proj_buffer.is_cuda(), "WeightCache.sparse_forward: CUDA tensors required");
+    TORCH_CHECK(input.scalar_type() == dtype_ && down_proj_buffer.scalar_type() == dtype_,
+                "WeightCache.sparse_forward: tensors must have the cache's dtype");
+    const int act = stx_act_from_name(activation_fn.c_str());
+    TORCH_CHECK(act >= 0, "WeightCache.sparse_forward: unknown activation '", activation_fn, "'");
+    c10::cuda::CUDAGuard guard(device_);
+    auto shape = input.sizes().vec();
+    TORCH_CHECK(!shape.empty() && shape.back() == H_, "WeightCache.sparse_forward: last dimension must be ", H_);
+    auto x = input.contiguous().view({-1, H_});
+    const int64_t B = x.size(0);
+    if (down_proj_buffer.dim() != 2 || down_proj_buffer.size(0) != B || down_proj_buffer.size(1) != H_) down_proj_buffer.resize_({B, H_});
+    TORCH_CHECK(down_proj_buffer.is_contiguous(), "WeightCache.sparse_forward: the buffer must be contiguous");
+    if (!scratch_.defined() || scratch_rows_ < B) {
+      size_t bytes = 0;
+      check(stx_mlp_scratch_bytes(B, H_, I_, &bytes), "sparse_forward");
+      scratch_ = torch::zeros({static_cast<int64_t>(bytes)}, torch::TensorOptions().dtype(torch::kUInt8).device(device_));
+      scratch_rows_ = B;
+      scratch_last_ = B;
+    } else if (scratch_last_ != B) {  // the zeroed head of the scratch depends on the row count
+      scratch_.zero_();
+      scratch_last_ = B;
+    }
+    check(stx_cache_mlp_forward(c_, x.data_ptr(), B, down_proj_buffer.data_ptr(), act, scratch_.data_ptr(), cur_stream(device_)),
+          "sparse_forward");
+    return shape.size() > 2 ? down_proj_buffer.view(shape) : down_proj_buffer;
+  }
+
   stx_cache_t* handle() const { return c_; }
 
  private:
@@ -139,6 +170,8 @@ class WeightCache : public torch::CustomClassHolder {
   }
 
   stx_cache_t* c_ = nullptr;
+  torch::Tensor scratch_;  // of sparse_forward: sized for scratch_rows_ rows, last used with scratch_last_
+  int64_t scratch_rows_ = 0, scratch_last_ = 0;
   int64_t H_ = 0, I_ = 0;
   bool has_gate_ = true;
   c10::ScalarType dtype_ = c10::kFloat;
@@ -291,6 +324,7 @@ TORCH_LIBRARY(STX_TORCH_NAMESPACE, m) {
       .def("update_active_weights", &stxb::WeightCache::update_active_weights)
       .def("get_concat_weight", &stxb::WeightCache::get_concat_weight)
       .def("get_active_down_weight", &stxb::WeightCache::get_active_down_weight)
+      .def("sparse_forward", &stxb::WeightCache::sparse_forward)
       .def("get_num_active", &stxb::WeightCache::get_num_active)
       .def("get_active_indices", &stxb::WeightCache::get_active_indices);
   m.def("forward", stxb::sparse_mlp_forward);

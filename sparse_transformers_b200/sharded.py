@@ -127,7 +127,7 @@ class ShardedStack:
             from .layer import SparseStack
 
             st = SparseStack([l.local for l in self.layers], 1)
-            if st.launches_per_step <= 1 + 2 * self.L:
+            if st.launches_per_step <= 2 + 2 * self.L:  # one persistent kernel + plan and copy per layer + status collector
                 self._native = st
                 self.launches_per_step = st.launches_per_step
                 return

@@ -79,6 +79,7 @@ class SkipMLP(nn.Module):
         self.act_fn_name = act_fn
         self.act_fn = _ACT_FN[act_fn]
         self.use_weight_cache = use_weight_cache
+        self.fused_getters = True  # False: the reference's literal call sequence (getters + sparse_mlp_forward)
         self.register_buffer("init_mask", torch.ones(intermediate_size, dtype=torch.bool))
         self.weight_cache = None
         self.register_buffer("down_proj_buffer", torch.zeros(1, hidden_size), persistent=False)
@@ -108,8 +109,13 @@ class SkipMLP(nn.Module):
         if self.down_proj_buffer.dtype != x.dtype:
             self.down_proj_buffer = self.down_proj_buffer.to(x.dtype)
             self.combined_proj_buffer = self.combined_proj_buffer.to(x.dtype)
-        out = sparse_mlp_forward(x, self.weight_cache.get_concat_weight(), self.weight_cache.get_active_down_weight(),
-                                 self.down_proj_buffer, self.combined_proj_buffer, self.act_fn_name)
+        if self.fused_getters:
+            # same result without the two getters (each reads K back from the device): nothing synchronises,
+            # the decode step stays capturable in a CUDA graph
+            out = self.weight_cache.sparse_forward(x, self.down_proj_buffer, self.act_fn_name)
+        else:
+            out = sparse_mlp_forward(x, self.weight_cache.get_concat_weight(), self.weight_cache.get_active_down_weight(),
+                                     self.down_proj_buffer, self.combined_proj_buffer, self.act_fn_name)
         return out.clone()  # the op returns an alias of the persistent buffer
 
     def _forward_dense(self, x: torch.Tensor) -> torch.Tensor:

@@ -130,3 +130,46 @@ def test_against_live_reference(refmod):
         r = fwd(x, ref.get_concat_weight(), ref.get_active_down_weight(), db, cb, "relu", True)
         o = torch.ops.sparse_mlp.forward(x.to(DEV), mine.get_concat_weight(), mine.get_active_down_weight(), dbg, cbg, "relu", True)
         assert (o.cpu() - r).abs().max() <= 1e-5 * r.abs().max()
+
+
+@pytest.mark.parametrize("dtype,rows,H,I", [(torch.float16, 1, 1024, 2048), (torch.float32, 3, 256, 512), (torch.bfloat16, 12, 512, 1024),
+                                            (torch.float16, 1, 64, 256)])
+def test_sparse_forward_equals_getters_plus_forward(dtype, rows, H, I):
+    """WeightCache.sparse_forward (no getters, K stays on the device) gives what the reference's call
+    sequence get_concat_weight / get_active_down_weight / sparse_mlp_forward gives, update after
+    update and for changing row counts; a scratch-path shape (64-element rows) is among the cases,
+    and the MLP calls of a SkipMLP agree between the two forms."""
+    import sparse_transformers_b200 as stb
+
+    g = torch.Generator().manual_seed(rows + H)
+    gate, up, down = (torch.randn(I, H, generator=g) / H ** 0.5).to(dtype), (torch.randn(I, H, generator=g) / H ** 0.5).to(dtype), \
+        (torch.randn(H, I, generator=g) / I ** 0.5).to(dtype)
+    wc = stb.WeightCache(torch.ones(I, dtype=torch.bool), H, gate.to(DEV), up.to(DEV), down.to(DEV), True)
+    buf_a = torch.zeros(1, H, dtype=dtype, device=DEV)
+    buf_b = torch.zeros(1, H, dtype=dtype, device=DEV)
+    comb = torch.zeros(1, 2, dtype=dtype, device=DEV)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    for step, r in enumerate([rows, rows, 1, rows]):
+        mask = torch.rand(I, generator=g) < (0.2 + 0.1 * step)
+        wc.update_active_weights(mask.to(DEV))
+        x = torch.randn(r, H, generator=g).to(dtype).to(DEV)
+        got = wc.sparse_forward(x, buf_a, "silu").clone()
+        want = stb.sparse_mlp_forward(x, wc.get_concat_weight(), wc.get_active_down_weight(), buf_b, comb, "silu").clone()
+        assert got.shape == want.shape == (r, H)
+        err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+        assert err <= tol, (step, err)
+
+
+def test_skip_mlp_fused_getters_match_reference_sequence():
+    import sparse_transformers_b200 as stb
+
+    torch.manual_seed(0)
+    mlp = stb.SkipMLP(512, 1024, sparsity=0.8).to(DEV).half()
+    mlp.initialize_weight_cache()
+    lora = stb.FastLoRAProjection(512, 1024, 32).to(DEV).half()
+    x = torch.randn(1, 512, device=DEV, dtype=torch.float16)
+    stb.compute_binary_mask(x, lora, "naive", weight_cache=mlp.weight_cache)
+    a = mlp(x)
+    mlp.fused_getters = False
+    b = mlp(x)
+    assert float((a.float() - b.float()).abs().max() / b.float().abs().max()) <= 2e-2

@@ -67,7 +67,7 @@ def test_persistent_stack_matches_oracle(dtype, H, I, r, has_gate, act, density,
 
     w = Workload("stack", H=H, I=I, r=r, B=1, dtype=dtype, density=density, layers=layers, act=act, has_gate=has_gate)
     ks, n_launch = _stack_vs_oracle(w, steps=6, seed=layers)
-    assert n_launch == 1 + 2 * layers  # the persistent kernel + index plan and row copies per layer
+    assert n_launch == 2 + 2 * layers  # the persistent kernel + index plan and row copies per layer + the status collector
 
 
 def test_c2_full_shape_16_steps():
@@ -90,9 +90,9 @@ def test_stack_variants_agree(monkeypatch, env):
     w = WORKLOADS["C2"].scaled(I=4096, H=1024, layers=5)
     _, n_launch = _stack_vs_oracle(w, steps=5, seed=9)
     if "STX_STACK_KERNEL" in env:
-        assert n_launch == 5 * w.layers
+        assert n_launch == 5 * w.layers + 1
     elif "STX_STACK_GROUP" in env:
-        assert n_launch == 3 + 2 * w.layers
+        assert n_launch == 3 + 2 * w.layers + 1
 
 
 def test_stack_replay_is_deterministic():
@@ -118,3 +118,50 @@ def test_stack_replay_is_deterministic():
         torch.cuda.synchronize()
         assert torch.equal(oa, ob)
     sa.close(); sb.close()
+
+
+def test_expired_wait_makes_the_next_step_fail(monkeypatch):
+    """A wait that runs out inside a step must not pass silently.  World of two whose second rank does not
+    exist (its exchange buffer is a second buffer on this GPU that nobody writes): the stack kernel's wait for
+    the peer's partial sums expires after its poll limit, the step finishes (the context stays usable), the
+    error bits reach pinned host memory with the step's last node, and the next step call is refused."""
+    import ctypes
+
+    from sparse_transformers_b200 import SparseLayer, SparseStack
+    from sparse_transformers_b200 import _capi as C
+    from sparse_transformers_b200.synth import HiddenStream, WORKLOADS, layer_weights
+    from stxgpu import DEV
+
+    monkeypatch.setenv("STX_PEER_WAIT_ITERS", "500")
+    w = WORKLOADS["C2"].scaled(I=2048, H=512, layers=2)
+    a, b = ctypes.c_void_p(), ctypes.c_void_p()
+    C.check(C.lib.stx_peer_create(ctypes.byref(a), 0, 2, w.H))
+    C.check(C.lib.stx_peer_create(ctypes.byref(b), 1, 2, w.H))  # only its buffer is used
+    pa, pb = ctypes.c_void_p(), ctypes.c_void_p()
+    C.check(C.lib.stx_peer_local_buffer(a, ctypes.byref(pa)))
+    C.check(C.lib.stx_peer_local_buffer(b, ctypes.byref(pb)))
+    C.check(C.lib.stx_peer_connect_ptrs(a, (ctypes.c_void_p * 2)(pa.value, pb.value)))
+
+    class _Peer:
+        handle = a
+
+    gen = torch.Generator().manual_seed(3)
+    layers = [SparseLayer(*[t.to(DEV) for t in layer_weights(w, gen)], act=w.act, param=w.tau, max_batch=1) for _ in range(w.layers)]
+    for l in layers:
+        l.set_peer(_Peer)
+    stack = SparseStack(layers, 1)
+    try:
+        assert stack.launches_per_step == 2 + 2 * w.layers  # the persistent kernel carries the exchange
+        xs = HiddenStream(w, gen).take(2).to(DEV)
+        stack.step(xs[0])          # finishes: every wait for the absent peer gives up after 500 polls
+        torch.cuda.synchronize()
+        assert float((torch.ones(8, device=DEV) * 2).sum()) == 16.0  # context alive
+        with pytest.raises(C.StxError) as ei:
+            stack.step(xs[1])
+        assert ei.value.status == C.ERR_TIMEOUT and "bounded wait expired" in str(ei.value)
+    finally:
+        stack.close()
+        for l in layers:
+            l.close()
+        C.lib.stx_peer_destroy(a)
+        C.lib.stx_peer_destroy(b)
