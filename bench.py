@@ -382,6 +382,9 @@ def parity_check(synth, w, kept, dev, rank, world, allreduce, peer, dist):
     # ShardedStack warms up with two eager steps of its warm-up input: the reference side replays them
     stack = stb.SparseStack(layers, w.B) if world == 1 else ShardedStack(layers, w.B, xs[0].to(dev))
     warm = [xs[0]] * getattr(stack, "warmup_steps", 0)
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()  # start the first step together (bounded waits for the peers)
     local = [l if world == 1 else l.local for l in layers]
 
     ref = None
@@ -508,6 +511,7 @@ def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=Fals
 
     out_dev = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=dev)
     cursor = 1
+    barrier()  # the ranks built their shards at different speeds; a step's waits for the peers are bounded (seconds)
     for _ in range(W_steps):
         stack.step(xs_dev[cursor % n_x], out_dev)
         cursor += 1

@@ -142,6 +142,11 @@ class ShardedStack:
         self.launches_per_step = ((5 if fused else 6) + (0 if fused and peer else 1)) * self.L
         self._side = torch.cuda.Stream(device=self.device)    # index plans
         self._side2 = torch.cuda.Stream(device=self.device)   # row copies (so the next layer's plan does not queue behind them)
+        # Construction is collective: the ranks meet here, because the steps below wait (bounded, seconds)
+        # for the peers' partial sums and the ranks may have built their shards at very different speeds.
+        if dist.is_initialized() and dist.get_world_size(self.layers[0].group) > 1:
+            torch.cuda.synchronize()
+            dist.barrier(self.layers[0].group)
         # eager warm-up on a side stream (NCCL communicators, function attributes), then capture
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
