@@ -120,19 +120,15 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
   }
   pdl_wait();
   pdl_launch_dependents();
-  // gridDim.y == 1: this block walks all groups of PRED_BT rows itself (its slice of Bm is loaded once, the
-  // union over the rows needs no atomics); else block (w, y) does group y only
-  const bool all_groups = gridDim.y == 1;
-  const int row0 = all_groups ? 0 : blockIdx.y * PRED_BT;
-  const int rows_here = all_groups ? B : min(PRED_BT, B - row0);
-  for (int k = tid; k < rows_here * r; k += blockDim.x) t_s[k] = t[static_cast<size_t>(row0) * r + k];
+  const int bg0 = blockIdx.y * PRED_BT;          // first batch row of this block's group
+  const int Bg = min(PRED_BT, B - bg0);           // rows in the group
+  for (int k = tid; k < Bg * r; k += blockDim.x) t_s[k] = t[static_cast<size_t>(bg0) * r + k];
   __syncthreads();
 
   const float tau_r = DT<T>::round_f(tau);
   bool on = false;
-  for (int b0 = 0; b0 < rows_here; b0 += PRED_BT) {  // b0: first row of the group inside t_s
-    const int bg0 = row0 + b0;                      // ... and in the batch
-    const int Bg = min(PRED_BT, rows_here - b0);
+  {
+    const int b0 = 0;  // row index inside the group (t_s holds the group's rows only)
     float acc[PRED_BT];
 #pragma unroll
     for (int b = 0; b < PRED_BT; ++b) acc[b] = 0.f;
@@ -217,19 +213,17 @@ template <typename T>
 static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
                           int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
                           int write_bits, unsigned parts, cudaStream_t s) {
-  unsigned groups = static_cast<unsigned>((B + PRED_BT - 1) / PRED_BT);
-  // the score kernel keeps all rows' t in shared memory when they fit (48 KB) and walks the groups itself
-  const bool walk = groups > 1 && static_cast<size_t>(B) * r * sizeof(float) <= 48 * 1024;
+  const unsigned groups = static_cast<unsigned>((B + PRED_BT - 1) / PRED_BT);
   if (parts & 1u)
     STX_CUDA(launch_pdl(k_pred_t<T>, dim3(static_cast<unsigned>(r), groups), dim3(pred_t_threads(static_cast<int>(H), DT<T>::V)),
                         0, s, static_cast<const T*>(x), static_cast<const T*>(A), t_scratch, static_cast<int>(B),
-                        static_cast<int>(H), static_cast<int>(r), (groups > 1 && !walk && write_bits && (parts & 2u)) ? bits : nullptr,
+                        static_cast<int>(H), static_cast<int>(r), (groups > 1 && write_bits && (parts & 2u)) ? bits : nullptr,
                         static_cast<int>((I + 31) / 32)));
   const int64_t W = (I + 31) / 32;
-  const size_t smem = static_cast<size_t>(walk ? B : std::min<int64_t>(B, PRED_BT)) * r * sizeof(float);
-  if ((parts & 2u) && !(parts & 1u) && groups > 1 && !walk && write_bits) STX_CUDA(cudaMemsetAsync(bits, 0, W * sizeof(uint32_t), s));
+  const size_t smem = static_cast<size_t>(std::min<int64_t>(B, PRED_BT)) * r * sizeof(float);
+  if ((parts & 2u) && !(parts & 1u) && groups > 1 && write_bits) STX_CUDA(cudaMemsetAsync(bits, 0, W * sizeof(uint32_t), s));
   if (parts & 2u)
-  STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W), walk ? 1u : groups), dim3(256), smem, s, t_scratch,
+  STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W), groups), dim3(256), smem, s, t_scratch,
                       static_cast<const T*>(Bm), bits, static_cast<T*>(scores_out), static_cast<int>(B),
                       static_cast<int>(r), static_cast<int>(I), tau, write_bits));
   
