@@ -779,9 +779,10 @@ def extra_summary(w, r, world, allreduce):
 
 
 def _finish_distributed(dist, world):
-    """Leave a multi-rank run: the peer objects are closed and every captured graph is released before
-    this point; the ranks meet once more and exit without destroy_process_group(), which was seen to
-    block at the end of such runs."""
+    """Leave a multi-rank run: the peer objects are closed and every captured graph is released before this
+    point.  The ranks meet once more and tear the process group down; a watchdog ends the process if the
+    teardown has not returned after 20 s (it blocked at the end of earlier runs of this benchmark) and says so
+    on stderr, so that the run can never hang on its way out."""
     if world > 1:
         import torch
 
@@ -789,7 +790,17 @@ def _finish_distributed(dist, world):
         dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+
+        def bail():
+            sys.stderr.write("bench.py: destroy_process_group() did not return within 20 s; leaving without it\n")
+            sys.stderr.flush()
+            os._exit(0)
+
+        t = threading.Timer(20.0, bail)
+        t.daemon = True
+        t.start()
+        dist.destroy_process_group()
+        t.cancel()
 
 
 # ------------------------------------------------------------------------------ other workloads
