@@ -458,6 +458,8 @@ def parity_check(synth, w, kept, dev, rank, world, allreduce, peer, dist):
                 reference_step(k, xs[0], masks, None, None, check=False)
     for t in range(1, PARITY_STEPS + 1):
         x = xs[t]
+        if world > 1:
+            dist.barrier()  # rank 0 checks against the CPU reference between steps: enter each collective step together
         stack.step(x.to(dev), out)
         torch.cuda.synchronize()
         got = out.cpu()

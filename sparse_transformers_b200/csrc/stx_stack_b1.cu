@@ -49,86 +49,13 @@
 #include "stx_common.cuh"
 #include "stx_tma.cuh"
 #include "stx_stack_b1.cuh"
+#include "stx_stack_dev.cuh"
 
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
 
 namespace stx {
-
-constexpr int SB1_THREADS = 512;
-constexpr int SB1_WARPS = SB1_THREADS / 32;
-constexpr int SB1_MAX_SLOTS = 16;
-constexpr int SB1_MY_CAP = 128;    // neurons of one CTA per layer: ceil(K / G) <= 128
-constexpr int SB1_MAX_PASS = 2;    // 16-byte column chunks per thread: H / V <= 2 * 512
-constexpr int SB1_OFF_AS = 256;    // a_s [2 buffers][4] floats
-constexpr int SB1_OFF_PD = 320;    // quarter sums [2 buffers][4 neurons][4 quarters] float2
-constexpr int SB1_OFF_T = 832;     // t of the layer in the score layout, <= 512 bytes
-constexpr int SB1_OFF_MY = 1344;   // the CTA's neurons of the layer [SB1_MY_CAP]
-constexpr int SB1_HEADER = 1920;   // x follows, then the slots
-constexpr uint32_t SB1_GRID_WAIT_LIMIT = 1u << 21;
-
-// sync words (uint32): [0] generation, then one counter per barrier, 128 bytes apart
-constexpr int SB1_SYNC_GEN = 0, SB1_SYNC_A = 32, SB1_SYNC_B = 64, SB1_SYNC_C = 96, SB1_SYNC_M = 128;
-
-__device__ __forceinline__ void red_release_add(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Bounded wait until the counter has reached `target` (wrap-safe).  False when the limit expired.
-__device__ __forceinline__ bool grid_wait(const uint32_t* ctr, uint32_t target) {
-  for (uint32_t it = 0; it < SB1_GRID_WAIT_LIMIT; ++it) {
-    if (static_cast<int32_t>(ld_acquire_u32(ctr) - target) >= 0) return true;
-  }
-  return false;
-}
-
-// acc + sum over the 8 (fp32: 4) elements of a 16-byte chunk of w[e] * x[e], in element order with one
-// rounding per step.  16-bit types use the mixed-precision fma (both factors 16-bit, fp32 addend and
-// result): the product of two 16-bit floats is exact in fp32, so the result equals convert + fmaf while
-// no conversion instruction is issued.
-template <typename T> struct MixDot;
-template <> struct MixDot<float> {
-  static __device__ __forceinline__ float run(const uint4& w, const uint4& x, float acc) {
-    acc = fmaf(__uint_as_float(w.x), __uint_as_float(x.x), acc);
-    acc = fmaf(__uint_as_float(w.y), __uint_as_float(x.y), acc);
-    acc = fmaf(__uint_as_float(w.z), __uint_as_float(x.z), acc);
-    acc = fmaf(__uint_as_float(w.w), __uint_as_float(x.w), acc);
-    return acc;
-  }
-};
-#define STX_MIXDOT_PAIR(SUFFIX)                                                                               \
-  asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\tmov.b32 {wl, wh}, %1;\n\tmov.b32 {xl, xh}, %2;\n\t"                  \
-      "fma.rn.f32." SUFFIX " %0, wl, xl, %0;\n\tfma.rn.f32." SUFFIX " %0, wh, xh, %0;\n\t}"                   \
-      : "+f"(acc)                                                                                             \
-      : "r"(ww), "r"(xx))
-template <> struct MixDot<__half> {
-  static __device__ __forceinline__ float run(const uint4& w, const uint4& x, float acc) {
-    const uint32_t wv[4] = {w.x, w.y, w.z, w.w}, xv[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t ww = wv[i], xx = xv[i];
-      STX_MIXDOT_PAIR("f16");
-    }
-    return acc;
-  }
-};
-template <> struct MixDot<__nv_bfloat16> {
-  static __device__ __forceinline__ float run(const uint4& w, const uint4& x, float acc) {
-    const uint32_t wv[4] = {w.x, w.y, w.z, w.w}, xv[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t ww = wv[i], xx = xv[i];
-      STX_MIXDOT_PAIR("bf16");
-    }
-    return acc;
-  }
-};
-#undef STX_MIXDOT_PAIR
 
 // PASS: 16-byte column chunks per thread (1: H / V <= 512, 2: up to 1024)
 template <typename T, int PASS>
@@ -309,7 +236,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_b1(const __grid_consta
   };
   auto barrier_wait = [&](int word, uint32_t target, int l) {
     if (tid == 0 && !s_dead) {
-      if (!grid_wait(q.sync + word, target)) {
+      if (!grid_wait(q.sync + word, target, grid_wait_limit(q.peer.world))) {
         s_dead = 1;
         if (q.layer[l].status) atomicOr(q.layer[l].status, DEV_TIMEOUT);
       }
@@ -627,15 +554,26 @@ bool stack_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype
 }
 
 size_t stack_b1_scratch_bytes(int64_t L, int64_t H, int64_t r) {
-  // sync words | t [L][r] | partial [2][G][H]
-  return 1024 + align_up(static_cast<size_t>(L) * r * 4, 256) + static_cast<size_t>(2) * stack_b1_grid() * H * 4;
+  // sync words | t [L][r] | partial [max(L, 2)][G][H] (the layer-by-layer kernel uses two of them)
+  return 1024 + align_up(static_cast<size_t>(L) * r * 4, 256) + static_cast<size_t>(std::max<int64_t>(L, 2)) * stack_b1_grid() * H * 4;
+}
+
+// STX_STACK_ORDER=layerwise keeps the layer-by-layer kernel also where the layers could flow (read when a
+// stack's graph is captured).
+static bool stack_flow_enabled() {
+  const char* e = getenv("STX_STACK_ORDER");
+  return !(e && !strcmp(e, "layerwise"));
 }
 
 template <typename T>
-static int launch_stack_b1(StackB1Args& a, cudaStream_t s) {
+static int launch_stack_b1(StackB1Args& a, int dtype, cudaStream_t s) {
   const int G = stack_b1_grid();
   a.nslot = sb1_slots<T>(a.H, a.has_gate);
   const size_t smem = sb1_fixed_bytes(a.H, sizeof(T)) + static_cast<size_t>(a.nslot) * a.H * sizeof(T) * (a.has_gate ? 3 : 2);
+  // Layers that do not feed one another flow (stx_stack_flow.cu).  Sharded, every layer needs its own place in the
+  // peer object's exchange buffer.
+  if (!a.strict && stack_flow_enabled() && (a.peer.world <= 1 || static_cast<long long>(a.L) * a.H <= a.peer.max_elems))
+    return stack_flow_launch(a, dtype, smem, sb1_smem_budget<T>(), s);
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -667,9 +605,9 @@ int stack_b1_forward(StackB1Args& a, void* scratch, int dtype, cudaStream_t s) {
   a.t_buf = reinterpret_cast<float*>(p + 1024);
   a.partial = reinterpret_cast<float*>(p + 1024 + align_up(static_cast<size_t>(a.L) * a.r * 4, 256));
   switch (dtype) {
-    case STX_F32: return launch_stack_b1<float>(a, s);
-    case STX_F16: return launch_stack_b1<__half>(a, s);
-    default: return launch_stack_b1<__nv_bfloat16>(a, s);
+    case STX_F32: return launch_stack_b1<float>(a, dtype, s);
+    case STX_F16: return launch_stack_b1<__half>(a, dtype, s);
+    default: return launch_stack_b1<__nv_bfloat16>(a, dtype, s);
   }
 }
 

@@ -23,7 +23,7 @@ struct StackB1Args {
   StackLayerDesc layer[STACK_B1_MAX_LAYERS];
   const void* x;     // [H]
   float* t_buf;      // [L][r]
-  float* partial;    // [2][G][H] per-CTA partial outputs, double-buffered by layer parity
+  float* partial;    // [max(L, 2)][G][H] per-CTA partial outputs (layer-by-layer kernel: two of them, by layer parity)
   uint32_t* sync;    // counters (see the kernel)
   int L, H, I, r, has_gate, nslot, strict;
   PeerArgs peer;     // world > 1: the output sum of a layer ends with the all-reduce over the shards
@@ -34,5 +34,8 @@ size_t stack_b1_scratch_bytes(int64_t L, int64_t H, int64_t r);
 // One launch for layers [0, a.L), a.L <= STACK_B1_MAX_LAYERS.  scratch: stack_b1_scratch_bytes(a.L, ..)
 // bytes, zeroed once at allocation and then owned by the launches of this group of layers.
 int stack_b1_forward(StackB1Args& a, void* scratch, int dtype, cudaStream_t s);
+// The flow kernel on the same arguments and scratch (stx_stack_flow.cu); stack_b1_forward picks it for layers
+// that do not feed one another.  smem: dynamic shared memory of the launch, smem_limit: the opt-in maximum.
+int stack_flow_launch(const StackB1Args& a, int dtype, size_t smem, size_t smem_limit, cudaStream_t s);
 
 }  // namespace stx

@@ -1,0 +1,542 @@
+// One decode token (a single row) through a stack of sparse layers as ONE persistent kernel whose row stream
+// never stops: the predictors of ALL layers first, then the active rows of layer after layer without a grid
+// barrier in between.
+//
+// stx_stack_step feeds every layer of the stack the same x (its contract), so nothing a layer computes is
+// an input of another layer.  The layer-by-layer kernel (stx_stack_b1.cu) still pays, per layer, two grid
+// barriers and a round trip to HBM during which no row is in flight: 15 us per layer of which the rows
+// need 5.  Here:
+//   phase T   t(l) = round(A(l) x) for all layers: L * r dot products, one per warp, spread over all CTAs,
+//             in the summation order of k_pred_t;                                             grid barrier
+//   phase S   for every layer the CTA's 8 mask bytes: scores in the arithmetic order of k_pred_scores,
+//             threshold, mask bytes to the layer's mask words (t and the CTA's slice of the predictor's up
+//             matrix of the next layer are requested while the current one is computed);      grid barrier
+//   phase R   the CTA walks the layers.  Per layer it scans the mask (its words were requested two layers
+//             earlier), takes the neurons of ranks [c*K/G, (c+1)*K/G) and consumes them four at a time from
+//             shared-memory slots (one bulk copy per neuron record, mbarrier completion) exactly as the
+//             layer-by-layer kernel does.  The slots are a ring over ALL layers: a group of four slots that
+//             has been consumed takes the CTA's next group, which may belong to the next layer, so the CTA
+//             always has two to three groups of rows in flight.  The CTA's partial output vector of a layer
+//             goes to its own place in global memory (fp32, [L][G][H]);                       grid barrier
+//   phase O   out[l] = sum of the G partial vectors in a fixed order: a warp per layer, a lane adds every
+//             fourth vector of a float4 column, the four lanes of a column meet by butterfly (deterministic,
+//             no atomics).  Sharded over several GPUs the warp pushes its sums to every peer's exchange
+//             buffer (stx_peer.cuh), every layer in its own place, and collects all layers afterwards: the
+//             NVLink round trip is paid once per token, not once per layer.
+// A model that feeds out[l] forward into layer l+1 cannot use this order: the layer-by-layer kernel with
+// `strict` is the one for it.
+//
+// Every wait is bounded (grid barriers, mbarriers, peer words); an expired wait sets DEV_TIMEOUT in a
+// layer's status word and the kernel falls through, so it always terminates.  The barrier counters only
+// grow; a launch derives its targets from a generation word that CTA 0 advances at the end, so a replayed
+// CUDA graph needs no reset.  The launch is cooperative: all CTAs are co-resident, which the barriers need.
+#include "stx_common.cuh"
+#include "stx_tma.cuh"
+#include "stx_stack_b1.cuh"
+#include "stx_stack_dev.cuh"
+
+namespace stx {
+
+template <typename T, int PASS>
+__global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_constant__ StackB1Args q) {
+  constexpr int V = DT<T>::V;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint32_t s_nib[16];
+  __shared__ int s_wsum[SB1_WARPS];
+  __shared__ int s_total;
+  __shared__ int s_dead;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = gridDim.x, c = blockIdx.x;
+  const int H = q.H, I = q.I, r = q.r, L = q.L, S = q.nslot;
+  const int nchunk = H / V, qchunk = nchunk >> 2;
+  const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+  const int ngu = q.has_gate ? 2 : 1;
+  const uint32_t slot_bytes = row_bytes * (ngu + 1);
+
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);  // one per slot
+  float* a_s = reinterpret_cast<float*>(smem + SB1_OFF_AS);
+  float2* pd = reinterpret_cast<float2*>(smem + SB1_OFF_PD);
+  float* t_s = reinterpret_cast<float*>(smem + SB1_OFF_T);    // phase S: t of the layer; phase R: the list of odd layers
+  int* list_even = reinterpret_cast<int*>(smem + SB1_OFF_MY);  // the CTA's neurons of a layer [SB1_MY_CAP], by layer parity
+  int* list_odd = reinterpret_cast<int*>(smem + SB1_OFF_T);
+  T* x_s = reinterpret_cast<T*>(smem + SB1_HEADER);
+  unsigned char* slots = smem + SB1_HEADER + (static_cast<size_t>(row_bytes) + 127) / 128 * 128;
+
+  if (tid == 0) {
+    for (int w = 0; w < SB1_MAX_SLOTS; ++w) mbar_init(&bar[w], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    s_dead = 0;
+  }
+  {
+    const uint4* xg = reinterpret_cast<const uint4*>(q.x);
+    uint4* xs4 = reinterpret_cast<uint4*>(x_s);
+    for (int i = tid; i < nchunk; i += SB1_THREADS) xs4[i] = __ldcg(xg + i);
+  }
+  const uint32_t gen = __ldcg(q.sync + SB1_SYNC_GEN);
+  const int peer_epoch0 = q.peer.world > 1 ? *reinterpret_cast<volatile int*>(q.peer.ctl) : 0;
+  __syncthreads();
+  bool timed_out = false;
+
+  auto barrier_arrive = [&](int word) {  // everything this CTA wrote before is published
+    __syncthreads();
+    if (tid == 0) red_release_add(q.sync + word, 1u);
+  };
+  auto barrier_wait = [&](int word) {
+    if (tid == 0 && !s_dead) {
+      if (!grid_wait(q.sync + word, (gen + 1u) * static_cast<uint32_t>(G), grid_wait_limit(q.peer.world))) {
+        s_dead = 1;
+        if (q.layer[0].status) atomicOr(q.layer[0].status, DEV_TIMEOUT);
+      }
+    }
+    __syncthreads();
+  };
+
+  // ---- score geometry (one pass of 8 mask bytes per CTA; the launcher guarantees nby <= 8)
+  const int rch = r / V, nc4 = (rch + 7) >> 3;  // nc4 <= 2
+  const int NBY = (I + 7) >> 3;
+  const int nby = NBY > c ? (NBY - 1 - c) / G + 1 : 0;
+  const int g8 = tid & 7;
+  const int kk = tid >> 6;                               // mask byte of the CTA this thread works on
+  const int my_n = 8 * (c + G * kk) + ((tid >> 3) & 7);  // its neuron
+  const bool n_ok = kk < nby && my_n < I;
+  const int NT = min(1024, (nchunk + 31) / 32 * 32);     // virtual threads of the t reduction (as k_pred_t's block)
+  const int W = (I + 31) >> 5;                           // mask words
+  const int WPT = (W + SB1_THREADS - 1) / SB1_THREADS;   // <= 4
+
+  uint4 wraw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  auto load_w = [&](int l, uint4 (&dst)[2]) {
+    const T* Bm = static_cast<const T*>(q.layer[l].Bm);
+#pragma unroll
+    for (int c4 = 0; c4 < 2; ++c4) {
+      const int ch = g8 + 8 * c4;
+      dst[c4] = make_uint4(0, 0, 0, 0);
+      if (n_ok && ch < rch) dst[c4] = ld_stream16(Bm + static_cast<size_t>(my_n) * r + ch * V);
+    }
+  };
+  load_w(0, wraw);  // weights do not depend on data: on their way while t is formed
+
+  // ================================================================== phase T: t of every layer
+  // Task (l, k) = row k of A(l) against x, one warp each.  Virtual thread v of k_pred_t owns the 16-byte chunk
+  // v; its block adds the chunk sums by butterfly inside each group of 32 and then over the group sums.  A warp
+  // reproduces that: group g's butterfly leaves the group sum in every lane, lane g keeps it, and a last
+  // butterfly over the lanes adds the group sums.
+  {
+    const int ntask = L * r, NTG = NT >> 5;
+    for (int task = c + G * warp; task < ntask; task += G * SB1_WARPS) {
+      const int l = task / r, k = task - l * r;
+      const T* arow = static_cast<const T*>(q.layer[l].A) + static_cast<size_t>(k) * H;
+      float mine = 0.f;
+      for (int g0 = 0; g0 < NTG; g0 += 4) {  // four chunks per lane in flight
+        uint4 w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int ch = (g0 + u) * 32 + lane;
+          w[u] = (g0 + u < NTG && ch < nchunk) ? ld_stream16(arow + ch * V) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (g0 + u < NTG) {
+            const int ch = (g0 + u) * 32 + lane;
+            float p = 0.f;
+            if (ch < nchunk) p = MixDot<T>::run(w[u], *reinterpret_cast<const uint4*>(x_s + ch * V), 0.f);
+            p = warp_sum_xor(p);
+            if (lane == g0 + u) mine = p;
+          }
+        }
+      }
+      const float s = warp_sum_xor(lane < NTG ? mine : 0.f);
+      if (lane == 0) q.t_buf[task] = DT<T>::round_f(s);
+    }
+  }
+  barrier_arrive(SB1_SYNC_FT);
+  barrier_wait(SB1_SYNC_FT);
+
+  // ================================================================== phase S: the masks of every layer
+  {
+    auto t_index = [&](int e) {  // element e of t in the layout the score loop reads
+      const int ch = e / V, v = e - ch * V;
+      return (((ch >> 3) * (V / 4) + (v >> 2)) * 8 + (ch & 7)) * 4 + (v & 3);
+    };
+    if (tid < r) t_s[t_index(tid)] = __ldcg(q.t_buf + tid);
+    __syncthreads();
+    for (int l = 0; l < L; ++l) {
+      const StackLayerDesc& ld = q.layer[l];
+      uint4 wn[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+      float tvn = 0.f;
+      if (l + 1 < L) {  // the next layer's operands travel while this one is computed
+        load_w(l + 1, wn);
+        if (tid < r) tvn = __ldcg(q.t_buf + static_cast<size_t>(l + 1) * r + tid);
+      }
+      const float tau_r = DT<T>::round_f(ld.tau);
+      float sc = 0.f;
+#pragma unroll
+      for (int c4 = 0; c4 < 2; ++c4) {
+        const int ch = g8 + 8 * c4;
+        if (c4 < nc4 && ch < rch) {
+          float w[V];
+          Unpack<T>::run(wraw[c4], w);
+          const float4* tb = reinterpret_cast<const float4*>(t_s) + (c4 * (V / 4)) * 8 + g8;
+#pragma unroll
+          for (int v4 = 0; v4 < V / 4; ++v4) {
+            const float4 tv = tb[v4 * 8];
+            sc = fmaf(tv.x, w[4 * v4], sc);
+            sc = fmaf(tv.y, w[4 * v4 + 1], sc);
+            sc = fmaf(tv.z, w[4 * v4 + 2], sc);
+            sc = fmaf(tv.w, w[4 * v4 + 3], sc);
+          }
+        }
+      }
+      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+      const bool on = n_ok && DT<T>::round_f(sc) >= tau_r;
+      const uint32_t bal = __ballot_sync(0xffffffffu, on && g8 == 0);
+      if (lane == 0) s_nib[warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
+      __syncthreads();  // the nibbles are there; nobody reads t_s any more
+      if (tid < 8 && tid < nby)
+        reinterpret_cast<uint8_t*>(ld.bits)[c + G * tid] = static_cast<uint8_t>(s_nib[2 * tid] | (s_nib[2 * tid + 1] << 4));
+      if (l + 1 < L && tid < r) t_s[t_index(tid)] = tvn;
+      wraw[0] = wn[0];
+      wraw[1] = wn[1];
+      __syncthreads();
+    }
+  }
+  barrier_arrive(SB1_SYNC_FM);
+  barrier_wait(SB1_SYNC_FM);
+
+  // ================================================================== phase R: the rows, layer after layer
+  // phase 1: warp w always works on quarter w & 3 of a row; its lanes' chunks of x stay in registers
+  const int sub = warp & 3, gi = warp >> 2;
+  uint4 xq[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int ch = lane + 32 * k;
+    xq[k] = ch < qchunk ? reinterpret_cast<const uint4*>(x_s)[sub * qchunk + ch] : make_uint4(0, 0, 0, 0);
+  }
+  auto load_words = [&](int l, uint32_t (&wv)[4]) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int w = tid * WPT + k;
+      wv[k] = (k < WPT && w < W) ? __ldcg(q.layer[l].bits + w) : 0u;
+    }
+  };
+  // The CTA's share of a layer's active neurons, ranks [c*K/G, (c+1)*K/G) of the set bits, into `dst`.  Returns
+  // their number.  Contains block barriers (three; the last one publishes the list).
+  auto build_list = [&](const uint32_t (&wv)[4], int* dst) {
+    int cnt = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) cnt += __popc(wv[k]);
+    int inc = cnt;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, off);
+      if (lane >= off) inc += v;
+    }
+    if (lane == 31) s_wsum[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      const int v = lane < SB1_WARPS ? s_wsum[lane] : 0;
+      int winc = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, winc, off);
+        if (lane >= off) winc += u;
+      }
+      if (lane < SB1_WARPS) s_wsum[lane] = winc - v;
+      if (lane == 31) s_total = winc;
+    }
+    __syncthreads();
+    const int K = s_total;
+    const int lo = static_cast<int>(static_cast<long long>(c) * K / G);
+    const int hi = static_cast<int>(static_cast<long long>(c + 1) * K / G);
+    const int n = min(hi - lo, SB1_MY_CAP);
+    int rho = s_wsum[warp] + inc - cnt;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t b = wv[k];
+      const int w = tid * WPT + k;
+      if (rho + __popc(b) > lo && rho < hi) {
+        while (b) {
+          const int id = w * 32 + __ffs(b) - 1;
+          b &= b - 1;
+          if (rho >= lo && rho - lo < n) dst[rho - lo] = id;
+          ++rho;
+        }
+      } else {
+        rho += __popc(b);
+      }
+    }
+    __syncthreads();
+    return n;
+  };
+
+  // The slots are a ring of nsg groups of four.  Groups of neurons are numbered through all layers of the CTA:
+  // group number j sits in slot group j % nsg.  n_cons groups have been consumed, n_issued requested; a slot
+  // group may be requested again once every thread has passed a block barrier behind its last read (n_safe).
+  // All of this is the same in every thread; warp 1 issues the copies.
+  const int nsg = S >> 2;
+  uint32_t ph = 0u;   // mbarrier phase parity per slot
+  int n_cons = 0, n_issued = 0, n_safe = 0, sg_cons = 0, sg_issue = 0;
+  int il = 0, ig = 0;  // layer and group of the next request
+  auto try_issue = [&](int l_cons, int n_c, int n_n, bool next_ok) {
+    while (n_issued - n_safe < nsg) {
+      if (il == l_cons && ig * 4 >= n_c) {
+        il = l_cons + 1;
+        ig = 0;
+      }
+      int n_of;
+      if (il == l_cons) n_of = n_c;
+      else if (il == l_cons + 1 && next_ok) n_of = n_n;
+      else break;
+      if (ig * 4 >= n_of) break;  // nothing more is known yet
+      const int nv = min(4, n_of - 4 * ig);
+      if (warp == 1 && lane < nv) {
+        // the slot was only READ since its last copy, and every reader has passed a block barrier: no proxy fence
+        const int* lst = (il & 1) ? list_odd : list_even;
+        const int s = sg_issue * 4 + lane;
+        mbar_expect_tx(&bar[s], slot_bytes);
+        bulk_load(slots + static_cast<size_t>(s) * slot_bytes,
+                  static_cast<const char*>(q.layer[il].cat) + static_cast<size_t>(lst[4 * ig + lane]) * slot_bytes, slot_bytes, &bar[s]);
+      }
+      ++ig;
+      ++n_issued;
+      sg_issue = sg_issue + 1 == nsg ? 0 : sg_issue + 1;
+    }
+  };
+
+  uint32_t wnext[4];
+  load_words(0, wnext);
+  int n_cur = build_list(wnext, list_even), n_next = 0;
+  if (L > 1) load_words(1, wnext);
+
+  for (int l = 0; l < L; ++l) {
+    const StackLayerDesc& ld = q.layer[l];
+    if (il < l) {
+      il = l;
+      ig = 0;
+    }
+    // the next layer's list from the words requested a layer ago; then the words of the layer after it
+    const bool next_ok = l + 1 < L;
+    n_next = 0;
+    if (next_ok) {
+      n_next = build_list(wnext, ((l + 1) & 1) ? list_odd : list_even);
+      if (l + 2 < L) load_words(l + 2, wnext);
+    } else {
+      __syncthreads();
+    }
+    n_safe = n_cons;  // every thread has passed a block barrier since the last group was read
+    try_issue(l, n_cur, n_next, next_ok);
+
+    float acc[PASS][V];
+#pragma unroll
+    for (int k = 0; k < PASS; ++k)
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[k][v] = 0.f;
+
+    const int ngroups = (n_cur + 3) >> 2;
+    for (int g = 0; g < ngroups; ++g) {
+      const int s0 = sg_cons * 4;
+      const int nv = min(4, n_cur - 4 * g);
+      float2* pdg = pd + (g & 1) * 16;
+      // ---- phase 1: a task is a quarter of a neuron's gate and up row against the matching quarter of x
+      if (gi < nv) {
+        const int sl_i = s0 + gi;
+        if (!mbar_wait_bounded(&bar[sl_i], (ph >> sl_i) & 1u)) timed_out = true;
+        const unsigned char* sl = slots + static_cast<size_t>(sl_i) * slot_bytes;
+        const uint4* grow = reinterpret_cast<const uint4*>(sl) + sub * qchunk;
+        const uint4* urow = reinterpret_cast<const uint4*>(sl + (q.has_gate ? row_bytes : 0)) + sub * qchunk;
+        float ag0 = 0.f, ag1 = 0.f, au0 = 0.f, au1 = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // the chunks whose x sits in registers
+          const int ch = lane + 32 * k;
+          if (ch < qchunk) {
+            if (k & 1) au1 = MixDot<T>::run(urow[ch], xq[k], au1);
+            else au0 = MixDot<T>::run(urow[ch], xq[k], au0);
+            if (q.has_gate) {
+              if (k & 1) ag1 = MixDot<T>::run(grow[ch], xq[k], ag1);
+              else ag0 = MixDot<T>::run(grow[ch], xq[k], ag0);
+            }
+          }
+          if (k == 1) asm volatile("" ::: "memory");  // two chunk pairs in flight, not four (registers)
+        }
+        for (int ch = lane + 128; ch < qchunk; ch += 32) {  // rows longer than 512 chunks: x from shared memory
+          const uint4 xv = reinterpret_cast<const uint4*>(x_s)[sub * qchunk + ch];
+          au0 = MixDot<T>::run(urow[ch], xv, au0);
+          if (q.has_gate) ag0 = MixDot<T>::run(grow[ch], xv, ag0);
+        }
+        const float u = warp_sum_xor(au0 + au1);
+        const float gs = q.has_gate ? warp_sum_xor(ag0 + ag1) : 0.f;
+        if (lane == 0) pdg[gi * 4 + sub] = make_float2(gs, u);
+      }
+      __syncthreads();  // the quarter sums of the group are there; every thread is done with the group before
+      n_safe = n_cons;
+      if (tid < nv) {
+        const float2 p0 = pdg[tid * 4], p1 = pdg[tid * 4 + 1], p2 = pdg[tid * 4 + 2], p3 = pdg[tid * 4 + 3];
+        const float gsum = (p0.x + p1.x) + (p2.x + p3.x);
+        const float usum = (p0.y + p1.y) + (p2.y + p3.y);
+        a_s[(g & 1) * 4 + tid] = q.has_gate ? apply_act(ld.act, gsum) * usum : apply_act(ld.act, usum);
+      }
+      try_issue(l, n_cur, n_next, next_ok);  // warp 1 requests while warp 0 forms a
+      __syncthreads();  // a of the group
+      // ---- phase 2: thread j owns the 16-byte column chunks j, j + 512
+#pragma unroll
+      for (int k = 0; k < PASS; ++k) {
+        const int cc = tid + k * SB1_THREADS;
+        if (cc < nchunk) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (i < nv) {
+              const float a = a_s[(g & 1) * 4 + i];
+              const T* drow = reinterpret_cast<const T*>(slots + static_cast<size_t>(s0 + i) * slot_bytes + static_cast<size_t>(ngu) * row_bytes);
+              float wd[V];
+              Unpack<T>::run(*reinterpret_cast<const uint4*>(drow + cc * V), wd);
+#pragma unroll
+              for (int v = 0; v < V; ++v) acc[k][v] = fmaf(a, wd[v], acc[k][v]);
+            }
+          }
+        }
+      }
+      ph ^= ((1u << nv) - 1u) << s0;
+      ++n_cons;
+      sg_cons = sg_cons + 1 == nsg ? 0 : sg_cons + 1;
+    }
+
+    // ---- the CTA's partial output vector of the layer
+    {
+      float* dst = q.partial + (static_cast<size_t>(l) * G + c) * H;
+#pragma unroll
+      for (int k = 0; k < PASS; ++k) {
+        const int cc = tid + k * SB1_THREADS;
+        if (cc < nchunk) {
+#pragma unroll
+          for (int v = 0; v < V; v += 4)
+            *reinterpret_cast<float4*>(dst + cc * V + v) = make_float4(acc[k][v], acc[k][v + 1], acc[k][v + 2], acc[k][v + 3]);
+        }
+      }
+    }
+    n_cur = n_next;
+  }
+  barrier_arrive(SB1_SYNC_FP);
+  barrier_wait(SB1_SYNC_FP);
+
+  // ================================================================== phase O: out[l] = sum of the partial vectors
+  // This CTA's columns: cpc float4 columns (<= 8).  Warp w sums layers w, w + 16, ...: lane = (vector group
+  // ps = lane >> 3, column lane & 7) adds the vectors ps, ps + 4, ps + 8, ... in that order, the four lanes of
+  // a column meet by butterfly.
+  {
+    const int ncol4 = H / 4;
+    const int cpc = (ncol4 + G - 1) / G;
+    const int col0 = c * cpc;
+    const int ncols = max(0, min(cpc, ncol4 - col0));
+    const int rcol = lane & 7, rps = lane >> 3;
+    const bool sharded = q.peer.world > 1;
+    const int epoch = peer_epoch0 + 1;
+    float4 mine[(STACK_B1_MAX_LAYERS + SB1_WARPS - 1) / SB1_WARPS];
+    int round = 0;
+    for (int l = warp; l < L; l += SB1_WARPS, ++round) {
+      const float* part = q.partial + static_cast<size_t>(l) * G * H;
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (rcol < ncols) {
+        for (int p0 = rps; p0 < G; p0 += 32) {  // eight vectors per lane in flight
+          float4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int p = p0 + 4 * u;
+            v[u] = p < G ? __ldcg(reinterpret_cast<const float4*>(part + static_cast<size_t>(p) * H) + col0 + rcol) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            sum.x += v[u].x;
+            sum.y += v[u].y;
+            sum.z += v[u].z;
+            sum.w += v[u].w;
+          }
+        }
+      }
+#pragma unroll
+      for (int off = 8; off <= 16; off <<= 1) {
+        sum.x += __shfl_xor_sync(0xffffffffu, sum.x, off);
+        sum.y += __shfl_xor_sync(0xffffffffu, sum.y, off);
+        sum.z += __shfl_xor_sync(0xffffffffu, sum.z, off);
+        sum.w += __shfl_xor_sync(0xffffffffu, sum.w, off);
+      }
+      if (sharded) {  // lane rps carries element rps of the column's four
+        const float own = rps == 0 ? sum.x : rps == 1 ? sum.y : rps == 2 ? sum.z : sum.w;
+        if (rcol < ncols) peer_push(q.peer, epoch, static_cast<long long>(l) * H + (col0 + rcol) * 4 + rps, own);
+      }
+#pragma unroll
+      for (int k = 0; k < static_cast<int>(sizeof(mine) / sizeof(mine[0])); ++k)
+        if (k == round) mine[k] = sum;
+    }
+    round = 0;
+    for (int l = warp; l < L; l += SB1_WARPS, ++round) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < static_cast<int>(sizeof(mine) / sizeof(mine[0])); ++k)
+        if (k == round) sum = mine[k];
+      float own = rps == 0 ? sum.x : rps == 1 ? sum.y : rps == 2 ? sum.z : sum.w;
+      if (rcol < ncols) {
+        if (sharded) {  // add what the peers pushed, in rank order
+          bool lost = false;
+          own = peer_collect(q.peer, epoch, static_cast<long long>(l) * H + (col0 + rcol) * 4 + rps, own, &lost);
+          if (lost) {
+            atomicOr(q.peer.ctl + 2, DEV_TIMEOUT);
+            if (q.layer[l].status) atomicOr(q.layer[l].status, DEV_TIMEOUT);
+          }
+        }
+        static_cast<T*>(q.layer[l].out)[(col0 + rcol) * 4 + rps] = DT<T>::from_f(own);
+      }
+    }
+  }
+
+  if (timed_out && q.layer[0].status) atomicOr(q.layer[0].status, DEV_TIMEOUT);
+  if (c == 0 && tid == 0) q.sync[SB1_SYNC_GEN] = gen + 1u;
+  if (q.peer.world > 1) {
+    // the launch's last CTA advances the peer object's exchange number (every CTA read it at the start, and
+    // every CTA is past its exchanges when it arrives here)
+    __syncthreads();
+    if (tid == 0 && atomicAdd(reinterpret_cast<unsigned*>(q.peer.ctl + 1), 1u) == gridDim.x - 1) {
+      q.peer.ctl[1] = 0;
+      *reinterpret_cast<volatile int*>(q.peer.ctl) = peer_epoch0 + 1;
+    }
+  }
+}
+
+template <typename T>
+static int launch_stack_flow(const StackB1Args& a, size_t smem, size_t smem_limit, cudaStream_t s) {
+  const int G = num_sms();
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
+    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(G);
+  cfg.blockDim = dim3(SB1_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeCooperative;  // all CTAs co-resident: they wait on one another
+  at[0].val.cooperative = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  if (a.H / DT<T>::V <= SB1_THREADS)
+    STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 1>, a));
+  else
+    STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 2>, a));
+  return STX_OK;
+}
+
+int stack_flow_launch(const StackB1Args& a, int dtype, size_t smem, size_t smem_limit, cudaStream_t s) {
+  switch (dtype) {
+    case STX_F32: return launch_stack_flow<float>(a, smem, smem_limit, s);
+    case STX_F16: return launch_stack_flow<__half>(a, smem, smem_limit, s);
+    default: return launch_stack_flow<__nv_bfloat16>(a, smem, smem_limit, s);
+  }
+}
+
+}  // namespace stx
