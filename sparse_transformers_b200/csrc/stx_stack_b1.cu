@@ -565,15 +565,18 @@ static bool stack_flow_enabled() {
   return !(e && !strcmp(e, "layerwise"));
 }
 
+// Layers that do not feed one another flow (stx_stack_flow.cu).  Sharded, every layer needs its own place in the
+// peer object's exchange buffer.
+static bool stack_flow_selected(const StackB1Args& a) {
+  return !a.strict && stack_flow_enabled() && (a.peer.world <= 1 || static_cast<long long>(a.L) * a.H <= a.peer.max_elems);
+}
+
 template <typename T>
 static int launch_stack_b1(StackB1Args& a, int dtype, cudaStream_t s) {
   const int G = stack_b1_grid();
   a.nslot = sb1_slots<T>(a.H, a.has_gate);
   const size_t smem = sb1_fixed_bytes(a.H, sizeof(T)) + static_cast<size_t>(a.nslot) * a.H * sizeof(T) * (a.has_gate ? 3 : 2);
-  // Layers that do not feed one another flow (stx_stack_flow.cu).  Sharded, every layer needs its own place in the
-  // peer object's exchange buffer.
-  if (!a.strict && stack_flow_enabled() && (a.peer.world <= 1 || static_cast<long long>(a.L) * a.H <= a.peer.max_elems))
-    return stack_flow_launch(a, dtype, smem, sb1_smem_budget<T>(), s);
+  if (stack_flow_selected(a)) return stack_flow_launch(a, dtype, smem, sb1_smem_budget<T>(), s);
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -9,8 +9,9 @@
 //   phase T   t(l) = round(A(l) x) for all layers: L * r dot products, one per warp, spread over all CTAs,
 //             in the summation order of k_pred_t;                                             grid barrier
 //   phase S   for every layer the CTA's 8 mask bytes: scores in the arithmetic order of k_pred_scores,
-//             threshold, mask bytes to the layer's mask words (t and the CTA's slice of the predictor's up
-//             matrix of the next layer are requested while the current one is computed);      grid barrier
+//             threshold, mask bytes to the layer's mask words.  t of all layers sits in shared memory, the
+//             CTA's slice of the predictor's up matrix is requested four layers ahead, and the loop over the
+//             layers contains no block barrier;                                               grid barrier
 //   phase R   the CTA walks the layers.  Per layer it scans the mask (its words were requested two layers
 //             earlier), takes the neurons of ranks [c*K/G, (c+1)*K/G) and consumes them four at a time from
 //             shared-memory slots (one bulk copy per neuron record, mbarrier completion) exactly as the
@@ -37,11 +38,23 @@
 
 namespace stx {
 
+constexpr int FLOW_LIST_CAP = 256;  // neurons of one CTA per layer (two lists of 16-bit ids fill 2 x 512 bytes of the header)
+
+// Layers are dealt to `ng` groups of CTAs (CTA c is in group c % ng and works on the layers l with l % ng equal to
+// its group): a layer's neurons then spread over G / ng CTAs, each with ng times as many neurons of a quarter of
+// the layers - the same work, but a layer leaves G / ng partial vectors instead of G, and the per-layer overhead
+// of a CTA (scan, list, partial vector) is paid L / ng times.  ng is the largest of 4, 2, 1 that divides L and
+// keeps a CTA's share of a full mask within its list.
+__host__ __device__ inline int flow_groups(int L, int G, int I) {
+  for (int n = 4; n >= 2; n >>= 1)
+    if (L % n == 0 && G / n >= 1 && (I + G / n - 1) / (G / n) <= FLOW_LIST_CAP) return n;
+  return 1;
+}
+
 template <typename T, int PASS>
 __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_constant__ StackB1Args q) {
   constexpr int V = DT<T>::V;
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ uint32_t s_nib[16];
   __shared__ int s_wsum[SB1_WARPS];
   __shared__ int s_total;
   __shared__ int s_dead;
@@ -57,9 +70,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);  // one per slot
   float* a_s = reinterpret_cast<float*>(smem + SB1_OFF_AS);
   float2* pd = reinterpret_cast<float2*>(smem + SB1_OFF_PD);
-  float* t_s = reinterpret_cast<float*>(smem + SB1_OFF_T);    // phase S: t of the layer; phase R: the list of odd layers
-  int* list_even = reinterpret_cast<int*>(smem + SB1_OFF_MY);  // the CTA's neurons of a layer [SB1_MY_CAP], by layer parity
-  int* list_odd = reinterpret_cast<int*>(smem + SB1_OFF_T);
+  // the CTA's neurons of a layer (16-bit ids, FLOW_LIST_CAP of them), two buffers used in turn
+  uint16_t* list_even = reinterpret_cast<uint16_t*>(smem + SB1_OFF_MY);
+  uint16_t* list_odd = reinterpret_cast<uint16_t*>(smem + SB1_OFF_T);
   T* x_s = reinterpret_cast<T*>(smem + SB1_HEADER);
   unsigned char* slots = smem + SB1_HEADER + (static_cast<size_t>(row_bytes) + 127) / 128 * 128;
 
@@ -104,7 +117,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   const int W = (I + 31) >> 5;                           // mask words
   const int WPT = (W + SB1_THREADS - 1) / SB1_THREADS;   // <= 4
 
-  uint4 wraw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  // the CTA's slice of the predictor's up matrix, four layers ahead (weights do not depend on data: the first
+  // four are on their way while t is formed)
+  uint4 wq[4][2];
   auto load_w = [&](int l, uint4 (&dst)[2]) {
     const T* Bm = static_cast<const T*>(q.layer[l].Bm);
 #pragma unroll
@@ -114,7 +129,11 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       if (n_ok && ch < rch) dst[c4] = ld_stream16(Bm + static_cast<size_t>(my_n) * r + ch * V);
     }
   };
-  load_w(0, wraw);  // weights do not depend on data: on their way while t is formed
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    wq[u][0] = wq[u][1] = make_uint4(0, 0, 0, 0);
+    if (u < L) load_w(u, wq[u]);
+  }
 
   // ================================================================== phase T: t of every layer
   // Task (l, k) = row k of A(l) against x, one warp each.  Virtual thread v of k_pred_t owns the 16-byte chunk
@@ -127,15 +146,15 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       const int l = task / r, k = task - l * r;
       const T* arow = static_cast<const T*>(q.layer[l].A) + static_cast<size_t>(k) * H;
       float mine = 0.f;
-      for (int g0 = 0; g0 < NTG; g0 += 4) {  // four chunks per lane in flight
-        uint4 w[4];
+      for (int g0 = 0; g0 < NTG; g0 += 8) {  // eight chunks per lane in flight
+        uint4 w[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
           const int ch = (g0 + u) * 32 + lane;
           w[u] = (g0 + u < NTG && ch < nchunk) ? ld_stream16(arow + ch * V) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
           if (g0 + u < NTG) {
             const int ch = (g0 + u) * 32 + lane;
             float p = 0.f;
@@ -153,53 +172,57 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   barrier_wait(SB1_SYNC_FT);
 
   // ================================================================== phase S: the masks of every layer
+  // t of all layers goes to shared memory once (the slot area is idle until phase R), in the layout the score
+  // loop reads; the loop over the layers then needs no block barrier: a warp's four mask nibbles per layer are
+  // collected in shared memory and the CTA's mask bytes of all layers are written in one pass at the end.
   {
-    auto t_index = [&](int e) {  // element e of t in the layout the score loop reads
+    float* t_all = reinterpret_cast<float*>(slots);                                           // [L][128]
+    uint32_t* nib_all = reinterpret_cast<uint32_t*>(slots + STACK_B1_MAX_LAYERS * 512);       // [L][16]
+    for (int i = tid; i < L * r; i += SB1_THREADS) {
+      const int l = i / r, e = i - l * r;
       const int ch = e / V, v = e - ch * V;
-      return (((ch >> 3) * (V / 4) + (v >> 2)) * 8 + (ch & 7)) * 4 + (v & 3);
-    };
-    if (tid < r) t_s[t_index(tid)] = __ldcg(q.t_buf + tid);
+      t_all[l * 128 + (((ch >> 3) * (V / 4) + (v >> 2)) * 8 + (ch & 7)) * 4 + (v & 3)] = __ldcg(q.t_buf + i);
+    }
     __syncthreads();
-    for (int l = 0; l < L; ++l) {
-      const StackLayerDesc& ld = q.layer[l];
-      uint4 wn[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-      float tvn = 0.f;
-      if (l + 1 < L) {  // the next layer's operands travel while this one is computed
-        load_w(l + 1, wn);
-        if (tid < r) tvn = __ldcg(q.t_buf + static_cast<size_t>(l + 1) * r + tid);
-      }
-      const float tau_r = DT<T>::round_f(ld.tau);
-      float sc = 0.f;
+    for (int l0 = 0; l0 < L; l0 += 4) {
 #pragma unroll
-      for (int c4 = 0; c4 < 2; ++c4) {
-        const int ch = g8 + 8 * c4;
-        if (c4 < nc4 && ch < rch) {
-          float w[V];
-          Unpack<T>::run(wraw[c4], w);
-          const float4* tb = reinterpret_cast<const float4*>(t_s) + (c4 * (V / 4)) * 8 + g8;
+      for (int u = 0; u < 4; ++u) {
+        const int l = l0 + u;
+        if (l < L) {
+          const float tau_r = DT<T>::round_f(q.layer[l].tau);
+          float sc = 0.f;
 #pragma unroll
-          for (int v4 = 0; v4 < V / 4; ++v4) {
-            const float4 tv = tb[v4 * 8];
-            sc = fmaf(tv.x, w[4 * v4], sc);
-            sc = fmaf(tv.y, w[4 * v4 + 1], sc);
-            sc = fmaf(tv.z, w[4 * v4 + 2], sc);
-            sc = fmaf(tv.w, w[4 * v4 + 3], sc);
+          for (int c4 = 0; c4 < 2; ++c4) {
+            const int ch = g8 + 8 * c4;
+            if (c4 < nc4 && ch < rch) {
+              float w[V];
+              Unpack<T>::run(wq[u][c4], w);
+              const float4* tb = reinterpret_cast<const float4*>(t_all + l * 128) + (c4 * (V / 4)) * 8 + g8;
+#pragma unroll
+              for (int v4 = 0; v4 < V / 4; ++v4) {
+                const float4 tv = tb[v4 * 8];
+                sc = fmaf(tv.x, w[4 * v4], sc);
+                sc = fmaf(tv.y, w[4 * v4 + 1], sc);
+                sc = fmaf(tv.z, w[4 * v4 + 2], sc);
+                sc = fmaf(tv.w, w[4 * v4 + 3], sc);
+              }
+            }
           }
+          if (l + 4 < L) load_w(l + 4, wq[u]);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+          sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+          const bool on = n_ok && DT<T>::round_f(sc) >= tau_r;
+          const uint32_t bal = __ballot_sync(0xffffffffu, on && g8 == 0);
+          if (lane == 0) nib_all[l * 16 + warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
         }
       }
-      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
-      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-      const bool on = n_ok && DT<T>::round_f(sc) >= tau_r;
-      const uint32_t bal = __ballot_sync(0xffffffffu, on && g8 == 0);
-      if (lane == 0) s_nib[warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
-      __syncthreads();  // the nibbles are there; nobody reads t_s any more
-      if (tid < 8 && tid < nby)
-        reinterpret_cast<uint8_t*>(ld.bits)[c + G * tid] = static_cast<uint8_t>(s_nib[2 * tid] | (s_nib[2 * tid + 1] << 4));
-      if (l + 1 < L && tid < r) t_s[t_index(tid)] = tvn;
-      wraw[0] = wn[0];
-      wraw[1] = wn[1];
-      __syncthreads();
+    }
+    __syncthreads();
+    for (int i = tid; i < L * 8; i += SB1_THREADS) {
+      const int l = i >> 3, j = i & 7;
+      if (j < nby)
+        reinterpret_cast<uint8_t*>(q.layer[l].bits)[c + G * j] = static_cast<uint8_t>(nib_all[l * 16 + 2 * j] | (nib_all[l * 16 + 2 * j + 1] << 4));
     }
   }
   barrier_arrive(SB1_SYNC_FM);
@@ -214,6 +237,12 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     const int ch = lane + 32 * k;
     xq[k] = ch < qchunk ? reinterpret_cast<const uint4*>(x_s)[sub * qchunk + ch] : make_uint4(0, 0, 0, 0);
   }
+  const int ng = flow_groups(L, G, I);
+  const int gq = c % ng, mem = c / ng;           // this CTA's group and its place in it
+  const int Gg = (G - gq + ng - 1) / ng;          // CTAs of the group
+  const int GgMax = (G + ng - 1) / ng;            // partial vectors kept per layer
+  const int nl = gq < L ? (L - gq + ng - 1) / ng : 0;  // layers of this CTA: gq, gq + ng, ...
+  auto layer_of = [&](int j) { return gq + j * ng; };
   auto load_words = [&](int l, uint32_t (&wv)[4]) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -221,9 +250,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       wv[k] = (k < WPT && w < W) ? __ldcg(q.layer[l].bits + w) : 0u;
     }
   };
-  // The CTA's share of a layer's active neurons, ranks [c*K/G, (c+1)*K/G) of the set bits, into `dst`.  Returns
-  // their number.  Contains block barriers (three; the last one publishes the list).
-  auto build_list = [&](const uint32_t (&wv)[4], int* dst) {
+  // The CTA's share of a layer's active neurons, ranks [m*K/Gg, (m+1)*K/Gg) of the set bits (m: its place in the
+  // group), into `dst`.  Returns their number.  Contains block barriers (three; the last one publishes the list).
+  auto build_list = [&](const uint32_t (&wv)[4], uint16_t* dst) {
     int cnt = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) cnt += __popc(wv[k]);
@@ -248,9 +277,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     }
     __syncthreads();
     const int K = s_total;
-    const int lo = static_cast<int>(static_cast<long long>(c) * K / G);
-    const int hi = static_cast<int>(static_cast<long long>(c + 1) * K / G);
-    const int n = min(hi - lo, SB1_MY_CAP);
+    const int lo = static_cast<int>(static_cast<long long>(mem) * K / Gg);
+    const int hi = static_cast<int>(static_cast<long long>(mem + 1) * K / Gg);
+    const int n = min(hi - lo, FLOW_LIST_CAP);
     int rho = s_wsum[warp] + inc - cnt;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -260,7 +289,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
         while (b) {
           const int id = w * 32 + __ffs(b) - 1;
           b &= b - 1;
-          if (rho >= lo && rho - lo < n) dst[rho - lo] = id;
+          if (rho >= lo && rho - lo < n) dst[rho - lo] = static_cast<uint16_t>(id);
           ++rho;
         }
       } else {
@@ -272,61 +301,66 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   };
 
   // The slots are a ring of nsg groups of four.  Groups of neurons are numbered through all layers of the CTA:
-  // group number j sits in slot group j % nsg.  n_cons groups have been consumed, n_issued requested; a slot
+  // group number i sits in slot group i % nsg.  n_cons groups have been consumed, n_issued requested; a slot
   // group may be requested again once every thread has passed a block barrier behind its last read (n_safe).
-  // All of this is the same in every thread; warp 1 issues the copies.
+  // All of this is the same in every thread; warp 1 issues the copies.  jl, jg: the CTA's layer (counted in its
+  // own layers) and the group of the next request.
   const int nsg = S >> 2;
   uint32_t ph = 0u;   // mbarrier phase parity per slot
   int n_cons = 0, n_issued = 0, n_safe = 0, sg_cons = 0, sg_issue = 0;
-  int il = 0, ig = 0;  // layer and group of the next request
-  auto try_issue = [&](int l_cons, int n_c, int n_n, bool next_ok) {
+  int jl = 0, jg = 0;
+  auto try_issue = [&](int j_cons, int n_c, int n_n, bool next_ok) {
     while (n_issued - n_safe < nsg) {
-      if (il == l_cons && ig * 4 >= n_c) {
-        il = l_cons + 1;
-        ig = 0;
+      if (jl == j_cons && jg * 4 >= n_c) {
+        jl = j_cons + 1;
+        jg = 0;
       }
       int n_of;
-      if (il == l_cons) n_of = n_c;
-      else if (il == l_cons + 1 && next_ok) n_of = n_n;
+      if (jl == j_cons) n_of = n_c;
+      else if (jl == j_cons + 1 && next_ok) n_of = n_n;
       else break;
-      if (ig * 4 >= n_of) break;  // nothing more is known yet
-      const int nv = min(4, n_of - 4 * ig);
+      if (jg * 4 >= n_of) break;  // nothing more is known yet
+      const int nv = min(4, n_of - 4 * jg);
       if (warp == 1 && lane < nv) {
         // the slot was only READ since its last copy, and every reader has passed a block barrier: no proxy fence
-        const int* lst = (il & 1) ? list_odd : list_even;
+        const uint16_t* lst = (jl & 1) ? list_odd : list_even;
         const int s = sg_issue * 4 + lane;
         mbar_expect_tx(&bar[s], slot_bytes);
         bulk_load(slots + static_cast<size_t>(s) * slot_bytes,
-                  static_cast<const char*>(q.layer[il].cat) + static_cast<size_t>(lst[4 * ig + lane]) * slot_bytes, slot_bytes, &bar[s]);
+                  static_cast<const char*>(q.layer[layer_of(jl)].cat) + static_cast<size_t>(lst[4 * jg + lane]) * slot_bytes, slot_bytes, &bar[s]);
       }
-      ++ig;
+      ++jg;
       ++n_issued;
       sg_issue = sg_issue + 1 == nsg ? 0 : sg_issue + 1;
     }
   };
 
-  uint32_t wnext[4];
-  load_words(0, wnext);
-  int n_cur = build_list(wnext, list_even), n_next = 0;
-  if (L > 1) load_words(1, wnext);
+  uint32_t wnext[4] = {0u, 0u, 0u, 0u};
+  int n_cur = 0, n_next = 0;
+  if (nl > 0) {
+    load_words(layer_of(0), wnext);
+    n_cur = build_list(wnext, list_even);
+    if (nl > 1) load_words(layer_of(1), wnext);
+  }
 
-  for (int l = 0; l < L; ++l) {
+  for (int j = 0; j < nl; ++j) {
+    const int l = layer_of(j);
     const StackLayerDesc& ld = q.layer[l];
-    if (il < l) {
-      il = l;
-      ig = 0;
+    if (jl < j) {
+      jl = j;
+      jg = 0;
     }
-    // the next layer's list from the words requested a layer ago; then the words of the layer after it
-    const bool next_ok = l + 1 < L;
+    // the list of the CTA's next layer from the words requested a layer ago; then the words of the one after it
+    const bool next_ok = j + 1 < nl;
     n_next = 0;
     if (next_ok) {
-      n_next = build_list(wnext, ((l + 1) & 1) ? list_odd : list_even);
-      if (l + 2 < L) load_words(l + 2, wnext);
+      n_next = build_list(wnext, ((j + 1) & 1) ? list_odd : list_even);
+      if (j + 2 < nl) load_words(layer_of(j + 2), wnext);
     } else {
       __syncthreads();
     }
     n_safe = n_cons;  // every thread has passed a block barrier since the last group was read
-    try_issue(l, n_cur, n_next, next_ok);
+    try_issue(j, n_cur, n_next, next_ok);
 
     float acc[PASS][V];
 #pragma unroll
@@ -377,9 +411,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
         const float usum = (p0.y + p1.y) + (p2.y + p3.y);
         a_s[(g & 1) * 4 + tid] = q.has_gate ? apply_act(ld.act, gsum) * usum : apply_act(ld.act, usum);
       }
-      try_issue(l, n_cur, n_next, next_ok);  // warp 1 requests while warp 0 forms a
+      try_issue(j, n_cur, n_next, next_ok);  // warp 1 requests while warp 0 forms a
       __syncthreads();  // a of the group
-      // ---- phase 2: thread j owns the 16-byte column chunks j, j + 512
+      // ---- phase 2: thread t owns the 16-byte column chunks t, t + 512
 #pragma unroll
       for (int k = 0; k < PASS; ++k) {
         const int cc = tid + k * SB1_THREADS;
@@ -404,7 +438,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
 
     // ---- the CTA's partial output vector of the layer
     {
-      float* dst = q.partial + (static_cast<size_t>(l) * G + c) * H;
+      float* dst = q.partial + (static_cast<size_t>(l) * GgMax + mem) * H;
 #pragma unroll
       for (int k = 0; k < PASS; ++k) {
         const int cc = tid + k * SB1_THREADS;
@@ -422,8 +456,8 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
 
   // ================================================================== phase O: out[l] = sum of the partial vectors
   // This CTA's columns: cpc float4 columns (<= 8).  Warp w sums layers w, w + 16, ...: lane = (vector group
-  // ps = lane >> 3, column lane & 7) adds the vectors ps, ps + 4, ps + 8, ... in that order, the four lanes of
-  // a column meet by butterfly.
+  // ps = lane >> 3, column lane & 7) adds the vectors ps, ps + 4, ps + 8, ... of the layer's group in that order,
+  // the four lanes of a column meet by butterfly.
   {
     const int ncol4 = H / 4;
     const int cpc = (ncol4 + G - 1) / G;
@@ -435,18 +469,19 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     float4 mine[(STACK_B1_MAX_LAYERS + SB1_WARPS - 1) / SB1_WARPS];
     int round = 0;
     for (int l = warp; l < L; l += SB1_WARPS, ++round) {
-      const float* part = q.partial + static_cast<size_t>(l) * G * H;
+      const float* part = q.partial + static_cast<size_t>(l) * GgMax * H;
+      const int nvec = (G - (l % ng) + ng - 1) / ng;  // CTAs of the layer's group
       float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
       if (rcol < ncols) {
-        for (int p0 = rps; p0 < G; p0 += 32) {  // eight vectors per lane in flight
-          float4 v[8];
+        for (int p0 = rps; p0 < nvec; p0 += 64) {  // sixteen vectors per lane in flight
+          float4 v[16];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < 16; ++u) {
             const int p = p0 + 4 * u;
-            v[u] = p < G ? __ldcg(reinterpret_cast<const float4*>(part + static_cast<size_t>(p) * H) + col0 + rcol) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[u] = p < nvec ? __ldcg(reinterpret_cast<const float4*>(part + static_cast<size_t>(p) * H) + col0 + rcol) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < 16; ++u) {
             sum.x += v[u].x;
             sum.y += v[u].y;
             sum.z += v[u].z;
