@@ -271,9 +271,12 @@ def workload_config(w, n_gpus, allreduce="peer"):
             + ("peer-memory stores inside the step's kernels" if allreduce == "peer" else "NCCL") + ")",
             "inputs": "weights (seed 0) and AR(1) hidden states (seed 1) generated on the CPU and uploaded",
             "cache_rows": "copied every step (eager), on side branches of the step's graph",
-            "layer_order": "every layer reads the same x; t of layer l+1 and the output sum of layer l overlap the "
-                           "row stream (value_strict_layer_order: nothing of layer l+1 starts before out[l] is complete)"
-                           if n_gpus == 1 and w.B == 1 else "layer after layer on one stream",
+            "layer_order": "every layer reads the same x (the stack's contract), so the layers are independent: one kernel "
+                           "forms the masks of all layers, then streams the active rows of layer after layer without a "
+                           "grid barrier in between (value_layer_by_layer: the same layers one after the other with two "
+                           "grid barriers each; value_strict_layer_order: nothing of layer l+1 starts before out[l] is "
+                           "complete, the order a model needs that feeds out[l] into layer l+1)"
+                           if w.B == 1 else "layer after layer on one stream",
             "l2": "distinct weights per layer: one step touches more bytes than the 126 MB L2"}
 
 
@@ -582,6 +585,7 @@ def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=Fals
     if world == 1 and not extras_mode and not args.no_variants:
         res["value_lazy_cache_rows"] = variant(lazy=True)
         if w.B == 1:
+            res["value_layer_by_layer"] = variant({"STX_STACK_ORDER": "layerwise"})
             res["value_strict_layer_order"] = variant({"STX_STACK_STRICT": "1"})
             res["value_per_layer_kernels"] = variant({"STX_STACK_KERNEL": "layers"})
 
@@ -630,7 +634,7 @@ def stack_measure(synth, w, args, dev, rank, world, dist, peer, extras_mode=Fals
         if persistent:
             # one launch = all layers: per layer the active gate/up/down rows + both predictor matrices + x + t + mask
             # bytes (read and written).  The per-CTA partial vectors are an artefact of the implementation, not counted.
-            top, k1, launches = "stack_kernel", "k_stack_b1", 1
+            top, k1, launches = "stack_kernel", "k_stack_flow", 1
             alg_layer = es * nmat * k_mean * w.H + es * (w.I * w.r + w.r * w.H) + 2 * es * w.H + 8 * w.r + 2 * w.I / 8
             alg = alg_layer * w.layers
             us = stages_us[top] * w.layers
@@ -718,7 +722,7 @@ def run_native(args):
             "gpu_launches_per_step": r["launches_per_step"],
             "clocks": r["clocks"],
         }
-        for k in ("value_lazy_cache_rows", "value_strict_layer_order", "value_per_layer_kernels", "roofline", "stages_us_per_layer",
+        for k in ("value_lazy_cache_rows", "value_layer_by_layer", "value_strict_layer_order", "value_per_layer_kernels", "roofline", "stages_us_per_layer",
                   "active_neurons_mean", "rows_rewritten_mean", "step_algorithmic_gbs", "step_frac_of_peak", "parity", "peer_wait_timed_out"):
             if k in r:
                 line[k] = r[k]

@@ -276,16 +276,23 @@ int stx_layer_step_host(stx_layer_t* l, const void* x_host, int64_t B, void* out
  * capture; the layers stay owned by the caller.
  *
  * One row (B == 1) under the threshold rule, all layers of one shape: the whole stack runs
- * as ONE persistent, cooperatively launched kernel (k_stack_b1) whose CTAs meet at grid-wide
- * barriers between the links of a layer; each cache then gets a second copy of its pools
- * with one contiguous record per neuron (ALLOCATED at create time), and the index plans and
- * row copies of all layers follow the kernel on parallel branches of the graph.  Because
- * every layer reads the same x, t = A x of layer l+1 and the output sum of layer l are
- * formed while rows stream.  Environment, read when a stack is created:
- *   STX_STACK_STRICT=1      nothing of layer l+1 starts before out[l] is complete (the order a
- *                           model needs that feeds a layer's output forward)
- *   STX_STACK_KERNEL=layers keep the per-layer kernels (k_pred_t, k_mlp_b1, k_partial_reduce)
- *   STX_STACK_GROUP=n       at most n layers per launch of the persistent kernel (1..36)
+ * as ONE persistent, cooperatively launched kernel; each cache then gets a second copy of
+ * its pools with one contiguous record per neuron (ALLOCATED at create time), and the index
+ * plans and row copies of all layers follow the kernel on parallel branches of the graph.
+ * Because every layer reads the same x, no layer waits for another one: the kernel
+ * (k_stack_flow) forms the masks of all layers first and then streams the active rows of
+ * layer after layer without a grid barrier in between; the output sums come last.  Sharded
+ * (stx_layer_set_peer), the layers' sums are exchanged side by side in one go, which needs
+ * L*H elements in the peer object (max_elems of stx_peer_create); with less room the layers
+ * run one after the other (k_stack_b1: two grid barriers and one exchange per layer).
+ * Environment, read when a stack is created:
+ *   STX_STACK_STRICT=1        nothing of layer l+1 starts before out[l] is complete: the order
+ *                             a model needs that feeds a layer's output forward (k_stack_b1,
+ *                             four grid barriers per layer)
+ *   STX_STACK_ORDER=layerwise k_stack_b1 in its overlapped order: layer after layer, t of
+ *                             layer l+1 and the sum of layer l formed while rows stream
+ *   STX_STACK_KERNEL=layers   keep the per-layer kernels (k_pred_t, k_mlp_b1, k_partial_reduce)
+ *   STX_STACK_GROUP=n         at most n layers per launch of the persistent kernel (1..36)
  * Other shapes and batch sizes: the per-layer kernels, serialised on one stream, each layer's
  * cache upkeep on side branches.                                                         */
 int stx_stack_create(stx_stack_t** out, stx_layer_t* const* layers, int64_t L, int64_t B);

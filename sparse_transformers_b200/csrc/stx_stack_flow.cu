@@ -250,9 +250,10 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       wv[k] = (k < WPT && w < W) ? __ldcg(q.layer[l].bits + w) : 0u;
     }
   };
-  // The CTA's share of a layer's active neurons, ranks [m*K/Gg, (m+1)*K/Gg) of the set bits (m: its place in the
-  // group), into `dst`.  Returns their number.  Contains block barriers (three; the last one publishes the list).
-  auto build_list = [&](const uint32_t (&wv)[4], uint16_t* dst) {
+  // The CTA's share of the active neurons of its j-th layer, ranks [s*K/Gg, (s+1)*K/Gg) of the set bits (s: its
+  // share number in the group), into `dst`.  Returns their number.  Contains block barriers (three; the last one
+  // publishes the list).
+  auto build_list = [&](const uint32_t (&wv)[4], uint16_t* dst, int j) {
     int cnt = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) cnt += __popc(wv[k]);
@@ -276,9 +277,12 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       if (lane == 31) s_total = winc;
     }
     __syncthreads();
+    // Which shares are one neuron larger is a fixed pattern in the share number: the CTAs take the shares
+    // rotated by the layer count, so that nobody collects the extra neuron of every layer.
     const int K = s_total;
-    const int lo = static_cast<int>(static_cast<long long>(mem) * K / Gg);
-    const int hi = static_cast<int>(static_cast<long long>(mem + 1) * K / Gg);
+    const int share = (mem + j * 5) % Gg;
+    const int lo = static_cast<int>(static_cast<long long>(share) * K / Gg);
+    const int hi = static_cast<int>(static_cast<long long>(share + 1) * K / Gg);
     const int n = min(hi - lo, FLOW_LIST_CAP);
     int rho = s_wsum[warp] + inc - cnt;
 #pragma unroll
@@ -339,7 +343,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   int n_cur = 0, n_next = 0;
   if (nl > 0) {
     load_words(layer_of(0), wnext);
-    n_cur = build_list(wnext, list_even);
+    n_cur = build_list(wnext, list_even, 0);
     if (nl > 1) load_words(layer_of(1), wnext);
   }
 
@@ -354,7 +358,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     const bool next_ok = j + 1 < nl;
     n_next = 0;
     if (next_ok) {
-      n_next = build_list(wnext, ((j + 1) & 1) ? list_odd : list_even);
+      n_next = build_list(wnext, ((j + 1) & 1) ? list_odd : list_even, j + 1);
       if (j + 2 < nl) load_words(layer_of(j + 2), wnext);
     } else {
       __syncthreads();

@@ -32,7 +32,9 @@ def _rank_main(rank, world, port, out_dir, mode, batch):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
     w = Workload("shard", H=1024, I=4096, r=32, B=batch, dtype=torch.bfloat16, density=0.2, alpha=0.5, layers=2)
-    peer = PeerExchange(w.B * w.H) if mode == "peer" else None
+    # "peer": room for every layer's sums side by side (single-row stacks then run the flow kernel, all layers
+    # exchanged at once); "peer1": room for one layer (the layer-by-layer kernel exchanges layer after layer)
+    peer = PeerExchange(w.B * w.H * (w.layers if mode == "peer" else 1)) if mode.startswith("peer") else None
     ok = True
     if peer is not None:  # the stand-alone collective first: every rank contributes rank + 1
         for dt in (torch.float32, torch.float16, torch.bfloat16):
@@ -95,7 +97,7 @@ def _rank_main(rank, world, port, out_dir, mode, batch):
     os._exit(0)  # not destroy_process_group(): it blocked after collectives were captured in a graph
 
 
-@pytest.mark.parametrize("mode,batch", [("nccl", 4), ("peer", 4), ("peer", 1), ("nccl", 1)])
+@pytest.mark.parametrize("mode,batch", [("nccl", 4), ("peer", 4), ("peer", 1), ("peer1", 1), ("nccl", 1)])
 def test_two_gpu_sharded_stack_matches_single_gpu(tmp_path, mode, batch):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
