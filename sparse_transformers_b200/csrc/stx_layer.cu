@@ -6,6 +6,7 @@
 #include "stx_cache.cuh"
 #include "stx_peer.cuh"
 #include "stx_stack_b1.cuh"
+#include "stx_cache_plan.cuh"
 
 #include <cstdlib>
 
@@ -78,6 +79,7 @@ struct stx_stack {
   // Device status of the step (bounded waits that expired, bounds checks that skipped an access): the last
   // node of the graph ORs the layers' status words into status_dev and copies it to the pinned status_host,
   // which the NEXT stx_stack_step call reads without synchronising.
+  stx::UpkeepArgs* upkeep_args = nullptr;  // device [L]: the layers' caches for upkeep that runs inside the flow kernel
   int** status_ptrs = nullptr;  // device [L]
   int* status_dev = nullptr;
   int* status_host = nullptr;
@@ -383,6 +385,7 @@ int stx_stack_destroy(stx_stack_t* s) {
   if (s->graph) cudaGraphDestroy(s->graph);
   for (cudaEvent_t ev : s->events) cudaEventDestroy(ev);
   for (void* p : s->b1_scratch) cudaFree(p);
+  cudaFree(s->upkeep_args);
   cudaFree(s->status_ptrs);
   cudaFree(s->status_dev);
   if (s->status_host) cudaFreeHost(s->status_host);
@@ -436,6 +439,7 @@ static int capture_persistent(stx_stack* s, unsigned stages, cudaStream_t cs, st
   const bool strict = getenv("STX_STACK_STRICT") && atoi(getenv("STX_STACK_STRICT")) != 0;
   const bool upkeep = (stages & (STX_STAGE_PLAN | STX_STAGE_COPY)) != 0;
   size_t ev = 0;
+  std::vector<bool> forked((L + gsz - 1) / gsz, false);
   for (int64_t g0 = 0, gi = 0; g0 < L; g0 += gsz, ++gi) {
     const int64_t n = std::min<int64_t>(gsz, L - g0);
     StackB1Args a = {};
@@ -471,10 +475,20 @@ static int capture_persistent(stx_stack* s, unsigned stages, cudaStream_t cs, st
         return STX_ERR_INVALID_ARG;
       }
     }
+    // where it has the room, the flow kernel keeps the caches up to date itself (plans, then row copies)
+    const unsigned both = STX_STAGE_PLAN | STX_STAGE_COPY;
+    const bool inside = (stages & both) == both && s->upkeep_args && stack_flow_upkeep_inside(a, l0->cache->dtype);
+    a.upkeep = inside ? s->upkeep_args + g0 : nullptr;
     int rc = stack_b1_forward(a, s->b1_scratch[gi], l0->cache->dtype, cs);
     if (rc != STX_OK) return rc;
+    if (inside) {
+      for (int64_t i = 0; i < n; ++i)
+        if (s->layers[g0 + i]->lazy) s->layers[g0 + i]->cache->lazy_used = true;
+      continue;
+    }
     if (!upkeep) continue;
     // the masks of the group exist now: one branch per layer
+    forked[gi] = true;
     STX_CUDA(cudaEventRecord(s->events[ev], cs));
     const cudaEvent_t fork_ev = s->events[ev++];
     for (int64_t i = 0; i < n; ++i) {
@@ -491,11 +505,10 @@ static int capture_persistent(stx_stack* s, unsigned stages, cudaStream_t cs, st
       }
     }
   }
-  if (upkeep) {
-    for (int64_t i = 0; i < L; ++i) {  // join
-      STX_CUDA(cudaEventRecord(s->events[ev], sides[i]));
-      STX_CUDA(cudaStreamWaitEvent(cs, s->events[ev++], 0));
-    }
+  for (int64_t i = 0; i < L; ++i) {  // join the branches of the groups that forked
+    if (!forked[i / gsz]) continue;
+    STX_CUDA(cudaEventRecord(s->events[ev], sides[i]));
+    STX_CUDA(cudaStreamWaitEvent(cs, s->events[ev++], 0));
   }
   return STX_OK;
 }
@@ -582,6 +595,25 @@ int stx_stack_create_stages(stx_stack_t** out, stx_layer_t* const* layers, int64
       if (e == cudaSuccess) sides.push_back(st);
     }
     for (int64_t i = 0; i < L && e == cudaSuccess && rc == STX_OK; ++i) rc = cache_ensure_cat(s->layers[i]->cache, nullptr);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&s->upkeep_args), sizeof(UpkeepArgs) * L);
+    if (e == cudaSuccess) {
+      std::vector<UpkeepArgs> hu(L);
+      for (int64_t i = 0; i < L; ++i) {
+        const stx_cache* c = s->layers[i]->cache;
+        UpkeepArgs& u = hu[i];
+        u = UpkeepArgs{};
+        u.cur_bits = c->cur_bits, u.active = c->active, u.pos_of = c->pos_of, u.lists = c->lists, u.jobs = c->jobs;
+        u.state = c->state, u.stale = c->stale, u.lazy = s->layers[i]->lazy ? 1 : 0;
+        if (c->has_gate) {
+          u.pool[0] = c->pool_gate, u.pool[1] = c->pool_up, u.pool[2] = c->pool_down;
+          u.pk[0] = c->pk_gate, u.pk[1] = c->pk_up, u.pk[2] = c->pk_down;
+        } else {
+          u.pool[0] = c->pool_up, u.pool[1] = c->pool_down;
+          u.pk[0] = c->pk_up, u.pk[1] = c->pk_down;
+        }
+      }
+      e = cudaMemcpy(s->upkeep_args, hu.data(), sizeof(UpkeepArgs) * L, cudaMemcpyHostToDevice);
+    }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();  // cleared counters and per-neuron pools are in place before the first launch
     if (e == cudaSuccess && rc == STX_OK) e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeRelaxed);
     if (e == cudaSuccess && rc == STX_OK) {

@@ -50,6 +50,7 @@
 #include "stx_tma.cuh"
 #include "stx_stack_b1.cuh"
 #include "stx_stack_dev.cuh"
+#include "stx_cache_plan.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -569,6 +570,16 @@ static bool stack_flow_enabled() {
 // peer object's exchange buffer.
 static bool stack_flow_selected(const StackB1Args& a) {
   return !a.strict && stack_flow_enabled() && (a.peer.world <= 1 || static_cast<long long>(a.L) * a.H <= a.peer.max_elems);
+}
+
+// STX_STACK_UPKEEP=kernels keeps the index plans and row copies of the layers' caches in kernels of their own
+// behind the flow kernel (read when a stack's graph is captured).
+bool stack_flow_upkeep_inside(const StackB1Args& a, int dtype) {
+  const char* e = getenv("STX_STACK_UPKEEP");
+  if (e && !strcmp(e, "kernels")) return false;
+  if (!stack_flow_selected(a) || a.L > stack_b1_grid() || (a.I + 31) / 32 > 2 * SB1_THREADS) return false;
+  const size_t slot = static_cast<size_t>(a.H) * dtype_size(dtype) * (a.has_gate ? 3 : 2);
+  return plan_smem_words(a.I) * sizeof(int32_t) <= static_cast<size_t>(sb1_slots_dt(a.H, a.has_gate, dtype)) * slot;
 }
 
 template <typename T>

@@ -35,9 +35,11 @@
 #include "stx_tma.cuh"
 #include "stx_stack_b1.cuh"
 #include "stx_stack_dev.cuh"
+#include "stx_cache_plan.cuh"
 
 namespace stx {
 
+constexpr int FLOW_PLAN_WEIGHT = 12;  // share of a CTA that also runs an index plan, in sixteenths of a full share
 constexpr int FLOW_LIST_CAP = 256;  // neurons of one CTA per layer (two lists of 16-bit ids fill 2 x 512 bytes of the header)
 
 // Layers are dealt to `ng` groups of CTAs (CTA c is in group c % ng and works on the layers l with l % ng equal to
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   const uint32_t slot_bytes = row_bytes * (ngu + 1);
 
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);  // one per slot
+  uint64_t* bar2 = reinterpret_cast<uint64_t*>(smem + 128);  // sixteen more for the row buffers of phase C
   float* a_s = reinterpret_cast<float*>(smem + SB1_OFF_AS);
   float2* pd = reinterpret_cast<float2*>(smem + SB1_OFF_PD);
   // the CTA's neurons of a layer (16-bit ids, FLOW_LIST_CAP of them), two buffers used in turn
@@ -77,7 +80,10 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   unsigned char* slots = smem + SB1_HEADER + (static_cast<size_t>(row_bytes) + 127) / 128 * 128;
 
   if (tid == 0) {
-    for (int w = 0; w < SB1_MAX_SLOTS; ++w) mbar_init(&bar[w], 1);
+    for (int w = 0; w < SB1_MAX_SLOTS; ++w) {
+      mbar_init(&bar[w], 1);
+      mbar_init(&bar2[w], 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_dead = 0;
   }
@@ -243,6 +249,8 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   const int GgMax = (G + ng - 1) / ng;            // partial vectors kept per layer
   const int nl = gq < L ? (L - gq + ng - 1) / ng : 0;  // layers of this CTA: gq, gq + ng, ...
   auto layer_of = [&](int j) { return gq + j * ng; };
+  // CTAs c < L plan layer c's cache behind their rows: in a group these are its first Pm CTAs
+  const int Pm = q.upkeep != nullptr ? min(Gg, max(0, (min(L, G) - gq + ng - 1) / ng)) : 0;
   auto load_words = [&](int l, uint32_t (&wv)[4]) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -279,10 +287,19 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     __syncthreads();
     // Which shares are one neuron larger is a fixed pattern in the share number: the CTAs take the shares
     // rotated by the layer count, so that nobody collects the extra neuron of every layer.
+    // The CTAs that run an index plan afterwards (the first Pm of the group) take FLOW_PLAN_WEIGHT sixteenths
+    // of a share; in share order they are the cyclic interval [rot, rot + Pm).
     const int K = s_total;
-    const int share = (mem + j * 5) % Gg;
-    const int lo = static_cast<int>(static_cast<long long>(share) * K / Gg);
-    const int hi = static_cast<int>(static_cast<long long>(share + 1) * K / Gg);
+    const int rot = (j * 5) % Gg;
+    const int share = (mem + rot) % Gg;
+    auto weight_below = [&](int p) {  // sum of the weights of the shares 0 .. p-1
+      const int b = rot + Pm;
+      const int planners = b <= Gg ? min(max(p - rot, 0), Pm) : min(p, b - Gg) + max(p - rot, 0);
+      return 16 * p - (16 - FLOW_PLAN_WEIGHT) * planners;
+    };
+    const int wtot = 16 * Gg - (16 - FLOW_PLAN_WEIGHT) * Pm;
+    const int lo = static_cast<int>(static_cast<long long>(K) * weight_below(share) / wtot);
+    const int hi = static_cast<int>(static_cast<long long>(K) * weight_below(share + 1) / wtot);
     const int n = min(hi - lo, FLOW_LIST_CAP);
     int rho = s_wsum[warp] + inc - cnt;
 #pragma unroll
@@ -455,6 +472,14 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     }
     n_cur = n_next;
   }
+  // ---- the index plan of layer c's weight cache (CTAs c < L; they took a smaller share of the rows to have the
+  // time).  The masks are final since barrier FM; the plan's work space is the slot area, idle from here on.
+  if (q.upkeep != nullptr && c < L) {
+    __syncthreads();  // every thread is done with the slots
+    const UpkeepArgs* ua = q.upkeep + c;
+    plan_block(q.layer[c].bits, ua->cur_bits, ua->active, ua->pos_of, ua->lists, ua->jobs, ua->state, ua->stale, ua->lazy, I,
+               reinterpret_cast<int32_t*>(slots));
+  }
   barrier_arrive(SB1_SYNC_FP);
   barrier_wait(SB1_SYNC_FP);
 
@@ -527,6 +552,86 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
         static_cast<T*>(q.layer[l].out)[(col0 + rcol) * 4 + rps] = DT<T>::from_f(own);
       }
     }
+  }
+
+  // ================================================================== phase C: the rewritten rows of every cache
+  // packed[m][pos] = pool[m][active[pos]] for every slot the plans listed (k_cache_copy_rows's work), all layers
+  // at once.  A unit is (layer, listed slot, matrix) = one row; the units are dealt round robin to the CTAs.  A
+  // CTA first looks up source and destination of up to 512 of its units, one per thread (two dependent loads,
+  // issued while nothing else is in flight: behind bulk traffic such a load waits microseconds), then moves the
+  // rows through NB row buffers in the idle slot area, one bulk copy in and one out per row.  Each buffer has an
+  // owner thread, two per warp, so that the requests of a round do not queue behind one another in one warp.
+  if (q.upkeep != nullptr) {
+    struct RowJob {
+      const char* sp;
+      char* dp;  // null: nothing to copy
+    };
+    const int nrows = S * (ngu + 1);
+    const size_t tail_bytes = STACK_B1_MAX_LAYERS * sizeof(UpkeepArgs) + 48 * sizeof(int) + SB1_THREADS * sizeof(RowJob);
+    const int reserve = static_cast<int>((tail_bytes + row_bytes - 1) / row_bytes);
+    const int NB = min(2 * SB1_WARPS, nrows - reserve);
+    unsigned char* tail = slots + static_cast<size_t>(nrows - reserve) * row_bytes;
+    UpkeepArgs* ua_s = reinterpret_cast<UpkeepArgs*>(tail);                                                   // [L]
+    int* pre = reinterpret_cast<int*>(tail + STACK_B1_MAX_LAYERS * sizeof(UpkeepArgs));                       // [L + 1] units before layer l
+    RowJob* table = reinterpret_cast<RowJob*>(tail + STACK_B1_MAX_LAYERS * sizeof(UpkeepArgs) + 48 * sizeof(int));  // [512]
+    __syncthreads();
+    for (int i = tid; i < L * static_cast<int>(sizeof(UpkeepArgs) / 8); i += SB1_THREADS)
+      reinterpret_cast<uint64_t*>(ua_s)[i] = reinterpret_cast<const uint64_t*>(q.upkeep)[i];
+    __syncthreads();
+    const int nmat = ngu + 1;
+    if (tid < L) pre[tid + 1] = ua_s[tid].lazy ? 0 : max(0, min(__ldcg(ua_s[tid].state + ST_NJOBS), I)) * nmat;
+    __syncthreads();
+    if (tid == 0) {
+      pre[0] = 0;
+      for (int l = 0; l < L; ++l) pre[l + 1] += pre[l];
+    }
+    __syncthreads();
+    const int total = pre[L];
+    const int mine = total > c ? (total - c + G - 1) / G : 0;  // units c, c + G, c + 2G, ...
+    const int b = warp * 2 + lane;                              // buffer of an owner thread (lanes 0 and 1)
+    const bool owner = lane < 2 && b < NB;
+    uint64_t* mb = b < SB1_MAX_SLOTS ? &bar[b] : bar2 + ((b - SB1_MAX_SLOTS) & (SB1_MAX_SLOTS - 1));
+    uint32_t par = b < SB1_MAX_SLOTS ? (ph >> b) & 1u : 0u;
+    unsigned char* buf = slots + static_cast<size_t>(owner ? b : 0) * row_bytes;
+    for (int k0 = 0; k0 < mine && NB > 0; k0 += SB1_THREADS) {
+      RowJob rj{nullptr, nullptr};
+      if (k0 + tid < mine) {
+        const int u = (k0 + tid) * G + c;
+        int lyr = 0;
+        while (lyr + 1 < L && pre[lyr + 1] <= u) ++lyr;
+        const int v = u - pre[lyr];
+        const int job = v / nmat, m = v - job * nmat;
+        const int pos = __ldcg(ua_s[lyr].jobs + job);
+        if (pos >= 0 && pos < I) {
+          const int src = __ldcg(ua_s[lyr].active + pos);
+          if (src >= 0 && src < I) {
+            rj.sp = static_cast<const char*>(ua_s[lyr].pool[m]) + static_cast<size_t>(src) * row_bytes;
+            rj.dp = static_cast<char*>(ua_s[lyr].pk[m]) + static_cast<size_t>(pos) * row_bytes;
+          }
+        }
+      }
+      table[tid] = rj;
+      __syncthreads();
+      if (owner) {
+        const int n = min(SB1_THREADS, mine - k0);
+        for (int k = b; k < n; k += NB) {
+          const RowJob w = table[k];
+          if (w.dp == nullptr) continue;
+          mbar_expect_tx(mb, row_bytes);
+          bulk_load(buf, w.sp, row_bytes, mb);
+          if (!mbar_wait_bounded(mb, par)) {  // the row never arrived: report it, write nothing, stop
+            timed_out = true;
+            break;
+          }
+          par ^= 1u;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(w.dp), "r"(smem_u32(buf)), "r"(row_bytes) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the buffer may be overwritten
+        }
+      }
+      __syncthreads();
+    }
+    if (owner) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   if (timed_out && q.layer[0].status) atomicOr(q.layer[0].status, DEV_TIMEOUT);

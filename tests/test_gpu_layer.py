@@ -106,7 +106,7 @@ def test_stack_graph_matches_eager_layers():
     mk = lambda: [SparseLayer(*[t.to(DEV) for t in lw], act=w.act, param=w.tau, max_batch=w.B) for lw in ws]
     eager, graphed = mk(), mk()
     stack = SparseStack(graphed, w.B)
-    assert stack.launches_per_step >= 2 + 2 * w.layers  # persistent kernel + plan and row copies per layer + status collector
+    assert stack.launches_per_step >= 2  # persistent kernel (+ plan and row copies per layer where it does not run them itself) + status collector
     xs = HiddenStream(w, gen)
     out = torch.empty(w.layers, w.B, w.H, dtype=w.dtype, device=DEV)
     xh = torch.empty(w.B, w.H, dtype=w.dtype).pin_memory()

@@ -67,7 +67,9 @@ def test_persistent_stack_matches_oracle(dtype, H, I, r, has_gate, act, density,
 
     w = Workload("stack", H=H, I=I, r=r, B=1, dtype=dtype, density=density, layers=layers, act=act, has_gate=has_gate)
     ks, n_launch = _stack_vs_oracle(w, steps=6, seed=layers)
-    assert n_launch == 2 + 2 * layers  # the persistent kernel + index plan and row copies per layer + the status collector
+    # the persistent kernel + the status collector; where the kernel's CTAs lack the shared memory to run the index plans
+    # themselves, also an index plan and a row-copy kernel per layer
+    assert n_launch in (2, 2 + 2 * layers)
 
 
 def test_c2_full_shape_16_steps():
@@ -92,7 +94,7 @@ def test_stack_variants_agree(monkeypatch, env):
     if "STX_STACK_KERNEL" in env:
         assert n_launch == 5 * w.layers + 1
     elif "STX_STACK_GROUP" in env:
-        assert n_launch == 3 + 2 * w.layers + 1
+        assert n_launch in (3 + 1, 3 + 2 * w.layers + 1)  # three launches of the persistent kernel
 
 
 def test_stack_replay_is_deterministic():
@@ -151,7 +153,7 @@ def test_expired_wait_makes_the_next_step_fail(monkeypatch):
         l.set_peer(_Peer)
     stack = SparseStack(layers, 1)
     try:
-        assert stack.launches_per_step == 2 + 2 * w.layers  # the persistent kernel carries the exchange
+        assert stack.launches_per_step in (2, 2 + 2 * w.layers)  # the persistent kernel carries the exchange
         xs = HiddenStream(w, gen).take(2).to(DEV)
         stack.step(xs[0])          # finishes: every wait for the absent peer gives up after 500 polls
         torch.cuda.synchronize()
