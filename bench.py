@@ -270,7 +270,8 @@ def workload_config(w, n_gpus, allreduce="peer"):
             f"intermediate dim sharded over {n_gpus} GPUs + all-reduce per layer ("
             + ("peer-memory stores inside the step's kernels" if allreduce == "peer" else "NCCL") + ")",
             "inputs": "weights (seed 0) and AR(1) hidden states (seed 1) generated on the CPU and uploaded",
-            "cache_rows": "copied every step (eager), on side branches of the step's graph",
+            "cache_rows": "copied every step (eager): inside the step's kernel for single-row stacks, else on side branches "
+                          "of the step's graph",
             "layer_order": "every layer reads the same x (the stack's contract), so the layers are independent: one kernel "
                            "forms the masks of all layers, then streams the active rows of layer after layer without a "
                            "grid barrier in between (value_layer_by_layer: the same layers one after the other with two "

@@ -277,11 +277,11 @@ int stx_layer_step_host(stx_layer_t* l, const void* x_host, int64_t B, void* out
  *
  * One row (B == 1) under the threshold rule, all layers of one shape: the whole stack runs
  * as ONE persistent, cooperatively launched kernel; each cache then gets a second copy of
- * its pools with one contiguous record per neuron (ALLOCATED at create time), and the index
- * plans and row copies of all layers follow the kernel on parallel branches of the graph.
+ * its pools with one contiguous record per neuron (ALLOCATED at create time).
  * Because every layer reads the same x, no layer waits for another one: the kernel
  * (k_stack_flow) forms the masks of all layers first and then streams the active rows of
- * layer after layer without a grid barrier in between; the output sums come last.  Sharded
+ * layer after layer without a grid barrier in between; the output sums come last, and then
+ * the caches' index plans and row copies, inside the same launch.  Sharded
  * (stx_layer_set_peer), the layers' sums are exchanged side by side in one go, which needs
  * L*H elements in the peer object (max_elems of stx_peer_create); with less room the layers
  * run one after the other (k_stack_b1: two grid barriers and one exchange per layer).
@@ -291,6 +291,9 @@ int stx_layer_step_host(stx_layer_t* l, const void* x_host, int64_t B, void* out
  *                             four grid barriers per layer)
  *   STX_STACK_ORDER=layerwise k_stack_b1 in its overlapped order: layer after layer, t of
  *                             layer l+1 and the sum of layer l formed while rows stream
+ *   STX_STACK_UPKEEP=kernels  index plans and row copies of the layers' caches in kernels of their
+ *                             own behind k_stack_flow (default: inside its launch, where a CTA
+ *                             has the shared memory for the plan's work space)
  *   STX_STACK_KERNEL=layers   keep the per-layer kernels (k_pred_t, k_mlp_b1, k_partial_reduce)
  *   STX_STACK_GROUP=n         at most n layers per launch of the persistent kernel (1..36)
  * Other shapes and batch sizes: the per-layer kernels, serialised on one stream, each layer's
