@@ -71,7 +71,6 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
 
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem);  // one per slot
   uint64_t* bar2 = reinterpret_cast<uint64_t*>(smem + 128);  // sixteen more for the row buffers of phase C
-  uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + 288);  // phase S: the CTA's slices of the predictors' up matrices
   float* a_s = reinterpret_cast<float*>(smem + SB1_OFF_AS);
   float2* pd = reinterpret_cast<float2*>(smem + SB1_OFF_PD);
   // the CTA's neurons of a layer (16-bit ids, FLOW_LIST_CAP of them), two buffers used in turn
@@ -85,7 +84,6 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       mbar_init(&bar[w], 1);
       mbar_init(&bar2[w], 1);
     }
-    mbar_init(bar_s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_dead = 0;
   }
@@ -125,17 +123,8 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   const int W = (I + 31) >> 5;                           // mask words
   const int WPT = (W + SB1_THREADS - 1) / SB1_THREADS;   // <= 4
 
-  // Phase S operands.  The CTA's slice of a layer's predictor up matrix Bm is nby runs of 8 neurons (8 r
-  // elements, contiguous).  Where the slices of ALL layers fit the slot area (idle until phase R) next to t and the
-  // mask nibbles, one bulk copy per run brings them in while t is formed, all on one mbarrier; otherwise the
-  // threads load their 16-byte pieces four layers ahead (weights do not depend on data either way).
-  const int tstride = nc4 * (V / 4) * 32;  // floats of one layer's t in the layout the score loop reads
-  const size_t off_nib = static_cast<size_t>(L) * tstride * sizeof(float);
-  const size_t off_bm = (off_nib + static_cast<size_t>(L) * 16 * sizeof(uint32_t) + 127) / 128 * 128;
-  const uint32_t run_bytes = 8u * static_cast<uint32_t>(r) * sizeof(T);
-  const bool staged = off_bm + static_cast<size_t>(L) * nby * run_bytes <= static_cast<size_t>(S) * slot_bytes &&
-                      static_cast<size_t>(L) * nby * run_bytes < (1u << 20);
-  unsigned char* bm_s = slots + off_bm;
+  // the CTA's slice of the predictor's up matrix, four layers ahead (weights do not depend on data: the first
+  // four are on their way while t is formed)
   uint4 wq[4][2];
   auto load_w = [&](int l, uint4 (&dst)[2]) {
     const T* Bm = static_cast<const T*>(q.layer[l].Bm);
@@ -147,24 +136,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     }
   };
 #pragma unroll
-  for (int u = 0; u < 4; ++u) wq[u][0] = wq[u][1] = make_uint4(0, 0, 0, 0);
-  if (staged) {
-    if (tid == 0) {
-      uint32_t per_layer = 0;
-      for (int k = 0; k < nby; ++k) per_layer += static_cast<uint32_t>(min(8, I - 8 * (c + G * k))) * r * sizeof(T);
-      mbar_expect_tx(bar_s, per_layer * static_cast<uint32_t>(L));
-    }
-    __syncthreads();
-    for (int i = tid; i < L * nby; i += SB1_THREADS) {
-      const int l = i / nby, k = i - l * nby;
-      const int n0 = 8 * (c + G * k);
-      bulk_load(bm_s + static_cast<size_t>(i) * run_bytes, static_cast<const T*>(q.layer[l].Bm) + static_cast<size_t>(n0) * r,
-                static_cast<uint32_t>(min(8, I - n0)) * r * sizeof(T), bar_s);
-    }
-  } else {
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (u < L) load_w(u, wq[u]);
+  for (int u = 0; u < 4; ++u) {
+    wq[u][0] = wq[u][1] = make_uint4(0, 0, 0, 0);
+    if (u < L) load_w(u, wq[u]);
   }
 
   // ================================================================== phase T: t of every layer
@@ -208,17 +182,14 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   // loop reads; the loop over the layers then needs no block barrier: a warp's four mask nibbles per layer are
   // collected in shared memory and the CTA's mask bytes of all layers are written in one pass at the end.
   {
-    float* t_all = reinterpret_cast<float*>(slots);                   // [L][tstride]
-    uint32_t* nib_all = reinterpret_cast<uint32_t*>(slots + off_nib);  // [L][16]
+    float* t_all = reinterpret_cast<float*>(slots);                                           // [L][128]
+    uint32_t* nib_all = reinterpret_cast<uint32_t*>(slots + STACK_B1_MAX_LAYERS * 512);       // [L][16]
     for (int i = tid; i < L * r; i += SB1_THREADS) {
       const int l = i / r, e = i - l * r;
       const int ch = e / V, v = e - ch * V;
-      t_all[l * tstride + (((ch >> 3) * (V / 4) + (v >> 2)) * 8 + (ch & 7)) * 4 + (v & 3)] = __ldcg(q.t_buf + i);
+      t_all[l * 128 + (((ch >> 3) * (V / 4) + (v >> 2)) * 8 + (ch & 7)) * 4 + (v & 3)] = __ldcg(q.t_buf + i);
     }
-    if (staged && !mbar_wait_bounded(bar_s, 0u)) timed_out = true;
     __syncthreads();
-    // this thread's neuron inside the CTA's slice of a layer: run kk, neuron (tid >> 3) & 7
-    const unsigned char* my_w = bm_s + (static_cast<size_t>(kk) * 8 + ((tid >> 3) & 7)) * r * sizeof(T);
     for (int l0 = 0; l0 < L; l0 += 4) {
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -231,9 +202,8 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
             const int ch = g8 + 8 * c4;
             if (c4 < nc4 && ch < rch) {
               float w[V];
-              const uint4 wv = (staged && n_ok) ? *reinterpret_cast<const uint4*>(my_w + static_cast<size_t>(l) * nby * run_bytes + ch * 16) : wq[u][c4];
-              Unpack<T>::run(wv, w);
-              const float4* tb = reinterpret_cast<const float4*>(t_all + l * tstride) + (c4 * (V / 4)) * 8 + g8;
+              Unpack<T>::run(wq[u][c4], w);
+              const float4* tb = reinterpret_cast<const float4*>(t_all + l * 128) + (c4 * (V / 4)) * 8 + g8;
 #pragma unroll
               for (int v4 = 0; v4 < V / 4; ++v4) {
                 const float4 tv = tb[v4 * 8];
@@ -244,7 +214,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
               }
             }
           }
-          if (!staged && l + 4 < L) load_w(l + 4, wq[u]);
+          if (l + 4 < L) load_w(l + 4, wq[u]);
           sc += __shfl_xor_sync(0xffffffffu, sc, 4);
           sc += __shfl_xor_sync(0xffffffffu, sc, 2);
           sc += __shfl_xor_sync(0xffffffffu, sc, 1);
