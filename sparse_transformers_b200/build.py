@@ -20,7 +20,7 @@ INCLUDE = os.path.join(ROOT, "include")
 LIBSTX = os.path.join(HERE, "libstx.so")
 LIBSHIM = os.path.join(HERE, "libstx_torch.so")
 
-CU_SOURCES = ["stx_api.cu", "stx_cache.cu", "stx_predictor.cu", "stx_select.cu", "stx_mlp.cu", "stx_mlp_tma.cu", "stx_stack_b1.cu", "stx_stack_flow.cu", "stx_prefill.cu", "stx_peer.cu", "stx_attn.cu", "stx_layer.cu"]
+CU_SOURCES = ["stx_api.cu", "stx_cache.cu", "stx_predictor.cu", "stx_select.cu", "stx_mlp.cu", "stx_mlp_tma.cu", "stx_mlp_batch.cu", "stx_mlp_row.cu", "stx_stack_b1.cu", "stx_stack_flow.cu", "stx_prefill.cu", "stx_peer.cu", "stx_attn.cu", "stx_layer.cu"]
 
 def _newer(target: str, sources: list[str]) -> bool:
     if not os.path.isfile(target):

@@ -461,7 +461,7 @@ size_t prefill_scratch_bytes(int64_t B, int64_t H, int64_t K) {
          (z1 > 1 ? align_up(static_cast<size_t>(z1) * B * 2 * K8 * sizeof(float), 1024) : 0);
 }
 
-// Implemented in stx_mlp_tma.cu: out[i] = sum over g < G of partial[g][i], g ascending (n % 128 == 0).
+// Implemented in stx_mlp_row.cu: out[i] = sum over g < G of partial[g][i], g ascending (n % 128 == 0).
 int partial_sum(const float* partial, int G, int64_t n, void* out, int dtype, cudaStream_t s);
 
 // Row blocks of STX_GEMM_MIN_ROWS and more (16-bit, gated) run as tensor-core GEMMs.

@@ -39,7 +39,7 @@
 
 namespace stx {
 
-constexpr int FLOW_PLAN_WEIGHT = 12;  // share of a CTA that also runs an index plan, in sixteenths of a full share
+constexpr int FLOW_PLAN_WEIGHT = 11;  // share of a CTA that also runs an index plan, in sixteenths of a full share
 constexpr int FLOW_LIST_CAP = 256;  // neurons of one CTA per layer (two lists of 16-bit ids fill 2 x 512 bytes of the header)
 
 // Layers are dealt to `ng` groups of CTAs (CTA c is in group c % ng and works on the layers l with l % ng equal to
