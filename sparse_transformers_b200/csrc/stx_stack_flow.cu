@@ -39,6 +39,7 @@
 
 namespace stx {
 
+constexpr int FLOW_AHEAD = 4;         // layers whose predictor slices a thread has requested ahead of the one it scores
 constexpr int FLOW_PLAN_WEIGHT = 11;  // share of a CTA that also runs an index plan, in sixteenths of a full share
 constexpr int FLOW_LIST_CAP = 256;  // neurons of one CTA per layer (two lists of 16-bit ids fill 2 x 512 bytes of the header)
 
@@ -123,9 +124,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   const int W = (I + 31) >> 5;                           // mask words
   const int WPT = (W + SB1_THREADS - 1) / SB1_THREADS;   // <= 4
 
-  // the CTA's slice of the predictor's up matrix, four layers ahead (weights do not depend on data: the first
-  // four are on their way while t is formed)
-  uint4 wq[4][2];
+  // the CTA's slice of the predictor's up matrix, FLOW_AHEAD layers ahead (weights do not depend on data: the
+  // first ones are on their way while t is formed)
+  uint4 wq[FLOW_AHEAD][2];
   auto load_w = [&](int l, uint4 (&dst)[2]) {
     const T* Bm = static_cast<const T*>(q.layer[l].Bm);
 #pragma unroll
@@ -136,7 +137,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     }
   };
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < FLOW_AHEAD; ++u) {
     wq[u][0] = wq[u][1] = make_uint4(0, 0, 0, 0);
     if (u < L) load_w(u, wq[u]);
   }
@@ -190,9 +191,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       t_all[l * 128 + (((ch >> 3) * (V / 4) + (v >> 2)) * 8 + (ch & 7)) * 4 + (v & 3)] = __ldcg(q.t_buf + i);
     }
     __syncthreads();
-    for (int l0 = 0; l0 < L; l0 += 4) {
+    for (int l0 = 0; l0 < L; l0 += FLOW_AHEAD) {
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < FLOW_AHEAD; ++u) {
         const int l = l0 + u;
         if (l < L) {
           const float tau_r = DT<T>::round_f(q.layer[l].tau);
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
               }
             }
           }
-          if (l + 4 < L) load_w(l + 4, wq[u]);
+          if (l + FLOW_AHEAD < L) load_w(l + FLOW_AHEAD, wq[u]);
           sc += __shfl_xor_sync(0xffffffffu, sc, 4);
           sc += __shfl_xor_sync(0xffffffffu, sc, 2);
           sc += __shfl_xor_sync(0xffffffffu, sc, 1);

@@ -12,7 +12,7 @@ from test_gpu_layer import ODT, TOL, OracleLayer
 pytestmark = pytest.mark.gpu
 
 
-def _stack_vs_oracle(w, steps, seed=0, check_every=1):
+def _stack_vs_oracle(w, steps, seed=0, check_every=1, lazy=False):
     from sparse_transformers_b200 import SparseLayer, SparseStack
     from sparse_transformers_b200.synth import HiddenStream, layer_weights
     from stxgpu import DEV, rel_err
@@ -21,7 +21,7 @@ def _stack_vs_oracle(w, steps, seed=0, check_every=1):
     ws = [layer_weights(w, gen) for _ in range(w.layers)]
     xs = HiddenStream(w, gen)
     layers = [SparseLayer(*[t.to(DEV) for t in lw], act=w.act, method="threshold", param=w.tau, max_batch=1,
-                          has_gate=w.has_gate) for lw in ws]
+                          has_gate=w.has_gate, lazy_cache=lazy) for lw in ws]
     ols = [OracleLayer(w, *lw) for lw in ws]
     stack = SparseStack(layers, 1)
     out = torch.empty(w.layers, 1, w.H, dtype=w.dtype, device=DEV)
@@ -81,10 +81,12 @@ def test_c2_full_shape_16_steps():
     assert 0.15 * w.I < np.mean(ks[4:]) < 0.25 * w.I
 
 
-@pytest.mark.parametrize("env", [{"STX_STACK_STRICT": "1"}, {"STX_STACK_KERNEL": "layers"}, {"STX_STACK_GROUP": "2"}])
+@pytest.mark.parametrize("env", [{"STX_STACK_STRICT": "1"}, {"STX_STACK_ORDER": "layerwise"}, {"STX_STACK_UPKEEP": "kernels"},
+                                 {"STX_STACK_KERNEL": "layers"}, {"STX_STACK_GROUP": "2"}])
 def test_stack_variants_agree(monkeypatch, env):
-    """Strict layer order, groups of two layers per launch and the per-layer kernels give the same
-    masks and cache orders as the oracle, outputs within tolerance."""
+    """Every documented switch of the stack - strict layer order, layer by layer in the overlapped order, cache
+    upkeep in kernels of their own, the per-layer kernels, groups of two layers per launch - gives the same masks,
+    cache orders and packed rows as the oracle, outputs within tolerance."""
     from sparse_transformers_b200.synth import WORKLOADS
 
     for k, v in env.items():
@@ -95,6 +97,15 @@ def test_stack_variants_agree(monkeypatch, env):
         assert n_launch == 5 * w.layers + 1
     elif "STX_STACK_GROUP" in env:
         assert n_launch in (3 + 1, 3 + 2 * w.layers + 1)  # three launches of the persistent kernel
+
+
+def test_stack_with_lazy_cache_rows():
+    """Lazy cache rows: the stack's kernel runs the index plans itself and leaves the rewritten slots in the stale
+    bitmap; reading the cache (every check of the packed rows) brings the rows up to date."""
+    from sparse_transformers_b200.synth import WORKLOADS
+
+    w = WORKLOADS["C2"].scaled(I=4096, H=1024, layers=4)
+    _stack_vs_oracle(w, steps=6, seed=11, lazy=True)
 
 
 def test_stack_replay_is_deterministic():
