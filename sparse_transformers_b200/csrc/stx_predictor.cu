@@ -17,6 +17,7 @@
 #include "stx_common.cuh"
 
 #include <algorithm>
+#include <cmath>
 
 namespace stx {
 
@@ -209,6 +210,199 @@ k_pred_scores(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* _
   }
 }
 
+
+// Row blocks of 16-bit weights under the threshold rule: the scores on the tensor pipe, the mask bit-exact.
+//
+// k_pred_scores fixes the order of the r multiply-adds of a score (eight partial sums per neuron, then a butterfly)
+// because the mask has to match the reference bit for bit, and at 64 rows it is the longest kernel of a layer (117 M
+// FMAs that wait for shared-memory operands).  Here a warp owns one mask word: two 16-neuron tiles against all rows,
+// mma.sync m16n8k16 with fp32 accumulation - and next to every score s' the same product of the ABSOLUTE values,
+// S = sum |t_k| |w_k|.  The exact score s (in the fixed order) and s' are both sums of the same exactly
+// representable products, so |s' - s| <= r * 2^-20 * S with a wide margin, and the mask bit "round(s) >= tau" is
+// "s above the midpoint m between tau and its predecessor in the model dtype".  Only a score within that bound
+// of m is evaluated again in the fixed order (a few hundred of 64 x 14336); all others are decided by s'.
+// Operand fragments are 16-byte chunks straight from global / shared memory: the k index of a product does not
+// matter for a sum, so thread t takes the four k-pairs of its A and B fragments of two k16 steps from the same chunk.
+template <typename T> struct MmaScores;
+template <> struct MmaScores<__half> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+template <> struct MmaScores<__nv_bfloat16> {
+  static __device__ __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+
+constexpr int PSM_WARPS = 4;      // mask words per block
+constexpr int PSM_MAX_SPANS = 8;  // r <= 256: a thread keeps 2 x r / 32 chunks of its two neurons in registers
+
+// Dynamic shared memory: t in the model dtype, [Bpad][r + 8] (rows of 16 bytes more than r elements: the 16-byte
+// fragment loads of eight rows then fall into different banks), Bpad = B rounded up to 8, rows >= B zero.
+template <typename T>
+__global__ void __launch_bounds__(PSM_WARPS * 32)
+k_pred_scores_mma(const float* __restrict__ t, const T* __restrict__ Bm, uint32_t* __restrict__ bits, int B, int r, int I, float tau) {
+  extern __shared__ __align__(16) unsigned char psm_raw[];
+  T* t_s = reinterpret_cast<T*>(psm_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, tq = lane & 3;
+  const int Bpad = (B + 7) & ~7, ts = r + 8, nspan = r >> 5;
+  const int W = (I + 31) >> 5;
+  const int w = blockIdx.x * PSM_WARPS + warp;
+  const int i0 = w * 32;
+
+  // weights first (they do not depend on the previous kernel): the chunks of this thread's four neurons
+  uint4 alo[2][PSM_MAX_SPANS], ahi[2][PSM_MAX_SPANS];
+  int ra[2], rb[2];
+#pragma unroll
+  for (int tt = 0; tt < 2; ++tt) {
+    ra[tt] = i0 + 16 * tt + g;
+    rb[tt] = ra[tt] + 8;
+    const T* pa = Bm + static_cast<size_t>(min(ra[tt], I - 1)) * r;
+    const T* pb = Bm + static_cast<size_t>(min(rb[tt], I - 1)) * r;
+#pragma unroll
+    for (int sp = 0; sp < PSM_MAX_SPANS; ++sp) {
+      if (sp < nspan && w < W) {
+        alo[tt][sp] = ld_stream16(pa + sp * 32 + tq * 8);
+        ahi[tt][sp] = ld_stream16(pb + sp * 32 + tq * 8);
+      } else {
+        alo[tt][sp] = ahi[tt][sp] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  {
+    // t holds values of the model dtype: the conversion is exact.  Four values per load, eight loads in flight.
+    const int r4 = r >> 2, n4 = Bpad * r4;
+    const float4* t4 = reinterpret_cast<const float4*>(t);
+#pragma unroll 8
+    for (int k = tid; k < n4; k += PSM_WARPS * 32) {
+      const int b = k / r4, e = (k - b * r4) * 4;
+      const float4 v = b < B ? __ldcg(t4 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      T* dst = t_s + b * ts + e;
+      dst[0] = DT<T>::from_f(v.x);
+      dst[1] = DT<T>::from_f(v.y);
+      dst[2] = DT<T>::from_f(v.z);
+      dst[3] = DT<T>::from_f(v.w);
+    }
+  }
+  __syncthreads();
+  if (w >= W) return;
+
+  // "round(s) >= tau_r"  <=>  s above the midpoint between tau_r and its predecessor (ties: evaluated exactly)
+  const float tau_r = DT<T>::round_f(tau);
+  float mid;
+  {
+    T tv = DT<T>::from_f(tau_r);
+    unsigned short u = *reinterpret_cast<unsigned short*>(&tv);
+    if (tau_r > 0.f) u -= 1;
+    else if (tau_r < 0.f) u += 1;
+    else u = 0x8001;  // the largest value below zero
+    const float pred = DT<T>::to_f(*reinterpret_cast<T*>(&u));
+    mid = 0.5f * pred + 0.5f * tau_r;
+  }
+  const float eps_scale = static_cast<float>(r) * (1.0f / 1048576.0f);  // r * 2^-20
+
+  uint32_t word = 0u;
+#pragma unroll
+  for (int tt = 0; tt < 2; ++tt) {
+    bool on_a = false, on_b = false;  // neuron ra / rb active for some row
+    for (int cg = 0; cg < Bpad; cg += 8) {
+      float d[4] = {0.f, 0.f, 0.f, 0.f}, da[4] = {0.f, 0.f, 0.f, 0.f};
+      const T* trow = t_s + (cg + g) * ts + tq * 8;
+#pragma unroll
+      for (int sp = 0; sp < PSM_MAX_SPANS; ++sp) {
+        if (sp < nspan) {
+          const uint4 tb = *reinterpret_cast<const uint4*>(trow + sp * 32);
+          const uint4 lo = alo[tt][sp], hi = ahi[tt][sp];
+          MmaScores<T>::run(d, lo.x, hi.x, lo.y, hi.y, tb.x, tb.y);
+          MmaScores<T>::run(d, lo.z, hi.z, lo.w, hi.w, tb.z, tb.w);
+          constexpr uint32_t M = 0x7fff7fffu;
+          MmaScores<T>::run(da, lo.x & M, hi.x & M, lo.y & M, hi.y & M, tb.x & M, tb.y & M);
+          MmaScores<T>::run(da, lo.z & M, hi.z & M, lo.w & M, hi.w & M, tb.z & M, tb.w & M);
+        }
+      }
+      // d[0], d[1]: neuron ra, rows cg + 2 tq, + 1;  d[2], d[3]: neuron rb, same rows
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int b = cg + 2 * tq + (j & 1);
+        const int i = (j < 2) ? ra[tt] : rb[tt];
+        const bool valid = b < B && i < I;
+        const float eps = eps_scale * da[j];
+        bool on = valid && d[j] > mid + eps;
+        // Too close to call: the warp evaluates such scores in the arithmetic order of k_pred_scores, four at a
+        // time - a group of eight lanes per score, lane g of the group owns the chunks g, g + 8, ... of the r
+        // products, the eight partial sums meet by butterfly (xor 4, 2, 1).
+        uint32_t um = __ballot_sync(0xffffffffu, valid && !on && !(d[j] < mid - eps));
+        while (um) {
+          int src[4];
+          uint32_t m = um;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            src[q] = m ? __ffs(m) - 1 : -1;
+            m &= m - 1;
+          }
+          const int grp = lane >> 3, gl = lane & 7;
+          const int mine = grp == 0 ? src[0] : grp == 1 ? src[1] : grp == 2 ? src[2] : src[3];
+          const int sl = mine < 0 ? 0 : mine;
+          const int bq = __shfl_sync(0xffffffffu, b, sl), iq = __shfl_sync(0xffffffffu, i, sl);
+          float acc = 0.f;
+          if (mine >= 0) {
+            const T* wrow = Bm + static_cast<size_t>(iq) * r;
+            const T* tr = t_s + bq * ts;
+            for (int c = gl; c < (r >> 3); c += 8) {
+              float wv[8], tv[8];
+              Unpack<T>::run(ld_stream16(wrow + c * 8), wv);
+              Unpack<T>::run(*reinterpret_cast<const uint4*>(tr + c * 8), tv);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) acc = fmaf(tv[v], wv[v], acc);
+            }
+          }
+          acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+          acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+          acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+          const bool res = DT<T>::round_f(acc) >= tau_r;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const bool rq = __shfl_sync(0xffffffffu, res, q * 8);
+            if (lane == src[q]) on = rq;
+          }
+          um = m;
+        }
+        if (j < 2) on_a = on_a || on;
+        else on_b = on_b || on;
+      }
+    }
+    // the four threads of a quad hold the rows of the same two neurons
+    const uint32_t ba = __ballot_sync(0xffffffffu, on_a), bb = __ballot_sync(0xffffffffu, on_b);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if ((ba >> (4 * q)) & 0xfu) word |= 1u << (16 * tt + q);
+      if ((bb >> (4 * q)) & 0xfu) word |= 1u << (16 * tt + 8 + q);
+    }
+  }
+  if (lane == 0) bits[w] = word;
+}
+
+template <typename T>
+static int launch_scores_mma(const float* t_scratch, const void* Bm, uint32_t* bits, int64_t B, int64_t r, int64_t I, float tau,
+                             size_t smem, cudaStream_t s) {
+  const int64_t W = (I + 31) / 32;
+  STX_CUDA(launch_pdl(k_pred_scores_mma<T>, dim3(static_cast<unsigned>((W + PSM_WARPS - 1) / PSM_WARPS)), dim3(PSM_WARPS * 32), smem, s,
+                      t_scratch, static_cast<const T*>(Bm), bits, static_cast<int>(B), static_cast<int>(r), static_cast<int>(I), tau));
+  return STX_OK;
+}
+template <>
+int launch_scores_mma<float>(const float*, const void*, uint32_t*, int64_t, int64_t, int64_t, float, size_t, cudaStream_t) {
+  return STX_ERR_UNSUPPORTED;
+}
+
 template <typename T>
 static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, int64_t r, const void* Bm,
                           int64_t I, float tau, uint32_t* bits, void* scores_out, float* t_scratch,
@@ -221,6 +415,11 @@ static int launch_predict(const void* x, int64_t B, int64_t H, const void* A, in
                         static_cast<int>((I + 31) / 32)));
   const int64_t W = (I + 31) / 32;
   const size_t smem = static_cast<size_t>(std::min<int64_t>(B, PRED_BT)) * r * sizeof(float);
+  // row blocks of 16-bit weights under the threshold rule: scores on the tensor pipe (the mask stays bit-exact)
+  const size_t smem_mma = static_cast<size_t>((B + 7) / 8 * 8) * (r + 8) * sizeof(T);
+  if ((parts & 2u) && sizeof(T) == 2 && write_bits && !scores_out && B >= 9 && r % 32 == 0 && r <= 32 * PSM_MAX_SPANS &&
+      smem_mma <= 48 * 1024 && std::isfinite(tau) && (reinterpret_cast<uintptr_t>(Bm) & 15) == 0)
+    return launch_scores_mma<T>(t_scratch, Bm, bits, B, r, I, tau, smem_mma, s);
   if ((parts & 2u) && !(parts & 1u) && groups > 1 && write_bits) STX_CUDA(cudaMemsetAsync(bits, 0, W * sizeof(uint32_t), s));
   if (parts & 2u)
   STX_CUDA(launch_pdl(k_pred_scores<T>, dim3(static_cast<unsigned>(W), groups), dim3(256), smem, s, t_scratch,
