@@ -241,6 +241,7 @@ template <> struct MmaScores<__nv_bfloat16> {
 
 constexpr int PSM_WARPS = 4;      // mask words per block
 constexpr int PSM_MAX_SPANS = 8;  // r <= 256: a thread keeps 2 x r / 32 chunks of its two neurons in registers
+constexpr int PSM_LIST = 64;      // scores of a warp that wait for their evaluation in the fixed order
 
 // Dynamic shared memory: t in the model dtype, [Bpad][r + 8] (rows of 16 bytes more than r elements: the 16-byte
 // fragment loads of eight rows then fall into different banks), Bpad = B rounded up to 8, rows >= B zero.
@@ -309,74 +310,98 @@ k_pred_scores_mma(const float* __restrict__ t, const T* __restrict__ Bm, uint32_
   }
   const float eps_scale = static_cast<float>(r) * (1.0f / 1048576.0f);  // r * 2^-20
 
+  // Scores too close to call wait in a list of the warp ((row << 8) | neuron inside the word) and are evaluated at
+  // the end in the arithmetic order of k_pred_scores, four at a time: a group of eight lanes per score, lane g of
+  // the group owns the chunks g, g + 8, ... of the r products, the eight partial sums meet by butterfly (xor 4, 2,
+  // 1).  A neuron's bit is the OR over the rows, so a result only has to reach the word.
+  __shared__ int s_unc[PSM_WARPS][PSM_LIST];
+  int* unc = s_unc[warp];
+  int n_unc = 0;
   uint32_t word = 0u;
+  auto flush = [&]() {
+    for (int k0 = 0; k0 < n_unc; k0 += 4) {
+      const int grp = lane >> 3, gl = lane & 7;
+      const bool have = k0 + grp < n_unc;
+      const int e = have ? unc[k0 + grp] : 0;
+      const int bq = e >> 8, il = e & 0xff;
+      float acc = 0.f;
+      if (have) {
+        const T* wrow = Bm + static_cast<size_t>(i0 + il) * r;
+        const T* tr = t_s + bq * ts;
+        for (int c = gl; c < (r >> 3); c += 8) {
+          float wv[8], tv[8];
+          Unpack<T>::run(ld_stream16(wrow + c * 8), wv);
+          Unpack<T>::run(*reinterpret_cast<const uint4*>(tr + c * 8), tv);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) acc = fmaf(tv[v], wv[v], acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      const bool res = have && DT<T>::round_f(acc) >= tau_r;
+      const uint32_t rb4 = __ballot_sync(0xffffffffu, res && gl == 0);  // bits 0, 8, 16, 24: the four results
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int eq = __shfl_sync(0xffffffffu, e, q * 8);
+        if ((rb4 >> (8 * q)) & 1u) word |= 1u << (eq & 0xff);
+      }
+    }
+    n_unc = 0;
+    __syncwarp();
+  };
+
 #pragma unroll
   for (int tt = 0; tt < 2; ++tt) {
     bool on_a = false, on_b = false;  // neuron ra / rb active for some row
-    for (int cg = 0; cg < Bpad; cg += 8) {
-      float d[4] = {0.f, 0.f, 0.f, 0.f}, da[4] = {0.f, 0.f, 0.f, 0.f};
-      const T* trow = t_s + (cg + g) * ts + tq * 8;
+    for (int cg0 = 0; cg0 < Bpad; cg0 += 16) {  // two groups of eight rows in flight
+      float d[2][4], da[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) d[h][j] = da[h][j] = 0.f;
+      const bool two = cg0 + 8 < Bpad;
+      const T* trow0 = t_s + (cg0 + g) * ts + tq * 8;
+      const T* trow1 = t_s + ((two ? cg0 + 8 : cg0) + g) * ts + tq * 8;
 #pragma unroll
       for (int sp = 0; sp < PSM_MAX_SPANS; ++sp) {
         if (sp < nspan) {
-          const uint4 tb = *reinterpret_cast<const uint4*>(trow + sp * 32);
           const uint4 lo = alo[tt][sp], hi = ahi[tt][sp];
-          MmaScores<T>::run(d, lo.x, hi.x, lo.y, hi.y, tb.x, tb.y);
-          MmaScores<T>::run(d, lo.z, hi.z, lo.w, hi.w, tb.z, tb.w);
+          const uint4 tb0 = *reinterpret_cast<const uint4*>(trow0 + sp * 32);
+          const uint4 tb1 = *reinterpret_cast<const uint4*>(trow1 + sp * 32);
           constexpr uint32_t M = 0x7fff7fffu;
-          MmaScores<T>::run(da, lo.x & M, hi.x & M, lo.y & M, hi.y & M, tb.x & M, tb.y & M);
-          MmaScores<T>::run(da, lo.z & M, hi.z & M, lo.w & M, hi.w & M, tb.z & M, tb.w & M);
+          MmaScores<T>::run(d[0], lo.x, hi.x, lo.y, hi.y, tb0.x, tb0.y);
+          MmaScores<T>::run(d[1], lo.x, hi.x, lo.y, hi.y, tb1.x, tb1.y);
+          MmaScores<T>::run(da[0], lo.x & M, hi.x & M, lo.y & M, hi.y & M, tb0.x & M, tb0.y & M);
+          MmaScores<T>::run(da[1], lo.x & M, hi.x & M, lo.y & M, hi.y & M, tb1.x & M, tb1.y & M);
+          MmaScores<T>::run(d[0], lo.z, hi.z, lo.w, hi.w, tb0.z, tb0.w);
+          MmaScores<T>::run(d[1], lo.z, hi.z, lo.w, hi.w, tb1.z, tb1.w);
+          MmaScores<T>::run(da[0], lo.z & M, hi.z & M, lo.w & M, hi.w & M, tb0.z & M, tb0.w & M);
+          MmaScores<T>::run(da[1], lo.z & M, hi.z & M, lo.w & M, hi.w & M, tb1.z & M, tb1.w & M);
         }
       }
-      // d[0], d[1]: neuron ra, rows cg + 2 tq, + 1;  d[2], d[3]: neuron rb, same rows
+      // d[h][0], d[h][1]: neuron ra, rows cg + 2 tq, + 1;  d[h][2], d[h][3]: neuron rb, same rows
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int b = cg + 2 * tq + (j & 1);
-        const int i = (j < 2) ? ra[tt] : rb[tt];
-        const bool valid = b < B && i < I;
-        const float eps = eps_scale * da[j];
-        bool on = valid && d[j] > mid + eps;
-        // Too close to call: the warp evaluates such scores in the arithmetic order of k_pred_scores, four at a
-        // time - a group of eight lanes per score, lane g of the group owns the chunks g, g + 8, ... of the r
-        // products, the eight partial sums meet by butterfly (xor 4, 2, 1).
-        uint32_t um = __ballot_sync(0xffffffffu, valid && !on && !(d[j] < mid - eps));
-        while (um) {
-          int src[4];
-          uint32_t m = um;
+      for (int h = 0; h < 2; ++h) {
+        const int cg = cg0 + 8 * h;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            src[q] = m ? __ffs(m) - 1 : -1;
-            m &= m - 1;
+        for (int j = 0; j < 4; ++j) {
+          const int b = cg + 2 * tq + (j & 1);
+          const int i = (j < 2) ? ra[tt] : rb[tt];
+          const bool valid = (h == 0 || two) && b < B && i < I;
+          const float eps = eps_scale * da[h][j];
+          const bool on = valid && d[h][j] > mid + eps;
+          const bool close = valid && !on && !(d[h][j] < mid - eps);
+          const uint32_t um = __ballot_sync(0xffffffffu, close);
+          if (um) {
+            if (n_unc + __popc(um) > PSM_LIST) flush();
+            if (close) unc[n_unc + __popc(um & ((1u << lane) - 1u))] = (b << 8) | (i - i0);
+            n_unc += __popc(um);
+            __syncwarp();
           }
-          const int grp = lane >> 3, gl = lane & 7;
-          const int mine = grp == 0 ? src[0] : grp == 1 ? src[1] : grp == 2 ? src[2] : src[3];
-          const int sl = mine < 0 ? 0 : mine;
-          const int bq = __shfl_sync(0xffffffffu, b, sl), iq = __shfl_sync(0xffffffffu, i, sl);
-          float acc = 0.f;
-          if (mine >= 0) {
-            const T* wrow = Bm + static_cast<size_t>(iq) * r;
-            const T* tr = t_s + bq * ts;
-            for (int c = gl; c < (r >> 3); c += 8) {
-              float wv[8], tv[8];
-              Unpack<T>::run(ld_stream16(wrow + c * 8), wv);
-              Unpack<T>::run(*reinterpret_cast<const uint4*>(tr + c * 8), tv);
-#pragma unroll
-              for (int v = 0; v < 8; ++v) acc = fmaf(tv[v], wv[v], acc);
-            }
-          }
-          acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-          acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-          acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-          const bool res = DT<T>::round_f(acc) >= tau_r;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const bool rq = __shfl_sync(0xffffffffu, res, q * 8);
-            if (lane == src[q]) on = rq;
-          }
-          um = m;
+          if (j < 2) on_a = on_a || on;
+          else on_b = on_b || on;
         }
-        if (j < 2) on_a = on_a || on;
-        else on_b = on_b || on;
       }
     }
     // the four threads of a quad hold the rows of the same two neurons
@@ -387,6 +412,7 @@ k_pred_scores_mma(const float* __restrict__ t, const T* __restrict__ Bm, uint32_
       if ((bb >> (4 * q)) & 0xfu) word |= 1u << (16 * tt + 8 + q);
     }
   }
+  flush();
   if (lane == 0) bits[w] = word;
 }
 
