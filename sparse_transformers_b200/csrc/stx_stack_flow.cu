@@ -456,6 +456,13 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
       ph ^= ((1u << nv) - 1u) << s0;
       ++n_cons;
       sg_cons = sg_cons + 1 == nsg ? 0 : sg_cons + 1;
+      if (nsg == 1) {
+        // Rows so long that a CTA holds a single group of four slots: the next group can only be requested into
+        // the slots this one just left, so the request cannot wait for the next group's barrier.
+        __syncthreads();
+        n_safe = n_cons;
+        try_issue(j, n_cur, n_next, next_ok);
+      }
     }
 
     // ---- the CTA's partial output vector of the layer
