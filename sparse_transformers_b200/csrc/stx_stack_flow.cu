@@ -12,18 +12,22 @@
 //             threshold, mask bytes to the layer's mask words.  t of all layers sits in shared memory, the
 //             CTA's slice of the predictor's up matrix is requested four layers ahead, and the loop over the
 //             layers contains no block barrier;                                               grid barrier
-//   phase R   the CTA walks the layers.  Per layer it scans the mask (its words were requested two layers
-//             earlier), takes the neurons of ranks [c*K/G, (c+1)*K/G) and consumes them four at a time from
-//             shared-memory slots (one bulk copy per neuron record, mbarrier completion) exactly as the
-//             layer-by-layer kernel does.  The slots are a ring over ALL layers: a group of four slots that
-//             has been consumed takes the CTA's next group, which may belong to the next layer, so the CTA
-//             always has two to three groups of rows in flight.  The CTA's partial output vector of a layer
-//             goes to its own place in global memory (fp32, [L][G][H]);                       grid barrier
-//   phase O   out[l] = sum of the G partial vectors in a fixed order: a warp per layer, a lane adds every
+//   phase R   the layers are dealt to groups of CTAs (flow_groups below); a CTA walks the layers of its group.  Per
+//             layer it scans the mask (its words were requested a layer earlier), takes its share of the set
+//             bits by rank and consumes those neurons four at a time from shared-memory slots (one bulk copy
+//             per neuron record, mbarrier completion) exactly as the layer-by-layer kernel does.  The slots are
+//             a ring over ALL its layers: a group of four slots that has been consumed takes the CTA's next
+//             group of neurons, which may belong to its next layer, so rows never stop streaming.  The CTA's
+//             partial output vector of a layer goes to its own place in global memory (fp32);
+//   plan      (with the cache upkeep inside the launch) CTA l < L then runs the index plan of layer l's weight
+//             cache, with a smaller share of the rows to have the time;                       grid barrier
+//   phase O   out[l] = sum of the layer's partial vectors in a fixed order: a warp per layer, a lane adds every
 //             fourth vector of a float4 column, the four lanes of a column meet by butterfly (deterministic,
 //             no atomics).  Sharded over several GPUs the warp pushes its sums to every peer's exchange
 //             buffer (stx_peer.cuh), every layer in its own place, and collects all layers afterwards: the
 //             NVLink round trip is paid once per token, not once per layer.
+//   phase C   (cache upkeep inside the launch) the rows of every slot the plans rewrote, all layers at once, by
+//             bulk copies through row buffers in the idle slot area.
 // A model that feeds out[l] forward into layer l+1 cannot use this order: the layer-by-layer kernel with
 // `strict` is the one for it.
 //
