@@ -404,7 +404,12 @@ static bool stack_persistent_wanted(const stx_stack* s, unsigned stages) {
   if (s->B != 1 || (stages & need) != need) return false;
   const stx_layer* l0 = s->layers[0];
   const stx_cache* c0 = l0->cache;
-  if (!stack_b1_supported(c0->H, c0->I, l0->r, c0->has_gate, c0->dtype)) return false;
+  // which of the two persistent kernels will run decides how large I may be
+  const char* st = getenv("STX_STACK_STRICT");
+  const bool strict = st && atoi(st) != 0;
+  const int64_t gsz = std::min<int64_t>(static_cast<int64_t>(s->layers.size()), STACK_B1_MAX_LAYERS);
+  const bool flow = !strict && !(l0->peer && l0->peer->world > 1 && gsz * c0->H > l0->peer->max_elems);
+  if (!stack_b1_supported(c0->H, c0->I, l0->r, c0->has_gate, c0->dtype, flow)) return false;
   for (const stx_layer* l : s->layers) {
     const stx_cache* c = l->cache;
     if (!single_row_fusable(l, 1) || l->peer != l0->peer || c->I != c0->I || c->has_gate != c0->has_gate || l->r != l0->r) return false;

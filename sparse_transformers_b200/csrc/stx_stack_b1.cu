@@ -540,14 +540,16 @@ static int sb1_slots_dt(int H, int has_gate, int dtype) {
 
 static int stack_b1_grid() { return num_sms(); }
 
-bool stack_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype) {
+static bool stack_flow_enabled();
+
+bool stack_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype, bool flow) {
   if (!stack_b1_enabled()) return false;
   const size_t es = dtype_size(dtype);
   const int V = static_cast<int>(16 / es);
   const int G = stack_b1_grid();
   if (G < 2 || H % (4 * V) != 0 || H / V > SB1_MAX_PASS * SB1_THREADS || H / V < 64) return false;  // quarter rows of whole chunks
   if (r % V != 0 || r / V > 16 || r > G || r > SB1_THREADS) return false;
-  if (((I + 7) / 8 + G - 1) / G > 8) return false;         // one pass of 8 mask bytes per CTA
+  if (((I + 7) / 8 + G - 1) / G > (flow && stack_flow_enabled() ? 8 * FLOW_MAX_PASSES : 8)) return false;  // passes of 8 mask bytes per CTA
   if ((I + 31) / 32 > 4 * SB1_THREADS) return false;        // four mask words per thread
   if ((I + G - 1) / G > SB1_MY_CAP) return false;           // the CTA's list of a layer
   if ((H / 4 + G - 1) / G > 8 || G > 192) return false;  // the output sum: <= 8 float4 columns per CTA, <= 3 x 64 vectors

@@ -34,7 +34,9 @@ struct StackB1Args {
                              // caller launches the plan and copy kernels.
 };
 
-bool stack_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype);
+constexpr int FLOW_MAX_PASSES = 2;  // the flow kernel scores a CTA's mask bytes eight at a time, in up to two passes
+// flow: the flow kernel will run (not the layer-by-layer one, whose CTAs score eight mask bytes in a single pass)
+bool stack_b1_supported(int64_t H, int64_t I, int64_t r, int has_gate, int dtype, bool flow = false);
 size_t stack_b1_scratch_bytes(int64_t L, int64_t H, int64_t r);
 // One launch for layers [0, a.L), a.L <= STACK_B1_MAX_LAYERS.  scratch: stack_b1_scratch_bytes(a.L, ..)
 // bytes, zeroed once at allocation and then owned by the launches of this group of layers.

@@ -58,7 +58,8 @@ __host__ __device__ inline int flow_groups(int L, int G, int I) {
   return 1;
 }
 
-template <typename T, int PASS>
+// NP: passes in which a CTA scores its mask bytes of a layer, eight bytes per pass (1: ceil(ceil(I / 8) / G) <= 8)
+template <typename T, int PASS, int NP>
 __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_constant__ StackB1Args q) {
   constexpr int V = DT<T>::V;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -116,34 +117,42 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     __syncthreads();
   };
 
-  // ---- score geometry (one pass of 8 mask bytes per CTA; the launcher guarantees nby <= 8)
+  // ---- score geometry: CTA c owns the mask bytes c, c + G, ... (nby of them; the launcher guarantees
+  // nby <= 8 * FLOW_MAX_PASSES); a pass of the 512 threads scores 8 of them (64 neurons x 8 lanes)
   const int rch = r / V, nc4 = (rch + 7) >> 3;  // nc4 <= 2
   const int NBY = (I + 7) >> 3;
   const int nby = NBY > c ? (NBY - 1 - c) / G + 1 : 0;
   const int g8 = tid & 7;
-  const int kk = tid >> 6;                               // mask byte of the CTA this thread works on
-  const int my_n = 8 * (c + G * kk) + ((tid >> 3) & 7);  // its neuron
-  const bool n_ok = kk < nby && my_n < I;
+  const int kk = tid >> 6;  // mask byte of a pass this thread works on
+  // this thread's neuron in pass p, or -1
+  auto neuron_of = [&](int p) {
+    const int by = kk + 8 * p;
+    const int n = 8 * (c + G * by) + ((tid >> 3) & 7);
+    return (by < nby && n < I) ? n : -1;
+  };
   const int NT = min(1024, (nchunk + 31) / 32 * 32);     // virtual threads of the t reduction (as k_pred_t's block)
   const int W = (I + 31) >> 5;                           // mask words
   const int WPT = (W + SB1_THREADS - 1) / SB1_THREADS;   // <= 4
 
   // the CTA's slice of the predictor's up matrix, FLOW_AHEAD layers ahead (weights do not depend on data: the
   // first ones are on their way while t is formed)
+  // An item of phase S is (layer, pass): item it = l * NP + p.
+  const int nitem = L * NP;
   uint4 wq[FLOW_AHEAD][2];
-  auto load_w = [&](int l, uint4 (&dst)[2]) {
+  auto load_w = [&](int it, uint4 (&dst)[2]) {
+    const int l = it / NP, n = neuron_of(it - l * NP);
     const T* Bm = static_cast<const T*>(q.layer[l].Bm);
 #pragma unroll
     for (int c4 = 0; c4 < 2; ++c4) {
       const int ch = g8 + 8 * c4;
       dst[c4] = make_uint4(0, 0, 0, 0);
-      if (n_ok && ch < rch) dst[c4] = ld_stream16(Bm + static_cast<size_t>(my_n) * r + ch * V);
+      if (n >= 0 && ch < rch) dst[c4] = ld_stream16(Bm + static_cast<size_t>(n) * r + ch * V);
     }
   };
 #pragma unroll
   for (int u = 0; u < FLOW_AHEAD; ++u) {
     wq[u][0] = wq[u][1] = make_uint4(0, 0, 0, 0);
-    if (u < L) load_w(u, wq[u]);
+    if (u < nitem) load_w(u, wq[u]);
   }
 
   // ================================================================== phase T: t of every layer
@@ -188,18 +197,20 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
   // collected in shared memory and the CTA's mask bytes of all layers are written in one pass at the end.
   {
     float* t_all = reinterpret_cast<float*>(slots);                                           // [L][128]
-    uint32_t* nib_all = reinterpret_cast<uint32_t*>(slots + STACK_B1_MAX_LAYERS * 512);       // [L][16]
+    uint32_t* nib_all = reinterpret_cast<uint32_t*>(slots + STACK_B1_MAX_LAYERS * 512);       // [L * NP][16]
     for (int i = tid; i < L * r; i += SB1_THREADS) {
       const int l = i / r, e = i - l * r;
       const int ch = e / V, v = e - ch * V;
       t_all[l * 128 + (((ch >> 3) * (V / 4) + (v >> 2)) * 8 + (ch & 7)) * 4 + (v & 3)] = __ldcg(q.t_buf + i);
     }
     __syncthreads();
-    for (int l0 = 0; l0 < L; l0 += FLOW_AHEAD) {
+    for (int it0 = 0; it0 < nitem; it0 += FLOW_AHEAD) {
 #pragma unroll
       for (int u = 0; u < FLOW_AHEAD; ++u) {
-        const int l = l0 + u;
-        if (l < L) {
+        const int it = it0 + u;
+        if (it < nitem) {
+          const int l = it / NP;
+          const bool n_ok = neuron_of(it - l * NP) >= 0;
           const float tau_r = DT<T>::round_f(q.layer[l].tau);
           float sc = 0.f;
 #pragma unroll
@@ -219,21 +230,22 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
               }
             }
           }
-          if (l + FLOW_AHEAD < L) load_w(l + FLOW_AHEAD, wq[u]);
+          if (it + FLOW_AHEAD < nitem) load_w(it + FLOW_AHEAD, wq[u]);
           sc += __shfl_xor_sync(0xffffffffu, sc, 4);
           sc += __shfl_xor_sync(0xffffffffu, sc, 2);
           sc += __shfl_xor_sync(0xffffffffu, sc, 1);
           const bool on = n_ok && DT<T>::round_f(sc) >= tau_r;
           const uint32_t bal = __ballot_sync(0xffffffffu, on && g8 == 0);
-          if (lane == 0) nib_all[l * 16 + warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
+          if (lane == 0) nib_all[it * 16 + warp] = (bal & 1u) | ((bal >> 7) & 2u) | ((bal >> 14) & 4u) | ((bal >> 21) & 8u);
         }
       }
     }
     __syncthreads();
-    for (int i = tid; i < L * 8; i += SB1_THREADS) {
-      const int l = i >> 3, j = i & 7;
-      if (j < nby)
-        reinterpret_cast<uint8_t*>(q.layer[l].bits)[c + G * j] = static_cast<uint8_t>(nib_all[l * 16 + 2 * j] | (nib_all[l * 16 + 2 * j + 1] << 4));
+    for (int i = tid; i < nitem * 8; i += SB1_THREADS) {
+      const int it = i >> 3, j = i & 7;
+      const int l = it / NP, by = j + 8 * (it - l * NP);
+      if (by < nby)
+        reinterpret_cast<uint8_t*>(q.layer[l].bits)[c + G * by] = static_cast<uint8_t>(nib_all[it * 16 + 2 * j] | (nib_all[it * 16 + 2 * j + 1] << 4));
     }
   }
   barrier_arrive(SB1_SYNC_FM);
@@ -666,8 +678,10 @@ static int launch_stack_flow(const StackB1Args& a, size_t smem, size_t smem_limi
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
-    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
+    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
+    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
+    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
+    STX_CUDA(cudaFuncSetAttribute(k_stack_flow<T, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_limit)));
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -680,10 +694,16 @@ static int launch_stack_flow(const StackB1Args& a, size_t smem, size_t smem_limi
   at[0].val.cooperative = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  if (a.H / DT<T>::V <= SB1_THREADS)
-    STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 1>, a));
-  else
-    STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 2>, a));
+  const bool one = a.H / DT<T>::V <= SB1_THREADS;
+  const bool single = ((a.I + 7) / 8 + G - 1) / G <= 8;  // one pass of eight mask bytes per CTA and layer
+  static_assert(FLOW_MAX_PASSES == 2, "two instantiations of the pass count");
+  if (single) {
+    if (one) STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 1, 1>, a));
+    else STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 2, 1>, a));
+  } else {
+    if (one) STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 1, 2>, a));
+    else STX_CUDA(cudaLaunchKernelEx(&cfg, k_stack_flow<T, 2, 2>, a));
+  }
   return STX_OK;
 }
 

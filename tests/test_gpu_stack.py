@@ -62,6 +62,7 @@ def _stack_vs_oracle(w, steps, seed=0, check_every=1, lazy=False):
     (torch.float16, 2048, 8192, 64, True, "silu", 0.9, 2),        # dense mask: several rounds of row spaces per pair
     (torch.bfloat16, 512, 1024, 64, True, "silu", 0.02, 3),       # nearly empty: pairs without neurons
     (torch.float16, 4096, 4096, 64, True, "silu", 0.2, 3),        # two groups of slots
+    (torch.bfloat16, 4096, 14336, 128, True, "silu", 0.15, 2),    # Mistral-7B shape: two score passes per CTA and layer
 ])
 def test_persistent_stack_matches_oracle(dtype, H, I, r, has_gate, act, density, layers):
     from sparse_transformers_b200.synth import Workload
