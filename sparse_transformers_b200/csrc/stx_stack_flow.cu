@@ -248,6 +248,9 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
         reinterpret_cast<uint8_t*>(q.layer[l].bits)[c + G * by] = static_cast<uint8_t>(nib_all[it * 16 + 2 * j] | (nib_all[it * 16 + 2 * j + 1] << 4));
     }
   }
+  // t and the nibbles were written to the slot area with ordinary stores; the bulk copies of phase R write the same
+  // bytes through the async proxy
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   barrier_arrive(SB1_SYNC_FM);
   barrier_wait(SB1_SYNC_FM);
 
@@ -503,6 +506,8 @@ __global__ void __launch_bounds__(SB1_THREADS, 1) k_stack_flow(const __grid_cons
     const UpkeepArgs* ua = q.upkeep + c;
     plan_block(q.layer[c].bits, ua->cur_bits, ua->active, ua->pos_of, ua->lists, ua->jobs, ua->state, ua->stale, ua->lazy, I,
                reinterpret_cast<int32_t*>(slots));
+    // the plan's work space becomes row buffers of phase C, which bulk copies write through the async proxy
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   barrier_arrive(SB1_SYNC_FP);
   barrier_wait(SB1_SYNC_FP);
