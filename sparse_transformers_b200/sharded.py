@@ -47,7 +47,11 @@ _DTYPE = {torch.float32: C.F32, torch.float16: C.F16, torch.bfloat16: C.BF16}
 class PeerExchange:
     """This rank's exchange buffer for sums over the process group's GPUs (one node, one process
     per GPU, current CUDA device).  Construction is collective: the ranks swap the buffers'
-    interprocess handles through torch.distributed and map each other's memory."""
+    interprocess handles through torch.distributed and map each other's memory.
+
+    max_elems: the largest sum that will go through the buffer, in elements ([B, H] of a layer: B * H).  A stack
+    of L layers stepped with one row exchanges the sums of all its layers side by side, once per token, when the
+    buffer has room for them (L * H elements); with less it exchanges layer after layer."""
 
     def __init__(self, max_elems: int, group=None):
         self.group = group
