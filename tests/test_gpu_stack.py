@@ -135,11 +135,14 @@ def test_stack_replay_is_deterministic():
     sa.close(); sb.close()
 
 
-def test_expired_wait_makes_the_next_step_fail(monkeypatch):
+@pytest.mark.parametrize("room_for_layers", [1, 2])
+def test_expired_wait_makes_the_next_step_fail(monkeypatch, room_for_layers):
     """A wait that runs out inside a step must not pass silently.  World of two whose second rank does not
     exist (its exchange buffer is a second buffer on this GPU that nobody writes): the stack kernel's wait for
     the peer's partial sums expires after its poll limit, the step finishes (the context stays usable), the
-    error bits reach pinned host memory with the step's last node, and the next step call is refused."""
+    error bits reach pinned host memory with the step's last node, and the next step call is refused.  With
+    room for one layer's sums in the exchange buffer the layer-by-layer kernel runs, with room for both layers
+    the flow kernel (all layers exchanged at once)."""
     import ctypes
 
     from sparse_transformers_b200 import SparseLayer, SparseStack
@@ -150,8 +153,8 @@ def test_expired_wait_makes_the_next_step_fail(monkeypatch):
     monkeypatch.setenv("STX_PEER_WAIT_ITERS", "500")
     w = WORKLOADS["C2"].scaled(I=2048, H=512, layers=2)
     a, b = ctypes.c_void_p(), ctypes.c_void_p()
-    C.check(C.lib.stx_peer_create(ctypes.byref(a), 0, 2, w.H))
-    C.check(C.lib.stx_peer_create(ctypes.byref(b), 1, 2, w.H))  # only its buffer is used
+    C.check(C.lib.stx_peer_create(ctypes.byref(a), 0, 2, room_for_layers * w.H))
+    C.check(C.lib.stx_peer_create(ctypes.byref(b), 1, 2, room_for_layers * w.H))  # only its buffer is used
     pa, pb = ctypes.c_void_p(), ctypes.c_void_p()
     C.check(C.lib.stx_peer_local_buffer(a, ctypes.byref(pa)))
     C.check(C.lib.stx_peer_local_buffer(b, ctypes.byref(pb)))
