@@ -12,9 +12,11 @@
 //   phase A  one warp per neuron: both dot products with x (shared memory), warp-shuffle
 //            reduction, activation and product in registers -> a[j,b] in shared memory
 //   phase B  one thread per 16-byte column chunk: acc[b,chunk] += a[j,b] * down[j,chunk]
-//            over the block's neurons, then one vector fp32 reduction per chunk into the
-//            global accumulator
-//   the last block to finish converts the accumulator to the output dtype and re-zeroes it.
+//            over the block's neurons -> the block's partial output [B,H] (fp32) in the scratch
+//   the last block to finish adds the partial outputs in block order (deterministic, no atomics on
+//   data) and converts to the output dtype.  The partial outputs live where the scratch has room for
+//   them - the accumulator region and the a[K][B] region of the streaming kernels - and the launcher
+//   takes no more blocks than fit there.
 #include "stx_common.cuh"
 
 #include <algorithm>
@@ -31,7 +33,8 @@ struct MlpArgs {
   const void* down;
   void* combined;        // optional [B, 2K] (or [B,K]) in dtype
   void* out;             // [B,H] in dtype
-  float* out_acc;        // [B,H] fp32, zero on entry, zero on exit
+  float* out_acc;        // [B,H] fp32: partial output of block 0 (zero on exit)
+  float* part_rest;      // [gridDim.x - 1][B,H] fp32: partial outputs of the other blocks
   unsigned* counter;     // zero on entry, zero on exit
   const int32_t* K_dev;  // device K (may be null -> K_host)
   int K_host;
@@ -168,12 +171,13 @@ __global__ void __launch_bounds__(256, 2) k_mlp_fused(const MlpArgs p) {
             for (int v = 0; v < V; ++v) acc[b][v] = fmaf(a, wd[v], acc[b][v]);
           }
         }
+        float* mine = blockIdx.x == 0 ? p.out_acc : p.part_rest + static_cast<size_t>(blockIdx.x - 1) * p.B * H;
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
           if (b < nb) {
-            float* dst = p.out_acc + static_cast<size_t>(b0 + b) * H + c * V;
+            float* dst = mine + static_cast<size_t>(b0 + b) * H + c * V;
 #pragma unroll
-            for (int v = 0; v < V; v += 4) red_add_f32x4(dst + v, acc[b][v], acc[b][v + 1], acc[b][v + 2], acc[b][v + 3]);
+            for (int v = 0; v < V; v += 4) *reinterpret_cast<float4*>(dst + v) = make_float4(acc[b][v], acc[b][v + 1], acc[b][v + 2], acc[b][v + 3]);
           }
         }
       }
@@ -181,7 +185,8 @@ __global__ void __launch_bounds__(256, 2) k_mlp_fused(const MlpArgs p) {
     __syncthreads();
   }
 
-  // ---- last block converts and re-zeroes
+  // ---- the last block adds the partial outputs of the blocks that had neurons (the first min(gridDim.x, K)), in
+  //      block order, and converts
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -193,14 +198,24 @@ __global__ void __launch_bounds__(256, 2) k_mlp_fused(const MlpArgs p) {
     __threadfence();
     T* out = static_cast<T*>(p.out);
     const int n4 = p.B * H / 4;
-    float4* acc4 = reinterpret_cast<float4*>(p.out_acc);
+    const int nact = min(static_cast<int>(gridDim.x), K);
+    const float4* first = reinterpret_cast<const float4*>(p.out_acc);
+    const float4* rest = reinterpret_cast<const float4*>(p.part_rest);
     for (int i = tid; i < n4; i += blockDim.x) {
-      const float4 v = __ldcg(acc4 + i);
+      float4 v = nact > 0 ? __ldcg(first + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int blk = 1; blk < nact; ++blk) {
+        const float4 u = __ldcg(rest + static_cast<size_t>(blk - 1) * n4 + i);
+        v.x += u.x;
+        v.y += u.y;
+        v.z += u.z;
+        v.w += u.w;
+      }
       out[4 * i + 0] = DT<T>::from_f(v.x);
       out[4 * i + 1] = DT<T>::from_f(v.y);
       out[4 * i + 2] = DT<T>::from_f(v.z);
       out[4 * i + 3] = DT<T>::from_f(v.w);
-      acc4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      // the accumulator region is handed back zeroed, as callers of the scratch may expect of its head
+      reinterpret_cast<float4*>(p.out_acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (tid == 0) *p.counter = 0u;
   }
@@ -321,6 +336,12 @@ int mlp_forward(const void* x, int64_t B, int64_t H, const void* gate, const voi
   threads = std::min(256, std::max(64, (threads + 31) / 32 * 32));
   int grid = num_sms() * 2;
   if (!K_dev) grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(grid, K_host)));
+  // one partial output per block: block 0 in the accumulator region, the others in the a[K][B] region behind it
+  // (scratch layout: 256 | fp32 [B,H] | 256 | fp32 a[K][B], see decode_scratch_bytes_min)
+  const size_t acc_bytes = static_cast<size_t>(B) * H * sizeof(float);
+  const size_t a_bytes = align_up(static_cast<size_t>(B) * std::max<int64_t>(K_cap, 1) * sizeof(float), 256);
+  grid = static_cast<int>(std::min<size_t>(static_cast<size_t>(grid), 1 + a_bytes / acc_bytes));
+  a.part_rest = reinterpret_cast<float*>(static_cast<char*>(scratch) + 256 + align_up(acc_bytes, 256) + 256);
   a.a_cap = static_cast<int>((K_cap + grid - 1) / grid);
   switch (dtype) {
     case STX_F32: return dispatch_nb<float>(a, grid, threads, s);

@@ -62,6 +62,8 @@ def test_noalloc_clears_what_the_fallback_kernel_accumulates_into():
         assert rel_err(out.cpu().numpy(), ref.cpu().numpy()) <= 1e-5
         want, _ = orc.sparse_mlp(x.cpu().numpy(), cw.cpu().numpy(), dp.cpu().numpy(), "silu", True)
         assert rel_err(out.cpu().numpy(), want) <= 1e-5
+        again, _ = _noalloc(x, cw, dp, "silu")
+        assert torch.equal(out, again)  # the blocks' partial outputs are added in block order: same bits every time
     # no active neuron: the output is zero, as the regular entry point gives
     x = torch.randn(2, 64, generator=g).to(DEV)
     cw = torch.zeros(0, 64, device=DEV)
